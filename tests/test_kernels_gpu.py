@@ -1,0 +1,190 @@
+"""Numerics of every sm_100a kernel against an fp32 PyTorch reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from torchft_b200.ops import kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (200, 328, 136), (1024, 1024, 4096)])
+def test_gemm_layouts(a_mn, b_mn, M, N, K_):
+    torch.manual_seed(1)
+    a = torch.randn((K_, M) if a_mn else (M, K_), device=DEV).bfloat16()
+    b = torch.randn((K_, N) if b_mn else (N, K_), device=DEV).bfloat16()
+    out = K.gemm(a, b, a_mn, b_mn)
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    ref = af @ bf
+    K.check_status(out.device)
+    assert rel_err(out, ref) < 1e-2
+    # fp32 output + accumulate
+    acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+    K.gemm(a, b, a_mn, b_mn, out=acc, accumulate=True)
+    assert rel_err(acc, ref + 1.0) < 1e-2
+
+
+def test_gemm_many_tiles_persistent():
+    torch.manual_seed(2)
+    M, N, K_ = 2048, 4096, 512
+    a = torch.randn(M, K_, device=DEV).bfloat16()
+    b = torch.randn(N, K_, device=DEV).bfloat16()
+    ref = a.float() @ b.float().t()
+    for ctas in (0, 7, 1):
+        out = K.gemm(a, b, max_ctas=ctas)
+        assert rel_err(out, ref) < 1e-2
+    K.check_status(a.device)
+
+
+def test_linear_trio_matches_autograd():
+    torch.manual_seed(3)
+    T, Kd, Nd = 512, 384, 640
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    w = (torch.randn(Nd, Kd, device=DEV) * 0.05).bfloat16()
+    dy = torch.randn(T, Nd, device=DEV).bfloat16()
+    assert rel_err(K.linear_fwd(x, w), x.float() @ w.float().t()) < 1e-2
+    assert rel_err(K.linear_dgrad(dy, w), dy.float() @ w.float()) < 1e-2
+    assert rel_err(K.linear_wgrad(dy, x), dy.float().t() @ x.float()) < 1e-2
+
+
+@pytest.mark.parametrize("T,D", [(64, 256), (33, 4096), (7, 1024)])
+def test_rmsnorm(T, D):
+    torch.manual_seed(4)
+    x = torch.randn(T, D, device=DEV).bfloat16()
+    res = torch.randn(T, D, device=DEV).bfloat16()
+    w = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
+    out, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
+    ro, rr, _ = K.ref_rmsnorm_fwd(x, w, 1e-5)
+    assert rel_err(out, ro) < 1e-2 and rel_err(rstd, rr) < 1e-4
+    out2, rstd2, h = K.rmsnorm_fwd(x, w, 1e-5, res=res)
+    ro2, rr2, rh = K.ref_rmsnorm_fwd(x, w, 1e-5, res)
+    assert rel_err(out2, ro2) < 1e-2 and rel_err(h, rh) < 1e-2
+    dy = torch.randn(T, D, device=DEV).bfloat16()
+    dres = torch.randn(T, D, device=DEV).bfloat16()
+    dx, dw = K.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
+    rdx, rdw = K.ref_rmsnorm_bwd(dy, x, w, rr, dres)
+    assert rel_err(dx, rdx) < 1e-2
+    assert rel_err(dw, rdw) < 2e-2
+
+
+def test_rope_roundtrip_and_ref():
+    torch.manual_seed(5)
+    S, Hq, Hkv, Dh = 64, 4, 2, 64
+    T = 2 * S
+    buf = torch.randn(T, (Hq + 2 * Hkv) * Dh, device=DEV).bfloat16()
+    orig = buf.clone()
+    table = K.rope_table(S, Dh, 500000.0, DEV)
+    ref = K.ref_rope(orig, table, S, Hq + Hkv, Dh)
+    K.rope_(buf, table, S, Hq + Hkv, Dh)
+    assert rel_err(buf, ref) < 1e-2
+    assert torch.equal(buf[:, (Hq + Hkv) * Dh:], orig[:, (Hq + Hkv) * Dh:])
+    K.rope_(buf, table, S, Hq + Hkv, Dh, backward=True)
+    assert rel_err(buf, orig) < 2e-2
+
+
+def test_swiglu():
+    torch.manual_seed(6)
+    T, Fd = 96, 512
+    gu = torch.randn(T, 2 * Fd, device=DEV).bfloat16()
+    ds = torch.randn(T, Fd, device=DEV).bfloat16()
+    assert rel_err(K.swiglu_fwd(gu), K.ref_swiglu_fwd(gu)) < 1e-2
+    ref = K.ref_swiglu_bwd(ds, gu)
+    got = K.swiglu_bwd(ds, gu.clone())
+    assert rel_err(got, ref) < 1e-2
+    inplace = gu.clone()
+    K.swiglu_bwd(ds, inplace, dgu=inplace)
+    assert rel_err(inplace, ref) < 1e-2
+
+
+@pytest.mark.parametrize("T,V", [(16, 1024), (5, 128256), (64, 8192)])
+def test_cross_entropy(T, V):
+    torch.manual_seed(7)
+    logits = (torch.randn(T, V, device=DEV) * 3).bfloat16()
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    rl, rg = K.ref_cross_entropy(logits, tgt, 1.0 / T)
+    loss = K.cross_entropy_(logits, tgt, 1.0 / T)
+    assert rel_err(loss, rl) < 1e-3
+    assert rel_err(logits, rg) < 1e-2
+
+
+@pytest.mark.parametrize("gdt", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("n", [8, 1000, 1 << 20, (1 << 20) + 3])
+def test_adamw(gdt, n):
+    torch.manual_seed(8)
+    master = torch.randn(n, device=DEV)
+    m = torch.zeros(n, device=DEV)
+    v = torch.zeros(n, device=DEV)
+    lp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    rm, rmm, rv = master.clone(), m.clone(), v.clone()
+    scale = torch.tensor([0.5], device=DEV)
+    for step in (1, 2, 3):
+        g = torch.randn(n, device=DEV).to(gdt)
+        K.adamw_(master, m, v, g, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, scale)
+        K.ref_adamw(rm, rmm, rv, g, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 0.5)
+    assert rel_err(master, rm) < 1e-5
+    assert rel_err(m, rmm) < 1e-5 and rel_err(v, rv) < 1e-5
+    assert torch.equal(lp, master.bfloat16())
+
+
+def test_sumsq_and_clip():
+    torch.manual_seed(9)
+    x = torch.randn((1 << 18) + 5, device=DEV).bfloat16()
+    out = torch.zeros(1, device=DEV)
+    K.sumsq_(x, out)
+    ref = x.float().pow(2).sum()
+    assert abs(out.item() - ref.item()) / ref.item() < 1e-4
+    coef = torch.zeros(1, device=DEV)
+    nrm = torch.zeros(1, device=DEV)
+    K.clip_coef_(out, 1.0, coef, nrm)
+    assert abs(nrm.item() - math.sqrt(ref.item())) / nrm.item() < 1e-4
+    assert abs(coef.item() - 1.0 / (nrm.item() + 1e-6)) < 1e-6
+
+
+def test_embedding():
+    torch.manual_seed(10)
+    V, D, T = 512, 256, 300
+    table = torch.randn(V, D, device=DEV).bfloat16()
+    tok = torch.randint(0, V, (T,), device=DEV)
+    assert torch.equal(K.embedding_fwd(tok, table), table[tok])
+    dout = torch.randn(T, D, device=DEV).bfloat16()
+    dtab = torch.zeros(V, D, device=DEV, dtype=torch.bfloat16)
+    K.embedding_bwd(tok, dout, dtab)
+    ref = torch.zeros(V, D, device=DEV).index_add_(0, tok, dout.float())
+    assert rel_err(dtab, ref) < 2e-2
+
+
+def test_engine_matches_autograd_gpu():
+    from torchft_b200.models.llama import LLAMA_TINY, TorchLlama, _Fields
+    from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
+
+    torch.manual_seed(0)
+    cfg = LLAMA_TINY
+    B, S = 2, 128
+    dev = torch.device("cuda")
+    tr = ShardedLlamaTrainer(cfg, B, S, dev, logit_chunks=2)
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), device=dev)
+    targets = torch.randint(0, cfg.vocab_size, (B, S), device=dev)
+    loss = tr.forward_backward(tokens, targets)
+    ref = TorchLlama(cfg).to(dev, torch.float32)
+    ref.load_units(lambda u: tr._param_unit(u))
+    rl = torch.nn.functional.cross_entropy(ref(tokens).float().view(-1, cfg.vocab_size), targets.view(-1))
+    rl.backward()
+    K.check_status(dev)
+    assert abs(loss.item() - rl.item()) < 3e-2
+    g = _Fields(tr._grad_unit(1), cfg.unit_fields(1))
+    for name in ("wqkv", "wo", "wgu", "wd", "attn_norm", "ffn_norm"):
+        assert rel_err(getattr(g, name), getattr(ref.layers[0], name).grad) < 0.08, name
+    l0 = loss.item()
+    for _ in range(3):
+        tr.optimizer_step()
+        l1 = tr.forward_backward(tokens, targets).item()
+    assert l1 < l0

@@ -1,0 +1,391 @@
+"""Llama-3 style decoder trained by an explicit (autograd-free) forward/backward engine.
+
+The reference project ships no model code; its Llama runs come from an external
+trainer layered on ``torchft``.  Here the model is part of the framework because the
+fault-tolerant HSDP step is built around it: parameters live in flat per-layer
+*units* (the FSDP sharding granule), every activation that backward needs sits in a
+preallocated buffer, and each hot op is one of the sm_100a kernels in
+:mod:`torchft_b200.ops.kernels`.
+
+Unit layout (bf16, every field a multiple of 8 elements so all views are 16-byte
+aligned)::
+
+    layer unit : attn_norm[D] | wqkv[(Hq+2Hkv)*Dh, D] | wo[D, D] | ffn_norm[D] | wgu[2F, D] | wd[D, F]
+    embed unit : tok_embeddings[V, D]
+    head  unit : final_norm[D] | lm_head[V, D]
+
+RoPE rotates interleaved pairs ``(2i, 2i+1)`` with ``theta = rope_theta``.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import kernels as K
+
+
+@dataclass
+class LlamaConfig:
+    dim: int = 4096
+    n_layers: int = 32
+    n_heads: int = 32
+    n_kv_heads: int = 8
+    ffn_dim: int = 14336
+    vocab_size: int = 128256
+    rope_theta: float = 500000.0
+    norm_eps: float = 1e-5
+    name: str = "llama3-8b"
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+    @property
+    def qkv_dim(self) -> int:
+        return (self.n_heads + 2 * self.n_kv_heads) * self.head_dim
+
+    def layer_fields(self) -> List[Tuple[str, Tuple[int, ...]]]:
+        D, Fd = self.dim, self.ffn_dim
+        return [
+            ("attn_norm", (D,)),
+            ("wqkv", (self.qkv_dim, D)),
+            ("wo", (D, D)),
+            ("ffn_norm", (D,)),
+            ("wgu", (2 * Fd, D)),
+            ("wd", (D, Fd)),
+        ]
+
+    def unit_fields(self, unit: int) -> List[Tuple[str, Tuple[int, ...]]]:
+        """Unit 0 is the embedding, 1..n_layers the blocks, n_layers+1 the head."""
+        if unit == 0:
+            return [("tok_embeddings", (self.vocab_size, self.dim))]
+        if unit == self.n_layers + 1:
+            return [("final_norm", (self.dim,)), ("lm_head", (self.vocab_size, self.dim))]
+        return self.layer_fields()
+
+    @property
+    def n_units(self) -> int:
+        return self.n_layers + 2
+
+    def unit_numel(self, unit: int) -> int:
+        return sum(math.prod(s) for _, s in self.unit_fields(unit))
+
+    def num_params(self) -> int:
+        return sum(self.unit_numel(u) for u in range(self.n_units))
+
+    def flops_per_token(self, seq_len: int) -> float:
+        """Model FLOPs per token for one training step (matmuls + causal attention)."""
+        dense = self.num_params() - self.vocab_size * self.dim  # the embedding lookup is not a matmul
+        attn = 6 * self.n_layers * self.dim * seq_len  # 12*L*D*S halved by causality
+        return 6.0 * dense + attn
+
+
+LLAMA3_8B = LlamaConfig()
+LLAMA3_1B = LlamaConfig(dim=2048, n_layers=16, n_heads=32, n_kv_heads=8, ffn_dim=8192, name="llama3-1b")
+LLAMA_TINY = LlamaConfig(dim=256, n_layers=2, n_heads=4, n_kv_heads=2, ffn_dim=512, vocab_size=1024, name="llama-tiny")
+LLAMA_SMALL = LlamaConfig(dim=1024, n_layers=4, n_heads=8, n_kv_heads=2, ffn_dim=2816, vocab_size=8192, name="llama-small")
+
+CONFIGS = {c.name: c for c in (LLAMA3_8B, LLAMA3_1B, LLAMA_TINY, LLAMA_SMALL)}
+
+
+class _Fields:
+    """Named views into one flat unit buffer."""
+
+    def __init__(self, flat: torch.Tensor, fields: List[Tuple[str, Tuple[int, ...]]]):
+        off = 0
+        for name, shape in fields:
+            n = math.prod(shape)
+            setattr(self, name, flat[off : off + n].view(*shape))
+            off += n
+
+
+class SdpaAttention:
+    """Causal GQA attention through ``torch``'s fused SDPA (library kernel).
+
+    Used where the hand-written attention kernel is not selected; keeps a one-op
+    autograd graph per layer so that backward reuses the library's saved statistics.
+    """
+
+    def __init__(self, cfg: LlamaConfig):
+        self.cfg = cfg
+        self._saved: Dict[int, Tuple[torch.Tensor, ...]] = {}
+
+    def forward(self, layer: int, qkv: torch.Tensor, batch: int, seq: int, out: torch.Tensor, need_grad: bool) -> None:
+        c = self.cfg
+        Hq, Hkv, Dh = c.n_heads, c.n_kv_heads, c.head_dim
+        q = qkv[:, : Hq * Dh].view(batch, seq, Hq, Dh).transpose(1, 2)
+        k = qkv[:, Hq * Dh : (Hq + Hkv) * Dh].view(batch, seq, Hkv, Dh).transpose(1, 2)
+        v = qkv[:, (Hq + Hkv) * Dh :].view(batch, seq, Hkv, Dh).transpose(1, 2)
+        if need_grad:
+            q, k, v = (t.detach().requires_grad_(True) for t in (q, k, v))
+            with torch.enable_grad():
+                o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+            self._saved[layer] = (q, k, v, o)
+        else:
+            with torch.no_grad():
+                o = F.scaled_dot_product_attention(q, k, v, is_causal=True, enable_gqa=True)
+        out.view(batch, seq, Hq, Dh).copy_(o.detach().transpose(1, 2))
+
+    def backward(self, layer: int, dout: torch.Tensor, batch: int, seq: int, dqkv: torch.Tensor) -> None:
+        c = self.cfg
+        Hq, Hkv, Dh = c.n_heads, c.n_kv_heads, c.head_dim
+        q, k, v, o = self._saved.pop(layer)
+        do = dout.view(batch, seq, Hq, Dh).transpose(1, 2)
+        dq, dk, dv = torch.autograd.grad(o, (q, k, v), do)
+        dqkv[:, : Hq * Dh].view(batch, seq, Hq, Dh).copy_(dq.transpose(1, 2))
+        dqkv[:, Hq * Dh : (Hq + Hkv) * Dh].view(batch, seq, Hkv, Dh).copy_(dk.transpose(1, 2))
+        dqkv[:, (Hq + Hkv) * Dh :].view(batch, seq, Hkv, Dh).copy_(dv.transpose(1, 2))
+
+    def reset(self) -> None:
+        self._saved.clear()
+
+
+class LlamaEngine:
+    """Forward/backward of a Llama decoder over externally owned parameter/grad units.
+
+    ``param_unit(u)`` returns the full (gathered) bf16 flat buffer of unit ``u`` and
+    ``grad_unit(u)`` the full flat gradient buffer to write; ``unit_ready`` /
+    ``grad_done`` hooks let a sharding layer prefetch parameters and reduce
+    gradients while compute continues.
+    """
+
+    def __init__(
+        self,
+        cfg: LlamaConfig,
+        batch: int,
+        seq_len: int,
+        device: torch.device,
+        param_unit: Callable[[int], torch.Tensor],
+        grad_unit: Callable[[int], torch.Tensor],
+        before_unit: Optional[Callable[[int, bool], None]] = None,
+        grad_done: Optional[Callable[[int], None]] = None,
+        attention: Optional[object] = None,
+        logit_chunks: int = 4,
+    ):
+        self.cfg, self.B, self.S, self.device = cfg, batch, seq_len, device
+        self.T = batch * seq_len
+        self.param_unit, self.grad_unit = param_unit, grad_unit
+        self.before_unit = before_unit or (lambda u, backward: None)
+        self.grad_done = grad_done or (lambda u: None)
+        self.attn = attention if attention is not None else SdpaAttention(cfg)
+        self.logit_chunks = max(1, logit_chunks)
+        while self.T % self.logit_chunks:
+            self.logit_chunks -= 1
+        T, D, Fd, QKV, L = self.T, cfg.dim, cfg.ffn_dim, cfg.qkv_dim, cfg.n_layers
+        bf = dict(dtype=torch.bfloat16, device=device)
+        f32 = dict(dtype=torch.float32, device=device)
+        # saved activations
+        self.x = [torch.empty(T, D, **bf) for _ in range(L + 1)]  # residual stream entering layer l (x[L]: final)
+        self.h = [torch.empty(T, D, **bf) for _ in range(L)]
+        self.qkv = [torch.empty(T, QKV, **bf) for _ in range(L)]
+        self.att = [torch.empty(T, D, **bf) for _ in range(L)]
+        self.gu = [torch.empty(T, 2 * Fd, **bf) for _ in range(L)]
+        self.rstd1 = [torch.empty(T, **f32) for _ in range(L + 1)]
+        self.rstd2 = [torch.empty(T, **f32) for _ in range(L)]
+        # workspaces
+        self.ws_n = torch.empty(T, D, **bf)
+        self.ws_proj = torch.empty(T, D, **bf)
+        self.ws_s = torch.empty(T, Fd, **bf)
+        self.ws_ds = torch.empty(T, Fd, **bf)
+        self.ws_dn = torch.empty(T, D, **bf)
+        self.ws_dh = torch.empty(T, D, **bf)
+        self.ws_dy = torch.empty(T, D, **bf)
+        self.ws_dqkv = torch.empty(T, QKV, **bf)
+        self.logits = torch.empty(T // self.logit_chunks, cfg.vocab_size, **bf)
+        self.loss_rows = torch.empty(T, **f32)
+        self.rope = K.rope_table(seq_len, cfg.head_dim, cfg.rope_theta, device)
+        self.kernel_launches = 0
+
+    # -- helpers ---------------------------------------------------------------------------
+    def _p(self, u: int) -> _Fields:
+        return _Fields(self.param_unit(u), self.cfg.unit_fields(u))
+
+    def _g(self, u: int) -> _Fields:
+        return _Fields(self.grad_unit(u), self.cfg.unit_fields(u))
+
+    # -- forward ---------------------------------------------------------------------------
+    def forward(self, tokens: torch.Tensor, targets: Optional[torch.Tensor], train: bool = True) -> torch.Tensor:
+        """Runs the decoder; with ``targets`` returns the mean token loss and leaves
+        ``dlogits``-derived gradients of the head computed (head backward is fused into
+        the loss pass so that the logits never exist in full)."""
+        c, T, B, S = self.cfg, self.T, self.B, self.S
+        L = c.n_layers
+        tok = tokens.reshape(-1)
+        self.before_unit(0, False)
+        K.embedding_fwd(tok, self._p(0).tok_embeddings, out=self.x[0])
+        delta: Optional[torch.Tensor] = None
+        for l in range(L):
+            u = l + 1
+            self.before_unit(u, False)
+            W = self._p(u)
+            # x[l] = stream (+ delta of the previous block); n1 = norm(x[l])
+            if delta is None:
+                K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
+            else:
+                K.rmsnorm_fwd(self.h[l - 1], W.attn_norm, c.norm_eps, res=delta, h_out=self.x[l], out=self.ws_n,
+                              rstd=self.rstd1[l])
+            K.linear_fwd(self.ws_n, W.wqkv, out=self.qkv[l])
+            K.rope_(self.qkv[l], self.rope, S, c.n_heads + c.n_kv_heads, c.head_dim)
+            self.attn.forward(l, self.qkv[l], B, S, self.att[l], train)
+            K.linear_fwd(self.att[l], W.wo, out=self.ws_proj)
+            K.rmsnorm_fwd(self.x[l], W.ffn_norm, c.norm_eps, res=self.ws_proj, h_out=self.h[l], out=self.ws_n,
+                          rstd=self.rstd2[l])
+            K.linear_fwd(self.ws_n, W.wgu, out=self.gu[l])
+            K.swiglu_fwd(self.gu[l], out=self.ws_s)
+            K.linear_fwd(self.ws_s, W.wd, out=self.ws_proj)
+            delta = self.ws_proj
+        u = L + 1
+        self.before_unit(u, False)
+        W = self._p(u)
+        if delta is None:
+            K.rmsnorm_fwd(self.x[L], W.final_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[L])
+        else:
+            K.rmsnorm_fwd(self.h[L - 1], W.final_norm, c.norm_eps, res=delta, h_out=self.x[L], out=self.ws_n,
+                          rstd=self.rstd1[L])
+        if targets is None:
+            return K.linear_fwd(self.ws_n[-1:].contiguous(), W.lm_head)
+        # head: logits -> loss -> dlogits -> (dW_head, d_norm) chunk by chunk
+        tgt = targets.reshape(-1)
+        G = self._g(u) if train else None
+        rows = T // self.logit_chunks
+        for ci in range(self.logit_chunks):
+            sl = slice(ci * rows, (ci + 1) * rows)
+            K.linear_fwd(self.ws_n[sl], W.lm_head, out=self.logits)
+            K.cross_entropy_(self.logits, tgt[sl], 1.0 / T, loss=self.loss_rows[sl])
+            if train:
+                K.linear_wgrad(self.logits, self.ws_n[sl], out=G.lm_head, accumulate=ci > 0)
+                K.linear_dgrad(self.logits, W.lm_head, out=self.ws_dn[sl])
+        return self.loss_rows.mean()
+
+    # -- backward --------------------------------------------------------------------------
+    def backward(self, tokens: torch.Tensor) -> None:
+        """Backward through the blocks and the embedding; expects :meth:`forward` with
+        targets to have run (``ws_dn`` then holds the gradient of the final norm output)."""
+        c, T, B, S = self.cfg, self.T, self.B, self.S
+        L = c.n_layers
+        u = L + 1
+        W, G = self._p(u), self._g(u)
+        K.rmsnorm_bwd(self.ws_dn, self.x[L], W.final_norm, self.rstd1[L], dres=None, dx=self.ws_dy, dw=G.final_norm)
+        self.grad_done(u)
+        dy = self.ws_dy
+        for l in reversed(range(L)):
+            u = l + 1
+            self.before_unit(u, True)
+            W, G = self._p(u), self._g(u)
+            # ---- FFN
+            K.swiglu_fwd(self.gu[l], out=self.ws_s)
+            K.linear_wgrad(dy, self.ws_s, out=G.wd)
+            K.linear_dgrad(dy, W.wd, out=self.ws_ds)
+            K.swiglu_bwd(self.ws_ds, self.gu[l], dgu=self.gu[l])
+            K.rmsnorm_fwd(self.h[l], W.ffn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd2[l])
+            K.linear_wgrad(self.gu[l], self.ws_n, out=G.wgu)
+            K.linear_dgrad(self.gu[l], W.wgu, out=self.ws_dn)
+            K.rmsnorm_bwd(self.ws_dn, self.h[l], W.ffn_norm, self.rstd2[l], dres=dy, dx=self.ws_dh, dw=G.ffn_norm)
+            # ---- attention
+            K.linear_wgrad(self.ws_dh, self.att[l], out=G.wo)
+            K.linear_dgrad(self.ws_dh, W.wo, out=self.ws_dn)
+            self.attn.backward(l, self.ws_dn, B, S, self.ws_dqkv)
+            K.rope_(self.ws_dqkv, self.rope, S, c.n_heads + c.n_kv_heads, c.head_dim, backward=True)
+            K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
+            K.linear_wgrad(self.ws_dqkv, self.ws_n, out=G.wqkv)
+            K.linear_dgrad(self.ws_dqkv, W.wqkv, out=self.ws_dn)
+            K.rmsnorm_bwd(self.ws_dn, self.x[l], W.attn_norm, self.rstd1[l], dres=self.ws_dh, dx=self.ws_dy,
+                          dw=G.attn_norm)
+            self.grad_done(u)
+            dy = self.ws_dy
+        self.before_unit(0, True)
+        G = self._g(0)
+        G.tok_embeddings.zero_()
+        K.embedding_bwd(tokens.reshape(-1), dy, G.tok_embeddings)
+        self.grad_done(0)
+
+
+def init_unit_(cfg: LlamaConfig, unit: int, flat: torch.Tensor, seed: int) -> None:
+    """Deterministic random init of one full unit (norm weights 1, matrices N(0, 0.02))."""
+    g = torch.Generator(device=flat.device)
+    g.manual_seed(seed * 1000 + unit)
+    f = _Fields(flat, cfg.unit_fields(unit))
+    for name, shape in cfg.unit_fields(unit):
+        t = getattr(f, name)
+        if len(shape) == 1:
+            t.fill_(1.0)
+        else:
+            std = 0.02
+            if name in ("wo", "wd"):
+                std = 0.02 / math.sqrt(2 * cfg.n_layers)
+            # generate in chunks to bound the fp32 temporary
+            flat_t = t.view(-1)
+            step = 1 << 26
+            for s in range(0, flat_t.numel(), step):
+                e = min(flat_t.numel(), s + step)
+                flat_t[s:e] = (torch.randn(e - s, generator=g, device=flat.device, dtype=torch.float32) * std).to(flat.dtype)
+
+
+class TorchLlama(torch.nn.Module):
+    """Plain PyTorch (autograd) restatement of the same decoder: the numerical oracle
+    of :class:`LlamaEngine` and a module users can wrap with the FT DDP wrapper."""
+
+    def __init__(self, cfg: LlamaConfig):
+        super().__init__()
+        self.cfg = cfg
+        D, Fd = cfg.dim, cfg.ffn_dim
+        self.tok_embeddings = torch.nn.Parameter(torch.empty(cfg.vocab_size, D))
+        self.layers = torch.nn.ModuleList()
+        for _ in range(cfg.n_layers):
+            m = torch.nn.Module()
+            for name, shape in cfg.layer_fields():
+                setattr(m, name, torch.nn.Parameter(torch.empty(*shape)))
+            self.layers.append(m)
+        self.final_norm = torch.nn.Parameter(torch.empty(D))
+        self.lm_head = torch.nn.Parameter(torch.empty(cfg.vocab_size, D))
+
+    def load_units(self, unit_fn: Callable[[int], torch.Tensor]) -> None:
+        cfg = self.cfg
+        with torch.no_grad():
+            self.tok_embeddings.copy_(_Fields(unit_fn(0), cfg.unit_fields(0)).tok_embeddings)
+            for l, m in enumerate(self.layers):
+                f = _Fields(unit_fn(l + 1), cfg.unit_fields(l + 1))
+                for name, _ in cfg.layer_fields():
+                    getattr(m, name).copy_(getattr(f, name))
+            f = _Fields(unit_fn(cfg.n_layers + 1), cfg.unit_fields(cfg.n_layers + 1))
+            self.final_norm.copy_(f.final_norm)
+            self.lm_head.copy_(f.lm_head)
+
+    def _norm(self, x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.norm_eps) * w.float()).to(x.dtype)
+
+    def forward(self, tokens: torch.Tensor) -> torch.Tensor:
+        c = self.cfg
+        B, S = tokens.shape
+        Hq, Hkv, Dh = c.n_heads, c.n_kv_heads, c.head_dim
+        x = self.tok_embeddings[tokens]
+        table = K.rope_table(S, Dh, c.rope_theta, x.device)
+        cos, sin = table[..., 0][None, :, None, :], table[..., 1][None, :, None, :]
+
+        def rot(t):
+            t2 = t.float().reshape(*t.shape[:-1], Dh // 2, 2)
+            a, b = t2[..., 0], t2[..., 1]
+            return torch.stack([a * cos - b * sin, a * sin + b * cos], dim=-1).reshape(t.shape).to(t.dtype)
+
+        for m in self.layers:
+            n1 = self._norm(x, m.attn_norm)
+            qkv = n1 @ m.wqkv.t()
+            q = rot(qkv[..., : Hq * Dh].reshape(B, S, Hq, Dh))
+            k = rot(qkv[..., Hq * Dh : (Hq + Hkv) * Dh].reshape(B, S, Hkv, Dh))
+            v = qkv[..., (Hq + Hkv) * Dh :].reshape(B, S, Hkv, Dh)
+            rep = Hq // Hkv
+            a = F.scaled_dot_product_attention(
+                q.transpose(1, 2), k.transpose(1, 2).repeat_interleave(rep, 1), v.transpose(1, 2).repeat_interleave(rep, 1),
+                is_causal=True,
+            ).transpose(1, 2).reshape(B, S, Hq * Dh)
+            x = x + a @ m.wo.t()
+            n2 = self._norm(x, m.ffn_norm)
+            gu = n2 @ m.wgu.t()
+            x = x + (F.silu(gu[..., : c.ffn_dim]) * gu[..., c.ffn_dim :]) @ m.wd.t()
+        return self._norm(x, self.final_norm) @ self.lm_head.t()

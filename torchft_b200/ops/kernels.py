@@ -1,0 +1,429 @@
+"""Python entry points of the sm_100a kernels, with plain-PyTorch references.
+
+Every public function dispatches on the device of its arguments:
+
+* CUDA tensors run the hand-written kernel from ``libftb200_kernels.so`` on the
+  current stream (never an eager fallback);
+* CPU tensors run the ``ref_*`` function of the same name, an fp32 PyTorch
+  restatement of the kernel's math.  The ``ref_*`` functions are also the oracles of
+  the GPU numerics tests.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import _native as N
+from ._native import c_float, c_int, c_ll, c_void_p, ptr, stream_ptr
+
+# --------------------------------------------------------------------------- status word
+
+_status_words: dict = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word that kernels with bounded waits write a code into."""
+    key = (device.type, device.index)
+    w = _status_words.get(key)
+    if w is None:
+        w = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = w
+    return w
+
+
+def check_status(device: torch.device) -> None:
+    """Synchronising read of the status word; raises if any kernel reported a failure."""
+    w = status_word(device)
+    code = int(w.item())
+    if code != 0:
+        w.zero_()
+        raise N.KernelError(f"device-side status: {N.STATUS.get(code, code)}")
+
+
+# --------------------------------------------------------------------------- GEMM
+
+
+def _check_2d_bf16(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 2 or t.dtype != torch.bfloat16 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be a 2-D bf16 tensor with unit inner stride")
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_mn_major: bool = False,
+    b_mn_major: bool = False,
+    out: Optional[torch.Tensor] = None,
+    accumulate: bool = False,
+    out_dtype: torch.dtype = torch.bfloat16,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    """``out (+)= A @ B^T`` with logical ``A [M,K]`` and ``B [N,K]``.
+
+    ``a_mn_major`` says ``a`` is stored as the row-major ``[K, M]`` matrix (and likewise
+    for ``b``), which is how the dgrad and wgrad GEMMs of a linear layer read their
+    operands without transposed copies.
+    """
+    _check_2d_bf16(a, "a")
+    _check_2d_bf16(b, "b")
+    if a_mn_major:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn_major:
+        Kb, Nn = b.shape
+    else:
+        Nn, Kb = b.shape
+    if K != Kb:
+        raise ValueError(f"reduction dims differ: {K} vs {Kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate needs an output tensor")
+        out = torch.empty(M, Nn, dtype=out_dtype, device=a.device)
+    if out.shape != (M, Nn) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("bad output tensor")
+    if not a.is_cuda:
+        af = a.float().t() if a_mn_major else a.float()
+        bf = b.float() if b_mn_major else b.float().t()
+        r = af @ bf
+        if accumulate:
+            r = r + out.float()
+        out.copy_(r.to(out.dtype))
+        return out
+    flags = (1 if out.dtype == torch.float32 else 0) | (2 if accumulate else 0)
+    rc = N.lib().ftb200_gemm_bf16(
+        ptr(a), ptr(b), ptr(out), c_int(M), c_int(Nn), c_int(K), c_int(int(a_mn_major)), c_int(int(b_mn_major)),
+        c_ll(a.stride(0)), c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(flags), ptr(status_word(a.device)),
+        c_int(max_ctas), stream_ptr(),
+    )
+    N.check(rc, "gemm_bf16")
+    return out
+
+
+def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = x @ w^T`` (x ``[T,K]``, w ``[N,K]``)."""
+    return gemm(x, w, False, False, out=out)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 accumulate: bool = False) -> torch.Tensor:
+    """``dx = dy @ w`` (dy ``[T,N]``, w ``[N,K]``)."""
+    return gemm(dy, w, False, True, out=out, accumulate=accumulate)
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``dw = dy^T @ x`` (dy ``[T,N]``, x ``[T,K]``) -> ``[N,K]``."""
+    return gemm(dy, x, True, True, out=out, accumulate=accumulate, out_dtype=out_dtype)
+
+
+# --------------------------------------------------------------------------- embedding
+
+
+def embedding_fwd(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T = tokens.numel()
+    V, D = table.shape
+    if out is None:
+        out = torch.empty(T, D, dtype=table.dtype, device=table.device)
+    if not table.is_cuda:
+        out.copy_(table[tokens.reshape(-1)])
+        return out
+    N.check(N.lib().ftb200_embedding_fwd(ptr(tokens), ptr(table), ptr(out), c_int(T), c_int(D), c_int(V), stream_ptr()),
+            "embedding_fwd")
+    return out
+
+
+def embedding_bwd(tokens: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor) -> torch.Tensor:
+    """``dtable[tokens[t]] += dout[t]`` (``dtable`` must be zeroed by the caller)."""
+    T = tokens.numel()
+    V, D = dtable.shape
+    if not dtable.is_cuda:
+        dtable.copy_(dtable.float().index_add_(0, tokens.reshape(-1), dout.float()).to(dtable.dtype))
+        return dtable
+    N.check(N.lib().ftb200_embedding_bwd(ptr(tokens), ptr(dout), ptr(dtable), c_int(T), c_int(D), c_int(V), stream_ptr()),
+            "embedding_bwd")
+    return dtable
+
+
+# --------------------------------------------------------------------------- RMSNorm
+
+
+def ref_rmsnorm_fwd(x, w, eps, res=None):
+    h = x.float()
+    if res is not None:
+        h = (h + res.float()).to(x.dtype).float()
+    rstd = torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps)
+    return (h * rstd * w.float()).to(x.dtype), rstd.squeeze(-1), h.to(x.dtype)
+
+
+def rmsnorm_fwd(
+    x: torch.Tensor,
+    w: torch.Tensor,
+    eps: float = 1e-5,
+    res: Optional[torch.Tensor] = None,
+    h_out: Optional[torch.Tensor] = None,
+    out: Optional[torch.Tensor] = None,
+    rstd: Optional[torch.Tensor] = None,
+    want_out: bool = True,
+) -> Tuple[Optional[torch.Tensor], torch.Tensor, torch.Tensor]:
+    """Returns ``(normed, rstd, h)`` where ``h = x + res`` (or ``x``)."""
+    T, D = x.shape
+    if rstd is None:
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+    if res is not None and h_out is None:
+        h_out = torch.empty_like(x)
+    if want_out and out is None:
+        out = torch.empty_like(x)
+    if not x.is_cuda:
+        o, r, h = ref_rmsnorm_fwd(x, w, eps, res)
+        rstd.copy_(r)
+        if res is not None:
+            h_out.copy_(h)
+        if want_out:
+            out.copy_(o)
+        return (out if want_out else None), rstd, (h_out if res is not None else x)
+    N.check(
+        N.lib().ftb200_rmsnorm_fwd(ptr(x), ptr(res), ptr(h_out), ptr(w), ptr(out if want_out else None), ptr(rstd),
+                                   c_int(T), c_int(D), c_float(eps), stream_ptr()),
+        "rmsnorm_fwd",
+    )
+    return (out if want_out else None), rstd, (h_out if res is not None else x)
+
+
+def ref_rmsnorm_bwd(dy, x, w, rstd, dres=None):
+    dyf, xf, wf = dy.float(), x.float(), w.float()
+    r = rstd.float().unsqueeze(-1)
+    D = x.shape[-1]
+    dot = (dyf * wf * xf).sum(-1, keepdim=True)
+    dx = r * wf * dyf - xf * dot * r.pow(3) / D
+    if dres is not None:
+        dx = dx + dres.float()
+    dw = (dyf * xf * r).sum(0)
+    return dx.to(x.dtype), dw
+
+
+_rms_scratch: dict = {}
+
+
+def rmsnorm_bwd(
+    dy: torch.Tensor,
+    x: torch.Tensor,
+    w: torch.Tensor,
+    rstd: torch.Tensor,
+    dres: Optional[torch.Tensor] = None,
+    dx: Optional[torch.Tensor] = None,
+    dw: Optional[torch.Tensor] = None,
+    accumulate_dw: bool = False,
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    T, D = x.shape
+    if dx is None:
+        dx = torch.empty_like(x)
+    if dw is None:
+        dw = torch.zeros(D, dtype=w.dtype, device=x.device)
+    if not x.is_cuda:
+        rdx, rdw = ref_rmsnorm_bwd(dy, x, w, rstd, dres)
+        dx.copy_(rdx)
+        dw.copy_(((dw.float() if accumulate_dw else 0) + rdw).to(dw.dtype))
+        return dx, dw
+    L = N.lib()
+    L.ftb200_rmsnorm_bwd_scratch_floats.restype = c_ll
+    need = int(L.ftb200_rmsnorm_bwd_scratch_floats(c_int(D)))
+    key = (x.device.index, need)
+    scratch = _rms_scratch.get(key)
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=x.device)
+        _rms_scratch[key] = scratch
+    N.check(
+        L.ftb200_rmsnorm_bwd(ptr(dy), ptr(x), ptr(w), ptr(rstd), ptr(dres), ptr(dx), ptr(dw), ptr(scratch), c_int(T),
+                             c_int(D), c_int(int(accumulate_dw)), stream_ptr()),
+        "rmsnorm_bwd",
+        launches=2,
+    )
+    return dx, dw
+
+
+# --------------------------------------------------------------------------- RoPE
+
+
+def rope_table(seq_len: int, head_dim: int, theta: float, device) -> torch.Tensor:
+    """``[S, head_dim/2, 2]`` fp32 table of (cos, sin) for interleaved-pair rotation."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.outer(torch.arange(seq_len, dtype=torch.float64), inv)
+    return torch.stack([ang.cos(), ang.sin()], dim=-1).float().to(device).contiguous()
+
+
+def ref_rope(buf, table, S, n_heads, head_dim, backward=False):
+    T = buf.shape[0]
+    rot = buf[:, : n_heads * head_dim].float().reshape(T, n_heads, head_dim // 2, 2)
+    pos = torch.arange(T, device=buf.device) % S
+    cs = table[pos].unsqueeze(1)  # T,1,Dh/2,2
+    c, s = cs[..., 0], cs[..., 1]
+    if backward:
+        s = -s
+    x0, x1 = rot[..., 0], rot[..., 1]
+    o = torch.stack([x0 * c - x1 * s, x0 * s + x1 * c], dim=-1).reshape(T, n_heads * head_dim)
+    res = buf.clone()
+    res[:, : n_heads * head_dim] = o.to(buf.dtype)
+    return res
+
+
+def rope_(buf: torch.Tensor, table: torch.Tensor, seq_len: int, n_heads: int, head_dim: int,
+          backward: bool = False) -> torch.Tensor:
+    """Rotate the first ``n_heads`` heads of every row of ``buf`` ``[T, >= n_heads*head_dim]`` in place."""
+    T = buf.shape[0]
+    if not buf.is_cuda:
+        buf.copy_(ref_rope(buf, table, seq_len, n_heads, head_dim, backward))
+        return buf
+    N.check(
+        N.lib().ftb200_rope(ptr(buf), ptr(table), c_ll(T), c_int(seq_len), c_int(n_heads), c_int(head_dim),
+                            c_ll(buf.stride(0)), c_int(int(backward)), stream_ptr()),
+        "rope",
+    )
+    return buf
+
+
+# --------------------------------------------------------------------------- SwiGLU
+
+
+def ref_swiglu_fwd(gu):
+    Fd = gu.shape[-1] // 2
+    g, u = gu[:, :Fd].float(), gu[:, Fd:].float()
+    return (F.silu(g) * u).to(gu.dtype)
+
+
+def swiglu_fwd(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T, F2 = gu.shape
+    Fd = F2 // 2
+    if out is None:
+        out = torch.empty(T, Fd, dtype=gu.dtype, device=gu.device)
+    if not gu.is_cuda:
+        out.copy_(ref_swiglu_fwd(gu))
+        return out
+    N.check(N.lib().ftb200_swiglu_fwd(ptr(gu), ptr(out), c_ll(T), c_int(Fd), stream_ptr()), "swiglu_fwd")
+    return out
+
+
+def ref_swiglu_bwd(ds, gu):
+    Fd = gu.shape[-1] // 2
+    g, u, d = gu[:, :Fd].float(), gu[:, Fd:].float(), ds.float()
+    sg = torch.sigmoid(g)
+    silu = g * sg
+    return torch.cat([d * u * (sg + silu * (1 - sg)), d * silu], dim=1).to(gu.dtype)
+
+
+def swiglu_bwd(ds: torch.Tensor, gu: torch.Tensor, dgu: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``dgu`` may alias ``gu`` (in place)."""
+    T, F2 = gu.shape
+    if dgu is None:
+        dgu = torch.empty_like(gu)
+    if not gu.is_cuda:
+        dgu.copy_(ref_swiglu_bwd(ds, gu))
+        return dgu
+    N.check(N.lib().ftb200_swiglu_bwd(ptr(ds), ptr(gu), ptr(dgu), c_ll(T), c_int(F2 // 2), stream_ptr()), "swiglu_bwd")
+    return dgu
+
+
+# --------------------------------------------------------------------------- cross-entropy
+
+
+def ref_cross_entropy(logits, target, grad_scale):
+    lf = logits.float()
+    loss = F.cross_entropy(lf, target, reduction="none")
+    p = torch.softmax(lf, dim=-1)
+    p[torch.arange(lf.shape[0]), target] -= 1.0
+    return loss, (p * grad_scale).to(logits.dtype)
+
+
+def cross_entropy_(logits: torch.Tensor, target: torch.Tensor, grad_scale: float,
+                   loss: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-row loss; ``logits`` is overwritten by ``(softmax - onehot) * grad_scale``."""
+    T, V = logits.shape
+    if loss is None:
+        loss = torch.empty(T, dtype=torch.float32, device=logits.device)
+    if not logits.is_cuda:
+        l, g = ref_cross_entropy(logits, target, grad_scale)
+        loss.copy_(l)
+        logits.copy_(g)
+        return loss
+    N.check(
+        N.lib().ftb200_cross_entropy(ptr(logits), ptr(target), ptr(loss), c_int(T), c_int(V), c_ll(logits.stride(0)),
+                                     c_float(grad_scale), stream_ptr()),
+        "cross_entropy",
+    )
+    return loss
+
+
+# --------------------------------------------------------------------------- AdamW / grad norm
+
+
+def ref_adamw(master, m, v, grad, lr, beta1, beta2, eps, wd, step, grad_scale=1.0):
+    g = grad.float() * grad_scale
+    m.mul_(beta1).add_(g, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(g, g, value=1 - beta2)
+    bc1 = 1 - beta1 ** step
+    bc2s = math.sqrt(1 - beta2 ** step)
+    denom = v.sqrt() / bc2s + eps
+    master.mul_(1 - lr * wd).addcdiv_(m, denom, value=-lr / bc1)
+
+
+def adamw_(master: torch.Tensor, m: torch.Tensor, v: torch.Tensor, grad: torch.Tensor,
+           param_lp: Optional[torch.Tensor], lr: float, beta1: float, beta2: float, eps: float, wd: float,
+           step: int, grad_scale: Optional[torch.Tensor] = None) -> None:
+    """One fused AdamW step over flat buffers (fp32 state, bf16 or fp32 grads, bf16 write-back)."""
+    n = master.numel()
+    if not master.is_cuda:
+        gs = float(grad_scale.item()) if grad_scale is not None else 1.0
+        ref_adamw(master.view(-1), m.view(-1), v.view(-1), grad.reshape(-1), lr, beta1, beta2, eps, wd, step, gs)
+        if param_lp is not None:
+            param_lp.view(-1).copy_(master.view(-1).to(param_lp.dtype))
+        return
+    N.check(
+        N.lib().ftb200_adamw(ptr(master), ptr(m), ptr(v), ptr(grad), c_int(int(grad.dtype == torch.float32)),
+                             ptr(param_lp), c_ll(n), c_float(lr), c_float(beta1), c_float(beta2), c_float(eps),
+                             c_float(wd), c_int(step), ptr(grad_scale), stream_ptr()),
+        "adamw",
+    )
+
+
+def sumsq_(x: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out += sum(x^2)`` (``out`` is a 1-element fp32 tensor)."""
+    if not x.is_cuda:
+        out.add_(x.float().pow(2).sum())
+        return out
+    N.check(N.lib().ftb200_sumsq(ptr(x), c_int(int(x.dtype == torch.float32)), c_ll(x.numel()), ptr(out), stream_ptr()),
+            "sumsq")
+    return out
+
+
+def clip_coef_(sumsq: torch.Tensor, max_norm: float, coef: torch.Tensor, norm_out: Optional[torch.Tensor] = None) -> None:
+    if not sumsq.is_cuda:
+        nrm = sumsq.sqrt()
+        if norm_out is not None:
+            norm_out.copy_(nrm)
+        coef.copy_(torch.clamp(max_norm / (nrm + 1e-6), max=1.0) if max_norm > 0 else torch.ones_like(nrm))
+        return
+    N.check(N.lib().ftb200_clip_coef(ptr(sumsq), c_float(max_norm), ptr(coef), ptr(norm_out), stream_ptr()), "clip_coef")
+
+
+# --------------------------------------------------------------------------- attention
+
+
+def ref_attention(q, k, v, causal=True):
+    """q ``[B,S,Hq,Dh]``, k/v ``[B,S,Hkv,Dh]`` -> ``[B,S,Hq,Dh]`` (fp32 math)."""
+    B, S, Hq, Dh = q.shape
+    Hkv = k.shape[2]
+    rep = Hq // Hkv
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(Dh)
+    if causal:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return (p @ vf).permute(0, 2, 1, 3).to(q.dtype)

@@ -1,0 +1,236 @@
+"""Fault-tolerant HSDP trainer for the Llama engine.
+
+Sharding (inside a replica group) is FSDP-style over flat per-layer units: every rank
+owns ``1/shard_size`` of each unit as a bf16 working shard plus fp32 master weights and
+AdamW moments.  Full (gathered) bf16 units stay resident between forward and backward
+(B200 has the HBM for it), so each unit is all-gathered once per step, prefetched one
+unit ahead on a communication stream.  Gradients are produced into double-buffered
+full units, reduce-scattered to shards as soon as a unit's backward ends, then averaged
+over the replica dimension through ``Manager.allreduce`` -- the only place the
+fault-tolerant world size appears.  ``Manager.should_commit`` gates the optimizer step.
+
+The replica dimension mirrors what the reference obtains by giving FSDP2 a device mesh
+whose replicate dimension is a ``ManagedProcessGroup`` (torchft/device_mesh.py:307-340).
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..models.llama import LlamaConfig, LlamaEngine, init_unit_
+from ..ops import kernels as K
+from .shard_comm import LocalShardComm, ShardComm
+
+
+def _round_up(x: int, m: int) -> int:
+    return (x + m - 1) // m * m
+
+
+class ShardedLlamaTrainer:
+    def __init__(
+        self,
+        cfg: LlamaConfig,
+        batch: int,
+        seq_len: int,
+        device: torch.device,
+        shard_comm: Optional[ShardComm] = None,
+        manager=None,
+        lr: float = 3e-4,
+        betas=(0.9, 0.95),
+        eps: float = 1e-8,
+        weight_decay: float = 0.1,
+        max_grad_norm: float = 1.0,
+        seed: int = 0,
+        attention=None,
+        logit_chunks: int = 4,
+    ):
+        self.cfg, self.device = cfg, device
+        self.comm = shard_comm or LocalShardComm()
+        self.manager = manager
+        self.lr, self.betas, self.eps, self.wd = lr, betas, eps, weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.opt_step = 0
+        ws, rank = self.comm.size, self.comm.rank
+        self.cuda = device.type == "cuda"
+        U = cfg.n_units
+        self.unit_numel = [cfg.unit_numel(u) for u in range(U)]
+        self.shard_numel = [_round_up(n, ws * 8) // ws for n in self.unit_numel]
+        self.full_numel = [s * ws for s in self.shard_numel]
+
+        bf, f32 = torch.bfloat16, torch.float32
+        A = self.comm.alloc
+        self.p_shard = [A(n, bf, device) for n in self.shard_numel]
+        self.g_shard = [A(n, bf, device) for n in self.shard_numel]
+        self.master = [torch.empty(n, dtype=f32, device=device) for n in self.shard_numel]
+        self.m = [torch.zeros(n, dtype=f32, device=device) for n in self.shard_numel]
+        self.v = [torch.zeros(n, dtype=f32, device=device) for n in self.shard_numel]
+        if ws == 1:
+            self.p_full = self.p_shard
+            self._g_bufs: Dict[int, List[torch.Tensor]] = {}
+        else:
+            self.p_full = [A(n, bf, device) for n in self.full_numel]
+            sizes = sorted(set(self.full_numel))
+            self._g_bufs = {s: [A(s, bf, device) for _ in range(2 if self.full_numel.count(s) > 1 else 1)] for s in sizes}
+        self._g_slot = [0] * U
+        cnt: Dict[int, int] = {}
+        for u in range(U):
+            s = self.full_numel[u]
+            self._g_slot[u] = cnt.get(s, 0) % 2
+            cnt[s] = cnt.get(s, 0) + 1
+
+        # deterministic init: every rank generates the full unit, keeps its slice
+        for u in range(U):
+            if ws == 1:
+                init_unit_(cfg, u, self.p_full[u][: self.unit_numel[u]], seed)
+                self.p_full[u][self.unit_numel[u]:].zero_()
+            else:
+                full = self.p_full[u]
+                full.zero_()
+                init_unit_(cfg, u, full[: self.unit_numel[u]], seed)
+                n = self.shard_numel[u]
+                self.p_shard[u].copy_(full[rank * n : (rank + 1) * n])
+            self.master[u].copy_(self.p_shard[u].float())
+
+        self.comm_stream = torch.cuda.Stream(device=device, priority=-1) if self.cuda and ws > 1 else None
+        self._ag_event: List[Optional[torch.cuda.Event]] = [None] * U
+        self._rs_event: Dict[int, Optional[torch.cuda.Event]] = {}
+        self._gathered = [ws == 1] * U
+        self._works: List = []
+        self.sumsq = torch.zeros(1, dtype=f32, device=device)
+        self.clip = torch.ones(1, dtype=f32, device=device)
+        self.grad_norm = torch.zeros(1, dtype=f32, device=device)
+        self.engine = LlamaEngine(
+            cfg, batch, seq_len, device, self._param_unit, self._grad_unit, self._before_unit, self._grad_done,
+            attention=attention, logit_chunks=logit_chunks,
+        )
+
+    # ---- unit plumbing -------------------------------------------------------------------
+    def _param_unit(self, u: int) -> torch.Tensor:
+        return self.p_full[u][: self.unit_numel[u]]
+
+    def _grad_buf(self, u: int) -> torch.Tensor:
+        if self.comm.size == 1:
+            return self.g_shard[u]
+        return self._g_bufs[self.full_numel[u]][self._g_slot[u] % len(self._g_bufs[self.full_numel[u]])]
+
+    def _grad_unit(self, u: int) -> torch.Tensor:
+        return self._grad_buf(u)[: self.unit_numel[u]]
+
+    def _issue_all_gather(self, u: int) -> None:
+        if self._gathered[u] or u >= self.cfg.n_units:
+            return
+        if self.comm_stream is not None:
+            with torch.cuda.stream(self.comm_stream):
+                self.comm.all_gather(self.p_shard[u], self.p_full[u])
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+            self._ag_event[u] = ev
+        else:
+            self.comm.all_gather(self.p_shard[u], self.p_full[u])
+        self._gathered[u] = True
+
+    def _before_unit(self, u: int, backward: bool) -> None:
+        if self.comm.size == 1:
+            return
+        if not backward:
+            self._issue_all_gather(u)
+            ev = self._ag_event[u]
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+                self._ag_event[u] = None
+            if u + 1 < self.cfg.n_units:
+                self._issue_all_gather(u + 1)
+        else:
+            # the gradient buffer about to be written may still feed an earlier reduce-scatter
+            key = self._grad_buf(u).data_ptr()
+            ev = self._rs_event.pop(key, None)
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+
+    def _grad_done(self, u: int) -> None:
+        ws = self.comm.size
+        if ws > 1:
+            buf = self._grad_buf(u)
+            pad = self.full_numel[u] - self.unit_numel[u]
+            if pad:
+                buf[self.unit_numel[u]:].zero_()
+            if self.comm_stream is not None:
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    self.comm.reduce_scatter(buf, self.g_shard[u])
+                    self._replica_allreduce(u)
+                    ev = torch.cuda.Event()
+                    ev.record(self.comm_stream)
+                self._rs_event[buf.data_ptr()] = ev
+            else:
+                self.comm.reduce_scatter(buf, self.g_shard[u])
+                self._replica_allreduce(u)
+        else:
+            self._replica_allreduce(u)
+
+    def _replica_allreduce(self, u: int) -> None:
+        if self.manager is not None:
+            self._works.append(self.manager.allreduce(self.g_shard[u]))
+
+    # ---- public step ---------------------------------------------------------------------
+    def forward_backward(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        if self.cuda and self.comm.size > 1:
+            # head/embedding units use single gradient buffers: order against last step's readers
+            pass
+        loss = self.engine.forward(tokens, targets, train=True)
+        self.engine.backward(tokens)
+        return loss
+
+    def _finish_comm(self) -> None:
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        for w in self._works:
+            w.wait()
+        self._works.clear()
+        self._rs_event.clear()
+
+    def optimizer_step(self) -> None:
+        self.opt_step += 1
+        self.sumsq.zero_()
+        for u in range(self.cfg.n_units):
+            K.sumsq_(self.g_shard[u], self.sumsq)
+        self.comm.all_reduce_sum_(self.sumsq)
+        K.clip_coef_(self.sumsq, self.max_grad_norm, self.clip, self.grad_norm)
+        b1, b2 = self.betas
+        for u in range(self.cfg.n_units):
+            K.adamw_(self.master[u], self.m[u], self.v[u], self.g_shard[u], self.p_shard[u], self.lr, b1, b2, self.eps,
+                     self.wd, self.opt_step, self.clip)
+        if self.comm.size > 1:
+            self._gathered = [False] * self.cfg.n_units
+
+    def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
+        """One fault-tolerant step: quorum, forward/backward with overlapped gradient
+        reduction, commit vote, optimizer step."""
+        if self.manager is not None:
+            self.manager.start_quorum()
+        loss = self.forward_backward(tokens, targets)
+        self._finish_comm()
+        if self.manager is None or self.manager.should_commit():
+            self.optimizer_step()
+        return loss
+
+    # ---- state dict (heal / durable checkpoints) -------------------------------------------
+    def state_dict(self) -> Dict[str, object]:
+        return {
+            "opt_step": self.opt_step,
+            "master": self.master,
+            "m": self.m,
+            "v": self.v,
+        }
+
+    def load_state_dict(self, sd: Dict[str, object]) -> None:
+        self.opt_step = int(sd["opt_step"])
+        for u in range(self.cfg.n_units):
+            self.master[u].copy_(sd["master"][u])
+            self.m[u].copy_(sd["m"][u])
+            self.v[u].copy_(sd["v"][u])
+            self.p_shard[u].copy_(self.master[u].to(torch.bfloat16))
+        if self.comm.size > 1:
+            self._gathered = [False] * self.cfg.n_units
