@@ -1,0 +1,332 @@
+"""Control-plane tests: the quorum mathematics on hand-built states (the vectors come from
+the behaviour the reference's Rust unit tests pin down, src/lighthouse.rs:627-1112 and
+src/manager.rs:880-1107) and end-to-end runs over real sockets in-process."""
+import threading
+import time
+import urllib.request
+from datetime import timedelta
+
+import pytest
+
+from torchft_b200 import _ftcp as C
+
+M = C.QuorumMember
+
+
+def member(rid, step=1, shrink_only=False, commit_failures=0):
+    return M(replica_id=rid, address=f"addr_{rid}", store_address=f"store_{rid}", step=step, world_size=1,
+             shrink_only=shrink_only, commit_failures=commit_failures)
+
+
+def quorum_of(ids, qid=1, steps=None):
+    q = C.Quorum()
+    q.quorum_id = qid
+    q.participants = [member(i, step=(steps or {}).get(i, 1)) for i in ids]
+    return q
+
+
+def compute(now, parts, hbs, prev=None, min_replicas=1, join_ms=60000, hb_ms=5000):
+    got, reason = C.quorum_compute(now, parts, hbs, prev, min_replicas, join_ms, hb_ms)
+    return (None if got is None else [m.replica_id for m in got]), reason
+
+
+HOUR_MS = 3600 * 1000
+
+
+def test_quorum_join_timeout():
+    now = 1e6
+    ids, reason = compute(now, [], {}, join_ms=HOUR_MS)
+    assert ids is None
+    assert "New quorum not ready, only have 0 participants, need min_replicas 1 [0/0 participants healthy]" in reason
+    parts = [(member("a"), now), (member("b"), now)]
+    hbs = {"a": now, "b": now}
+    assert compute(now, parts, hbs, join_ms=HOUR_MS)[0] == ["a", "b"]
+    # a third replica heartbeats but has not joined: wait for it
+    hbs["c"] = now
+    ids, reason = compute(now, parts, hbs, join_ms=HOUR_MS)
+    assert ids is None and "join timeout" in reason
+    # ... unless the first joiner has already waited longer than the join timeout
+    parts_old = [(member("a"), now - 10 * 3600), (member("b"), now)]
+    assert compute(now, parts_old, hbs, join_ms=HOUR_MS)[0] == ["a", "b"]
+
+
+def test_quorum_heartbeats():
+    now = 1e6
+    ids, reason = compute(now, [(member("a"), now)], {"a": now - 10}, join_ms=0)
+    assert ids is None and "[0/1 participants healthy][0 heartbeating]" in reason
+    ids, _ = compute(now, [(member("a"), now), (member("b"), now)], {"a": now - 10, "b": now}, join_ms=0)
+    assert ids == ["b"]
+
+
+def test_quorum_fast_prev_quorum():
+    now = 1e6
+    prev = quorum_of(["a"])
+    # a is back, b heartbeats but has not joined: fast quorum does not wait for b
+    ids, reason = compute(now, [(member("a"), now)], {"a": now, "b": now}, prev, join_ms=HOUR_MS)
+    assert ids == ["a"] and "Fast quorum" in reason
+    # a new joiner rides along
+    ids, _ = compute(now, [(member("a"), now), (member("b"), now)], {"a": now, "b": now}, prev, join_ms=HOUR_MS)
+    assert ids == ["a", "b"]
+
+
+def test_quorum_shrink_only():
+    now = 1e6
+    prev = quorum_of(["a", "b"])
+    parts = [(member("a", shrink_only=True), now), (member("c", shrink_only=True), now)]
+    ids, reason = compute(now, parts, {"a": now, "c": now}, prev, join_ms=0)
+    assert ids == ["a"] and "[shrink_only=true]" in reason
+
+
+def test_quorum_split_brain():
+    now = 1e6
+    ids, reason = compute(now, [(member("a"), now)], {"a": now, "b": now}, join_ms=0)
+    assert ids is None
+    assert "need at least half of 2 healthy workers [1/1 participants healthy][2 heartbeating]" in reason
+    ids, _ = compute(now, [(member("a"), now), (member("b"), now)], {"a": now, "b": now, "c": now}, join_ms=0)
+    assert ids == ["a", "b"]
+
+
+def test_quorum_changed():
+    a, b = member("1"), member("1")
+    assert not C.quorum_changed([a], [b])
+    b.address, b.store_address, b.step = "other", "other", 9
+    assert not C.quorum_changed([a], [b])
+    assert C.quorum_changed([a], [member("2")])
+    assert C.quorum_changed([a], [a, member("2")])
+
+
+def test_compute_quorum_results_first_step():
+    q = quorum_of(["replica_0", "replica_1"], qid=1, steps={"replica_0": 0, "replica_1": 0})
+    r = C.compute_quorum_results("replica_0", 0, q, True)
+    assert (r.heal, r.replica_rank, r.recover_src_replica_rank, r.recover_dst_replica_ranks) == (False, 0, None, [1])
+    r = C.compute_quorum_results("replica_1", 0, q, True)
+    assert (r.heal, r.replica_rank, r.recover_src_replica_rank, r.recover_dst_replica_ranks) == (True, 1, 0, [])
+    assert r.recover_src_manager_address == "addr_replica_0"
+    # the primary rotates with the local rank
+    r = C.compute_quorum_results("replica_1", 1, q, True)
+    assert (r.heal, r.replica_rank, r.recover_dst_replica_ranks) == (False, 1, [0])
+    assert r.store_address == "store_replica_1"
+
+
+def test_compute_quorum_results_recovery():
+    steps = {"replica_0": 0, "replica_1": 1, "replica_2": 0, "replica_3": 1, "replica_4": 0}
+    q = quorum_of(sorted(steps), qid=1, steps=steps)
+    r = C.compute_quorum_results("replica_0", 0, q, True)
+    assert r.heal and r.recover_src_replica_rank == 1 and r.recover_src_manager_address == "addr_replica_1"
+    assert (r.max_step, r.max_replica_rank, r.max_world_size, r.replica_world_size) == (1, None, 2, 5)
+    r = C.compute_quorum_results("replica_1", 0, q, True)
+    assert not r.heal and r.recover_dst_replica_ranks == [0, 4] and r.max_replica_rank == 0
+    assert r.store_address == "store_replica_1"
+    r = C.compute_quorum_results("replica_3", 0, q, True)
+    assert not r.heal and r.recover_dst_replica_ranks == [2] and r.max_replica_rank == 1
+    # local rank 1 shifts the striping
+    r = C.compute_quorum_results("replica_1", 1, q, True)
+    assert r.recover_dst_replica_ranks == [2] and r.store_address == "store_replica_3"
+
+
+def test_compute_quorum_results_skip_init_sync():
+    q = quorum_of(["replica_0", "replica_1"], steps={"replica_0": 0, "replica_1": 0})
+    assert C.compute_quorum_results("replica_1", 0, q, True).heal
+    assert not C.compute_quorum_results("replica_1", 0, q, False).heal
+    q = quorum_of(["replica_0", "replica_1"], steps={"replica_0": 1, "replica_1": 0})
+    assert C.compute_quorum_results("replica_1", 0, q, False).heal
+
+
+def test_compute_quorum_results_commit_failures_and_missing():
+    q = C.Quorum()
+    q.quorum_id = 1
+    q.participants = [member("replica_0", 0, commit_failures=0), member("replica_1", 0, commit_failures=2)]
+    assert C.compute_quorum_results("replica_0", 0, q, True).commit_failures == 2
+    with pytest.raises(RuntimeError, match="not participating"):
+        C.compute_quorum_results("nobody", 0, q, True)
+
+
+# ----------------------------------------------------------------------------- sockets
+
+
+def test_lighthouse_e2e_and_dashboard():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    try:
+        cl = C.LighthouseClient(lh.address(), timedelta(seconds=5))
+        cl.heartbeat("foo")
+        q = cl.quorum("foo", timedelta(seconds=5), address="addr", store_address="store", step=10, world_size=1,
+                      data={"my_key": "my_value"})
+        assert q.quorum_id == 1 and len(q.participants) == 1
+        assert q.participants[0].replica_id == "foo" and q.participants[0].step == 10
+        assert q.participants[0].data == {"my_key": "my_value"}
+        assert q.created.seconds > 0
+        port = lh.address().rsplit(":", 1)[1]
+        html = urllib.request.urlopen(f"http://localhost:{port}/status", timeout=5).read().decode()
+        assert "Previous quorum id: 1" in html and "foo" in html
+        index = urllib.request.urlopen(f"http://localhost:{port}/", timeout=5).read().decode()
+        assert "Lighthouse Dashboard" in index
+    finally:
+        lh.shutdown()
+
+
+def test_lighthouse_join_timeout_bound():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=400, quorum_tick_ms=10)
+    try:
+        cl = C.LighthouseClient(lh.address(), timedelta(seconds=5))
+        cl.heartbeat("straggler")  # healthy but never joins
+        t0 = time.time()
+        # split-brain guard: 1 of 2 heartbeating is not a majority until the straggler expires
+        with pytest.raises(TimeoutError):
+            cl.quorum("a", timedelta(milliseconds=300))
+        assert time.time() - t0 < 2.0
+    finally:
+        lh.shutdown()
+
+
+def test_lighthouse_heartbeat_expiry_lets_survivor_continue():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10, heartbeat_timeout_ms=300)
+    stop = threading.Event()
+    try:
+        a = C.LighthouseClient(lh.address(), timedelta(seconds=5))
+        b = C.LighthouseClient(lh.address(), timedelta(seconds=5))
+        hb = C.LighthouseClient(lh.address(), timedelta(seconds=5))
+        a.heartbeat("a")
+        b.heartbeat("b")
+
+        def beat():  # what a live manager does every heartbeat interval
+            while not stop.is_set():
+                hb.heartbeat("a")
+                time.sleep(0.05)
+
+        threading.Thread(target=beat, daemon=True).start()
+        out = {}
+        tb = threading.Thread(target=lambda: out.setdefault("b", b.quorum("b", timedelta(seconds=5))))
+        tb.start()
+        qa = a.quorum("a", timedelta(seconds=5))
+        tb.join()
+        assert {p.replica_id for p in qa.participants} == {"a", "b"} and qa.quorum_id == 1
+        # b dies (no more heartbeats); a alone gets a new quorum once b's heartbeat expires
+        t0 = time.time()
+        qa2 = a.quorum("a", timedelta(seconds=5))
+        assert [p.replica_id for p in qa2.participants] == ["a"] and qa2.quorum_id == 2
+        assert time.time() - t0 < 2.0
+    finally:
+        stop.set()
+        lh.shutdown()
+
+
+def test_lighthouse_commit_failures_bump_quorum_id():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    try:
+        cl = C.LighthouseClient(lh.address(), timedelta(seconds=5))
+        assert cl.quorum("a", timedelta(seconds=5)).quorum_id == 1
+        assert cl.quorum("a", timedelta(seconds=5)).quorum_id == 1
+    finally:
+        lh.shutdown()
+
+
+def _manager(lh, rid="rep", world_size=1, retries=0):
+    return C.ManagerServer(replica_id=rid, lighthouse_addr=lh.address(), hostname="localhost", bind="[::]:0",
+                           store_addr="store:1", world_size=world_size, heartbeat_interval=timedelta(milliseconds=50),
+                           connect_timeout=timedelta(seconds=5), quorum_retries=retries)
+
+
+def test_manager_quorum_single_replica():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    ms = _manager(lh, "rep_id")
+    try:
+        c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+        r = c._quorum(group_rank=0, step=123, checkpoint_metadata="addr", shrink_only=False,
+                      timeout=timedelta(seconds=5), init_sync=True, commit_failures=0)
+        assert (r.quorum_id, r.max_step, r.max_replica_rank, r.max_world_size) == (1, 123, 0, 1)
+        assert (r.replica_rank, r.replica_world_size, r.heal, r.store_address) == (0, 1, False, "store:1")
+        assert c._checkpoint_metadata(0, timedelta(seconds=5)) == "addr"
+        with pytest.raises(RuntimeError, match="rank not found"):
+            c._checkpoint_metadata(7, timedelta(seconds=5))
+    finally:
+        ms.shutdown()
+        lh.shutdown()
+
+
+def test_manager_should_commit_barrier_and_timeout():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    ms = _manager(lh, world_size=2)
+    try:
+        out = {}
+
+        def vote(rank, v):
+            c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+            out[rank] = c.should_commit(rank, 1, v, timedelta(seconds=5))
+
+        for votes, want in (((True, True), True), ((True, False), False), ((True, True), True)):
+            ts = [threading.Thread(target=vote, args=(r, v)) for r, v in enumerate(votes)]
+            [t.start() for t in ts]
+            [t.join() for t in ts]
+            assert out == {0: want, 1: want}
+        c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+        t0 = time.time()
+        with pytest.raises(TimeoutError):
+            c.should_commit(0, 2, True, timedelta(milliseconds=100))
+        assert time.time() - t0 < 1.0
+        # the vote that timed out must not leak into the next round
+        ts = [threading.Thread(target=vote, args=(r, True)) for r in range(2)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert out == {0: True, 1: True}
+    finally:
+        ms.shutdown()
+        lh.shutdown()
+
+
+def test_two_replica_groups_heal_assignment():
+    lh = C.LighthouseServer("[::]:0", 2, join_timeout_ms=100, quorum_tick_ms=10)
+    m0, m1 = _manager(lh, "rep_0"), _manager(lh, "rep_1")
+    try:
+        res = {}
+
+        def go(ms, name, step):
+            c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+            res[name] = c._quorum(group_rank=0, step=step, checkpoint_metadata=name, shrink_only=False,
+                                  timeout=timedelta(seconds=5), init_sync=True, commit_failures=0)
+
+        ts = [threading.Thread(target=go, args=(m0, "rep_0", 5)), threading.Thread(target=go, args=(m1, "rep_1", 0))]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        a, b = res["rep_0"], res["rep_1"]
+        assert a.quorum_id == b.quorum_id == 1
+        assert not a.heal and a.recover_dst_replica_ranks == [1] and a.max_replica_rank == 0
+        assert b.heal and b.recover_src_replica_rank == 0 and b.recover_src_manager_address == m0.address()
+        assert b.max_replica_rank is None and b.max_world_size == 1 and b.replica_world_size == 2
+        assert C.ManagerClient(b.recover_src_manager_address, timedelta(seconds=5))._checkpoint_metadata(
+            0, timedelta(seconds=5)) == "rep_0"
+    finally:
+        m0.shutdown()
+        m1.shutdown()
+        lh.shutdown()
+
+
+def test_manager_reports_lighthouse_failure_to_all_ranks():
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    ms = _manager(lh, world_size=2, retries=1)
+    lh.shutdown()  # lighthouse gone: the round must fail for both ranks, promptly
+    try:
+        errs = {}
+
+        def go(rank):
+            c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+            try:
+                c._quorum(group_rank=rank, step=0, checkpoint_metadata="", shrink_only=False,
+                          timeout=timedelta(seconds=2), init_sync=True, commit_failures=0)
+            except (RuntimeError, TimeoutError) as e:
+                errs[rank] = e
+
+        t0 = time.time()
+        ts = [threading.Thread(target=go, args=(r,)) for r in range(2)]
+        [t.start() for t in ts]
+        [t.join() for t in ts]
+        assert set(errs) == {0, 1}
+        assert time.time() - t0 < 8.0
+    finally:
+        ms.shutdown()
+
+
+def test_connect_timeout_raises_timeout_error():
+    t0 = time.time()
+    with pytest.raises(TimeoutError):
+        C.ManagerClient("localhost:1", timedelta(milliseconds=300))
+    assert time.time() - t0 < 3.0

@@ -1,0 +1,114 @@
+"""Micro-benchmarks of the sm_100a kernels (CUDA-event timing, warm-up, L2-exceeding inputs).
+
+    python -m torchft_b200.ops.bench_kernels gemm --m 8192 --n 8192 --k 8192 --layout fwd
+    python -m torchft_b200.ops.bench_kernels adamw --n 1073741824
+    python -m torchft_b200.ops.bench_kernels all
+
+Each line printed is JSON: achieved TFLOP/s or GB/s and the fraction of the measured
+peaks in ``MEASURED_PEAKS.json`` (cuBLAS bf16 burst and STREAM-style copy) when that
+file is present next to the package.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from typing import Callable
+
+import torch
+
+from . import kernels as K
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d.get("hbm_gbs", 6650.0), d.get("bf16_tflops", 1590.0), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn: Callable[[], None], iters: int = 10, warmup: int = 3) -> float:
+    """Milliseconds per call (CUDA events on the current stream)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def bench_gemm(m: int, n: int, k: int, layout: str, iters: int, compare: bool) -> dict:
+    dev = "cuda"
+    x = torch.randn(m, k, device=dev).bfloat16()
+    w = torch.randn(n, k, device=dev).bfloat16()
+    dy = torch.randn(m, n, device=dev).bfloat16()
+    fns = {
+        "fwd": (lambda: K.linear_fwd(x, w), lambda: torch.matmul(x, w.t())),
+        "dgrad": (lambda: K.linear_dgrad(dy, w), lambda: torch.matmul(dy, w)),
+        "wgrad": (lambda: K.linear_wgrad(dy, x), lambda: torch.matmul(dy.t(), x)),
+    }
+    ours, lib = fns[layout]
+    ms = timeit(ours, iters)
+    K.check_status(x.device)
+    hbm, tf, how = _peaks()
+    fl = 2.0 * m * n * k
+    out = {"kernel": "gemm_bf16_tcgen05", "layout": layout, "m": m, "n": n, "k": k, "ms": ms,
+           "tflops": fl / ms / 1e9, f"frac_of_{how}_cublas_peak": fl / ms / 1e9 / tf}
+    if compare:
+        out["cublas_tflops"] = fl / timeit(lib, iters) / 1e9
+    return out
+
+
+def bench_adamw(n: int, iters: int) -> dict:
+    dev = "cuda"
+    master, m, v = (torch.zeros(n, device=dev) for _ in range(3))
+    g = torch.randn(n, device=dev, dtype=torch.bfloat16)
+    lp = torch.empty(n, device=dev, dtype=torch.bfloat16)
+    ms = timeit(lambda: K.adamw_(master, m, v, g, lp, 1e-3, 0.9, 0.95, 1e-8, 0.1, 1), iters)
+    hbm, _, how = _peaks()
+    gbs = n * 28 / ms / 1e6
+    return {"kernel": "adamw", "n": n, "ms": ms, "gbs": gbs, f"frac_of_{how}_copy_bw": gbs / hbm}
+
+
+def bench_rmsnorm(t: int, d: int, iters: int) -> dict:
+    dev = "cuda"
+    x = torch.randn(t, d, device=dev).bfloat16()
+    r = torch.randn(t, d, device=dev).bfloat16()
+    w = torch.ones(d, device=dev).bfloat16()
+    h = torch.empty_like(x)
+    o = torch.empty_like(x)
+    rs = torch.empty(t, device=dev)
+    ms = timeit(lambda: K.rmsnorm_fwd(x, w, 1e-5, res=r, h_out=h, out=o, rstd=rs), iters)
+    hbm, _, how = _peaks()
+    gbs = t * d * 2 * 4 / ms / 1e6
+    return {"kernel": "rmsnorm_fwd(add+norm)", "t": t, "d": d, "ms": ms, "gbs": gbs, f"frac_of_{how}_copy_bw": gbs / hbm}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["gemm", "adamw", "rmsnorm", "all"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--no-compare", action="store_true")
+    a = ap.parse_args()
+    if a.what in ("gemm", "all"):
+        layouts = ["fwd", "dgrad", "wgrad"] if a.what == "all" else [a.layout]
+        for lay in layouts:
+            print(json.dumps(bench_gemm(a.m, a.n, a.k, lay, a.iters, not a.no_compare)), flush=True)
+    if a.what in ("adamw", "all"):
+        print(json.dumps(bench_adamw(1 << 28 if a.what == "all" else a.n, a.iters)), flush=True)
+    if a.what in ("rmsnorm", "all"):
+        print(json.dumps(bench_rmsnorm(8192, 4096, a.iters)), flush=True)
+
+
+if __name__ == "__main__":
+    main()
