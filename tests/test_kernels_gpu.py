@@ -15,13 +15,14 @@ def rel_err(a, b):
     return ((a - b).norm() / (b.norm() + 1e-12)).item()
 
 
+@pytest.mark.parametrize("impl", ["1cta", "2cta"])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (256, 512, 256), (384, 768, 1024), (200, 328, 136), (1024, 1024, 4096)])
-def test_gemm_layouts(a_mn, b_mn, M, N, K_):
+def test_gemm_layouts(a_mn, b_mn, M, N, K_, impl):
     torch.manual_seed(1)
     a = torch.randn((K_, M) if a_mn else (M, K_), device=DEV).bfloat16()
     b = torch.randn((K_, N) if b_mn else (N, K_), device=DEV).bfloat16()
-    out = K.gemm(a, b, a_mn, b_mn)
+    out = K.gemm(a, b, a_mn, b_mn, impl=impl)
     af = a.float().t() if a_mn else a.float()
     bf = b.float() if b_mn else b.float().t()
     ref = af @ bf
@@ -29,18 +30,19 @@ def test_gemm_layouts(a_mn, b_mn, M, N, K_):
     assert rel_err(out, ref) < 1e-2
     # fp32 output + accumulate
     acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
-    K.gemm(a, b, a_mn, b_mn, out=acc, accumulate=True)
+    K.gemm(a, b, a_mn, b_mn, out=acc, accumulate=True, impl=impl)
     assert rel_err(acc, ref + 1.0) < 1e-2
 
 
-def test_gemm_many_tiles_persistent():
+@pytest.mark.parametrize("impl", ["1cta", "2cta"])
+def test_gemm_many_tiles_persistent(impl):
     torch.manual_seed(2)
     M, N, K_ = 2048, 4096, 512
     a = torch.randn(M, K_, device=DEV).bfloat16()
     b = torch.randn(N, K_, device=DEV).bfloat16()
     ref = a.float() @ b.float().t()
     for ctas in (0, 7, 1):
-        out = K.gemm(a, b, max_ctas=ctas)
+        out = K.gemm(a, b, max_ctas=ctas, impl=impl)
         assert rel_err(out, ref) < 1e-2
     K.check_status(a.device)
 

@@ -1,0 +1,424 @@
+// bf16 GEMM with 2-SM tensor-core instructions (tcgen05.mma.cta_group::2).
+//
+// Same contract as the 1-CTA kernel in gemm_tcgen05.cu.  Two CTAs of a cluster share
+// one 256x256 output tile: each stages its own 128 rows of A and its own 128 of the 256
+// B columns (32 KiB per 64-deep K slab instead of 48 KiB), the pair's leader issues one
+// M=256 MMA that reads both halves of B, and each CTA's TMEM receives the accumulator of
+// its own 128 rows.  Per SM that is a third less shared-memory fill traffic per FLOP and
+// room for a 6-stage ring, which is what the 1-CTA kernel lacks: its tensor pipe idles
+// ~40% of the time waiting for operand tiles in flight.
+//
+// Synchronisation inside the pair:
+//   full[s]   (leader)  both CTAs' TMA loads complete_tx on the leader's barrier
+//   empty[s]  (each)    the leader's tcgen05.commit arrives on both CTAs' barriers
+//   tfull[a]  (each)    likewise, after the last MMA of a tile
+//   tempty[a] (leader)  the 2 x 128 epilogue threads of the pair arrive (remote arrive
+//                       from the peer)
+// All waits are bounded as in the 1-CTA kernel.
+#include <algorithm>
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include "ftb200_common.cuh"
+#include "tcgen05_helpers.cuh"
+
+namespace {
+
+constexpr int BM = 128;  // rows per CTA (256 per pair)
+constexpr int BN = 256;  // columns per pair
+constexpr int BNH = BN / 2;
+constexpr int BK = 64;
+constexpr int STAGES = 6;
+constexpr int UMMA_K = 16;
+constexpr uint32_t A_BYTES = BM * BK * 2;
+constexpr uint32_t B_BYTES = BNH * BK * 2;
+constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr int GROUP_M = 8;  // in 256-row pair tiles
+
+using namespace ftb200::tc;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA tile load issued by one CTA of a pair; the completion bytes are signalled on a
+// barrier that may live in the partner CTA (address in the cluster window).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], "
+      "[%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// Arrive (once all MMAs issued so far have completed) on the barrier at the same
+// shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(mask)
+               : "memory");
+}
+
+struct GemmParams {
+  int M, N, K;
+  int a_mn, b_mn;
+  int out_fp32;
+  int accumulate;
+  long long ldc;
+  void* C;
+  int* status;
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                              const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(tfull_bar(s), 1);
+      mbar_init(tempty_bar(s), 256);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything signals them
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_m = (p.M + 2 * BM - 1) / (2 * BM);
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_k = (p.K + BK - 1) / BK;
+  const int tiles_per_group = GROUP_M * num_n;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  auto tile_coords = [&](int t, int& m0, int& n0) {
+    const int g = t / tiles_per_group;
+    const int first_m = g * GROUP_M;
+    const int gsz = min(num_m - first_m, GROUP_M);
+    const int r = t - g * tiles_per_group;
+    m0 = (first_m + r % gsz) * (2 * BM) + static_cast<int>(rank) * BM;  // this CTA's rows
+    n0 = (r / gsz) * BN;
+  };
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        int m0, n0;
+        tile_coords(t, m0, n0);
+        const int nb = n0 + static_cast<int>(rank) * BNH;  // this CTA's half of the B tile
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+          const int k0 = kb * BK;
+          if (leader) mbar_expect_tx(full_bar(stage), 2 * STAGE_BYTES);
+          const uint32_t fb = map_to_cta(full_bar(stage), 0);
+          if (p.a_mn == 0) {
+            tma_load_2d_pair(sa, &tmA, fb, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmA, fb, m0 + 64 * j, k0);
+          }
+          if (p.b_mn == 0) {
+            tma_load_2d_pair(sb, &tmB, fb, k0, nb);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BNH / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), &tmB, fb, nb + 64 * j, k0);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        const uint64_t t0 = ftb200::globaltimer_ns();
+        while (ftb200::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader && lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(p.a_mn) << 15) |
+                             (static_cast<uint32_t>(p.b_mn) << 16) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                             (static_cast<uint32_t>((2 * BM) >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn ? BK * 128 : 16, a_step = p.a_mn ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn ? BK * 128 : 16, b_step = p.b_mn ? 2048 : 32;
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t sa = smem_base + stage * STAGE_BYTES;
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t adesc = make_smem_desc(sa + kk * a_step, a_lbo, 1024);
+            const uint64_t bdesc = make_smem_desc(sb + kk * b_step, b_lbo, 1024);
+            umma_bf16_pair(d_tmem, adesc, bdesc, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(empty_bar(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit_pair(tfull_bar(acc));
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
+    const int q = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const bool vec_ok = p.out_fp32 ? ((p.ldc & 3) == 0) : ((p.ldc & 7) == 0);
+    for (int t = cluster_id; t < num_tiles; t += num_clusters) {
+      int m0, n0;
+      tile_coords(t, m0, n0);
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = m0 + q * 32 + lane;
+      const uint32_t taddr0 = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(taddr0 + c * 32, r);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          const bool full = vec_ok && (col0 + 32 <= p.N);
+          if (p.out_fp32) {
+            float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                if (p.accumulate) {
+                  const float4 o = reinterpret_cast<const float4*>(dst)[j];
+                  v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
+                reinterpret_cast<float4*>(dst)[j] = v;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  const float v = __uint_as_float(r[j]);
+                  dst[j] = p.accumulate ? dst[j] + v : v;
+                }
+              }
+            }
+          } else {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
+            if (full) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+                if (p.accumulate) {
+                  float o[8];
+                  ftb200::unpack8(reinterpret_cast<const ftb200::bf16x8*>(dst)[j], o);
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) f[e] += o[e];
+                }
+                reinterpret_cast<ftb200::bf16x8*>(dst)[j] = ftb200::pack8(f);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  float v = __uint_as_float(r[j]);
+                  if (p.accumulate) v += __bfloat162float(dst[j]);
+                  dst[j] = __float2bfloat16(v);
+                }
+              }
+            }
+          }
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (threadIdx.x == 0 && *abort_flag && p.status != nullptr) atomicExch(p.status, FTB200_ST_TIMEOUT);
+  cluster_sync_all();  // neither CTA retires while its partner may still touch its barriers or operands
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(sym);
+    }
+  }
+  return fn;
+}
+
+int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols, long long ld, int box_cols,
+              int box_rows) {
+  auto fn = get_encode_fn();
+  if (fn == nullptr) return FTB200_E_DRIVER;
+  cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t gstride[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : FTB200_E_DRIVER;
+}
+
+}  // namespace
+
+// Same arguments as ftb200_gemm_bf16; pairs of CTAs cooperate on 256x256 tiles.
+FTB200_API int ftb200_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major,
+                                     int b_mn_major, long long lda, long long ldb, long long ldc, int flags, int* status,
+                                     int max_ctas, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || A == nullptr || B == nullptr || C == nullptr) return FTB200_E_BADARG;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
+    return FTB200_E_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(C) & 15)) return FTB200_E_ALIGN;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!a_mn_major)
+    rc = encode_2d(&tmA, A, M, K, lda, BK, BM);
+  else
+    rc = encode_2d(&tmA, A, K, M, lda, 64, BK);
+  if (rc) return rc;
+  if (!b_mn_major)
+    rc = encode_2d(&tmB, B, N, K, ldb, BK, BNH);
+  else
+    rc = encode_2d(&tmB, B, K, N, ldb, 64, BK);
+  if (rc) return rc;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(gemm_bf16_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess)
+      return FTB200_E_CUDA;
+    attr_set = true;
+  }
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn = a_mn_major ? 1 : 0;
+  p.b_mn = b_mn_major ? 1 : 0;
+  p.out_fp32 = flags & 1;
+  p.accumulate = (flags >> 1) & 1;
+  p.ldc = ldc;
+  p.C = C;
+  p.status = status;
+  const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  int ctas = ftb200::sm_count() & ~1;
+  if (max_ctas > 0 && max_ctas < ctas) ctas = std::max(2, max_ctas & ~1);
+  if (2 * tiles < ctas) ctas = 2 * tiles;
+  gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -53,6 +54,11 @@ def _check_2d_bf16(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be a 2-D bf16 tensor with unit inner stride")
 
 
+# Which GEMM kernel `gemm` launches: "2cta" (pairs of CTAs, tcgen05.mma.cta_group::2) or
+# "1cta".  Overridable per call and through the FTB200_GEMM environment variable.
+GEMM_IMPL = os.environ.get("FTB200_GEMM", "2cta")
+
+
 def gemm(
     a: torch.Tensor,
     b: torch.Tensor,
@@ -62,6 +68,7 @@ def gemm(
     accumulate: bool = False,
     out_dtype: torch.dtype = torch.bfloat16,
     max_ctas: int = 0,
+    impl: Optional[str] = None,
 ) -> torch.Tensor:
     """``out (+)= A @ B^T`` with logical ``A [M,K]`` and ``B [N,K]``.
 
@@ -96,7 +103,8 @@ def gemm(
         out.copy_(r.to(out.dtype))
         return out
     flags = (1 if out.dtype == torch.float32 else 0) | (2 if accumulate else 0)
-    rc = N.lib().ftb200_gemm_bf16(
+    fn = N.lib().ftb200_gemm_bf16_2cta if (impl or GEMM_IMPL) == "2cta" else N.lib().ftb200_gemm_bf16
+    rc = fn(
         ptr(a), ptr(b), ptr(out), c_int(M), c_int(Nn), c_int(K), c_int(int(a_mn_major)), c_int(int(b_mn_major)),
         c_ll(a.stride(0)), c_ll(b.stride(0)), c_ll(out.stride(0)), c_int(flags), ptr(status_word(a.device)),
         c_int(max_ctas), stream_ptr(),
