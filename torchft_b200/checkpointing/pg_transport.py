@@ -1,0 +1,172 @@
+"""Checkpoint transport over the fault-tolerant process group (send/recv).
+
+The sender streams, to every destination rank: an ``int64`` byte count, a pickled header
+describing the pytree (leaf kinds, tensor dtypes/shapes, non-tensor leaves) and then each
+tensor's bytes as a flat ``uint8`` message.  The receiver can be given a callback that
+returns its *existing* state dict; tensors are then received straight into that memory
+(no allocation, no host hop) -- the mode used for large sharded states.  Protocol role
+of torchft/checkpointing/pg_transport.py:163-300 (tags 1, 2, 3+i), with contiguous
+tensor payloads instead of whole storages.
+"""
+
+from __future__ import annotations
+
+import logging
+import pickle
+import time
+from contextlib import contextmanager
+from dataclasses import dataclass, field
+from datetime import timedelta
+from typing import Callable, Generator, Generic, List, Optional, Tuple, TypeVar, Union
+
+import torch
+from torch.utils._pytree import TreeSpec, tree_flatten, tree_unflatten
+
+from .transport import CheckpointTransport
+
+try:
+    from torch.distributed.tensor import DTensor
+except Exception:  # pragma: no cover
+    DTensor = None  # type: ignore
+
+logger = logging.getLogger(__name__)
+T = TypeVar("T")
+
+
+@dataclass
+class _TensorLeaf:
+    shape: Tuple[int, ...]
+    dtype: torch.dtype
+    nbytes: int
+    dtensor_spec: Optional[object] = None  # (device_mesh, placements, global shape/stride) for DTensor leaves
+
+
+@dataclass
+class _Header:
+    step: int
+    treespec: TreeSpec
+    leaves: List[Union[_TensorLeaf, object]] = field(default_factory=list)  # _TensorLeaf or the literal leaf
+    is_tensor: List[bool] = field(default_factory=list)
+
+
+@contextmanager
+def _timed(what: str) -> Generator[None, None, None]:
+    t0 = time.perf_counter()
+    yield
+    logger.info("%s took %.3fs", what, time.perf_counter() - t0)
+
+
+def _local(v: torch.Tensor) -> Tuple[torch.Tensor, Optional[object]]:
+    if DTensor is not None and isinstance(v, DTensor):
+        return v._local_tensor, (v.device_mesh, v.placements, tuple(v.shape), tuple(v.stride()))
+    return v, None
+
+
+class PGTransport(CheckpointTransport[T], Generic[T]):
+    """
+    Args:
+        pg: process group with point-to-point ``send``/``recv`` (the manager's replica-dim group)
+        timeout: per-message timeout
+        device: device receive buffers are allocated on when not receiving in place
+        state_dict: optional callable returning the receiver's current state dict; when
+            given, tensors are received in place into it
+    """
+
+    def __init__(self, pg, timeout: timedelta, device: torch.device,
+                 state_dict: Optional[Callable[[], T]] = None) -> None:
+        self._pg = pg
+        self._timeout = timeout
+        self._device = torch.device(device)
+        self._state_dict_fn = state_dict
+
+    def metadata(self) -> str:
+        return "<n/a>"
+
+    def disallow_checkpoint(self) -> None:
+        pass
+
+    # ------------------------------------------------------------------ send
+    def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
+        with _timed("preparing state_dict"):
+            leaves, spec = tree_flatten(state_dict)
+            hdr = _Header(step=step, treespec=spec)
+            payloads: List[torch.Tensor] = []
+            for v in leaves:
+                if isinstance(v, torch.Tensor):
+                    local, dspec = _local(v)
+                    flat = local.detach().contiguous().view(-1).view(torch.uint8)
+                    hdr.leaves.append(_TensorLeaf(tuple(local.shape), local.dtype, flat.numel(), dspec))
+                    hdr.is_tensor.append(True)
+                    payloads.append(flat)
+                else:
+                    hdr.leaves.append(v)
+                    hdr.is_tensor.append(False)
+        with _timed("send pickle"):
+            blob = torch.frombuffer(bytearray(pickle.dumps(hdr)), dtype=torch.uint8).to(self._device)
+            length = torch.tensor([blob.numel()], dtype=torch.int64, device=self._device)
+        works = []
+        with _timed(f"send checkpoint to {dst_ranks}"):
+            for dst in dst_ranks:
+                works.append(self._pg.send([length], dst, tag=1))
+                works.append(self._pg.send([blob], dst, tag=2))
+            for i, flat in enumerate(payloads):
+                dev_flat = flat if flat.device == self._device else flat.to(self._device)
+                for dst in dst_ranks:
+                    works.append(self._pg.send([dev_flat], dst, tag=3 + i))
+                # bound the number of in-flight messages (and staging copies)
+                if len(works) >= 64:
+                    for w in works:
+                        w.wait(timeout)
+                    works = []
+            for w in works:
+                w.wait(timeout)
+
+    # ------------------------------------------------------------------ recv
+    def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
+        inplace_leaves: Optional[List[object]] = None
+        if self._state_dict_fn is not None:
+            inplace_leaves, _ = tree_flatten(self._state_dict_fn())
+
+        length = torch.zeros(1, dtype=torch.int64, device=self._device)
+        self._pg.recv([length], src_rank, tag=1).wait(timeout)
+        blob = torch.empty(int(length.item()), dtype=torch.uint8, device=self._device)
+        self._pg.recv([blob], src_rank, tag=2).wait(timeout)
+        hdr: _Header = pickle.loads(blob.cpu().numpy().tobytes())
+        if hdr.step != step:
+            raise RuntimeError(f"checkpoint step mismatch: wanted {step}, peer sent {hdr.step}")
+
+        out: List[object] = []
+        ti = 0
+        for idx, (leaf, is_t) in enumerate(zip(hdr.leaves, hdr.is_tensor)):
+            if not is_t:
+                out.append(leaf)
+                continue
+            assert isinstance(leaf, _TensorLeaf)
+            target: Optional[torch.Tensor] = None
+            wrapped: Optional[object] = None
+            if inplace_leaves is not None:
+                cand = inplace_leaves[idx]
+                if isinstance(cand, torch.Tensor):
+                    local, _ = _local(cand)
+                    if tuple(local.shape) == leaf.shape and local.dtype == leaf.dtype and local.is_contiguous():
+                        target, wrapped = local, cand
+            if target is not None and target.device == self._device:
+                buf = target.view(-1).view(torch.uint8)
+                self._pg.recv([buf], src_rank, tag=3 + ti).wait(timeout)
+                out.append(wrapped)
+            else:
+                buf = torch.empty(leaf.nbytes, dtype=torch.uint8, device=self._device)
+                self._pg.recv([buf], src_rank, tag=3 + ti).wait(timeout)
+                t = buf.view(leaf.dtype).view(leaf.shape)
+                if target is not None:
+                    target.copy_(t)
+                    out.append(wrapped)
+                else:
+                    # receive on the device, keep on the host: bounds device memory while healing
+                    t = t.cpu() if self._device.type != "cpu" else t
+                    if leaf.dtensor_spec is not None and DTensor is not None:
+                        mesh, placements, gshape, gstride = leaf.dtensor_spec
+                        t = DTensor.from_local(t, mesh, placements, run_check=False, shape=torch.Size(gshape), stride=gstride)
+                    out.append(t)
+            ti += 1
+        return tree_unflatten(out, hdr.treespec)
