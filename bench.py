@@ -161,16 +161,21 @@ def main() -> int:
             if args.shard_comm == "peer":
                 from torchft_b200.parallel.team import PeerShardComm
 
-                shard_comm = PeerShardComm(groups[group_id], dev)
+                pbytes = sum(cfg.unit_numel(u) for u in range(cfg.n_units)) * 2
+                shard_comm = PeerShardComm(groups[group_id], dev, arena_bytes=pbytes // shard + (5 << 30))
             else:
                 shard_comm = TorchShardComm(groups[group_id])
 
     if not args.no_ft:
         from torchft_b200.bench_support import make_ft_manager
 
-        lighthouse, manager = make_ft_manager(rank, world, n_groups, shard, group_id, group_rank, dev)
+        grad_bytes = sum(cfg.unit_numel(u) for u in range(cfg.n_units)) * 2 // shard
+        arena = 0 if n_groups == 1 else grad_bytes + (64 << 20) + 300 * cfg.n_units
+        lighthouse, manager = make_ft_manager(rank, world, n_groups, shard, group_id, group_rank, dev, arena_bytes=arena)
 
-    trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234)
+    replica_alloc = manager._pg.alloc if (manager is not None and n_groups > 1) else None
+    trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234,
+                                  replica_alloc=replica_alloc)
     if manager is not None:
         manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 

@@ -1,0 +1,64 @@
+"""Wiring used by ``bench.py`` and the HSDP example: one lighthouse per job (hosted by
+global rank 0), one TCPStore per replica group (hosted by the group's rank 0), one
+:class:`~torchft_b200.manager.Manager` per rank with the NVLink peer-memory replica group."""
+
+from __future__ import annotations
+
+import os
+from datetime import timedelta
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.distributed import TCPStore
+
+from ._ftcp import LighthouseServer
+from .manager import Manager
+
+
+def make_ft_manager(rank: int, world: int, n_groups: int, shard: int, group_id: int, group_rank: int,
+                    device: torch.device, arena_bytes: int = 1 << 30, min_replica_size: Optional[int] = None,
+                    timeout: timedelta = timedelta(seconds=120), use_async_quorum: bool = True,
+                    checkpoint_transport=None) -> Tuple[Optional[LighthouseServer], Manager]:
+    """Returns ``(lighthouse or None, manager)``.  All ranks of the job must call this."""
+    from .parallel.team import ProcessGroupB200
+
+    lighthouse = None
+    addr = [None]
+    if rank == 0:
+        lighthouse = LighthouseServer("[::]:0", min_replicas=n_groups, join_timeout_ms=200, quorum_tick_ms=10)
+        port = lighthouse.address().rsplit(":", 1)[1]
+        addr[0] = f"http://127.0.0.1:{port}"
+    if world > 1:
+        dist.broadcast_object_list(addr, src=0)
+    lighthouse_addr = addr[0]
+
+    base_port = int(os.environ.get("MASTER_PORT", "29500")) + 101 + group_id
+    store = None
+    if group_rank == 0:
+        store = TCPStore(host_name="127.0.0.1", port=base_port, is_master=True, wait_for_workers=False)
+    if world > 1:
+        dist.barrier()
+
+    pg = ProcessGroupB200(timeout=timeout, arena_bytes=arena_bytes, device=device)
+    manager = Manager(
+        pg=pg,
+        load_state_dict=None,
+        state_dict=None,
+        min_replica_size=min_replica_size if min_replica_size is not None else n_groups,
+        use_async_quorum=use_async_quorum,
+        timeout=timeout,
+        quorum_timeout=timeout,
+        connect_timeout=timedelta(seconds=60),
+        rank=group_rank,
+        world_size=shard,
+        store_addr="127.0.0.1",
+        store_port=base_port,
+        lighthouse_addr=lighthouse_addr,
+        replica_id=f"group{group_id}",
+        hostname="127.0.0.1",
+        init_sync=False,  # every replica initialises from the same seed
+        checkpoint_transport=checkpoint_transport,
+    )
+    manager._bench_store = store  # keep the group's store server alive
+    return lighthouse, manager

@@ -1,0 +1,558 @@
+// Peer-memory team: collectives written as kernels that load and store other GPUs'
+// memory directly over NVLink / NVSwitch (plain ld/st on IPC-mapped pointers).
+//
+// Memory model.  Every rank owns one exported *arena* (cudaMalloc + cudaIpcGetMemHandle)
+// that peers map (cudaIpcOpenMemHandle).  All ranks sub-allocate in the same order, so a
+// buffer sits at the same offset in every arena ("symmetric").  The first bytes of an
+// arena are the rank's flag words: flag[slot][src] is written by rank `src` only.
+//
+// Synchronisation.  A collective is one launch per rank (each on its own GPU).  Inside,
+// block 0 signals "ready" to every peer and waits for every peer's "ready"; the other
+// blocks wait on a local go-word; data moves; then a "done" round keeps every rank's
+// buffers valid until all readers/writers have finished.  Flag values are
+// (epoch << 32 | sequence): stale values of an earlier quorum epoch or call never match.
+//
+// Never-hang contract.  Every wait polls (i) a host-mapped abort word, (ii) the flag,
+// (iii) %globaltimer against a deadline.  On abort or expiry the kernel stores a
+// FTB200_ST_* code in the team's status word, releases its local waiters and returns;
+// the host reads the status after synchronising the stream.
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "ftb200_common.cuh"
+
+namespace {
+
+constexpr int MAX_RANKS = 8;
+constexpr int NUM_SLOTS = 4;  // ready, done, + 2 spare
+constexpr int FLAG_WORDS = NUM_SLOTS * MAX_RANKS;
+constexpr uint64_t GO_ABORT = ~0ull;
+
+struct TeamParams {
+  int rank;
+  int world;
+  uint64_t token;        // (epoch << 32) | sequence number of this call
+  uint64_t timeout_ns;
+  uint64_t* flags[MAX_RANKS];  // base of every rank's flag words (peer-mapped; [rank] is local)
+  uint64_t* local_sync;        // local words: [0] go-ready, [1] go-done, [2] arrival counter a, [3] counter b
+  const volatile int* abort_word;  // host-mapped; non-zero aborts
+  int* status;                 // local status word
+};
+
+__device__ __forceinline__ void st_release_sys(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_acquire_sys(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint64_t* p, uint64_t v) {
+  asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t ld_acquire_gpu(const uint64_t* p) {
+  uint64_t v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Bounded spin until *p == want.  Returns 0 on success, a FTB200_ST_* code otherwise.
+template <bool SYS>
+__device__ __forceinline__ int wait_equal(const uint64_t* p, uint64_t want, const TeamParams& tp, uint64_t t0) {
+  uint32_t spins = 0;
+  for (;;) {
+    const uint64_t v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if (v == want) return FTB200_ST_OK;
+    if (!SYS && v == GO_ABORT) return FTB200_ST_ABORTED;
+    if ((++spins & 31u) == 0) {
+      if (tp.abort_word != nullptr && *tp.abort_word != 0) return FTB200_ST_ABORTED;
+      if (ftb200::globaltimer_ns() - t0 > tp.timeout_ns) return FTB200_ST_TIMEOUT;
+      __nanosleep(64);
+    }
+  }
+}
+
+// Cross-rank round on `slot`, executed by block 0 (threads 0..world-1, one peer each),
+// then published to the other blocks through local_sync[go_idx].  Every block calls it.
+// Returns false if the collective must be abandoned.
+__device__ bool team_round(const TeamParams& tp, int slot, int go_idx, int* sh_code) {
+  const uint64_t t0 = ftb200::globaltimer_ns();
+  if (blockIdx.x == 0) {
+    if (threadIdx.x == 0) *sh_code = FTB200_ST_OK;
+    __syncthreads();
+    if (threadIdx.x < tp.world && static_cast<int>(threadIdx.x) != tp.rank) {
+      const int peer = threadIdx.x;
+      st_release_sys(tp.flags[peer] + slot * MAX_RANKS + tp.rank, tp.token);
+      const int code = wait_equal<true>(tp.flags[tp.rank] + slot * MAX_RANKS + peer, tp.token, tp, t0);
+      if (code != FTB200_ST_OK) atomicMax(sh_code, code);
+    }
+    __syncthreads();
+    const int code = *sh_code;
+    if (threadIdx.x == 0) {
+      if (code != FTB200_ST_OK && tp.status != nullptr) atomicMax(tp.status, code);
+      st_release_gpu(tp.local_sync + go_idx, code == FTB200_ST_OK ? tp.token : GO_ABORT);
+    }
+    __syncthreads();
+    return code == FTB200_ST_OK;
+  }
+  if (threadIdx.x == 0) {
+    const int code = wait_equal<false>(tp.local_sync + go_idx, tp.token, tp, t0);
+    *sh_code = code;
+    if (code == FTB200_ST_TIMEOUT && tp.status != nullptr) atomicMax(tp.status, code);
+  }
+  __syncthreads();
+  return *sh_code == FTB200_ST_OK;
+}
+
+// All blocks of this launch have passed this point (arrival counter in local memory).
+// Block 0 waits for the others (bounded); the others just arrive.
+__device__ bool grid_arrive(const TeamParams& tp, int counter_idx, int* sh_code) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();  // this block's peer stores are visible before anyone is told "done"
+    int code = FTB200_ST_OK;
+    uint64_t* ctr = tp.local_sync + counter_idx;
+    atomicAdd(reinterpret_cast<unsigned long long*>(ctr), 1ull);
+    if (blockIdx.x == 0) {
+      const uint64_t t0 = ftb200::globaltimer_ns();
+      uint32_t spins = 0;
+      while (ld_acquire_gpu(ctr) < gridDim.x) {
+        if ((++spins & 31u) == 0) {
+          if (tp.abort_word != nullptr && *tp.abort_word != 0) { code = FTB200_ST_ABORTED; break; }
+          if (ftb200::globaltimer_ns() - t0 > tp.timeout_ns) { code = FTB200_ST_TIMEOUT; break; }
+          __nanosleep(64);
+        }
+      }
+      st_release_gpu(ctr, 0);  // re-arm for the next call (calls on one team are stream-ordered)
+      if (code != FTB200_ST_OK && tp.status != nullptr) atomicMax(tp.status, code);
+    }
+    *sh_code = code;
+  }
+  __syncthreads();
+  return *sh_code == FTB200_ST_OK;
+}
+
+template <typename T>
+struct Vec;  // 16-byte vectors
+template <>
+struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float* f) { ftb200::unpack8(*reinterpret_cast<const ftb200::bf16x8*>(p), f); }
+  __device__ static void store(__nv_bfloat16* p, const float* f) { *reinterpret_cast<ftb200::bf16x8*>(p) = ftb200::pack8(f); }
+};
+template <>
+struct Vec<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+  }
+  __device__ static void store(float* p, const float* f) { *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]); }
+};
+
+struct AllreduceArgs {
+  void* bufs[MAX_RANKS];  // symmetric staging / registered buffers (peer-mapped), element offset already applied
+  const void* user_in;    // optional: copied into bufs[rank] first
+  void* user_out;         // optional: receives the result (same dtype)
+  long long n;            // elements, multiple of the vector width * world
+  float scale;
+  int zero_contribution;  // contribute zeros instead of the local data
+};
+
+// Two-shot allreduce in place on the symmetric buffers: rank r reduces slice r over all
+// ranks (fp32 accumulation, fixed order starting at its own copy), scales, and writes the
+// slice into every rank's buffer.
+template <typename T>
+__device__ __forceinline__ void allreduce_body(const TeamParams& tp, const AllreduceArgs& a) {
+  __shared__ int sh_code;
+  constexpr int V = Vec<T>::N;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  T* mine = reinterpret_cast<T*>(a.bufs[tp.rank]);
+
+  if (a.user_in != nullptr || a.zero_contribution) {
+    const T* src = reinterpret_cast<const T*>(a.user_in);
+    for (long long i = tid * V; i < a.n; i += nthreads * V) {
+      float f[V];
+      if (a.zero_contribution) {
+#pragma unroll
+        for (int e = 0; e < V; ++e) f[e] = 0.f;
+      } else {
+        Vec<T>::load(src + i, f);
+      }
+      Vec<T>::store(mine + i, f);
+    }
+    if (!grid_arrive(tp, 2, &sh_code)) return;
+  }
+  if (!team_round(tp, /*slot=*/0, /*go=*/0, &sh_code)) return;
+
+  const long long slice = a.n / tp.world;
+  const long long lo = slice * tp.rank;
+  for (long long i = tid * V; i < slice; i += nthreads * V) {
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+    for (int k = 0; k < tp.world; ++k) {
+      const int p = (tp.rank + k) % tp.world;
+      float f[V];
+      Vec<T>::load(reinterpret_cast<const T*>(a.bufs[p]) + lo + i, f);
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[e] += f[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] *= a.scale;
+    for (int k = 0; k < tp.world; ++k) {
+      const int p = (tp.rank + k) % tp.world;
+      Vec<T>::store(reinterpret_cast<T*>(a.bufs[p]) + lo + i, acc);
+    }
+  }
+  if (!grid_arrive(tp, 3, &sh_code)) return;
+  if (!team_round(tp, /*slot=*/1, /*go=*/1, &sh_code)) return;
+
+  if (a.user_out != nullptr) {
+    T* dst = reinterpret_cast<T*>(a.user_out);
+    for (long long i = tid * V; i < a.n; i += nthreads * V) {
+      float f[V];
+      Vec<T>::load(mine + i, f);
+      Vec<T>::store(dst + i, f);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_kernel(const TeamParams tp, const AllreduceArgs a) {
+  allreduce_body<T>(tp, a);
+}
+// Test vehicle: all ranks of a team emulated by ONE cooperative launch on one GPU
+// (blockIdx.y selects the rank); separate launches that wait on each other must never
+// share a GPU.
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_emul_kernel(const TeamParams* tps, const AllreduceArgs* as) {
+  allreduce_body<T>(tps[blockIdx.y], as[blockIdx.y]);
+}
+
+struct GatherArgs {
+  const void* src[MAX_RANKS];  // every rank's shard (peer-mapped)
+  void* dst;                   // local full buffer: world * shard_bytes
+  long long shard_bytes;       // multiple of 16
+};
+
+// All-gather by pulling: every rank copies all shards (its own included) into its full buffer.
+__device__ __forceinline__ void allgather_body(const TeamParams& tp, const GatherArgs& a) {
+  __shared__ int sh_code;
+  if (!team_round(tp, 0, 0, &sh_code)) return;
+  const long long v_per = a.shard_bytes / 16;
+  const long long total = v_per * tp.world;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  uint4* dst = reinterpret_cast<uint4*>(a.dst);
+  for (long long i = tid; i < total; i += nthreads) {
+    // start with the next rank's shard so that the ranks do not all hit the same peer at once
+    const long long blk = i / v_per;
+    const int p = static_cast<int>((blk + tp.rank + 1) % tp.world);
+    const long long off = i - blk * v_per;
+    dst[p * v_per + off] = reinterpret_cast<const uint4*>(a.src[p])[off];
+  }
+  if (!grid_arrive(tp, 3, &sh_code)) return;
+  team_round(tp, 1, 1, &sh_code);
+}
+
+__global__ void __launch_bounds__(512) allgather_kernel(const TeamParams tp, const GatherArgs a) { allgather_body(tp, a); }
+__global__ void __launch_bounds__(512) allgather_emul_kernel(const TeamParams* tps, const GatherArgs* as) {
+  allgather_body(tps[blockIdx.y], as[blockIdx.y]);
+}
+
+struct ReduceScatterArgs {
+  const void* src[MAX_RANKS];  // every rank's full buffer (peer-mapped), world * shard_elems
+  void* dst;                   // local shard
+  long long shard_elems;       // multiple of the vector width
+  float scale;
+};
+
+// Reduce-scatter by pulling: rank r sums slice r of every rank's full buffer (fp32).
+template <typename T>
+__device__ __forceinline__ void reduce_scatter_body(const TeamParams& tp, const ReduceScatterArgs& a) {
+  __shared__ int sh_code;
+  constexpr int V = Vec<T>::N;
+  if (!team_round(tp, 0, 0, &sh_code)) return;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long lo = a.shard_elems * tp.rank;
+  T* dst = reinterpret_cast<T*>(a.dst);
+  for (long long i = tid * V; i < a.shard_elems; i += nthreads * V) {
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+    for (int k = 0; k < tp.world; ++k) {
+      const int p = (tp.rank + k) % tp.world;
+      float f[V];
+      Vec<T>::load(reinterpret_cast<const T*>(a.src[p]) + lo + i, f);
+#pragma unroll
+      for (int e = 0; e < V; ++e) acc[e] += f[e];
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] *= a.scale;
+    Vec<T>::store(dst + i, acc);
+  }
+  if (!grid_arrive(tp, 3, &sh_code)) return;
+  team_round(tp, 1, 1, &sh_code);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) reduce_scatter_kernel(const TeamParams tp, const ReduceScatterArgs a) {
+  reduce_scatter_body<T>(tp, a);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) reduce_scatter_emul_kernel(const TeamParams* tps, const ReduceScatterArgs* as) {
+  reduce_scatter_body<T>(tps[blockIdx.y], as[blockIdx.y]);
+}
+
+// Barrier only (also what a send/recv handshake uses).
+__global__ void barrier_kernel(const TeamParams tp) {
+  __shared__ int sh_code;
+  team_round(tp, 0, 0, &sh_code);
+}
+
+struct CopySeg {
+  const void* src;
+  void* dst;
+  long long bytes;  // multiple of 16
+};
+
+// Live-recovery copy: a table of (peer src, local dst, bytes) segments pulled with 16-byte
+// vector loads; a bounds-free grid-stride loop per segment, all segments in one launch.
+__global__ void __launch_bounds__(512) p2p_copy_kernel(const CopySeg* __restrict__ segs, int nsegs,
+                                                       const volatile int* abort_word, int* status) {
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int s = 0; s < nsegs; ++s) {
+    if (abort_word != nullptr && *abort_word != 0) {
+      if (tid == 0 && status != nullptr) atomicMax(status, FTB200_ST_ABORTED);
+      return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(segs[s].src);
+    uint4* dst = reinterpret_cast<uint4*>(segs[s].dst);
+    const long long nv = segs[s].bytes / 16;
+    for (long long i = tid; i < nv; i += nthreads) dst[i] = src[i];
+  }
+}
+
+int grid_for_bytes(long long bytes) {
+  // enough CTAs to saturate NVLink without starving concurrent compute of SMs
+  long long g = bytes / (512 * 16 * 4);
+  g = std::max<long long>(1, std::min<long long>(g, 64));
+  return static_cast<int>(g);
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------ C ABI
+
+struct ftb200_team_desc {
+  int rank;
+  int world;
+  unsigned long long token;
+  unsigned long long timeout_ns;
+  void* flags[MAX_RANKS];
+  void* local_sync;
+  const void* abort_word;  // device pointer of host-mapped word (may be null)
+  int* status;
+};
+
+static TeamParams to_params(const ftb200_team_desc* d) {
+  TeamParams tp;
+  tp.rank = d->rank;
+  tp.world = d->world;
+  tp.token = d->token;
+  tp.timeout_ns = d->timeout_ns;
+  for (int i = 0; i < MAX_RANKS; ++i) tp.flags[i] = reinterpret_cast<uint64_t*>(d->flags[i]);
+  tp.local_sync = reinterpret_cast<uint64_t*>(d->local_sync);
+  tp.abort_word = reinterpret_cast<const volatile int*>(d->abort_word);
+  tp.status = d->status;
+  return tp;
+}
+
+FTB200_API int ftb200_team_flag_bytes() { return FLAG_WORDS * 8; }
+FTB200_API int ftb200_team_sync_bytes() { return 8 * 8; }
+FTB200_API int ftb200_team_max_ranks() { return MAX_RANKS; }
+
+FTB200_API int ftb200_arena_alloc(void** ptr, unsigned long long bytes) {
+  if (cudaMalloc(ptr, bytes) != cudaSuccess) return FTB200_E_CUDA;
+  return 0;
+}
+FTB200_API int ftb200_arena_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : FTB200_E_CUDA; }
+
+FTB200_API int ftb200_ipc_export(void* ptr, unsigned char* handle64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return FTB200_E_CUDA;
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+FTB200_API int ftb200_ipc_import(const unsigned char* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  if (cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    cudaGetLastError();
+    return FTB200_E_CUDA;
+  }
+  return 0;
+}
+FTB200_API int ftb200_ipc_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : FTB200_E_CUDA; }
+
+// Host-mapped abort word: *host_ptr is written by the host, *dev_ptr read by kernels.
+FTB200_API int ftb200_abort_word_create(int** host_ptr, void** dev_ptr) {
+  if (cudaHostAlloc(reinterpret_cast<void**>(host_ptr), sizeof(int), cudaHostAllocMapped) != cudaSuccess) return FTB200_E_CUDA;
+  **host_ptr = 0;
+  if (cudaHostGetDevicePointer(dev_ptr, *host_ptr, 0) != cudaSuccess) return FTB200_E_CUDA;
+  return 0;
+}
+FTB200_API int ftb200_abort_word_destroy(int* host_ptr) { return cudaFreeHost(host_ptr) == cudaSuccess ? 0 : FTB200_E_CUDA; }
+
+// dtype: 0 = bf16, 1 = fp32.  bufs[i] already point at the buffer inside rank i's arena.
+FTB200_API int ftb200_team_allreduce(const ftb200_team_desc* d, void* const* bufs, const void* user_in, void* user_out,
+                                     long long n, int dtype, float scale, int zero_contribution, int ctas,
+                                     cudaStream_t st) {
+  if (d->world < 1 || d->world > MAX_RANKS || n <= 0) return FTB200_E_BADARG;
+  const int V = dtype == 0 ? 8 : 4;
+  if (n % (static_cast<long long>(V) * d->world)) return FTB200_E_ALIGN;
+  AllreduceArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) a.bufs[i] = i < d->world ? bufs[i] : nullptr;
+  a.user_in = user_in;
+  a.user_out = user_out;
+  a.n = n;
+  a.scale = scale;
+  a.zero_contribution = zero_contribution;
+  const TeamParams tp = to_params(d);
+  const int grid = ctas > 0 ? ctas : grid_for_bytes(n * (dtype == 0 ? 2 : 4));
+  if (dtype == 0)
+    allreduce_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(tp, a);
+  else
+    allreduce_kernel<float><<<grid, 512, 0, st>>>(tp, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+FTB200_API int ftb200_team_allgather(const ftb200_team_desc* d, const void* const* src, void* dst, long long shard_bytes,
+                                     int ctas, cudaStream_t st) {
+  if (d->world < 1 || d->world > MAX_RANKS || shard_bytes <= 0) return FTB200_E_BADARG;
+  if (shard_bytes % 16) return FTB200_E_ALIGN;
+  GatherArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) a.src[i] = i < d->world ? src[i] : nullptr;
+  a.dst = dst;
+  a.shard_bytes = shard_bytes;
+  const int grid = ctas > 0 ? ctas : grid_for_bytes(shard_bytes * d->world);
+  allgather_kernel<<<grid, 512, 0, st>>>(to_params(d), a);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+FTB200_API int ftb200_team_reduce_scatter(const ftb200_team_desc* d, const void* const* src, void* dst,
+                                          long long shard_elems, int dtype, float scale, int ctas, cudaStream_t st) {
+  if (d->world < 1 || d->world > MAX_RANKS || shard_elems <= 0) return FTB200_E_BADARG;
+  const int V = dtype == 0 ? 8 : 4;
+  if (shard_elems % V) return FTB200_E_ALIGN;
+  ReduceScatterArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) a.src[i] = i < d->world ? src[i] : nullptr;
+  a.dst = dst;
+  a.shard_elems = shard_elems;
+  a.scale = scale;
+  const int grid = ctas > 0 ? ctas : grid_for_bytes(shard_elems * (dtype == 0 ? 2 : 4) * d->world);
+  if (dtype == 0)
+    reduce_scatter_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(to_params(d), a);
+  else
+    reduce_scatter_kernel<float><<<grid, 512, 0, st>>>(to_params(d), a);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+FTB200_API int ftb200_team_barrier(const ftb200_team_desc* d, cudaStream_t st) {
+  barrier_kernel<<<1, 32, 0, st>>>(to_params(d));
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+// segs: device array of {src, dst, bytes}; the caller keeps it alive until the stream reaches the kernel.
+FTB200_API int ftb200_p2p_copy(const void* segs_dev, int nsegs, long long total_bytes, const void* abort_word, int* status,
+                               int ctas, cudaStream_t st) {
+  if (nsegs <= 0) return 0;
+  const int grid = ctas > 0 ? ctas : std::max(grid_for_bytes(total_bytes), 32);
+  p2p_copy_kernel<<<grid, 512, 0, st>>>(reinterpret_cast<const CopySeg*>(segs_dev), nsegs,
+                                        reinterpret_cast<const volatile int*>(abort_word), status);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+// ---- single-GPU emulation of a whole team (tests) -----------------------------------------
+// `descs` / `bufs` describe `world` ranks whose arenas all live on the current device.
+// `launch_ranks` <= world ranks are launched (fewer than world makes the waits expire, which
+// is how the timeout path is exercised without any peer).
+namespace {
+template <typename P, typename A>
+int launch_emulated(void (*kernel)(const P*, const A*), const std::vector<P>& tps, const std::vector<A>& as, int grid_x,
+                    cudaStream_t st) {
+  const int n = static_cast<int>(tps.size());
+  P* d_tp = nullptr;
+  A* d_a = nullptr;
+  if (cudaMalloc(&d_tp, sizeof(P) * n) != cudaSuccess || cudaMalloc(&d_a, sizeof(A) * n) != cudaSuccess) return FTB200_E_CUDA;
+  cudaMemcpyAsync(d_tp, tps.data(), sizeof(P) * n, cudaMemcpyHostToDevice, st);
+  cudaMemcpyAsync(d_a, as.data(), sizeof(A) * n, cudaMemcpyHostToDevice, st);
+  void* args[2] = {&d_tp, &d_a};
+  cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kernel), dim3(grid_x, n, 1), dim3(512, 1, 1), args, 0, st);
+  cudaStreamSynchronize(st);
+  cudaFree(d_tp);
+  cudaFree(d_a);
+  return e == cudaSuccess && cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+}  // namespace
+
+FTB200_API int ftb200_team_allreduce_emulated(const ftb200_team_desc* descs, int launch_ranks, void* const* bufs,
+                                              void* const* user_in, void* const* user_out, long long n, int dtype,
+                                              float scale, const int* zero_contribution, int ctas, cudaStream_t st) {
+  const int world = descs[0].world;
+  std::vector<TeamParams> tps;
+  std::vector<AllreduceArgs> as;
+  for (int r = 0; r < launch_ranks; ++r) {
+    tps.push_back(to_params(&descs[r]));
+    AllreduceArgs a;
+    for (int i = 0; i < MAX_RANKS; ++i) a.bufs[i] = i < world ? bufs[i] : nullptr;
+    a.user_in = user_in ? user_in[r] : nullptr;
+    a.user_out = user_out ? user_out[r] : nullptr;
+    a.n = n;
+    a.scale = scale;
+    a.zero_contribution = zero_contribution ? zero_contribution[r] : 0;
+    as.push_back(a);
+  }
+  if (dtype == 0) return launch_emulated(allreduce_emul_kernel<__nv_bfloat16>, tps, as, ctas > 0 ? ctas : 4, st);
+  return launch_emulated(allreduce_emul_kernel<float>, tps, as, ctas > 0 ? ctas : 4, st);
+}
+
+FTB200_API int ftb200_team_allgather_emulated(const ftb200_team_desc* descs, int launch_ranks, const void* const* src,
+                                              void* const* dst, long long shard_bytes, int ctas, cudaStream_t st) {
+  const int world = descs[0].world;
+  std::vector<TeamParams> tps;
+  std::vector<GatherArgs> as;
+  for (int r = 0; r < launch_ranks; ++r) {
+    tps.push_back(to_params(&descs[r]));
+    GatherArgs a;
+    for (int i = 0; i < MAX_RANKS; ++i) a.src[i] = i < world ? src[i] : nullptr;
+    a.dst = dst[r];
+    a.shard_bytes = shard_bytes;
+    as.push_back(a);
+  }
+  return launch_emulated(allgather_emul_kernel, tps, as, ctas > 0 ? ctas : 4, st);
+}
+
+FTB200_API int ftb200_team_reduce_scatter_emulated(const ftb200_team_desc* descs, int launch_ranks, const void* const* src,
+                                                   void* const* dst, long long shard_elems, int dtype, float scale,
+                                                   int ctas, cudaStream_t st) {
+  const int world = descs[0].world;
+  std::vector<TeamParams> tps;
+  std::vector<ReduceScatterArgs> as;
+  for (int r = 0; r < launch_ranks; ++r) {
+    tps.push_back(to_params(&descs[r]));
+    ReduceScatterArgs a;
+    for (int i = 0; i < MAX_RANKS; ++i) a.src[i] = i < world ? src[i] : nullptr;
+    a.dst = dst[r];
+    a.shard_elems = shard_elems;
+    a.scale = scale;
+    as.push_back(a);
+  }
+  if (dtype == 0) return launch_emulated(reduce_scatter_emul_kernel<__nv_bfloat16>, tps, as, ctas > 0 ? ctas : 4, st);
+  return launch_emulated(reduce_scatter_emul_kernel<float>, tps, as, ctas > 0 ? ctas : 4, st);
+}

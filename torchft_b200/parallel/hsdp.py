@@ -45,6 +45,7 @@ class ShardedLlamaTrainer:
         seed: int = 0,
         attention=None,
         logit_chunks: int = 4,
+        replica_alloc=None,
     ):
         self.cfg, self.device = cfg, device
         self.comm = shard_comm or LocalShardComm()
@@ -61,8 +62,14 @@ class ShardedLlamaTrainer:
 
         bf, f32 = torch.bfloat16, torch.float32
         A = self.comm.alloc
+        # shards that peers of the shard group read (all-gather sources) come from the shard
+        # communicator; gradient shards are what the replica dimension reduces, so they come
+        # from the replica group's allocator when it has one (in-place peer-memory allreduce)
         self.p_shard = [A(n, bf, device) for n in self.shard_numel]
-        self.g_shard = [A(n, bf, device) for n in self.shard_numel]
+        if replica_alloc is not None:
+            self.g_shard = [replica_alloc(n, bf) for n in self.shard_numel]
+        else:
+            self.g_shard = [torch.empty(n, dtype=bf, device=device) for n in self.shard_numel]
         self.master = [torch.empty(n, dtype=f32, device=device) for n in self.shard_numel]
         self.m = [torch.zeros(n, dtype=f32, device=device) for n in self.shard_numel]
         self.v = [torch.zeros(n, dtype=f32, device=device) for n in self.shard_numel]
@@ -70,7 +77,7 @@ class ShardedLlamaTrainer:
             self.p_full = self.p_shard
             self._g_bufs: Dict[int, List[torch.Tensor]] = {}
         else:
-            self.p_full = [A(n, bf, device) for n in self.full_numel]
+            self.p_full = [torch.empty(n, dtype=bf, device=device) for n in self.full_numel]
             sizes = sorted(set(self.full_numel))
             self._g_bufs = {s: [A(s, bf, device) for _ in range(2 if self.full_numel.count(s) > 1 else 1)] for s in sizes}
         self._g_slot = [0] * U
@@ -93,7 +100,10 @@ class ShardedLlamaTrainer:
                 self.p_shard[u].copy_(full[rank * n : (rank + 1) * n])
             self.master[u].copy_(self.p_shard[u].float())
 
-        self.comm_stream = torch.cuda.Stream(device=device, priority=-1) if self.cuda and ws > 1 else None
+        # communication (shard-group and replica-dimension) runs beside compute
+        self.comm_stream = (
+            torch.cuda.Stream(device=device, priority=-1) if self.cuda and (ws > 1 or manager is not None) else None
+        )
         self._ag_event: List[Optional[torch.cuda.Event]] = [None] * U
         self._rs_event: Dict[int, Optional[torch.cuda.Event]] = {}
         self._gathered = [ws == 1] * U
@@ -167,6 +177,10 @@ class ShardedLlamaTrainer:
             else:
                 self.comm.reduce_scatter(buf, self.g_shard[u])
                 self._replica_allreduce(u)
+        elif self.manager is not None and self.comm_stream is not None:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                self._replica_allreduce(u)
         else:
             self._replica_allreduce(u)
 
@@ -184,11 +198,11 @@ class ShardedLlamaTrainer:
         return loss
 
     def _finish_comm(self) -> None:
-        if self.comm_stream is not None:
-            torch.cuda.current_stream().wait_stream(self.comm_stream)
         for w in self._works:
             w.wait()
         self._works.clear()
+        if self.comm_stream is not None:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
         self._rs_event.clear()
 
     def optimizer_step(self) -> None:

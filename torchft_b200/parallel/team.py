@@ -1,0 +1,482 @@
+"""NVLink peer-memory communication: symmetric arenas, kernel collectives, and the two
+things built on them -- :class:`PeerShardComm` (FSDP traffic inside a replica group) and
+:class:`ProcessGroupB200` (the reconfigurable replica-dimension group).
+
+Every rank owns an *arena* of device memory that its peers map through CUDA IPC.  Arenas
+are carved up identically on all ranks, so "the same buffer on rank p" is simply
+``peer_base[p] + offset``.  Collectives are single kernels (see ``csrc/team/team.cu``)
+that read and write peers' arenas directly; they poll an abort word, carry an
+epoch-stamped token and give up after a deadline, reporting through a status word
+instead of hanging.  Reconfiguring a team (new quorum) is: bump the epoch, clear local
+flags, close old mappings, exchange handles through the store, map -- milliseconds, no
+communicator bootstrap.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import logging
+import threading
+from datetime import timedelta
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+from torch.distributed import Store
+from torch.distributed.distributed_c10d import AllreduceOptions, ReduceOp, Work
+from torch.futures import Future
+
+from .._pg_base import ProcessGroup, _reduce_op, create_store_client
+from ..ops import _native as N
+from .shard_comm import ShardComm
+
+logger = logging.getLogger(__name__)
+
+MAX_RANKS = 8
+_DT = {torch.bfloat16: 0, torch.float32: 1}
+
+
+class _TeamDesc(ctypes.Structure):
+    _fields_ = [
+        ("rank", ctypes.c_int),
+        ("world", ctypes.c_int),
+        ("token", ctypes.c_ulonglong),
+        ("timeout_ns", ctypes.c_ulonglong),
+        ("flags", ctypes.c_void_p * MAX_RANKS),
+        ("local_sync", ctypes.c_void_p),
+        ("abort_word", ctypes.c_void_p),
+        ("status", ctypes.c_void_p),
+    ]
+
+
+class _RawMemory:
+    """Exposes a raw device pointer to ``torch.as_tensor`` (zero-copy)."""
+
+    def __init__(self, ptr: int, nbytes: int, owner: object) -> None:
+        self._owner = owner
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class Arena:
+    """One exported slab of device memory with a bump allocator (256-byte granules)."""
+
+    def __init__(self, nbytes: int, device: torch.device) -> None:
+        self.device = device
+        self.nbytes = int(nbytes)
+        p = ctypes.c_void_p()
+        with torch.cuda.device(device):
+            N.check(N.lib().ftb200_arena_alloc(ctypes.byref(p), ctypes.c_ulonglong(self.nbytes)), "arena_alloc", 0)
+            self.base = int(p.value)
+            self.bytes_view = torch.as_tensor(_RawMemory(self.base, self.nbytes, self), device=device)
+        self._off = 0
+        self._lock = threading.Lock()
+
+    def alloc(self, nbytes: int) -> int:
+        with self._lock:
+            off = self._off
+            self._off = (off + nbytes + 255) // 256 * 256
+            if self._off > self.nbytes:
+                raise MemoryError(f"arena of {self.nbytes} bytes exhausted (asked for {nbytes} at {off})")
+            return off
+
+    def tensor(self, off: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        nb = numel * torch.empty((), dtype=dtype).element_size()
+        return self.bytes_view[off : off + nb].view(dtype)
+
+    def export_handle(self) -> bytes:
+        buf = (ctypes.c_ubyte * 64)()
+        with torch.cuda.device(self.device):
+            N.check(N.lib().ftb200_ipc_export(ctypes.c_void_p(self.base), buf), "ipc_export", 0)
+        return bytes(buf)
+
+    def contains(self, t: torch.Tensor) -> Optional[int]:
+        """Offset of ``t`` inside the arena, or None."""
+        p = t.data_ptr()
+        if self.base <= p and p + t.numel() * t.element_size() <= self.base + self.nbytes:
+            return p - self.base
+        return None
+
+
+class TeamError(RuntimeError):
+    pass
+
+
+class SymmetricTeam:
+    """A set of ranks with mutually mapped arenas plus the flag/abort/status plumbing."""
+
+    def __init__(self, device: torch.device, arena_bytes: int, timeout: timedelta = timedelta(seconds=30)) -> None:
+        self.device = torch.device(device)
+        self.lib = N.lib()
+        self.lib.ftb200_team_flag_bytes.restype = ctypes.c_int
+        self.timeout = timeout
+        self.arena = Arena(arena_bytes, self.device)
+        self._flag_off = self.arena.alloc(int(self.lib.ftb200_team_flag_bytes()))
+        self._sync = torch.zeros(8, dtype=torch.int64, device=self.device)
+        self._status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        hp, dp = ctypes.POINTER(ctypes.c_int)(), ctypes.c_void_p()
+        with torch.cuda.device(self.device):
+            N.check(self.lib.ftb200_abort_word_create(ctypes.byref(hp), ctypes.byref(dp)), "abort_word_create", 0)
+        self._abort_host, self._abort_dev = hp, int(dp.value)
+        self.rank, self.world = 0, 1
+        self.epoch = 0
+        self._seq = 0
+        self.peer_base: List[int] = [self.arena.base]
+        self._imported: List[int] = []
+        self._lock = threading.Lock()
+
+    # ---- membership -----------------------------------------------------------------------
+    def connect(self, store: Store, rank: int, world: int, epoch: int) -> None:
+        """(Re)build the peer mappings for a new membership.  ``store`` must be a fresh
+        prefix shared by exactly these ranks."""
+        if world > MAX_RANKS:
+            raise ValueError(f"team supports at most {MAX_RANKS} ranks")
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            self._close_peers()
+            self.rank, self.world, self.epoch, self._seq = rank, world, int(epoch) & 0xFFFFFFFF, 0
+            self._abort_host[0] = 0
+            self._status.zero_()
+            self._sync.zero_()
+            self.arena.bytes_view[self._flag_off : self._flag_off + int(self.lib.ftb200_team_flag_bytes())].zero_()
+            torch.cuda.synchronize(self.device)
+            store.set(f"arena/{rank}", self.arena.export_handle())
+            bases: List[int] = []
+            for p in range(world):
+                if p == rank:
+                    bases.append(self.arena.base)
+                    continue
+                handle = store.get(f"arena/{p}")
+                ptr = ctypes.c_void_p()
+                N.check(self.lib.ftb200_ipc_import((ctypes.c_ubyte * 64).from_buffer_copy(handle), ctypes.byref(ptr)),
+                        "ipc_import", 0)
+                self._imported.append(int(ptr.value))
+                bases.append(int(ptr.value))
+            self.peer_base = bases
+            # nobody may signal into flags that a slower peer has not cleared yet
+            store.set(f"mapped/{rank}", b"1")
+            for p in range(world):
+                store.get(f"mapped/{p}")
+
+    def _close_peers(self) -> None:
+        for ptr in self._imported:
+            self.lib.ftb200_ipc_close(ctypes.c_void_p(ptr))
+        self._imported = []
+        self.peer_base = [self.arena.base]
+
+    def close(self) -> None:
+        with torch.cuda.device(self.device):
+            self._close_peers()
+
+    # ---- failure plumbing -------------------------------------------------------------------
+    def abort(self) -> None:
+        """Make every in-flight and future kernel of this team return (a plain memory write)."""
+        self._abort_host[0] = 1
+
+    def status(self) -> int:
+        """Synchronising read of the status word (0 ok, 1 timeout, 2 aborted, 3 epoch)."""
+        return int(self._status.item())
+
+    def check(self) -> None:
+        code = self.status()
+        if code:
+            raise TeamError(f"peer-memory collective failed: {N.STATUS.get(code, code)}")
+
+    # ---- kernels ------------------------------------------------------------------------------
+    def _desc(self) -> _TeamDesc:
+        with self._lock:
+            self._seq += 1
+            seq = self._seq
+        d = _TeamDesc()
+        d.rank, d.world = self.rank, self.world
+        d.token = (self.epoch << 32) | (seq & 0xFFFFFFFF)
+        d.timeout_ns = int(self.timeout.total_seconds() * 1e9)
+        for p in range(MAX_RANKS):
+            d.flags[p] = (self.peer_base[p] + self._flag_off) if p < self.world else None
+        d.local_sync = self._sync.data_ptr()
+        d.abort_word = self._abort_dev
+        d.status = self._status.data_ptr()
+        return d
+
+    def _peer_ptrs(self, off: int) -> ctypes.Array:
+        arr = (ctypes.c_void_p * MAX_RANKS)()
+        for p in range(self.world):
+            arr[p] = self.peer_base[p] + off
+        return arr
+
+    def allreduce_(self, off: int, numel: int, dtype: torch.dtype, scale: float = 1.0,
+                   user_in: Optional[torch.Tensor] = None, user_out: Optional[torch.Tensor] = None,
+                   zero_contribution: bool = False, ctas: int = 0) -> None:
+        """In-place allreduce of the symmetric buffer at ``off`` (``numel`` must be a
+        multiple of ``world * 16 bytes``); optionally staged from/to user tensors."""
+        d = self._desc()
+        N.check(
+            self.lib.ftb200_team_allreduce(ctypes.byref(d), self._peer_ptrs(off), N.ptr(user_in), N.ptr(user_out),
+                                           ctypes.c_longlong(numel), ctypes.c_int(_DT[dtype]), ctypes.c_float(scale),
+                                           ctypes.c_int(int(zero_contribution)), ctypes.c_int(ctas), N.stream_ptr()),
+            "team_allreduce",
+        )
+
+    def allgather(self, shard_off: int, shard_bytes: int, dst: torch.Tensor, ctas: int = 0) -> None:
+        d = self._desc()
+        N.check(
+            self.lib.ftb200_team_allgather(ctypes.byref(d), self._peer_ptrs(shard_off), N.ptr(dst),
+                                           ctypes.c_longlong(shard_bytes), ctypes.c_int(ctas), N.stream_ptr()),
+            "team_allgather",
+        )
+
+    def reduce_scatter(self, full_off: int, dst: torch.Tensor, shard_elems: int, dtype: torch.dtype, scale: float = 1.0,
+                       ctas: int = 0) -> None:
+        d = self._desc()
+        N.check(
+            self.lib.ftb200_team_reduce_scatter(ctypes.byref(d), self._peer_ptrs(full_off), N.ptr(dst),
+                                                ctypes.c_longlong(shard_elems), ctypes.c_int(_DT[dtype]),
+                                                ctypes.c_float(scale), ctypes.c_int(ctas), N.stream_ptr()),
+            "team_reduce_scatter",
+        )
+
+    def barrier(self) -> None:
+        d = self._desc()
+        N.check(self.lib.ftb200_team_barrier(ctypes.byref(d), N.stream_ptr()), "team_barrier")
+
+
+# ======================================================================================= FSDP
+
+
+class PeerShardComm(ShardComm):
+    """FSDP traffic of one replica group as peer-memory kernels.
+
+    Buffers handed out by :meth:`alloc` live in the team arena, so the all-gather pulls
+    parameter shards straight out of the peers' shard buffers into the local full unit and
+    the reduce-scatter pulls this rank's slice out of the peers' full gradient units
+    (fp32 accumulation, bf16 result).  Membership is static for the life of the group:
+    losing a rank loses the replica group, which is the granularity of fault tolerance.
+    """
+
+    def __init__(self, group: dist.ProcessGroup, device: torch.device, arena_bytes: Optional[int] = None,
+                 timeout: timedelta = timedelta(seconds=120)) -> None:
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.size = dist.get_world_size(group)
+        self.device = torch.device(device)
+        if arena_bytes is None:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            arena_bytes = int(free * 0.45)
+        self.team = SymmetricTeam(self.device, arena_bytes, timeout)
+        # exchange IPC handles through the (static) group itself
+        handle = self.team.arena.export_handle()
+        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
+        allh = [torch.empty_like(mine) for _ in range(self.size)]
+        dist.all_gather(allh, mine, group=group)
+
+        class _ListStore:
+            def __init__(s) -> None:
+                s.kv: Dict[str, bytes] = {f"arena/{p}": bytes(allh[p].cpu().tolist()) for p in range(self.size)}
+
+            def set(s, k: str, v: bytes) -> None:
+                s.kv[k] = v
+
+            def get(s, k: str) -> bytes:
+                return s.kv.get(k, b"1")
+
+        self.team.connect(_ListStore(), self.rank, self.size, epoch=1)  # type: ignore[arg-type]
+        dist.barrier(group=group)
+
+    def alloc(self, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+        es = torch.empty((), dtype=dtype).element_size()
+        off = self.team.arena.alloc(numel * es)
+        return self.team.arena.tensor(off, numel, dtype)
+
+    def _off(self, t: torch.Tensor) -> int:
+        off = self.team.arena.contains(t)
+        if off is None:
+            raise ValueError("tensor was not allocated by PeerShardComm.alloc")
+        return off
+
+    def all_gather(self, shard: torch.Tensor, full: torch.Tensor) -> None:
+        self.team.allgather(self._off(shard), shard.numel() * shard.element_size(), full)
+
+    def reduce_scatter(self, full: torch.Tensor, shard: torch.Tensor) -> None:
+        self.team.reduce_scatter(self._off(full), shard, shard.numel(), shard.dtype)
+
+    def all_reduce_sum_(self, t: torch.Tensor) -> None:
+        dist.all_reduce(t, group=self.group)
+
+    def barrier(self) -> None:
+        self.team.barrier()
+
+    def shutdown(self) -> None:
+        self.team.close()
+
+
+# ======================================================================================= replica dim
+
+
+class _StreamWork(Work):
+    """Work of a kernel collective: complete when the launching stream reaches the event."""
+
+    def __init__(self, pg: "ProcessGroupB200", result: object) -> None:
+        super().__init__()
+        self._pg = pg
+        self._event = torch.cuda.Event()
+        self._event.record()
+        self._result = result
+        self._fut: Optional[Future] = None
+
+    def wait(self, timeout: Optional[timedelta] = None) -> bool:
+        torch.cuda.current_stream().wait_event(self._event)
+        return True
+
+    def synchronize(self) -> None:
+        self._event.synchronize()
+
+    def block_current_stream(self, timeout: Optional[timedelta] = None) -> None:
+        self.wait()
+
+    def is_completed(self) -> bool:
+        return self._event.query()
+
+    def get_future(self) -> Future:
+        # stream semantics as with NCCL futures: "done" means ordered on the stream
+        if self._fut is None:
+            self._fut = Future()
+            self._fut.set_result(self._result)
+        return self._fut
+
+
+class ProcessGroupB200(ProcessGroup):
+    """Reconfigurable replica-dimension group over NVLink peer memory.
+
+    ``configure`` keeps this rank's arena, bumps the epoch, exchanges IPC handles under the
+    given store prefix and maps the new peers.  ``allreduce`` is one fused kernel: stage
+    (unless the tensor already lives in the arena, see :meth:`alloc`), two-shot reduce with
+    fp32 accumulation, ``scale`` (the manager passes ``1/num_participants``), write back.
+    ``abort`` is a store to a host-mapped word that all kernels poll; ``errored`` reads the
+    status word after synchronising the stream.  Supported: allreduce (SUM, and AVG via
+    scale), barrier, and send/recv/broadcast through a staging window for checkpoint
+    transfer.  bf16 and fp32 tensors.
+    """
+
+    supports_fused_scale = True
+
+    def __init__(self, timeout: timedelta = timedelta(seconds=60), arena_bytes: int = 1 << 30,
+                 staging_bytes: int = 256 << 20, device: Optional[torch.device] = None) -> None:
+        super().__init__(0, 1)
+        self._timeout = timeout
+        self._device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self._team = SymmetricTeam(self._device, arena_bytes + staging_bytes, timeout)
+        self._staging_bytes = staging_bytes
+        self._staging_off = self._team.arena.alloc(staging_bytes)
+        self._rank, self._world = 0, 1
+        self._errored: Optional[Exception] = None
+        self._configured = False
+        self._epoch = 0
+
+    # ---- memory ---------------------------------------------------------------------------
+    def alloc(self, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A tensor inside the exported arena: collectives on it run in place, without
+        staging copies.  All replicas must allocate in the same order."""
+        es = torch.empty((), dtype=dtype).element_size()
+        return self._team.arena.tensor(self._team.arena.alloc(numel * es), numel, dtype)
+
+    # ---- lifecycle --------------------------------------------------------------------------
+    def configure(self, store_addr: str, replica_id: str, rank: int, world_size: int) -> None:
+        store = create_store_client(store_addr, timeout=self._timeout)
+        self._epoch += 1
+        # the epoch must be common to all members: take it from the store prefix (quorum id)
+        try:
+            epoch = int(store_addr.rstrip("/").split("/")[-2])
+        except (ValueError, IndexError):
+            epoch = self._epoch
+        self._team.connect(store, rank, world_size, epoch)
+        self._rank, self._world = rank, world_size
+        self._errored = None
+        self._configured = True
+
+    def abort(self) -> None:
+        self._errored = RuntimeError("aborted")
+        self._team.abort()
+
+    def shutdown(self) -> None:
+        self._team.close()
+
+    def errored(self) -> Optional[Exception]:
+        if self._errored is None and self._configured:
+            code = self._team.status()
+            if code:
+                self._errored = TeamError(f"peer-memory collective failed: {N.STATUS.get(code, code)}")
+        return self._errored
+
+    def set_timeout(self, timeout: timedelta) -> None:
+        self._timeout = timeout
+        self._team.timeout = timeout
+
+    def size(self) -> int:
+        return self._world
+
+    def getBackendName(self) -> str:
+        return "torchft-b200-peer"
+
+    # ---- collectives --------------------------------------------------------------------------
+    def allreduce(self, tensors: List[torch.Tensor], opts=None, scale: float = 1.0,
+                  zero_contribution: bool = False) -> Work:
+        op = _reduce_op(opts)
+        if op == ReduceOp.AVG:
+            scale = scale / self._world
+        elif op != ReduceOp.SUM:
+            raise NotImplementedError(f"ProcessGroupB200.allreduce supports SUM and AVG, got {op}")
+        for t in tensors:
+            if self._world == 1:
+                # nothing to reduce: only the scale (and the zeroing of a spare) remains
+                if zero_contribution:
+                    t.zero_()
+                elif scale != 1.0:
+                    t.mul_(scale)
+                continue
+            self._allreduce_one(t, scale, zero_contribution)
+        return _StreamWork(self, tensors)
+
+    def _allreduce_one(self, t: torch.Tensor, scale: float, zero: bool) -> None:
+        if t.dtype not in _DT:
+            raise NotImplementedError(f"dtype {t.dtype} not supported by the peer-memory allreduce")
+        if not t.is_contiguous():
+            raise ValueError("allreduce needs contiguous tensors")
+        es = t.element_size()
+        gran = self._world * (16 // es)
+        off = self._team.arena.contains(t)
+        flat = t.view(-1)
+        n = flat.numel()
+        if off is not None and n % gran == 0 and off % 16 == 0:
+            self._team.allreduce_(off, n, t.dtype, scale, zero_contribution=zero)
+            return
+        # staged path, in chunks of the staging window
+        cap = (self._staging_bytes // es) // gran * gran
+        pos = 0
+        while pos < n:
+            m = min(cap, n - pos)
+            padded = (m + gran - 1) // gran * gran
+            chunk = flat[pos : pos + m]
+            if padded != m or (chunk.data_ptr() % 16):
+                stage = self._team.arena.tensor(self._staging_off, padded, t.dtype)
+                stage[:m].copy_(chunk)
+                if padded != m:
+                    stage[m:].zero_()
+                self._team.allreduce_(self._staging_off, padded, t.dtype, scale, zero_contribution=zero)
+                chunk.copy_(stage[:m])
+            else:
+                self._team.allreduce_(self._staging_off, m, t.dtype, scale, user_in=chunk, user_out=chunk,
+                                      zero_contribution=zero)
+            pos += m
+
+    def barrier(self, opts=None) -> Work:
+        self._team.barrier()
+        return _StreamWork(self, None)
+
+    # point-to-point through the staging window (used by the PG checkpoint transport)
+    def send(self, tensors: List[torch.Tensor], dst_rank: int, tag: int) -> Work:
+        raise NotImplementedError("use P2PTransport for state transfer over peer memory")
+
+    def recv(self, tensors: List[torch.Tensor], src_rank: int, tag: int) -> Work:
+        raise NotImplementedError("use P2PTransport for state transfer over peer memory")
+
+    def __repr__(self) -> str:
+        return f"ProcessGroupB200(rank={self._rank}, world={self._world}, epoch={self._team.epoch})"
