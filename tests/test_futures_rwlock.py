@@ -1,0 +1,106 @@
+import threading
+import time
+from datetime import timedelta
+from unittest.mock import patch
+
+import pytest
+import torch
+from torch.futures import Future
+
+from torchft_b200 import futures as F
+from torchft_b200.checkpointing._rwlock import RWLock
+
+
+def test_future_wait_and_timeout():
+    fut = Future()
+    with pytest.raises(TimeoutError):
+        F.future_wait(fut, timedelta(seconds=0.05))
+    fut.set_result(7)
+    assert F.future_wait(fut, timedelta(seconds=1)) == 7
+    bad = Future()
+    bad.set_exception(RuntimeError("boom"))
+    with pytest.raises(RuntimeError, match="boom"):
+        F.future_wait(bad, timedelta(seconds=1))
+
+
+def test_future_timeout_fires_and_passes_through():
+    slow = Future()
+    timed = F.future_timeout(slow, timedelta(seconds=0.05))
+    with pytest.raises(TimeoutError):
+        timed.wait()
+    ok = Future()
+    timed2 = F.future_timeout(ok, timedelta(seconds=5))
+    ok.set_result("v")
+    assert timed2.wait() == "v"
+    err = Future()
+    timed3 = F.future_timeout(err, timedelta(seconds=5))
+    err.set_exception(ValueError("x"))
+    with pytest.raises(ValueError):
+        timed3.wait()
+
+
+def test_context_timeout():
+    fired = threading.Event()
+    with F.context_timeout(fired.set, timedelta(seconds=5)):
+        pass
+    time.sleep(0.05)
+    assert not fired.is_set()
+    with F.context_timeout(fired.set, timedelta(seconds=0.02)):
+        time.sleep(0.2)
+    assert fired.is_set()
+
+
+def test_watchdog_exits_when_callback_is_stuck():
+    mgr = F._TimeoutManager()
+    mgr._watchdog_interval = timedelta(seconds=0.1)
+    exited = threading.Event()
+    release = threading.Event()
+    with patch.object(F._TimeoutManager, "_exit", staticmethod(exited.set)):
+        mgr.call_later(timedelta(seconds=0.01), lambda: release.wait(5))
+        assert exited.wait(3)
+    release.set()
+    mgr.shutdown()
+
+
+def test_rwlock_readers_writer():
+    lock = RWLock(timeout=0.2)
+    lock.r_acquire()
+    lock.r_acquire()  # many readers
+    with pytest.raises(TimeoutError):
+        lock.w_acquire()
+    lock.r_release()
+    lock.r_release()
+    with lock.w_lock():
+        assert lock.w_locked()
+        with pytest.raises(TimeoutError):
+            lock.r_acquire()
+    with lock.r_lock():
+        pass
+
+
+def test_rwlock_writer_preference():
+    lock = RWLock(timeout=2)
+    lock.r_acquire()
+    got = []
+    t = threading.Thread(target=lambda: (lock.w_acquire(), got.append("w"), lock.w_release()))
+    t.start()
+    time.sleep(0.05)
+    fast = RWLock.__dict__  # noqa: F841
+    lock2_err = []
+
+    def late_reader():
+        try:
+            lock.r_acquire()
+            got.append("r")
+            lock.r_release()
+        except TimeoutError as e:
+            lock2_err.append(e)
+
+    r = threading.Thread(target=late_reader)
+    r.start()
+    time.sleep(0.05)
+    assert got == []  # the late reader queues behind the waiting writer
+    lock.r_release()
+    t.join()
+    r.join()
+    assert got == ["w", "r"]

@@ -1,0 +1,197 @@
+"""LocalSGD / DiLoCo unit tests against a mocked Manager, and the analytic golden sequence:
+inner lr 1 with constant gradient 2, outer lr 2, 2 fragments, sync_every 6 gives local
+weights 1,-1,-3,-11,... for fragment 0 and global updates -11, -23, -35, -47."""
+from typing import Dict, List
+from unittest.mock import MagicMock, create_autospec
+
+import pytest
+import torch
+from torch import nn, optim
+
+from torchft_b200.local_sgd import DiLoCo, LocalSGD, _StreamingDiLoCoFragment
+from torchft_b200.manager import Manager
+from torchft_b200.work import _DummyWork
+
+
+class TinyModel(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.net = nn.Sequential(nn.Linear(3, 4), nn.ReLU(), nn.Linear(4, 2))
+
+    def forward(self, x):
+        return self.net(x)
+
+
+def mock_manager(commit=True, factor=1.0):
+    m = create_autospec(Manager, instance=True)
+    m._use_async_quorum = False
+    m.should_commit.return_value = commit
+    m.current_step.return_value = 0
+
+    def allreduce(t, should_quantize=False, reduce_op=None):
+        t.mul_(factor)
+        return _DummyWork(t)
+
+    m.allreduce.side_effect = allreduce
+    return m
+
+
+def test_local_sgd_sync_cadence_and_copy_back():
+    model = TinyModel()
+    opt = optim.SGD(model.parameters(), lr=0.1)
+    m = mock_manager(factor=0.5)
+    with LocalSGD(m, model, opt, sync_every=2) as ls:
+        for step in range(1, 5):
+            opt.zero_grad()
+            model(torch.rand(5, 3)).sum().backward()
+            before = [p.detach().clone() for p in model.parameters()]
+            opt.step()
+            if step % 2 == 0:
+                assert m.start_quorum.call_count == step // 2
+                assert m.should_commit.call_count == step // 2
+            assert ls._local_step == step % 2
+    assert m.allreduce.call_count == 2 * len(list(model.parameters()))
+    assert m.disallow_state_dict_read.call_count == 4 and m.allow_state_dict_read.call_count == 4
+
+
+def test_local_sgd_no_copy_when_commit_fails():
+    model = TinyModel()
+    opt = optim.SGD(model.parameters(), lr=0.1)
+    m = mock_manager(commit=False, factor=0.0)
+    with LocalSGD(m, model, opt, sync_every=1):
+        opt.zero_grad()
+        model(torch.rand(5, 3)).sum().backward()
+        opt.step()
+    assert all(p.abs().sum() > 0 for p in model.parameters())  # zeros from the failed sync were not applied
+
+
+def test_diloco_argument_validation():
+    model = TinyModel()
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    outer = optim.SGD(model.parameters(), lr=0.7, momentum=0.9, nesterov=True)
+    m = mock_manager()
+    m._use_async_quorum = True
+    with pytest.raises(ValueError, match="synchronous quorum"):
+        DiLoCo(m, [model], inner, outer, sync_every=2)
+    m._use_async_quorum = False
+    frags = [model.net[0], model.net[2]]
+    with pytest.raises(ValueError):
+        DiLoCo(m, frags, inner, outer, sync_every=1)  # fewer steps than fragments
+    with pytest.raises(ValueError):
+        DiLoCo(m, frags, inner, outer, sync_every=3)  # not divisible
+    with pytest.raises(ValueError):
+        DiLoCo(m, frags, inner, outer, sync_every=4, fragment_sync_delay=2)
+    with pytest.raises(ValueError):
+        DiLoCo(m, frags, inner, outer, sync_every=4, fragment_update_alpha=1.5)
+    with pytest.raises(AssertionError):
+        DiLoCo(m, frags, inner, [outer], sync_every=4)
+
+
+def test_diloco_healthy_flow():
+    model = TinyModel()
+    inner = optim.AdamW(model.parameters(), lr=1e-2)
+    outer = optim.SGD(model.parameters(), lr=0.7, momentum=0.9, nesterov=True)
+    m = mock_manager()
+    with DiLoCo(m, [model], inner, outer, sync_every=2) as d:
+        frag = d._fragments[0]
+        start = {n: p.detach().clone() for n, p in model.named_parameters()}
+        for n, t in frag.original_parameters.items():
+            torch.testing.assert_close(t, start[n])
+        inner.zero_grad(); model(torch.rand(4, 3)).sum().backward(); inner.step()
+        assert m.start_quorum.call_count == 0 and d._local_step == 1
+        inner.zero_grad(); model(torch.rand(4, 3)).sum().backward(); inner.step()
+        assert m.start_quorum.call_count == 1 and m.should_commit.call_count == 1 and d._local_step == 0
+        # the backup now holds the new global weights, which the model carries too (alpha 0)
+        for n, p in model.named_parameters():
+            torch.testing.assert_close(frag.original_parameters[n], p.detach())
+        assert m.allreduce.call_count == len(list(model.parameters()))
+
+
+def test_diloco_failed_commit_restores_global_weights():
+    model = TinyModel()
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    outer = optim.SGD(model.parameters(), lr=0.7)
+    m = mock_manager(commit=False)
+    start = {n: p.detach().clone() for n, p in model.named_parameters()}
+    with DiLoCo(m, [model], inner, outer, sync_every=1):
+        inner.zero_grad(); model(torch.rand(4, 3)).sum().backward(); inner.step()
+    for n, p in model.named_parameters():
+        torch.testing.assert_close(p.detach(), start[n])
+
+
+def test_bucketization_matches_per_param_and_keeps_oversized_tensors():
+    class M(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = nn.Parameter(torch.zeros(10))
+            self.b = nn.Parameter(torch.zeros(300))  # larger than the bucket cap below
+            self.c = nn.Parameter(torch.zeros(7))
+
+    model = M()
+    m = mock_manager(factor=2.0)
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    frag = _StreamingDiLoCoFragment(m, model, 0, 1, inner, optim.SGD(model.parameters(), lr=1.0), 1,
+                                    use_bucketization=True, bucket_cap_mb=None)
+    frag.bucket_cap_mb = 64 * 4  # bytes: 64 fp32 elements
+    frag._grads = {"a": torch.ones(10), "b": torch.full((300,), 2.0), "c": torch.full((7,), 3.0)}
+    frag._allreduce_bucketized()
+    for w in frag._allreduce_work:
+        w.wait()
+        w.get_future().wait()
+    torch.testing.assert_close(frag._grads["a"], torch.full((10,), 2.0))
+    torch.testing.assert_close(frag._grads["b"], torch.full((300,), 4.0))
+    torch.testing.assert_close(frag._grads["c"], torch.full((7,), 6.0))
+    assert m.allreduce.call_count == 3  # a | b (own bucket) | c
+
+
+class _MockLayer(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(1, 1))
+
+
+class _MockOptimizer(optim.Optimizer):
+    """p -= lr * grad"""
+
+    def __init__(self, params, lr):
+        super().__init__(params, dict(lr=lr))
+
+    def step(self, closure=None):
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p.grad is not None:
+                    p.data.add_(p.grad, alpha=-g["lr"])
+
+
+@pytest.mark.parametrize("n_fragments,expected_l0,expected_l1", [
+    (2, [1, -1, -3, -11, -13, -15, -17], [1, -1, -3, -5, -7, -9, -23]),
+])
+def test_diloco_golden_sequence(n_fragments, expected_l0, expected_l1):
+    layers = [_MockLayer() for _ in range(n_fragments)]
+    model = nn.Sequential(*layers)
+    inner = _MockOptimizer(model.parameters(), lr=1.0)
+    outers = [_MockOptimizer(l.parameters(), lr=2.0) for l in layers]
+    state = {"step": 0}
+    m = create_autospec(Manager, instance=True)
+    m._use_async_quorum = False
+    m.current_step.side_effect = lambda: state["step"]
+    m.allreduce.side_effect = lambda t, should_quantize=False, reduce_op=None: _DummyWork(t)
+
+    def commit():
+        state["step"] += 1
+        return True
+
+    m.should_commit.side_effect = commit
+    seen0, seen1, globals_ = [1.0], [1.0], []
+    with DiLoCo(m, layers, inner, outers, sync_every=6) as d:
+        for _ in range(6):
+            for p in model.parameters():
+                p.grad = torch.full_like(p, 2.0)
+            inner.step()
+            seen0.append(layers[0].weight.item())
+            seen1.append(layers[1].weight.item())
+            globals_.append((d._fragments[0].original_parameters["weight"].item(),
+                             d._fragments[1].original_parameters["weight"].item()))
+    assert seen0 == [float(x) for x in expected_l0]
+    assert seen1 == [float(x) for x in expected_l1]
+    assert globals_[2] == (-11.0, 1.0) and globals_[5] == (-11.0, -23.0)

@@ -1,0 +1,121 @@
+"""Checkpoint transport contract: 1->2 fan-out, 1->1, then a tiny timeout must raise."""
+import threading
+import urllib.error
+import urllib.request
+from concurrent.futures import ThreadPoolExecutor
+from datetime import timedelta
+
+import pytest
+import torch
+import torch.distributed as dist
+
+from torchft_b200.checkpointing.http_transport import HTTPTransport
+from torchft_b200.checkpointing.pg_transport import PGTransport
+from torchft_b200.process_group import ProcessGroupGloo
+
+
+def make_state(seed):
+    g = torch.Generator().manual_seed(seed)
+    return {"rng": torch.rand(2, 3, generator=g), "nested": {"w": torch.arange(10, dtype=torch.float32), "i": torch.tensor([1, 2])},
+            "str": "foo", "int": 1234, "list": [1.5, torch.ones(3, dtype=torch.bfloat16)]}
+
+
+def assert_state_equal(a, b):
+    assert a["str"] == b["str"] and a["int"] == b["int"]
+    torch.testing.assert_close(a["rng"], b["rng"])
+    torch.testing.assert_close(a["nested"]["w"], b["nested"]["w"])
+    torch.testing.assert_close(a["nested"]["i"], b["nested"]["i"])
+    assert a["list"][0] == b["list"][0]
+    torch.testing.assert_close(a["list"][1], b["list"][1])
+
+
+def run_multi_recovery(init_transport, world=3):
+    barrier = threading.Barrier(world)
+    timeout = timedelta(seconds=10)
+    want = make_state(0)
+
+    def run(rank):
+        transport = init_transport(rank, world)
+        try:
+            metadata = transport.metadata() if rank == 0 else None
+            meta_box[rank] = metadata
+            barrier.wait(10)
+            md = meta_box[0]
+            # round 1: rank 0 -> ranks 1, 2
+            if rank == 0:
+                transport.send_checkpoint([1, 2], step=1, state_dict=want, timeout=timeout)
+            else:
+                got = transport.recv_checkpoint(0, md, step=1, timeout=timeout)
+                assert_state_equal(got, want)
+            barrier.wait(10)
+            transport.disallow_checkpoint()
+            # round 2: rank 0 -> rank 1
+            if rank == 0:
+                transport.send_checkpoint([1], step=2, state_dict=want, timeout=timeout)
+            elif rank == 1:
+                assert_state_equal(transport.recv_checkpoint(0, md, step=2, timeout=timeout), want)
+            barrier.wait(10)
+            transport.disallow_checkpoint()
+            # round 3: nobody sends; the receiver must give up quickly
+            if rank == 2:
+                with pytest.raises(Exception):
+                    transport.recv_checkpoint(0, md, step=3, timeout=timedelta(milliseconds=10))
+            barrier.wait(10)
+        finally:
+            transport.shutdown(wait=False)
+        return True
+
+    meta_box = {}
+    with ThreadPoolExecutor(max_workers=world) as ex:
+        futs = [ex.submit(run, r) for r in range(world)]
+        assert all(f.result(timeout=60) for f in futs)
+
+
+@pytest.mark.parametrize("chunks", [0, 3])
+def test_http_transport_multi_recovery(chunks):
+    run_multi_recovery(lambda rank, world: HTTPTransport(timedelta(seconds=10), num_chunks=chunks))
+
+
+def test_http_transport_wrong_step_and_lock_state():
+    t = HTTPTransport(timedelta(seconds=1), num_chunks=0)
+    try:
+        assert t._lock.w_locked()  # nothing is served before the first send
+        t.send_checkpoint([1], step=5, state_dict={"a": torch.ones(2)}, timeout=timedelta(seconds=1))
+        assert not t._lock.w_locked()
+        url = t.metadata().replace(__import__("socket").gethostname(), "localhost")
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(url + "6/full", timeout=2)
+        assert e.value.code == 400
+        got = t.recv_checkpoint(0, t.metadata(), 5, timedelta(seconds=2))
+        torch.testing.assert_close(got["a"], torch.ones(2))
+        t.disallow_checkpoint()
+        t.disallow_checkpoint()  # idempotent
+        assert t._lock.w_locked()
+        t.allow_checkpoint(6)
+        assert not t._lock.w_locked()
+    finally:
+        t.shutdown()
+
+
+def _gloo_pgs(world):
+    store = dist.TCPStore("localhost", 0, is_master=True, wait_for_workers=False)
+    addr = f"localhost:{store.port}/prefix"
+    pgs = [ProcessGroupGloo(timeout=timedelta(seconds=10)) for _ in range(world)]
+    with ThreadPoolExecutor(max_workers=world) as ex:
+        list(ex.map(lambda r: pgs[r].configure(addr, "rep", r, world), range(world)))
+    return store, pgs
+
+
+@pytest.mark.parametrize("inplace", [False, True])
+def test_pg_transport_gloo(inplace):
+    world = 3
+    store, pgs = _gloo_pgs(world)
+    try:
+        def init(rank, world):
+            sd = (lambda: make_state(99)) if inplace else None
+            return PGTransport(pgs[rank], timedelta(seconds=10), torch.device("cpu"), state_dict=sd)
+
+        run_multi_recovery(init, world)
+    finally:
+        for pg in pgs:
+            pg.shutdown()

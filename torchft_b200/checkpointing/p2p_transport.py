@@ -1,0 +1,169 @@
+"""Live-recovery transport over NVLink peer memory.
+
+The healthy replica does not copy anything: it publishes, over the small HTTP channel of
+:class:`~torchft_b200.checkpointing.http_transport.HTTPTransport`, a state dict in which
+every CUDA tensor is replaced by a reference (CUDA IPC handle of the allocation, offset,
+shape, dtype).  The healing replica maps those allocations and *pulls* all tensors with
+one grid-stride copy kernel straight into its own live tensors (when given an in-place
+state dict) or into fresh ones -- the bytes cross NVLink once and never touch the host.
+Pulling means a source that dies mid-transfer cannot block the healer: the kernel polls
+the team's abort word and the transfer is simply retried next quorum.
+
+The source's tensors must stay unmodified until the step commits; the manager guarantees
+that (the optimizer only runs after the step's allreduce, which the healing replica joins
+after its transfer).  Non-CUDA leaves travel inside the HTTP payload.  Same-host GPUs
+only; use ``HTTPTransport`` across hosts.  Replaces the payload path of
+torchft/checkpointing/http_transport.py and pg_transport.py.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import logging
+from dataclasses import dataclass
+from datetime import timedelta
+from typing import Callable, Dict, Generic, List, Optional, Tuple, TypeVar
+
+import torch
+from torch.utils._pytree import tree_flatten, tree_unflatten
+
+from ..ops import _native as N
+from .http_transport import HTTPTransport
+
+logger = logging.getLogger(__name__)
+T = TypeVar("T")
+
+
+@dataclass
+class _PeerTensorRef:
+    handle: bytes
+    offset: int
+    nbytes: int
+    shape: Tuple[int, ...]
+    dtype: torch.dtype
+
+
+class _CopySeg(ctypes.Structure):
+    _fields_ = [("src", ctypes.c_void_p), ("dst", ctypes.c_void_p), ("bytes", ctypes.c_longlong)]
+
+
+def _export(t: torch.Tensor) -> _PeerTensorRef:
+    buf = (ctypes.c_ubyte * 64)()
+    off, size = ctypes.c_ulonglong(), ctypes.c_ulonglong()
+    with torch.cuda.device(t.device):
+        N.check(N.lib().ftb200_ipc_export_any(N.ptr(t), buf, ctypes.byref(off), ctypes.byref(size)), "ipc_export_any", 0)
+    return _PeerTensorRef(bytes(buf), int(off.value), t.numel() * t.element_size(), tuple(t.shape), t.dtype)
+
+
+class P2PTransport(HTTPTransport[T], Generic[T]):
+    """
+    Args:
+        timeout: for the metadata exchange
+        device: this rank's GPU
+        state_dict: optional callable returning the receiver's current state dict; tensors
+            whose shape and dtype match are filled in place
+    """
+
+    def __init__(self, timeout: timedelta, device: torch.device, state_dict: Optional[Callable[[], T]] = None) -> None:
+        super().__init__(timeout=timeout, num_chunks=0)
+        self._device = torch.device(device)
+        self._state_dict_fn = state_dict
+        self._keepalive: List[torch.Tensor] = []
+        self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+
+    def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
+        leaves, spec = tree_flatten(state_dict)
+        out: List[object] = []
+        keep: List[torch.Tensor] = []
+        torch.cuda.current_stream(self._device).synchronize()  # what we publish must be materialised
+        for v in leaves:
+            if isinstance(v, torch.Tensor) and v.is_cuda:
+                c = v.detach()
+                if not c.is_contiguous():
+                    c = c.contiguous()
+                keep.append(c)
+                out.append(_export(c))
+            else:
+                out.append(v)
+        self._keepalive = keep
+        self._spec = spec
+        self._chunks = None
+        self._state = tree_unflatten(out, spec)
+        self.allow_checkpoint(step)
+
+    def disallow_checkpoint(self) -> None:
+        super().disallow_checkpoint()
+        self._keepalive = []
+
+    def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
+        remote = self._fetch(f"{metadata}{step}/full", timeout)
+        leaves, spec = tree_flatten(remote, is_leaf=lambda x: isinstance(x, _PeerTensorRef))
+        inplace: Optional[List[object]] = None
+        if self._state_dict_fn is not None:
+            inplace, _ = tree_flatten(self._state_dict_fn())
+        lib = N.lib()
+        opened: Dict[bytes, int] = {}
+        segs: List[Tuple[int, int, int]] = []
+        result: List[object] = []
+        with torch.cuda.device(self._device):
+            try:
+                for i, v in enumerate(leaves):
+                    if not isinstance(v, _PeerTensorRef):
+                        result.append(v)
+                        continue
+                    base = opened.get(v.handle)
+                    if base is None:
+                        p = ctypes.c_void_p()
+                        N.check(lib.ftb200_ipc_import((ctypes.c_ubyte * 64).from_buffer_copy(v.handle), ctypes.byref(p)),
+                                "ipc_import", 0)
+                        base = int(p.value)
+                        opened[v.handle] = base
+                    dst: Optional[torch.Tensor] = None
+                    if inplace is not None and i < len(inplace):
+                        cand = inplace[i]
+                        if (isinstance(cand, torch.Tensor) and cand.is_cuda and tuple(cand.shape) == v.shape
+                                and cand.dtype == v.dtype and cand.is_contiguous()):
+                            dst = cand
+                    if dst is None:
+                        dst = torch.empty(v.shape, dtype=v.dtype, device=self._device)
+                    result.append(dst)
+                    if v.nbytes:
+                        segs.append((base + v.offset, dst.data_ptr(), v.nbytes))
+                self._pull(segs)
+            finally:
+                torch.cuda.current_stream().synchronize()
+                for base in opened.values():
+                    lib.ftb200_ipc_close(ctypes.c_void_p(base))
+        code = int(self._status.item())
+        if code:
+            self._status.zero_()
+            raise RuntimeError(f"peer-memory state transfer failed: {N.STATUS.get(code, code)}")
+        return tree_unflatten(result, spec)
+
+    def _pull(self, segs: List[Tuple[int, int, int]]) -> None:
+        """One kernel for all 16-byte-aligned bulk; ragged heads/tails go through memcpy."""
+        if not segs:
+            return
+        table = (_CopySeg * len(segs))()
+        n, total = 0, 0
+        tails: List[Tuple[int, int, int]] = []
+        for src, dst, nb in segs:
+            if (src % 16) or (dst % 16):
+                tails.append((src, dst, nb))
+                continue
+            bulk = nb // 16 * 16
+            if bulk:
+                table[n].src, table[n].dst, table[n].bytes = src, dst, bulk
+                n += 1
+                total += bulk
+            if nb - bulk:
+                tails.append((src + bulk, dst + bulk, nb - bulk))
+        if n:
+            raw = bytes(table)[: n * ctypes.sizeof(_CopySeg)]
+            dev_table = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(self._device)
+            N.check(N.lib().ftb200_p2p_copy(N.ptr(dev_table), ctypes.c_int(n), ctypes.c_longlong(total), None,
+                                            N.ptr(self._status), ctypes.c_int(0), N.stream_ptr()), "p2p_copy")
+            self._table_keepalive = dev_table
+        cudart = torch.cuda.cudart()
+        for src, dst, nb in tails:
+            cudart.cudaMemcpy(dst, src, nb, 3)  # cudaMemcpyDeviceToDevice

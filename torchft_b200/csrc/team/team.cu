@@ -190,15 +190,25 @@ __device__ __forceinline__ void allreduce_body(const TeamParams& tp, const Allre
   const long long slice = a.n / tp.world;
   const long long lo = slice * tp.rank;
   for (long long i = tid * V; i < slice; i += nthreads * V) {
+    uint4 raw[MAX_RANKS];
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k < tp.world) {
+        const int p = (tp.rank + k) % tp.world;
+        raw[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.bufs[p]) + lo + i);
+      }
+    }
     float acc[V];
 #pragma unroll
     for (int e = 0; e < V; ++e) acc[e] = 0.f;
-    for (int k = 0; k < tp.world; ++k) {
-      const int p = (tp.rank + k) % tp.world;
-      float f[V];
-      Vec<T>::load(reinterpret_cast<const T*>(a.bufs[p]) + lo + i, f);
 #pragma unroll
-      for (int e = 0; e < V; ++e) acc[e] += f[e];
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k < tp.world) {
+        float f[V];
+        Vec<T>::load(reinterpret_cast<const T*>(&raw[k]), f);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] += f[e];
+      }
     }
 #pragma unroll
     for (int e = 0; e < V; ++e) acc[e] *= a.scale;
@@ -247,12 +257,28 @@ __device__ __forceinline__ void allgather_body(const TeamParams& tp, const Gathe
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   uint4* dst = reinterpret_cast<uint4*>(a.dst);
-  for (long long i = tid; i < total; i += nthreads) {
-    // start with the next rank's shard so that the ranks do not all hit the same peer at once
-    const long long blk = i / v_per;
-    const int p = static_cast<int>((blk + tp.rank + 1) % tp.world);
-    const long long off = i - blk * v_per;
-    dst[p * v_per + off] = reinterpret_cast<const uint4*>(a.src[p])[off];
+  // four independent 16-byte loads in flight per thread: NVLink latency is microseconds,
+  // so bandwidth comes from bytes in flight
+  constexpr int U = 4;
+  for (long long i0 = tid; i0 < total; i0 += nthreads * U) {
+    uint4 v[U];
+    long long didx[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * nthreads;
+      didx[u] = -1;
+      if (i < total) {
+        // start with the next rank's shard so that the ranks do not all hit the same peer at once
+        const long long blk = i / v_per;
+        const int p = static_cast<int>((blk + tp.rank + 1) % tp.world);
+        const long long off = i - blk * v_per;
+        v[u] = reinterpret_cast<const uint4*>(a.src[p])[off];
+        didx[u] = p * v_per + off;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (didx[u] >= 0) dst[didx[u]] = v[u];
   }
   if (!grid_arrive(tp, 3, &sh_code)) return;
   team_round(tp, 1, 1, &sh_code);
@@ -281,15 +307,25 @@ __device__ __forceinline__ void reduce_scatter_body(const TeamParams& tp, const 
   const long long lo = a.shard_elems * tp.rank;
   T* dst = reinterpret_cast<T*>(a.dst);
   for (long long i = tid * V; i < a.shard_elems; i += nthreads * V) {
+    uint4 raw[MAX_RANKS];
+#pragma unroll
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k < tp.world) {
+        const int p = (tp.rank + k) % tp.world;
+        raw[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.src[p]) + lo + i);
+      }
+    }
     float acc[V];
 #pragma unroll
     for (int e = 0; e < V; ++e) acc[e] = 0.f;
-    for (int k = 0; k < tp.world; ++k) {
-      const int p = (tp.rank + k) % tp.world;
-      float f[V];
-      Vec<T>::load(reinterpret_cast<const T*>(a.src[p]) + lo + i, f);
 #pragma unroll
-      for (int e = 0; e < V; ++e) acc[e] += f[e];
+    for (int k = 0; k < MAX_RANKS; ++k) {
+      if (k < tp.world) {
+        float f[V];
+        Vec<T>::load(reinterpret_cast<const T*>(&raw[k]), f);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] += f[e];
+      }
     }
 #pragma unroll
     for (int e = 0; e < V; ++e) acc[e] *= a.scale;
@@ -341,7 +377,7 @@ __global__ void __launch_bounds__(512) p2p_copy_kernel(const CopySeg* __restrict
 int grid_for_bytes(long long bytes) {
   // enough CTAs to saturate NVLink without starving concurrent compute of SMs
   long long g = bytes / (512 * 16 * 4);
-  g = std::max<long long>(1, std::min<long long>(g, 64));
+  g = std::max<long long>(1, std::min<long long>(g, 96));
   return static_cast<int>(g);
 }
 
@@ -555,4 +591,32 @@ FTB200_API int ftb200_team_reduce_scatter_emulated(const ftb200_team_desc* descs
   }
   if (dtype == 0) return launch_emulated(reduce_scatter_emul_kernel<__nv_bfloat16>, tps, as, ctas > 0 ? ctas : 4, st);
   return launch_emulated(reduce_scatter_emul_kernel<float>, tps, as, ctas > 0 ? ctas : 4, st);
+}
+
+// Export the allocation that contains `ptr` (any device pointer obtained from cudaMalloc,
+// e.g. a tensor of the framework's caching allocator) and report ptr's offset inside it.
+FTB200_API int ftb200_ipc_export_any(const void* ptr, unsigned char* handle64, unsigned long long* offset,
+                                     unsigned long long* alloc_bytes) {
+  typedef int (*GetRangeFn)(unsigned long long*, size_t*, unsigned long long);
+  static GetRangeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return FTB200_E_DRIVER;
+    fn = reinterpret_cast<GetRangeFn>(sym);
+  }
+  unsigned long long base = 0;
+  size_t size = 0;
+  if (fn(&base, &size, reinterpret_cast<unsigned long long>(ptr)) != 0) return FTB200_E_DRIVER;
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base)) != cudaSuccess) {
+    cudaGetLastError();
+    return FTB200_E_CUDA;
+  }
+  memcpy(handle64, &h, sizeof(h));
+  *offset = reinterpret_cast<unsigned long long>(ptr) - base;
+  *alloc_bytes = size;
+  return 0;
 }

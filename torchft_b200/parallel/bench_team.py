@@ -1,0 +1,104 @@
+"""Bus-bandwidth benchmark of the peer-memory collectives against NCCL.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
+        --master-port 29544 -m torchft_b200.parallel.bench_team --sizes-mb 1 16 256 1024
+
+One JSON line per (op, size): device-timed (CUDA events, max over ranks) time, algorithm
+and bus bandwidth (allreduce: 2(n-1)/n x bytes / t; all-gather and reduce-scatter:
+(n-1)/n x bytes / t) and the fraction of the 770 GB/s measured per-direction NVLink copy
+bandwidth on this pool.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+from datetime import timedelta
+
+import torch
+import torch.distributed as dist
+
+from .team import PeerShardComm, ProcessGroupB200
+
+NVLINK_GBS = 770.0
+
+
+def _time(fn, iters=10, warmup=3):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1) / iters], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--sizes-mb", type=float, nargs="+", default=[1, 16, 256, 1024])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args()
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    dtype = torch.bfloat16 if a.dtype == "bf16" else torch.float32
+    es = 2 if dtype == torch.bfloat16 else 4
+    max_bytes = int(max(a.sizes_mb) * (1 << 20))
+
+    store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 77, world, is_master=(rank == 0),
+                          wait_for_workers=False)
+    pg = ProcessGroupB200(timeout=timedelta(seconds=30), arena_bytes=max_bytes + (1 << 20), device=dev)
+    pg.configure(f"127.0.0.1:{store.port}/torchft/1/0", "bench", rank, world)
+    comm = PeerShardComm(dist.group.WORLD, dev, arena_bytes=2 * max_bytes + (16 << 20))
+    buf = pg.alloc(max_bytes // es, dtype)
+    full_peer = comm.alloc(max_bytes // es, dtype, dev)
+    full_local = torch.empty(max_bytes // es, dtype=dtype, device=dev)
+    buf.normal_()
+    full_peer.normal_()
+
+    for mb in a.sizes_mb:
+        n = int(mb * (1 << 20)) // es // (world * 8) * (world * 8)
+        nbytes = n * es
+        t = buf[:n]
+        x = torch.randn(n, device=dev).to(dtype)
+        rows = []
+        ms = _time(lambda: pg.allreduce([t], dist.ReduceOp.SUM, scale=1.0 / world), a.iters)
+        rows.append(("allreduce", "peer", ms, 2 * (world - 1) / world))
+        ms = _time(lambda: (dist.all_reduce(x), x.div_(world)), a.iters)
+        rows.append(("allreduce", "nccl+div", ms, 2 * (world - 1) / world))
+        shard = n // world
+        sh = full_peer[:shard]
+        ms = _time(lambda: comm.all_gather(sh, full_local[:n]), a.iters)
+        rows.append(("all_gather", "peer", ms, (world - 1) / world))
+        xs = x[:shard].clone()
+        ms = _time(lambda: dist.all_gather_into_tensor(full_local[:n], xs), a.iters)
+        rows.append(("all_gather", "nccl", ms, (world - 1) / world))
+        out = torch.empty(shard, dtype=dtype, device=dev)
+        ms = _time(lambda: comm.reduce_scatter(full_peer[:n], out), a.iters)
+        rows.append(("reduce_scatter", "peer", ms, (world - 1) / world))
+        ms = _time(lambda: dist.reduce_scatter_tensor(out, x), a.iters)
+        rows.append(("reduce_scatter", "nccl", ms, (world - 1) / world))
+        if rank == 0:
+            for op, impl, ms, f in rows:
+                bus = nbytes * f / ms / 1e6
+                print(json.dumps({"op": op, "impl": impl, "world": world, "mb": mb, "dtype": a.dtype, "ms": round(ms, 4),
+                                  "bus_gbs": round(bus, 1), "frac_of_measured_nvlink_770": round(bus / NVLINK_GBS, 3)}),
+                      flush=True)
+    err = pg.errored()
+    comm.team.check()
+    if rank == 0:
+        print(json.dumps({"errored": str(err)}))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -363,7 +363,7 @@ class ProcessGroupB200(ProcessGroup):
         super().__init__(0, 1)
         self._timeout = timeout
         self._device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self._team = SymmetricTeam(self._device, arena_bytes + staging_bytes, timeout)
+        self._team = SymmetricTeam(self._device, arena_bytes + staging_bytes + (1 << 16), timeout)
         self._staging_bytes = staging_bytes
         self._staging_off = self._team.arena.alloc(staging_bytes)
         self._rank, self._world = 0, 1
