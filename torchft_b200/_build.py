@@ -122,9 +122,9 @@ def build_kernels(verbose: bool = False) -> Path:
     """Compile every ``csrc/kernels/*.cu`` and ``csrc/team/*.cu`` for sm_100a."""
     with _lock:
         sources = sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "team").glob("*.cu"))
-        headers = sorted((CSRC / "kernels").glob("*.cuh")) + sorted((CSRC / "kernels").glob("*.h")) + sorted(
-            (CSRC / "team").glob("*.h")
-        )
+        headers = []
+        for d in ("kernels", "team"):
+            headers += sorted((CSRC / d).glob("*.cuh")) + sorted((CSRC / d).glob("*.h"))
         flags = NVCC_FLAGS + [f"-I{CSRC / 'kernels'}", f"-I{CSRC / 'team'}"]
         if os.environ.get("FTB200_BOUNDS_CHECK"):
             flags = flags + ["-DFT_BOUNDS_CHECK=1"]

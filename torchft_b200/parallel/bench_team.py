@@ -45,6 +45,7 @@ def main() -> None:
     ap.add_argument("--sizes-mb", type=float, nargs="+", default=[1, 16, 256, 1024])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp32"])
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--ctas", type=int, nargs="+", default=[0], help="CTA counts to sweep for the peer kernels (0 = default)")
     a = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
@@ -65,26 +66,33 @@ def main() -> None:
     buf.normal_()
     full_peer.normal_()
 
+    ms = _time(lambda: comm.team.barrier(), a.iters)
+    if rank == 0:
+        print(json.dumps({"op": "barrier", "impl": "peer", "world": world, "ms": round(ms, 4)}), flush=True)
     for mb in a.sizes_mb:
         n = int(mb * (1 << 20)) // es // (world * 8) * (world * 8)
         nbytes = n * es
         t = buf[:n]
         x = torch.randn(n, device=dev).to(dtype)
         rows = []
-        ms = _time(lambda: pg.allreduce([t], dist.ReduceOp.SUM, scale=1.0 / world), a.iters)
-        rows.append(("allreduce", "peer", ms, 2 * (world - 1) / world))
+        off = pg._team.arena.contains(t)
+        for c in a.ctas:
+            ms = _time(lambda: pg._team.allreduce_(off, n, dtype, 1.0 / world, ctas=c), a.iters)
+            rows.append(("allreduce", f"peer(ctas={c})", ms, 2 * (world - 1) / world))
         ms = _time(lambda: (dist.all_reduce(x), x.div_(world)), a.iters)
         rows.append(("allreduce", "nccl+div", ms, 2 * (world - 1) / world))
         shard = n // world
         sh = full_peer[:shard]
-        ms = _time(lambda: comm.all_gather(sh, full_local[:n]), a.iters)
-        rows.append(("all_gather", "peer", ms, (world - 1) / world))
+        for c in a.ctas:
+            ms = _time(lambda: comm.team.allgather(comm._off(sh), shard * es, full_local[:n], ctas=c), a.iters)
+            rows.append(("all_gather", f"peer(ctas={c})", ms, (world - 1) / world))
         xs = x[:shard].clone()
         ms = _time(lambda: dist.all_gather_into_tensor(full_local[:n], xs), a.iters)
         rows.append(("all_gather", "nccl", ms, (world - 1) / world))
         out = torch.empty(shard, dtype=dtype, device=dev)
-        ms = _time(lambda: comm.reduce_scatter(full_peer[:n], out), a.iters)
-        rows.append(("reduce_scatter", "peer", ms, (world - 1) / world))
+        for c in a.ctas:
+            ms = _time(lambda: comm.team.reduce_scatter(comm._off(full_peer), out, shard, dtype, ctas=c), a.iters)
+            rows.append(("reduce_scatter", f"peer(ctas={c})", ms, (world - 1) / world))
         ms = _time(lambda: dist.reduce_scatter_tensor(out, x), a.iters)
         rows.append(("reduce_scatter", "nccl", ms, (world - 1) / world))
         if rank == 0:

@@ -467,6 +467,31 @@ class ProcessGroupB200(ProcessGroup):
                                       zero_contribution=zero)
             pos += m
 
+    def allreduce_fp8(self, src: torch.Tensor, dst: torch.Tensor, scale: float = 1.0,
+                      minus: Optional[torch.Tensor] = None) -> None:
+        """Quantised allreduce of flat ``src`` (or ``src - minus``) into ``dst`` as one fused
+        kernel per rank: block-scaled e4m3 on the wire, fp32 accumulation, ``scale`` folded
+        in.  ``numel`` must be a multiple of ``128 * world``; runs on the current stream."""
+        from .. import quantization as Q
+
+        n = src.numel()
+        if n % (Q.BLOCK * self._world) or src.dtype not in _DT or not src.is_contiguous():
+            raise ValueError("allreduce_fp8 needs a contiguous bf16/fp32 tensor of 128*world-multiple length")
+        cap = self._staging_bytes * Q.BLOCK // (Q.BLOCK + 4) // (Q.BLOCK * self._world) * (Q.BLOCK * self._world)
+        pos = 0
+        while pos < n:
+            m = min(cap, n - pos)
+            d = self._team._desc()
+            N.check(
+                self._team.lib.ftb200_team_allreduce_fp8(
+                    ctypes.byref(d), self._team._peer_ptrs(self._staging_off), N.ptr(src[pos : pos + m]),
+                    N.ptr(minus[pos : pos + m] if minus is not None else None), N.ptr(dst[pos : pos + m]),
+                    ctypes.c_longlong(m), ctypes.c_int(_DT[src.dtype]), ctypes.c_float(scale), ctypes.c_int(0),
+                    ctypes.c_int(0), N.stream_ptr()),
+                "team_allreduce_fp8",
+            )
+            pos += m
+
     def barrier(self, opts=None) -> Work:
         self._team.barrier()
         return _StreamWork(self, None)
