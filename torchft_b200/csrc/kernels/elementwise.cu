@@ -473,3 +473,56 @@ FTB200_API int ftb200_clip_coef(const float* sumsq, float max_norm, float* coef,
   clip_coef_kernel<<<1, 1, 0, st>>>(sumsq, max_norm, coef, norm_out);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+// See ftb200_noalloc.h.  The scratch lives in the library image; host code must not pass
+// the symbol itself to a kernel (on the host it is only a stand-in), so its device address
+// is looked up once per device and cached.
+#include "ftb200_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[FTB200_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_noalloc_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+FTB200_API int ftb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                          const void* dres, void* dx, void* dw, int T, int D, int accumulate_dw,
+                                          cudaStream_t st) {
+  if (T <= 0 || D <= 0 || dy == nullptr || x == nullptr || w == nullptr || rstd == nullptr || dx == nullptr ||
+      dw == nullptr)
+    return FTB200_E_BADARG;
+  if (D % 8) return FTB200_E_ALIGN;
+  if (D > 8192) return FTB200_E_TOOBIG;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FTB200_E_CUDA;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return FTB200_E_CUDA;
+  const int nblk = std::min(T, sms * 2);
+  if (static_cast<long long>(nblk) * D > static_cast<long long>(FTB200_NOALLOC_SCRATCH_FLOATS)) return FTB200_E_TOOBIG;
+  if (g_noalloc_scratch_addr[dev] == nullptr) {
+    // one-time set-up for this device (which is current): resolve the array's device address
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return FTB200_E_CUDA;
+    }
+    g_noalloc_scratch_addr[dev] = p;
+  }
+  float* scratch = g_noalloc_scratch_addr[dev];
+  const int D8 = D / 8;
+  const int threads = 256;
+  const int maxv = (D8 + threads - 1) / threads;
+  if (maxv <= 1)
+    rmsnorm_bwd_kernel<1><<<nblk, threads, 0, st>>>((const bf16x8*)dy, (const bf16x8*)x, (const bf16x8*)w, rstd,
+                                                    (const bf16x8*)dres, (bf16x8*)dx, scratch, T, D8);
+  else if (maxv <= 2)
+    rmsnorm_bwd_kernel<2><<<nblk, threads, 0, st>>>((const bf16x8*)dy, (const bf16x8*)x, (const bf16x8*)w, rstd,
+                                                    (const bf16x8*)dres, (bf16x8*)dx, scratch, T, D8);
+  else
+    rmsnorm_bwd_kernel<4><<<nblk, threads, 0, st>>>((const bf16x8*)dy, (const bf16x8*)x, (const bf16x8*)w, rstd,
+                                                    (const bf16x8*)dres, (bf16x8*)dx, scratch, T, D8);
+  colsum_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
