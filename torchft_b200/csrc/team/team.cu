@@ -65,32 +65,40 @@ __device__ __forceinline__ void allreduce_body(const TeamParams& tp, const Allre
 
   const long long slice = a.n / tp.world;
   const long long lo = slice * tp.rank;
-  for (long long i = tid * V; i < slice; i += nthreads * V) {
+  // u positions x world peers = up to 8 independent 16-byte peer loads in flight per thread
+  const int u = MAX_RANKS / tp.world;
+  for (long long i0 = tid * V; i0 < slice; i0 += nthreads * V * u) {
     uint4 raw[MAX_RANKS];
 #pragma unroll
     for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k < tp.world) {
-        const int p = (tp.rank + k) % tp.world;
+      const int pos = k / tp.world, pk = k - pos * tp.world;
+      const long long i = i0 + pos * nthreads * V;
+      if (pos < u && i < slice) {
+        const int p = (tp.rank + pk) % tp.world;
         raw[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.bufs[p]) + lo + i);
       }
     }
-    float acc[V];
+    for (int pos = 0; pos < u; ++pos) {
+      const long long i = i0 + pos * nthreads * V;
+      if (i >= slice) break;
+      float acc[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+      for (int e = 0; e < V; ++e) acc[e] = 0.f;
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k < tp.world) {
-        float f[V];
-        Vec<T>::load(reinterpret_cast<const T*>(&raw[k]), f);
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k / tp.world == pos) {
+          float f[V];
+          Vec<T>::load(reinterpret_cast<const T*>(&raw[k]), f);
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[e] += f[e];
+          for (int e = 0; e < V; ++e) acc[e] += f[e];
+        }
       }
-    }
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] *= a.scale;
-    for (int k = 0; k < tp.world; ++k) {
-      const int p = (tp.rank + k) % tp.world;
-      Vec<T>::store(reinterpret_cast<T*>(a.bufs[p]) + lo + i, acc);
+      for (int e = 0; e < V; ++e) acc[e] *= a.scale;
+      for (int k = 0; k < tp.world; ++k) {
+        const int p = (tp.rank + k) % tp.world;
+        Vec<T>::store(reinterpret_cast<T*>(a.bufs[p]) + lo + i, acc);
+      }
     }
   }
   if (!grid_arrive(tp, 3, &sh_code)) return;
@@ -133,9 +141,9 @@ __device__ __forceinline__ void allgather_body(const TeamParams& tp, const Gathe
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   uint4* dst = reinterpret_cast<uint4*>(a.dst);
-  // four independent 16-byte loads in flight per thread: NVLink latency is microseconds,
+  // eight independent 16-byte loads in flight per thread: NVLink latency is microseconds,
   // so bandwidth comes from bytes in flight
-  constexpr int U = 4;
+  constexpr int U = 8;
   for (long long i0 = tid; i0 < total; i0 += nthreads * U) {
     uint4 v[U];
     long long didx[U];
@@ -182,30 +190,37 @@ __device__ __forceinline__ void reduce_scatter_body(const TeamParams& tp, const 
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
   const long long lo = a.shard_elems * tp.rank;
   T* dst = reinterpret_cast<T*>(a.dst);
-  for (long long i = tid * V; i < a.shard_elems; i += nthreads * V) {
+  const int u = MAX_RANKS / tp.world;
+  for (long long i0 = tid * V; i0 < a.shard_elems; i0 += nthreads * V * u) {
     uint4 raw[MAX_RANKS];
 #pragma unroll
     for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k < tp.world) {
-        const int p = (tp.rank + k) % tp.world;
+      const int pos = k / tp.world, pk = k - pos * tp.world;
+      const long long i = i0 + pos * nthreads * V;
+      if (pos < u && i < a.shard_elems) {
+        const int p = (tp.rank + pk) % tp.world;
         raw[k] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.src[p]) + lo + i);
       }
     }
-    float acc[V];
+    for (int pos = 0; pos < u; ++pos) {
+      const long long i = i0 + pos * nthreads * V;
+      if (i >= a.shard_elems) break;
+      float acc[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+      for (int e = 0; e < V; ++e) acc[e] = 0.f;
 #pragma unroll
-    for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k < tp.world) {
-        float f[V];
-        Vec<T>::load(reinterpret_cast<const T*>(&raw[k]), f);
+      for (int k = 0; k < MAX_RANKS; ++k) {
+        if (k / tp.world == pos) {
+          float f[V];
+          Vec<T>::load(reinterpret_cast<const T*>(&raw[k]), f);
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[e] += f[e];
+          for (int e = 0; e < V; ++e) acc[e] += f[e];
+        }
       }
-    }
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] *= a.scale;
-    Vec<T>::store(dst + i, acc);
+      for (int e = 0; e < V; ++e) acc[e] *= a.scale;
+      Vec<T>::store(dst + i, acc);
+    }
   }
   if (!grid_arrive(tp, 3, &sh_code)) return;
   team_round(tp, 1, 1, &sh_code);
@@ -253,7 +268,7 @@ __global__ void __launch_bounds__(512) p2p_copy_kernel(const CopySeg* __restrict
 int grid_for_bytes(long long bytes) {
   // enough CTAs to saturate NVLink without starving concurrent compute of SMs
   long long g = bytes / (512 * 16 * 4);
-  g = std::max<long long>(1, std::min<long long>(g, 96));
+  g = std::max<long long>(1, std::min<long long>(g, 128));
   return static_cast<int>(g);
 }
 

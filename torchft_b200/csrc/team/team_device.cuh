@@ -42,6 +42,9 @@ __device__ __forceinline__ uint64_t ld_acquire_gpu(const uint64_t* p) {
 }
 
 // Bounded spin until *p == want.  Returns 0 on success, a FTB200_ST_* code otherwise.
+// Only system-scope waits (block 0's per-peer threads) look at the host-mapped abort word,
+// and only every 256 polls: it sits across PCIe and many concurrent readers are slow.
+// Every other waiter learns of an abort through the GO_ABORT value of its go-word.
 template <bool SYS>
 __device__ __forceinline__ int wait_equal(const uint64_t* p, uint64_t want, const TeamParams& tp, uint64_t t0) {
   uint32_t spins = 0;
@@ -49,10 +52,11 @@ __device__ __forceinline__ int wait_equal(const uint64_t* p, uint64_t want, cons
     const uint64_t v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
     if (v == want) return FTB200_ST_OK;
     if (!SYS && v == GO_ABORT) return FTB200_ST_ABORTED;
-    if ((++spins & 31u) == 0) {
-      if (tp.abort_word != nullptr && *tp.abort_word != 0) return FTB200_ST_ABORTED;
+    ++spins;
+    if ((spins & 15u) == 0) {
       if (ftb200::globaltimer_ns() - t0 > tp.timeout_ns) return FTB200_ST_TIMEOUT;
-      __nanosleep(64);
+      if (SYS && (spins & 255u) == 0 && tp.abort_word != nullptr && *tp.abort_word != 0) return FTB200_ST_ABORTED;
+      if (!SYS) __nanosleep(32);
     }
   }
 }
@@ -102,14 +106,19 @@ __device__ __forceinline__ bool grid_arrive(const TeamParams& tp, int counter_id
       const uint64_t t0 = ftb200::globaltimer_ns();
       uint32_t spins = 0;
       while (ld_acquire_gpu(ctr) < gridDim.x) {
-        if ((++spins & 31u) == 0) {
-          if (tp.abort_word != nullptr && *tp.abort_word != 0) { code = FTB200_ST_ABORTED; break; }
+        ++spins;
+        if ((spins & 15u) == 0) {
           if (ftb200::globaltimer_ns() - t0 > tp.timeout_ns) { code = FTB200_ST_TIMEOUT; break; }
-          __nanosleep(64);
+          if ((spins & 1023u) == 0 && tp.abort_word != nullptr && *tp.abort_word != 0) { code = FTB200_ST_ABORTED; break; }
         }
       }
       st_release_gpu(ctr, 0);  // re-arm for the next call (calls on one team are stream-ordered)
-      if (code != FTB200_ST_OK && tp.status != nullptr) atomicMax(tp.status, code);
+      if (code != FTB200_ST_OK) {
+        if (tp.status != nullptr) atomicMax(tp.status, code);
+        // release the blocks that will wait on the go-words of the rounds that follow
+        st_release_gpu(tp.local_sync + 0, GO_ABORT);
+        st_release_gpu(tp.local_sync + 1, GO_ABORT);
+      }
     }
     *sh_code = code;
   }

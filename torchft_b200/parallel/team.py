@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import ctypes
 import logging
+import os
 import threading
 from datetime import timedelta
 from typing import Dict, List, Optional, Tuple
@@ -34,6 +35,9 @@ logger = logging.getLogger(__name__)
 
 MAX_RANKS = 8
 _DT = {torch.bfloat16: 0, torch.float32: 1}
+# CTAs per peer-memory collective (0 = sized from the message, up to 128).  Collectives that
+# overlap with compute can be given fewer so that they leave SMs to the GEMMs.
+DEFAULT_CTAS = int(os.environ.get("FTB200_COMM_CTAS", "0"))
 
 
 class _TeamDesc(ctypes.Structure):
@@ -212,7 +216,7 @@ class SymmetricTeam:
         N.check(
             self.lib.ftb200_team_allreduce(ctypes.byref(d), self._peer_ptrs(off), N.ptr(user_in), N.ptr(user_out),
                                            ctypes.c_longlong(numel), ctypes.c_int(_DT[dtype]), ctypes.c_float(scale),
-                                           ctypes.c_int(int(zero_contribution)), ctypes.c_int(ctas), N.stream_ptr()),
+                                           ctypes.c_int(int(zero_contribution)), ctypes.c_int(ctas or DEFAULT_CTAS), N.stream_ptr()),
             "team_allreduce",
         )
 
@@ -220,7 +224,7 @@ class SymmetricTeam:
         d = self._desc()
         N.check(
             self.lib.ftb200_team_allgather(ctypes.byref(d), self._peer_ptrs(shard_off), N.ptr(dst),
-                                           ctypes.c_longlong(shard_bytes), ctypes.c_int(ctas), N.stream_ptr()),
+                                           ctypes.c_longlong(shard_bytes), ctypes.c_int(ctas or DEFAULT_CTAS), N.stream_ptr()),
             "team_allgather",
         )
 
@@ -230,7 +234,7 @@ class SymmetricTeam:
         N.check(
             self.lib.ftb200_team_reduce_scatter(ctypes.byref(d), self._peer_ptrs(full_off), N.ptr(dst),
                                                 ctypes.c_longlong(shard_elems), ctypes.c_int(_DT[dtype]),
-                                                ctypes.c_float(scale), ctypes.c_int(ctas), N.stream_ptr()),
+                                                ctypes.c_float(scale), ctypes.c_int(ctas or DEFAULT_CTAS), N.stream_ptr()),
             "team_reduce_scatter",
         )
 
