@@ -1,0 +1,114 @@
+#!/usr/bin/env python
+"""Fault-tolerant DDP example: a LeNet-style CNN on synthetic 3x32x32 images.
+
+Start a lighthouse, then one process (group) per replica:
+
+    python -m torchft_b200.lighthouse_cli --min_replicas 1 --join_timeout_ms 1000 &
+    TORCHFT_LIGHTHOUSE=http://localhost:29510 REPLICA_GROUP_ID=0 NUM_REPLICA_GROUPS=2 \
+        torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 1 --master-port 29600 train_ddp.py
+    TORCHFT_LIGHTHOUSE=http://localhost:29510 REPLICA_GROUP_ID=1 NUM_REPLICA_GROUPS=2 \
+        torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 1 --master-port 29601 train_ddp.py
+
+Kill either trainer and restart it: it rejoins the quorum, copies the weights from the
+surviving replica and continues; the survivor never stops.  ``USE_PEER=1`` on GPUs of one
+NVSwitch domain selects the NVLink peer-memory process group and state transfer.
+Counterpart of the reference's train_ddp.py (CIFAR-10 replaced by seeded synthetic data).
+"""
+
+import logging
+import os
+import sys
+from datetime import timedelta
+
+import torch
+from torch import nn, optim
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from torchft_b200 import DistributedDataParallel, DistributedSampler, Manager, Optimizer, ProcessGroupGloo, ProcessGroupNCCL
+from torchft_b200.checkpointing.pg_transport import PGTransport
+from torchft_b200.models.lenet import LeNet
+
+logging.basicConfig(level=logging.INFO)
+
+
+class SyntheticImages(torch.utils.data.Dataset):
+    def __init__(self, n: int = 8192, seed: int = 0) -> None:
+        g = torch.Generator().manual_seed(seed)
+        self.x = torch.randn(n, 3, 32, 32, generator=g)
+        self.y = torch.randint(0, 10, (n,), generator=g)
+
+    def __len__(self) -> int:
+        return len(self.x)
+
+    def __getitem__(self, i):
+        return self.x[i], self.y[i]
+
+
+def main() -> None:
+    replica_group = int(os.environ.get("REPLICA_GROUP_ID", 0))
+    num_groups = int(os.environ.get("NUM_REPLICA_GROUPS", 2))
+    steps = int(os.environ.get("STEPS", 100))
+    use_cuda = torch.cuda.is_available()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+
+    data = SyntheticImages()
+    sampler = DistributedSampler(data, replica_rank=replica_group, num_replica_groups=num_groups, group_rank=0,
+                                 num_replicas=1, shuffle=True)
+    loader = torch.utils.data.DataLoader(data, batch_size=64, sampler=sampler, num_workers=0)
+
+    model = LeNet().to(device)
+    opt = optim.SGD(model.parameters(), lr=1e-3, momentum=0.9)
+
+    def load_state_dict(sd):
+        model.load_state_dict(sd["model"])
+        opt.load_state_dict(sd["optim"])
+
+    def state_dict():
+        return {"model": model.state_dict(), "optim": opt.state_dict()}
+
+    timeout = timedelta(seconds=30)
+    if use_cuda and os.environ.get("USE_PEER", "0") == "1":
+        from torchft_b200.checkpointing.p2p_transport import P2PTransport
+        from torchft_b200.parallel.team import ProcessGroupB200
+
+        pg = ProcessGroupB200(timeout=timeout, device=device)
+        transport = P2PTransport(timeout=timeout, device=device, state_dict=state_dict)
+    else:
+        pg = ProcessGroupNCCL(timeout=timeout) if use_cuda else ProcessGroupGloo(timeout=timeout)
+        transport = PGTransport(pg, timeout=timeout, device=device)
+
+    manager = Manager(
+        pg=pg,
+        min_replica_size=1,
+        load_state_dict=load_state_dict,
+        state_dict=state_dict,
+        replica_id=f"train_ddp_{replica_group}",
+        timeout=timeout,
+        checkpoint_transport=transport,
+    )
+    ddp = DistributedDataParallel(manager, model)
+    optimizer = Optimizer(manager, opt)
+    criterion = nn.CrossEntropyLoss()
+
+    while manager.current_step() < steps:
+        sampler.set_epoch(manager.current_step())
+        for x, y in loader:
+            x, y = x.to(device), y.to(device)
+            optimizer.zero_grad()          # joins the quorum
+            loss = criterion(ddp(x), y)
+            loss.backward()                # bucketed gradients are averaged through the manager
+            optimizer.step()               # applied only if the step commits
+            if manager.current_step() % 10 == 0:
+                print(f"[{replica_group}] step={manager.current_step()} batches={manager.batches_committed()} "
+                      f"participants={manager.num_participants()} loss={loss.item():.4f}", flush=True)
+            # a durable checkpoint would save state_dict(), manager.state_dict() and the loader position here
+            if manager.current_step() >= steps:
+                break
+    manager.shutdown()
+
+
+if __name__ == "__main__":
+    main()

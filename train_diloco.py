@@ -1,0 +1,101 @@
+#!/usr/bin/env python
+"""(Streaming) DiLoCo example: an MLP split into fragments, AdamW inside, Nesterov SGD outside.
+
+    python -m torchft_b200.lighthouse_cli --min_replicas 1 --join_timeout_ms 1000 &
+    TORCHFT_LIGHTHOUSE=http://localhost:29510 REPLICA_GROUP_ID=0 NUM_REPLICA_GROUPS=2 USE_STREAMING=1 \
+        torchrun --standalone --local-addr 127.0.0.1 --nproc-per-node 1 --master-port 29600 train_diloco.py
+
+Each replica takes ``sync_every`` local steps between synchronisations; with
+``USE_STREAMING=1`` the model is cut into two fragments that synchronise alternately and
+whose allreduce starts ``fragment_sync_delay`` steps early.  ``QUANTIZE=1`` sends the
+pseudo-gradients as block-scaled fp8.  Counterpart of the reference's train_diloco.py.
+"""
+
+import logging
+import os
+import sys
+from datetime import timedelta
+
+import torch
+from torch import nn, optim
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from torchft_b200 import Manager, ProcessGroupGloo, ProcessGroupNCCL
+from torchft_b200.checkpointing.http_transport import HTTPTransport
+from torchft_b200.local_sgd import DiLoCo
+
+logging.basicConfig(level=logging.INFO)
+
+
+def build_model(hidden: int = 256, layers: int = 4) -> nn.Sequential:
+    blocks = [nn.Sequential(nn.Linear(3 * 32 * 32 if i == 0 else hidden, hidden), nn.ReLU()) for i in range(layers)]
+    blocks.append(nn.Sequential(nn.Linear(hidden, 10)))
+    return nn.Sequential(*blocks)
+
+
+def main() -> None:
+    replica_group = int(os.environ.get("REPLICA_GROUP_ID", 0))
+    steps = int(os.environ.get("STEPS", 200))
+    streaming = os.environ.get("USE_STREAMING", "0") == "1"
+    quantize = os.environ.get("QUANTIZE", "0") == "1"
+    use_cuda = torch.cuda.is_available()
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(device)
+
+    torch.manual_seed(0)  # identical initial weights on every replica
+    model = build_model().to(device)
+    if streaming:
+        half = len(model) // 2
+        fragments = [model[:half], model[half:]]
+    else:
+        fragments = [model]
+
+    inner = optim.AdamW(model.parameters(), lr=4e-4, weight_decay=0.1, betas=(0.9, 0.95))
+    outers = [optim.SGD(f.parameters(), lr=0.7, momentum=0.9, nesterov=True) for f in fragments]
+
+    def load_state_dict(sd):
+        model.load_state_dict(sd["model"])
+        inner.load_state_dict(sd["inner_optim"])
+
+    def state_dict():
+        return {"model": model.state_dict(), "inner_optim": inner.state_dict()}
+
+    timeout = timedelta(seconds=30)
+    if use_cuda and os.environ.get("USE_PEER", "0") == "1":
+        from torchft_b200.parallel.team import ProcessGroupB200
+
+        pg = ProcessGroupB200(timeout=timeout, device=device)
+    else:
+        pg = ProcessGroupNCCL(timeout=timeout) if use_cuda else ProcessGroupGloo(timeout=timeout)
+    manager = Manager(
+        pg=pg,
+        min_replica_size=1,
+        load_state_dict=load_state_dict,
+        state_dict=state_dict,
+        replica_id=f"train_diloco_{replica_group}",
+        timeout=timeout,
+        use_async_quorum=False,  # DiLoCo heals synchronously, before the pseudo-gradient is formed
+        checkpoint_transport=HTTPTransport(timeout=timeout, num_chunks=0),
+    )
+    criterion = nn.CrossEntropyLoss()
+    g = torch.Generator().manual_seed(1000 + replica_group)
+    with DiLoCo(manager, fragments, inner, outers, sync_every=20 if streaming else 20,
+                fragment_sync_delay=5 if streaming else 0, should_quantize=quantize,
+                backup_device=device if use_cuda else None) as diloco:
+        for step in range(steps):
+            x = torch.randn(64, 3 * 32 * 32, generator=g).to(device)
+            y = torch.randint(0, 10, (64,), generator=g).to(device)
+            inner.zero_grad()
+            loss = criterion(model(x), y)
+            loss.backward()
+            inner.step()  # DiLoCo's hooks run the quorum / allreduce / outer step when due
+            if step % 20 == 0:
+                print(f"[{replica_group}] local_step={step} manager_step={manager.current_step()} loss={loss.item():.4f}",
+                      flush=True)
+    manager.shutdown()
+
+
+if __name__ == "__main__":
+    main()
