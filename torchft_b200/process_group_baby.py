@@ -59,7 +59,10 @@ _OPTS = {
 
 
 def _op_name(op) -> str:
-    return str(op).split(".")[-1]
+    for name in ("SUM", "AVG", "PRODUCT", "MIN", "MAX", "BAND", "BOR", "BXOR"):
+        if op == getattr(ReduceOp, name):
+            return name
+    raise ValueError(f"unsupported reduce op {op}")
 
 
 def _pack_opts(opts) -> Optional[Tuple[str, Dict[str, object]]]:
@@ -244,10 +247,12 @@ class ProcessGroupBaby(ProcessGroup):
     def _pump(self, pipe: _MonitoredPipe) -> None:
         while True:
             try:
-                op_id, err = pipe.recv(timedelta(days=365))
-            except (EOFError, OSError, TimeoutError, TypeError, ValueError):
-                break
-            except Exception:
+                op_id, err = pipe.recv(timedelta(seconds=1))
+            except TimeoutError:
+                if pipe.closed():
+                    break
+                continue
+            except (EOFError, OSError, TypeError, ValueError):
                 break
             with self._lock:
                 w = self._works.pop(op_id, None)
