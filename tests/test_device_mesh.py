@@ -1,0 +1,55 @@
+"""ManagedDeviceMesh over real gloo ranks (spawned processes): the replicate dimension is
+answered by the manager, the other dimensions by a real DeviceMesh."""
+import os
+import pickle
+from unittest.mock import MagicMock
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _worker(rank: int, world: int, port: int) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torchft_b200.device_mesh import ManagedDeviceMesh, ft_init_device_mesh
+        from torchft_b200.manager import Manager
+        from torchft_b200.process_group import ProcessGroupGloo
+
+        manager = MagicMock(spec=Manager)
+        manager._pg = ProcessGroupGloo()
+        manager.num_participants.return_value = 0
+        mesh = ft_init_device_mesh(device_type="cpu", mesh_shape=(2, world), mesh_dim_names=("dp_replicate", "dp_shard"),
+                                   replicate_dim=0, manager=manager)
+        assert mesh.ndim == 2
+        assert mesh.size(1) == world and mesh.get_local_rank("dp_shard") == rank
+        assert mesh["dp_shard"].size() == world
+        for n in (0, 1, 2):  # before any quorum the replicate size reads as 1
+            manager.num_participants.return_value = n
+            assert mesh.size() == world * max(n, 1)
+            assert mesh.size(0) == max(n, 1)
+        manager.num_participants.return_value = 2
+        assert mesh.shape == (2, world)
+        rep = mesh["dp_replicate"]
+        assert isinstance(rep, ManagedDeviceMesh) and rep.size() == 2
+        assert mesh.get_group("dp_replicate") is mesh.replicate_pg
+        both = mesh[("dp_replicate", "dp_shard")]
+        assert both.size() == 2 * world
+        flat = mesh._flatten("dp")
+        assert flat.size() == 2 * world
+        assert mesh["dp"] is flat
+        coord = mesh.get_coordinate()
+        assert coord is not None and len(coord) == 2 and coord[1] == rank
+        clone = pickle.loads(pickle.dumps(mesh))
+        assert clone.replicate_pg is mesh.replicate_pg
+        assert hash(mesh) == hash(mesh) and "ManagedDeviceMesh" in repr(mesh)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_managed_device_mesh_gloo():
+    world = 2
+    port = 29000 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port), nprocs=world, join=True)

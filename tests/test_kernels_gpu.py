@@ -190,3 +190,18 @@ def test_engine_matches_autograd_gpu():
         tr.optimizer_step()
         l1 = tr.forward_backward(tokens, targets).item()
     assert l1 < l0
+
+
+def test_linear_swiglu_fused_epilogue():
+    torch.manual_seed(11)
+    T, Kd, Fd = 384, 256, 352  # 2F = 704 = 22 * 32
+    x = torch.randn(T, Kd, device=DEV).bfloat16()
+    w = (torch.randn(2 * Fd, Kd, device=DEV) * 0.1).bfloat16()
+    gu = torch.empty(T, 2 * Fd, device=DEV, dtype=torch.bfloat16)
+    s = torch.empty(T, Fd, device=DEV, dtype=torch.bfloat16)
+    K.linear_swiglu_fwd(x, w, gu, s)
+    K.check_status(x.device)
+    ref_gu = x.float() @ w.float().t()
+    assert rel_err(gu, ref_gu) < 1e-2
+    assert rel_err(s, K.ref_swiglu_fwd(gu)) < 1e-2
+    assert rel_err(s, torch.nn.functional.silu(ref_gu[:, 0::2]) * ref_gu[:, 1::2]) < 2e-2

@@ -152,56 +152,73 @@ __global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_b
 
 // ------------------------------------------------------------------ RoPE (interleaved pairs)
 // buf rows are [n_rot_heads * Dh | untouched tail]; cs = [S, Dh/2] of (cos, sin).
-__global__ void rope_kernel(__nv_bfloat162* __restrict__ buf, const float2* __restrict__ cs, int64_t T, int S,
-                            int n_heads, int Dh2, int64_t row_stride2, float sin_sign) {
+// One thread rotates 8 consecutive elements (4 pairs): one 16-byte load/store of data and
+// two 16-byte loads of the table.
+__global__ void rope_kernel(bf16x8* __restrict__ buf, const float4* __restrict__ cs, int64_t T, int S, int n_heads,
+                            int Dh8, int64_t row_stride8, float sin_sign) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const int64_t per_row = static_cast<int64_t>(n_heads) * Dh2;
+  const int64_t per_row = static_cast<int64_t>(n_heads) * Dh8;
   if (idx >= T * per_row) return;
   const int64_t t = idx / per_row;
   const int r = static_cast<int>(idx - t * per_row);
-  const int pair = r % Dh2;
+  const int v = r % Dh8;  // which group of 4 pairs inside the head
   const int pos = static_cast<int>(t % S);
-  const float2 c = cs[static_cast<int64_t>(pos) * Dh2 + pair];
-  __nv_bfloat162* p = buf + t * row_stride2 + r;
-  const float2 v = __bfloat1622float2(*p);
-  const float sn = c.y * sin_sign;
-  *p = __floats2bfloat162_rn(v.x * c.x - v.y * sn, v.x * sn + v.y * c.x);
+  const float4* c = cs + (static_cast<int64_t>(pos) * Dh8 + v) * 2;  // 4 (cos, sin) pairs = 2 float4
+  const float4 c0 = c[0], c1 = c[1];
+  const float cosv[4] = {c0.x, c0.z, c1.x, c1.z};
+  const float sinv[4] = {c0.y * sin_sign, c0.w * sin_sign, c1.y * sin_sign, c1.w * sin_sign};
+  bf16x8* p = buf + t * row_stride8 + r;
+  float f[8];
+  unpack8(*p, f);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float a = f[2 * e], b = f[2 * e + 1];
+    f[2 * e] = a * cosv[e] - b * sinv[e];
+    f[2 * e + 1] = a * sinv[e] + b * cosv[e];
+  }
+  *p = pack8(f);
 }
 
 // ------------------------------------------------------------------ SwiGLU
-// gu rows are [gate(F) | up(F)]; out = silu(gate) * up
-__global__ void swiglu_fwd_kernel(const bf16x8* __restrict__ gu, bf16x8* __restrict__ out, int64_t T, int F8) {
-  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= T * F8) return;
-  const int64_t t = idx / F8;
-  const int i = static_cast<int>(idx - t * F8);
-  float g[8], u[8];
-  unpack8(gu[t * 2 * F8 + i], g);
-  unpack8(gu[t * 2 * F8 + F8 + i], u);
-#pragma unroll
-  for (int e = 0; e < 8; ++e) g[e] = g[e] / (1.f + __expf(-g[e])) * u[e];
-  out[idx] = pack8(g);
+// gu rows hold interleaved (gate_j, up_j) pairs: [g0 u0 g1 u1 ...] (2F values);
+// out[j] = silu(g_j) * u_j.  One thread handles 4 pairs.
+__device__ __forceinline__ void store4_bf16(__nv_bfloat16* p, const float* f) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(f[0], f[1]), hi = __floats2bfloat162_rn(f[2], f[3]);
+  uint2 o;
+  o.x = *reinterpret_cast<uint32_t*>(&lo);
+  o.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = o;
 }
 
-// dgu = [ds * u * dsilu(g) | ds * silu(g)]   (may alias gu: in place)
-__global__ void swiglu_bwd_kernel(const bf16x8* __restrict__ ds, const bf16x8* gu, bf16x8* dgu, int64_t T, int F8) {
+__global__ void swiglu_fwd_kernel(const bf16x8* __restrict__ gu, __nv_bfloat16* __restrict__ out, int64_t n8) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= T * F8) return;
-  const int64_t t = idx / F8;
-  const int i = static_cast<int>(idx - t * F8);
-  float g[8], u[8], d[8], dg[8], du[8];
-  unpack8(gu[t * 2 * F8 + i], g);
-  unpack8(gu[t * 2 * F8 + F8 + i], u);
-  unpack8(ds[idx], d);
+  if (idx >= n8) return;
+  float f[8], o[4];
+  unpack8(gu[idx], f);
 #pragma unroll
-  for (int e = 0; e < 8; ++e) {
-    const float sg = 1.f / (1.f + __expf(-g[e]));
-    const float silu = g[e] * sg;
-    dg[e] = d[e] * u[e] * (sg + silu * (1.f - sg));
-    du[e] = d[e] * silu;
+  for (int e = 0; e < 4; ++e) o[e] = f[2 * e] / (1.f + __expf(-f[2 * e])) * f[2 * e + 1];
+  store4_bf16(out + idx * 4, o);
+}
+
+// dgu pair = (ds * u * dsilu(g), ds * silu(g))   (may alias gu: in place)
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ ds, const bf16x8* gu, bf16x8* dgu, int64_t n8) {
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= n8) return;
+  float f[8], o[8];
+  unpack8(gu[idx], f);
+  const uint2 raw = *reinterpret_cast<const uint2*>(ds + idx * 4);
+  const float2 d01 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 d23 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  const float d[4] = {d01.x, d01.y, d23.x, d23.y};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float g = f[2 * e], u = f[2 * e + 1];
+    const float sg = 1.f / (1.f + __expf(-g));
+    const float silu = g * sg;
+    o[2 * e] = d[e] * u * (sg + silu * (1.f - sg));
+    o[2 * e + 1] = d[e] * silu;
   }
-  dgu[t * 2 * F8 + i] = pack8(dg);
-  dgu[t * 2 * F8 + F8 + i] = pack8(du);
+  dgu[idx] = pack8(o);
 }
 
 // ------------------------------------------------------------------ cross-entropy
@@ -409,23 +426,24 @@ FTB200_API int ftb200_rmsnorm_bwd(const void* dy, const void* x, const void* w, 
 // Rotates the first n_heads heads of every row in place.  backward != 0 applies the inverse rotation.
 FTB200_API int ftb200_rope(void* buf, const float* cos_sin, long long T, int S, int n_heads, int head_dim,
                            long long row_stride, int backward, cudaStream_t st) {
-  if (head_dim % 2 || row_stride % 2) return FTB200_E_ALIGN;
-  const int64_t total = T * n_heads * (head_dim / 2);
-  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((__nv_bfloat162*)buf, (const float2*)cos_sin, T, S, n_heads,
-                                                    head_dim / 2, row_stride / 2, backward ? -1.f : 1.f);
+  if (head_dim % 8 || row_stride % 8 || (reinterpret_cast<uintptr_t>(buf) & 15)) return FTB200_E_ALIGN;
+  const int64_t total = T * n_heads * (head_dim / 8);
+  rope_kernel<<<grid_for(total, 256), 256, 0, st>>>((bf16x8*)buf, (const float4*)cos_sin, T, S, n_heads, head_dim / 8,
+                                                    row_stride / 8, backward ? -1.f : 1.f);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
 FTB200_API int ftb200_swiglu_fwd(const void* gu, void* out, long long T, int F, cudaStream_t st) {
-  if (F % 8) return FTB200_E_ALIGN;
-  swiglu_fwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const bf16x8*)gu, (bf16x8*)out, T, F / 8);
+  if (F % 4) return FTB200_E_ALIGN;
+  const int64_t n8 = T * (F / 4);
+  swiglu_fwd_kernel<<<grid_for(n8, 256), 256, 0, st>>>((const bf16x8*)gu, (__nv_bfloat16*)out, n8);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
 FTB200_API int ftb200_swiglu_bwd(const void* ds, const void* gu, void* dgu, long long T, int F, cudaStream_t st) {
-  if (F % 8) return FTB200_E_ALIGN;
-  swiglu_bwd_kernel<<<grid_for(T * (F / 8), 256), 256, 0, st>>>((const bf16x8*)ds, (const bf16x8*)gu, (bf16x8*)dgu, T,
-                                                               F / 8);
+  if (F % 4) return FTB200_E_ALIGN;
+  const int64_t n8 = T * (F / 4);
+  swiglu_bwd_kernel<<<grid_for(n8, 256), 256, 0, st>>>((const __nv_bfloat16*)ds, (const bf16x8*)gu, (bf16x8*)dgu, n8);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 

@@ -101,6 +101,9 @@ struct GemmParams {
   long long ldc;
   void* C;
   int* status;
+  // fused SwiGLU: output columns are (gate, up) pairs; aux[row, j] = silu(C[row,2j]) * C[row,2j+1]
+  void* aux;
+  long long ld_aux;
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -313,7 +316,23 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
 #pragma unroll
                   for (int e = 0; e < 8; ++e) f[e] += o[e];
                 }
-                reinterpret_cast<ftb200::bf16x8*>(dst)[j] = ftb200::pack8(f);
+                const ftb200::bf16x8 packed = ftb200::pack8(f);
+                reinterpret_cast<ftb200::bf16x8*>(dst)[j] = packed;
+                if (p.aux != nullptr) {
+                  // activation of the rounded values, so that a later recompute from C agrees
+                  float g[8];
+                  ftb200::unpack8(packed, g);
+                  float sv[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) sv[e] = g[2 * e] / (1.f + __expf(-g[2 * e])) * g[2 * e + 1];
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(sv[0], sv[1]), hi = __floats2bfloat162_rn(sv[2], sv[3]);
+                  uint2 o2;
+                  o2.x = *reinterpret_cast<uint32_t*>(&lo);
+                  o2.y = *reinterpret_cast<uint32_t*>(&hi);
+                  __nv_bfloat16* adst =
+                      reinterpret_cast<__nv_bfloat16*>(p.aux) + static_cast<long long>(row) * p.ld_aux + (col0 >> 1) + 4 * j;
+                  *reinterpret_cast<uint2*>(adst) = o2;
+                }
               }
             } else {
 #pragma unroll
@@ -379,9 +398,9 @@ int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols
 }  // namespace
 
 // Same arguments as ftb200_gemm_bf16; pairs of CTAs cooperate on 256x256 tiles.
-FTB200_API int ftb200_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major,
-                                     int b_mn_major, long long lda, long long ldb, long long ldc, int flags, int* status,
-                                     int max_ctas, cudaStream_t stream) {
+static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, int b_mn_major,
+                          long long lda, long long ldb, long long ldc, int flags, int* status, int max_ctas, void* aux,
+                          long long ld_aux, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || A == nullptr || B == nullptr || C == nullptr) return FTB200_E_BADARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return FTB200_E_ALIGN;
@@ -415,10 +434,28 @@ FTB200_API int ftb200_gemm_bf16_2cta(const void* A, const void* B, void* C, int 
   p.ldc = ldc;
   p.C = C;
   p.status = status;
+  p.aux = aux;
+  p.ld_aux = ld_aux;
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   int ctas = ftb200::sm_count() & ~1;
   if (max_ctas > 0 && max_ctas < ctas) ctas = std::max(2, max_ctas & ~1);
   if (2 * tiles < ctas) ctas = 2 * tiles;
   gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+FTB200_API int ftb200_gemm_bf16_2cta(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major,
+                                     int b_mn_major, long long lda, long long ldb, long long ldc, int flags, int* status,
+                                     int max_ctas, cudaStream_t stream) {
+  return gemm_2cta_impl(A, B, C, M, N, K, a_mn_major, b_mn_major, lda, ldb, ldc, flags, status, max_ctas, nullptr, 0, stream);
+}
+
+// Forward GEMM of a gated MLP with the activation fused into the epilogue: B's rows are
+// interleaved (gate_0, up_0, gate_1, up_1, ...), C [M,N] receives the pre-activations and
+// aux [M,N/2] receives silu(gate) * up.  bf16 output, N a multiple of 32, no accumulate.
+FTB200_API int ftb200_gemm_bf16_swiglu(const void* A, const void* B, void* C, void* aux, int M, int N, int K, long long lda,
+                                       long long ldb, long long ldc, long long ld_aux, int* status, int max_ctas,
+                                       cudaStream_t stream) {
+  if (aux == nullptr || (N % 32) || (ldc & 7) || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 7)) return FTB200_E_ALIGN;
+  return gemm_2cta_impl(A, B, C, M, N, K, 0, 0, lda, ldb, ldc, 0, status, max_ctas, aux, ld_aux, stream);
 }

@@ -200,7 +200,7 @@ __device__ __forceinline__ void allreduce_fp8_body(const TeamParams& tp, const Q
 }
 
 template <typename T>
-__global__ void __launch_bounds__(512) allreduce_fp8_kernel(const TeamParams tp, const QuantAllreduceArgs a) {
+__global__ void __maxnreg__(72) allreduce_fp8_kernel(const TeamParams tp, const QuantAllreduceArgs a) {
   allreduce_fp8_body<T>(tp, a);
 }
 template <typename T>

@@ -115,7 +115,7 @@ __device__ __forceinline__ void allreduce_body(const TeamParams& tp, const Allre
 }
 
 template <typename T>
-__global__ void __launch_bounds__(512) allreduce_kernel(const TeamParams tp, const AllreduceArgs a) {
+__global__ void __maxnreg__(72) allreduce_kernel(const TeamParams tp, const AllreduceArgs a) {
   allreduce_body<T>(tp, a);
 }
 // Test vehicle: all ranks of a team emulated by ONE cooperative launch on one GPU
@@ -168,7 +168,7 @@ __device__ __forceinline__ void allgather_body(const TeamParams& tp, const Gathe
   team_round(tp, 1, 1, &sh_code);
 }
 
-__global__ void __launch_bounds__(512) allgather_kernel(const TeamParams tp, const GatherArgs a) { allgather_body(tp, a); }
+__global__ void __maxnreg__(72) allgather_kernel(const TeamParams tp, const GatherArgs a) { allgather_body(tp, a); }
 __global__ void __launch_bounds__(512) allgather_emul_kernel(const TeamParams* tps, const GatherArgs* as) {
   allgather_body(tps[blockIdx.y], as[blockIdx.y]);
 }
@@ -227,7 +227,7 @@ __device__ __forceinline__ void reduce_scatter_body(const TeamParams& tp, const 
 }
 
 template <typename T>
-__global__ void __launch_bounds__(512) reduce_scatter_kernel(const TeamParams tp, const ReduceScatterArgs a) {
+__global__ void __maxnreg__(72) reduce_scatter_kernel(const TeamParams tp, const ReduceScatterArgs a) {
   reduce_scatter_body<T>(tp, a);
 }
 template <typename T>

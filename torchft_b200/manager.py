@@ -647,6 +647,7 @@ class _ManagedWork(dist._Work):
             def chain(f: torch.futures.Future) -> object:
                 # runs once the collective is done; apply the recorded callbacks in order
                 with get_stream_context(stream):
+                    f.value()  # a failed collective fails the whole chain (reported by wrap_future)
                     cur: torch.futures.Future = f
                     for cb in callbacks:
                         nxt: torch.futures.Future = torch.futures.Future()

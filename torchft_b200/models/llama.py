@@ -11,6 +11,7 @@ Unit layout (bf16, every field a multiple of 8 elements so all views are 16-byte
 aligned)::
 
     layer unit : attn_norm[D] | wqkv[(Hq+2Hkv)*Dh, D] | wo[D, D] | ffn_norm[D] | wgu[2F, D] | wd[D, F]
+                 (rows of wgu interleave gate and up: gate_0, up_0, gate_1, up_1, ...)
     embed unit : tok_embeddings[V, D]
     head  unit : final_norm[D] | lm_head[V, D]
 
@@ -185,6 +186,7 @@ class LlamaEngine:
         self.qkv = [torch.empty(T, QKV, **bf) for _ in range(L)]
         self.att = [torch.empty(T, D, **bf) for _ in range(L)]
         self.gu = [torch.empty(T, 2 * Fd, **bf) for _ in range(L)]
+        self.s = [torch.empty(T, Fd, **bf) for _ in range(L)]  # silu(gate)*up, kept for the wd wgrad
         self.rstd1 = [torch.empty(T, **f32) for _ in range(L + 1)]
         self.rstd2 = [torch.empty(T, **f32) for _ in range(L)]
         # workspaces
@@ -235,9 +237,9 @@ class LlamaEngine:
             K.linear_fwd(self.att[l], W.wo, out=self.ws_proj)
             K.rmsnorm_fwd(self.x[l], W.ffn_norm, c.norm_eps, res=self.ws_proj, h_out=self.h[l], out=self.ws_n,
                           rstd=self.rstd2[l])
-            K.linear_fwd(self.ws_n, W.wgu, out=self.gu[l])
-            K.swiglu_fwd(self.gu[l], out=self.ws_s)
-            K.linear_fwd(self.ws_s, W.wd, out=self.ws_proj)
+            s_buf = self.s[l] if train else self.ws_s
+            K.linear_swiglu_fwd(self.ws_n, W.wgu, self.gu[l], s_buf)  # activation fused into the GEMM epilogue
+            K.linear_fwd(s_buf, W.wd, out=self.ws_proj)
             delta = self.ws_proj
         u = L + 1
         self.before_unit(u, False)
@@ -278,8 +280,7 @@ class LlamaEngine:
             self.before_unit(u, True)
             W, G = self._p(u), self._g(u)
             # ---- FFN
-            K.swiglu_fwd(self.gu[l], out=self.ws_s)
-            K.linear_wgrad(dy, self.ws_s, out=G.wd)
+            K.linear_wgrad(dy, self.s[l], out=G.wd)
             K.linear_dgrad(dy, W.wd, out=self.ws_ds)
             K.swiglu_bwd(self.ws_ds, self.gu[l], dgu=self.gu[l])
             K.rmsnorm_fwd(self.h[l], W.ffn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd2[l])
@@ -387,5 +388,5 @@ class TorchLlama(torch.nn.Module):
             x = x + a @ m.wo.t()
             n2 = self._norm(x, m.ffn_norm)
             gu = n2 @ m.wgu.t()
-            x = x + (F.silu(gu[..., : c.ffn_dim]) * gu[..., c.ffn_dim :]) @ m.wd.t()
+            x = x + (F.silu(gu[..., 0::2]) * gu[..., 1::2]) @ m.wd.t()
         return self._norm(x, self.final_norm) @ self.lm_head.t()

@@ -299,12 +299,13 @@ def rope_(buf: torch.Tensor, table: torch.Tensor, seq_len: int, n_heads: int, he
 
 
 def ref_swiglu_fwd(gu):
-    Fd = gu.shape[-1] // 2
-    g, u = gu[:, :Fd].float(), gu[:, Fd:].float()
+    """``gu`` rows are interleaved (gate, up) pairs."""
+    g, u = gu[:, 0::2].float(), gu[:, 1::2].float()
     return (F.silu(g) * u).to(gu.dtype)
 
 
 def swiglu_fwd(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``out[:, j] = silu(gu[:, 2j]) * gu[:, 2j+1]`` (interleaved gate/up columns)."""
     T, F2 = gu.shape
     Fd = F2 // 2
     if out is None:
@@ -317,11 +318,13 @@ def swiglu_fwd(gu: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
 
 
 def ref_swiglu_bwd(ds, gu):
-    Fd = gu.shape[-1] // 2
-    g, u, d = gu[:, :Fd].float(), gu[:, Fd:].float(), ds.float()
+    g, u, d = gu[:, 0::2].float(), gu[:, 1::2].float(), ds.float()
     sg = torch.sigmoid(g)
     silu = g * sg
-    return torch.cat([d * u * (sg + silu * (1 - sg)), d * silu], dim=1).to(gu.dtype)
+    out = torch.empty(gu.shape, dtype=torch.float32, device=gu.device)
+    out[:, 0::2] = d * u * (sg + silu * (1 - sg))
+    out[:, 1::2] = d * silu
+    return out.to(gu.dtype)
 
 
 def swiglu_bwd(ds: torch.Tensor, gu: torch.Tensor, dgu: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -334,6 +337,21 @@ def swiglu_bwd(ds: torch.Tensor, gu: torch.Tensor, dgu: Optional[torch.Tensor] =
         return dgu
     N.check(N.lib().ftb200_swiglu_bwd(ptr(ds), ptr(gu), ptr(dgu), c_ll(T), c_int(F2 // 2), stream_ptr()), "swiglu_bwd")
     return dgu
+
+
+def linear_swiglu_fwd(x: torch.Tensor, w_gu: torch.Tensor, gu_out: torch.Tensor, s_out: torch.Tensor) -> None:
+    """``gu_out = x @ w_gu^T`` and, from the same accumulator, ``s_out = silu(gate) * up``
+    where ``w_gu``'s rows (``gu_out``'s columns) interleave gate and up."""
+    T, Kd = x.shape
+    N2 = w_gu.shape[0]
+    if not x.is_cuda or N2 % 32 or GEMM_IMPL != "2cta":
+        gemm(x, w_gu, False, False, out=gu_out)
+        swiglu_fwd(gu_out, out=s_out)
+        return
+    rc = N.lib().ftb200_gemm_bf16_swiglu(
+        ptr(x), ptr(w_gu), ptr(gu_out), ptr(s_out), c_int(T), c_int(N2), c_int(Kd), c_ll(x.stride(0)), c_ll(w_gu.stride(0)),
+        c_ll(gu_out.stride(0)), c_ll(s_out.stride(0)), ptr(status_word(x.device)), c_int(0), stream_ptr())
+    N.check(rc, "gemm_bf16_swiglu")
 
 
 # --------------------------------------------------------------------------- cross-entropy
