@@ -174,8 +174,9 @@ def main() -> int:
         lighthouse, manager = make_ft_manager(rank, world, n_groups, shard, group_id, group_rank, dev, arena_bytes=arena)
 
     replica_alloc = manager._pg.alloc if (manager is not None and n_groups > 1) else None
+    # one logits chunk: the 2 GB of bf16 logits fit, and the head's wgrad then runs once with the full reduction depth
     trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234,
-                                  replica_alloc=replica_alloc)
+                                  replica_alloc=replica_alloc, logit_chunks=1)
     if manager is not None:
         manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 
