@@ -51,10 +51,15 @@ class _DualStackServer(ThreadingHTTPServer):
 
 
 def _leaf_to_cpu(v: object, pin: bool) -> object:
-    if isinstance(v, torch.Tensor) and v.device.type != "cpu":
-        out = torch.empty(v.shape, dtype=v.dtype, device="cpu", pin_memory=pin)
-        out.copy_(v, non_blocking=True)
-        return out
+    """Host snapshot of a leaf.  Tensors are always copied: what is staged must not change
+    when the trainer goes on mutating its weights (LocalSGD/DiLoCo take inner steps while a
+    peer is still fetching)."""
+    if isinstance(v, torch.Tensor):
+        if v.device.type != "cpu":
+            out = torch.empty(v.shape, dtype=v.dtype, device="cpu", pin_memory=pin)
+            out.copy_(v, non_blocking=True)
+            return out
+        return v.detach().clone()
     return v
 
 
@@ -149,6 +154,8 @@ class HTTPTransport(CheckpointTransport[T], Generic[T]):
             with torch.cuda.stream(self._stream):
                 leaves = [_leaf_to_cpu(v, self._pin) for v in leaves]
             self._stream.synchronize()
+        else:
+            leaves = [_leaf_to_cpu(v, False) for v in leaves]
         self._spec = spec
         if self._num_chunks > 0:
             self._chunks = [leaves[i :: self._num_chunks] for i in range(self._num_chunks)]

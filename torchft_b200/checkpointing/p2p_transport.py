@@ -62,10 +62,16 @@ class P2PTransport(HTTPTransport[T], Generic[T]):
         device: this rank's GPU
         state_dict: optional callable returning the receiver's current state dict; tensors
             whose shape and dtype match are filled in place
+        snapshot: publish device-side copies instead of the live tensors.  Needed when the
+            source keeps mutating its weights before the step commits (LocalSGD / DiLoCo
+            inner steps); FT-DDP / HSDP leave weights untouched until the commit and can
+            stay zero-copy
     """
 
-    def __init__(self, timeout: timedelta, device: torch.device, state_dict: Optional[Callable[[], T]] = None) -> None:
+    def __init__(self, timeout: timedelta, device: torch.device, state_dict: Optional[Callable[[], T]] = None,
+                 snapshot: bool = False) -> None:
         super().__init__(timeout=timeout, num_chunks=0)
+        self._snapshot = snapshot
         self._device = torch.device(device)
         self._state_dict_fn = state_dict
         self._keepalive: List[torch.Tensor] = []
@@ -79,7 +85,9 @@ class P2PTransport(HTTPTransport[T], Generic[T]):
         for v in leaves:
             if isinstance(v, torch.Tensor) and v.is_cuda:
                 c = v.detach()
-                if not c.is_contiguous():
+                if self._snapshot:
+                    c = c.clone(memory_format=torch.contiguous_format)
+                elif not c.is_contiguous():
                     c = c.contiguous()
                 keep.append(c)
                 out.append(_export(c))
