@@ -48,10 +48,15 @@ class EventInjector:
     def check(self, replica: int, rank: int, step: int, pg: Optional[FakeProcessGroupWrapper] = None) -> None:
         key = (replica, rank, step)
         with self._lock:
-            fail = key in self._fail
-            self._fail.discard(key)
-            far = key in self._fail_allreduce
-            self._fail_allreduce.discard(key)
+            # a replica that healed past the requested step still gets its failure: first check at or after it
+            due = [k for k in self._fail if k[0] == replica and k[1] == rank and step >= k[2]]
+            fail = bool(due)
+            for k in due:
+                self._fail.discard(k)
+            due = [k for k in self._fail_allreduce if k[0] == replica and k[1] == rank and step >= k[2]]
+            far = bool(due)
+            for k in due:
+                self._fail_allreduce.discard(k)
             bar = self._barriers.pop(key, None)
             if fail or far:
                 self.count += 1
