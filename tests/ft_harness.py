@@ -31,6 +31,8 @@ class EventInjector:
         self._fail: Set[Tuple[int, int, int]] = set()
         self._fail_allreduce: Set[Tuple[int, int, int]] = set()
         self._barriers: Dict[Tuple[int, int, int], threading.Barrier] = {}
+        self._gates: Set[Tuple[int, int]] = set()
+        self.rejoined = threading.Event()
         self.count = 0
 
     def fail_at(self, replica: int, step: int, rank: int = 0) -> "EventInjector":
@@ -40,6 +42,15 @@ class EventInjector:
     def fail_allreduce_at(self, replica: int, step: int, rank: int = 0) -> "EventInjector":
         self._fail_allreduce.add((replica, rank, step))
         return self
+
+    def gate_until_rejoin(self, replica: int, step: int) -> "EventInjector":
+        """``replica`` pauses at the first check at or after ``step`` until a restarted peer
+        has come back (keeps a fast survivor from finishing before the restart happens)."""
+        self._gates.add((replica, step))
+        return self
+
+    def notify_restarted(self) -> None:
+        self.rejoined.set()
 
     def barrier_at(self, replica: int, step: int, barrier: threading.Barrier, rank: int = 0) -> "EventInjector":
         self._barriers[(replica, rank, step)] = barrier
@@ -60,6 +71,11 @@ class EventInjector:
             bar = self._barriers.pop(key, None)
             if fail or far:
                 self.count += 1
+        gate = [g for g in self._gates if g[0] == replica and step >= g[1]]
+        if gate:
+            for g in gate:
+                self._gates.discard(g)
+            self.rejoined.wait(timeout=3)  # bounded: the peer may be the one that is waiting for us
         if fail:
             raise InjectedFailure(f"injected failure replica={replica} rank={rank} step={step}")
         if far:
@@ -91,6 +107,8 @@ class Runner:
 
     def run_replica(self) -> List[Dict[str, Any]]:
         for attempt in range(self.attempts):
+            if attempt > 0:
+                self.injector.notify_restarted()
             try:
                 return self._replica_main()
             except InjectedFailure as e:

@@ -123,7 +123,7 @@ def test_local_sgd_healthy():
 
 
 def test_local_sgd_recovery():
-    inj = EventInjector().fail_at(replica=1, step=2)
+    inj = EventInjector().fail_at(replica=1, step=2).gate_until_rejoin(replica=0, step=3)
     res, inj = _run(local_sgd_loop, injector=inj, min_replicas=1, total_syncs=5)
     assert inj.count == 1
     a, b = res[0][0]["state"], res[1][0]["state"]
@@ -139,7 +139,7 @@ def test_diloco_healthy(n_fragments, delay, alpha):
 
 
 def test_diloco_recovery_streaming():
-    inj = EventInjector().fail_at(replica=1, step=2)
+    inj = EventInjector().fail_at(replica=1, step=2).gate_until_rejoin(replica=0, step=3)
     res, inj = _run(diloco_loop, injector=inj, min_replicas=1, total_syncs=5, n_fragments=2, delay=1)
     assert inj.count == 1
     _assert_same_history(res)

@@ -87,7 +87,7 @@ def test_ddp_recovery_kill_and_heal(use_async_quorum):
     replica 1 dies at step 20 of 30 and heals from replica 0."""
     lh = LighthouseServer("[::]:0", 1, join_timeout_ms=100, heartbeat_timeout_ms=1000)
     try:
-        inj = EventInjector().fail_at(replica=1, step=20)
+        inj = EventInjector().fail_at(replica=1, step=20).gate_until_rejoin(replica=0, step=22)
         runners = [Runner(i, lh.address(), inj, None) for i in range(2)]  # type: ignore[arg-type]
         for r in runners:
             r.train_loop = lambda rank, store_port, runner: ddp_train_loop(rank, store_port, runner, total_steps=30,

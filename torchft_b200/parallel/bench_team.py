@@ -73,7 +73,11 @@ def main() -> None:
         n = int(mb * (1 << 20)) // es // (world * 8) * (world * 8)
         nbytes = n * es
         t = buf[:n]
-        x = torch.randn(n, device=dev).to(dtype)
+        xf = torch.randn(n, device=dev)
+        idx = torch.randint(0, n, (max(1, n // 1000),), device=dev)
+        xf[idx] *= 100.0  # 0.1 % outliers at x100
+        x = xf.to(dtype)
+        del xf
         rows = []
         off = pg._team.arena.contains(t)
         for c in a.ctas:
@@ -81,6 +85,23 @@ def main() -> None:
             rows.append(("allreduce", f"peer(ctas={c})", ms, 2 * (world - 1) / world))
         ms = _time(lambda: (dist.all_reduce(x), x.div_(world)), a.iters)
         rows.append(("allreduce", "nccl+div", ms, 2 * (world - 1) / world))
+        if n % (128 * world) == 0 and n * es <= (200 << 20) * 2:
+            # block-scaled fp8 on the wire, fused quantise/reduce/dequantise kernel; "bus_gbs" counts the
+            # bytes of the unquantised tensor, i.e. the effective bandwidth an unquantised allreduce would need
+            xq = x.clone()
+            ms = _time(lambda: pg.allreduce_fp8(xq, xq, 1.0 / world), a.iters)
+            rows.append(("allreduce", "peer-fp8(effective)", ms, 2 * (world - 1) / world))
+            ref = x.float().clone()
+            dist.all_reduce(ref)
+            ref /= world
+            y = x.clone()
+            pg.allreduce_fp8(y, y, 1.0 / world)
+            torch.cuda.synchronize()
+            err = ((y.float() - ref).abs().mean() / ref.abs().mean()).item()
+            mx = ((y.float() - ref).abs().max() / ref.abs().max()).item()
+            if rank == 0:
+                print(json.dumps({"op": "allreduce", "impl": "peer-fp8", "world": world, "mb": mb, "mean_rel_err": round(err, 5),
+                                  "max_abs_err_over_max": round(mx, 5)}), flush=True)
         shard = n // world
         sh = full_peer[:shard]
         for c in a.ctas:
