@@ -43,6 +43,7 @@ def _parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--shard-comm", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--no-ft", action="store_true", help="run without Manager/lighthouse (debug only)")
+    ap.add_argument("--no-fused-rs", action="store_true", help="separate reduce-scatter kernels instead of the GEMM-fused one")
     return ap.parse_args()
 
 
@@ -176,7 +177,7 @@ def main() -> int:
     replica_alloc = manager._pg.alloc if (manager is not None and n_groups > 1) else None
     # one logits chunk: the 2 GB of bf16 logits fit, and the head's wgrad then runs once with the full reduction depth
     trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234,
-                                  replica_alloc=replica_alloc, logit_chunks=1)
+                                  replica_alloc=replica_alloc, logit_chunks=1, fused_reduce_scatter=not args.no_fused_rs)
     if manager is not None:
         manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 
@@ -266,6 +267,7 @@ def main() -> int:
                 "l2": "working set per step (>100 GB of weights, optimizer state and activations) is far larger than L2",
                 "fault_tolerance": "off (debug)" if args.no_ft else "Manager quorum + should_commit every step",
                 "shard_comm": args.shard_comm if shard > 1 else "none",
+                "reduce_scatter": ("fused into the wgrad GEMM epilogue" if trainer.fused_rs else "separate kernel") if shard > 1 else "none",
             },
             "clocks": clocks,
             "e2e": {

@@ -104,6 +104,14 @@ struct GemmParams {
   // fused SwiGLU: output columns are (gate, up) pairs; aux[row, j] = silu(C[row,2j]) * C[row,2j+1]
   void* aux;
   long long ld_aux;
+  // fused reduce-scatter epilogue: C is not written locally; every 16-byte piece of the
+  // (contiguous, row-major) result goes to the rank that owns that slice of the flat
+  // gradient unit, into that rank's staging area for source rank `sc_src`.
+  int sc_world;                // 0 = off
+  int sc_src;
+  long long sc_shard;          // elements per shard (multiple of 8)
+  long long sc_off;            // element offset of C inside the flat unit (multiple of 8)
+  void* sc_peers[8];           // base of every rank's staging area (peer-mapped), [world][shard] elements
 };
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
@@ -304,7 +312,25 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
             }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-            if (full) {
+            if (full && p.sc_world > 0) {
+              // transfer overlaps the math tile by tile: plain 16-byte stores into peer memory
+              const long long flat0 = p.sc_off + static_cast<long long>(row) * p.ldc + col0;
+              long long owner = flat0 / p.sc_shard;
+              long long rem = flat0 - owner * p.sc_shard;
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float f[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+                if (rem >= p.sc_shard) {
+                  rem -= p.sc_shard;
+                  ++owner;
+                }
+                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.sc_peers[owner]);
+                *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(p.sc_src) * p.sc_shard + rem) = ftb200::pack8(f);
+                rem += 8;
+              }
+            } else if (full) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 float f[8];
@@ -398,10 +424,18 @@ int encode_2d(CUtensorMap* map, const void* base, long long rows, long long cols
 }  // namespace
 
 // Same arguments as ftb200_gemm_bf16; pairs of CTAs cooperate on 256x256 tiles.
+struct ScatterSpec {
+  int world = 0;
+  int src = 0;
+  long long shard = 0;
+  long long off = 0;
+  void* const* peers = nullptr;
+};
+
 static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, int b_mn_major,
                           long long lda, long long ldb, long long ldc, int flags, int* status, int max_ctas, void* aux,
-                          long long ld_aux, cudaStream_t stream) {
-  if (M <= 0 || N <= 0 || K <= 0 || A == nullptr || B == nullptr || C == nullptr) return FTB200_E_BADARG;
+                          long long ld_aux, cudaStream_t stream, const ScatterSpec* sc = nullptr) {
+  if (M <= 0 || N <= 0 || K <= 0 || A == nullptr || B == nullptr || (C == nullptr && sc == nullptr)) return FTB200_E_BADARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return FTB200_E_ALIGN;
   if ((reinterpret_cast<uintptr_t>(C) & 15)) return FTB200_E_ALIGN;
@@ -436,6 +470,18 @@ static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, i
   p.status = status;
   p.aux = aux;
   p.ld_aux = ld_aux;
+  p.sc_world = 0;
+  p.sc_src = 0;
+  p.sc_shard = 0;
+  p.sc_off = 0;
+  for (int i = 0; i < 8; ++i) p.sc_peers[i] = nullptr;
+  if (sc != nullptr) {
+    p.sc_world = sc->world;
+    p.sc_src = sc->src;
+    p.sc_shard = sc->shard;
+    p.sc_off = sc->off;
+    for (int i = 0; i < sc->world && i < 8; ++i) p.sc_peers[i] = sc->peers[i];
+  }
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   int ctas = ftb200::sm_count() & ~1;
   if (max_ctas > 0 && max_ctas < ctas) ctas = std::max(2, max_ctas & ~1);
@@ -458,4 +504,23 @@ FTB200_API int ftb200_gemm_bf16_swiglu(const void* A, const void* B, void* C, vo
                                        cudaStream_t stream) {
   if (aux == nullptr || (N % 32) || (ldc & 7) || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 7)) return FTB200_E_ALIGN;
   return gemm_2cta_impl(A, B, C, M, N, K, 0, 0, lda, ldb, ldc, 0, status, max_ctas, aux, ld_aux, stream);
+}
+
+// GEMM whose epilogue is the reduce-scatter's transfer: the [M,N] result (row-major, row
+// stride N) is one field of a flat gradient unit that `world` ranks shard evenly; each
+// 16-byte piece is stored straight into the owner rank's staging area
+// (peers[owner] + src_rank * shard_elems + offset-in-shard) over NVLink while the tensor
+// cores work on the next tile.  A team round and a local sum over the `world` staging
+// slices (ftb200_team_reduce_scatter on local pointers) finish the reduce-scatter.
+// N must be a multiple of 32; shard_elems and unit_off multiples of 8.
+FTB200_API int ftb200_gemm_bf16_scatter(const void* A, const void* B, int M, int N, int K, int a_mn_major, int b_mn_major,
+                                        long long lda, long long ldb, void* const* peers, int world, int src_rank,
+                                        long long shard_elems, long long unit_off, int* status, int max_ctas,
+                                        cudaStream_t stream) {
+  if (peers == nullptr || world < 1 || world > 8 || src_rank < 0 || src_rank >= world) return FTB200_E_BADARG;
+  if ((N % 32) || (shard_elems % 8) || (unit_off % 8)) return FTB200_E_ALIGN;
+  if (unit_off + static_cast<long long>(M) * N > shard_elems * world) return FTB200_E_TOOBIG;
+  ScatterSpec sc;
+  sc.world = world; sc.src = src_rank; sc.shard = shard_elems; sc.off = unit_off; sc.peers = peers;
+  return gemm_2cta_impl(A, B, nullptr, M, N, K, a_mn_major, b_mn_major, lda, ldb, N, 0, status, max_ctas, nullptr, 0, stream, &sc);
 }

@@ -70,44 +70,96 @@ __device__ __forceinline__ void decode4(uint32_t bits, float scale, float* f) {
   f[0] = v.x * scale; f[1] = v.y * scale; f[2] = v.z * scale; f[3] = v.w * scale;
 }
 
-// One warp quantises one block: lane l owns elements 4l..4l+3.
-__device__ __forceinline__ void quantize_block(const float* f, int lane, uint32_t* codes, float* scales, long long blk) {
-  float amax = fmaxf(fmaxf(fabsf(f[0]), fabsf(f[1])), fmaxf(fabsf(f[2]), fabsf(f[3])));
-  amax = ftb200::warp_max(amax);
+// Eight lanes quantise one 128-element block (16 consecutive elements per lane), so a warp
+// handles four blocks at a time and the abs-max needs three shuffles.
+constexpr int EPL = 16;                 // elements per lane
+constexpr int LPB = QB / EPL;           // lanes per block (8)
+constexpr int BPW = 32 / LPB;           // blocks per warp iteration (4)
+
+template <typename T>
+__device__ __forceinline__ void load16(const T* p, float* f) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) load4<T>(p + 4 * k, f + 4 * k);
+}
+template <typename T>
+__device__ __forceinline__ void store16(T* p, const float* f) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) store4<T>(p + 4 * k, f + 4 * k);
+}
+__device__ __forceinline__ float group8_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  return v;
+}
+__device__ __forceinline__ float absmax16(const float* f) {
+  float m = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) m = fmaxf(m, fabsf(f[e]));
+  return m;
+}
+__device__ __forceinline__ uint4 encode16(const float* f, float inv_scale) {
+  uint4 q;
+  q.x = encode4(f, inv_scale);
+  q.y = encode4(f + 4, inv_scale);
+  q.z = encode4(f + 8, inv_scale);
+  q.w = encode4(f + 12, inv_scale);
+  return q;
+}
+__device__ __forceinline__ void decode16(const uint4& q, float scale, float* f) {
+  decode4(q.x, scale, f);
+  decode4(q.y, scale, f + 4);
+  decode4(q.z, scale, f + 8);
+  decode4(q.w, scale, f + 12);
+}
+
+// Quantise the lane's 16 values of block `blk`; all 8 lanes of the block's group must call.
+__device__ __forceinline__ void quantize_block16(const float* f, int sub, uint4* codes, float* scales, long long blk) {
+  const float amax = group8_max(absmax16(f));
   const float scale = amax > 0.f ? amax / FP8_MAX : 1.f;
-  codes[blk * (QB / 4) + lane] = encode4(f, 1.f / scale);
-  if (lane == 0) scales[blk] = scale;
+  codes[blk * LPB + sub] = encode16(f, 1.f / scale);
+  if (sub == 0) scales[blk] = scale;
 }
 
 template <typename T>
-__global__ void quantize_kernel(const T* __restrict__ a, const T* __restrict__ b, uint32_t* __restrict__ codes,
+__global__ void quantize_kernel(const T* __restrict__ a, const T* __restrict__ b, uint4* __restrict__ codes,
                                 float* __restrict__ scales, long long nblocks) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane & (LPB - 1), bw = lane / LPB;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long blk = warp; blk < nblocks; blk += nwarps) {
-    float f[4];
-    load4<T>(a + blk * QB + lane * 4, f);
-    if (b != nullptr) {
-      float g[4];
-      load4<T>(b + blk * QB + lane * 4, g);
+  for (long long blk0 = warp * BPW; blk0 < nblocks; blk0 += nwarps * BPW) {
+    const long long blk = blk0 + bw;
+    const bool live = blk < nblocks;
+    float f[EPL];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) f[e] -= g[e];
+    for (int e = 0; e < EPL; ++e) f[e] = 0.f;
+    if (live) {
+      load16<T>(a + blk * QB + sub * EPL, f);
+      if (b != nullptr) {
+        float g[EPL];
+        load16<T>(b + blk * QB + sub * EPL, g);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) f[e] -= g[e];
+      }
     }
-    quantize_block(f, lane, codes, scales, blk);
+    const float amax = group8_max(absmax16(f));
+    if (live) {
+      const float scale = amax > 0.f ? amax / FP8_MAX : 1.f;
+      codes[blk * LPB + sub] = encode16(f, 1.f / scale);
+      if (sub == 0) scales[blk] = scale;
+    }
   }
 }
 
 template <typename T>
-__global__ void dequantize_kernel(const uint32_t* __restrict__ codes, const float* __restrict__ scales,
+__global__ void dequantize_kernel(const uint4* __restrict__ codes, const float* __restrict__ scales,
                                   T* __restrict__ out, long long nblocks) {
-  const int lane = threadIdx.x & 31;
-  const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
-  const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  for (long long blk = warp; blk < nblocks; blk += nwarps) {
-    float f[4];
-    decode4(codes[blk * (QB / 4) + lane], scales[blk], f);
-    store4<T>(out + blk * QB + lane * 4, f);
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;  // one 16-element piece each
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = idx; i < nblocks * LPB; i += stride) {
+    float f[EPL];
+    decode16(codes[i], scales[i / LPB], f);
+    store16<T>(out + i * EPL, f);
   }
 }
 
@@ -124,28 +176,37 @@ struct QuantAllreduceArgs {
 template <typename T>
 __device__ __forceinline__ void allreduce_fp8_body(const TeamParams& tp, const QuantAllreduceArgs& a) {
   __shared__ int sh_code;
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane & (LPB - 1), bw = lane / LPB;
   const long long warp = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const long long nblocks = a.n / QB;
-  uint32_t* my_codes = reinterpret_cast<uint32_t*>(a.arena[tp.rank]);
+  uint4* my_codes = reinterpret_cast<uint4*>(a.arena[tp.rank]);
   float* my_scales = reinterpret_cast<float*>(a.arena[tp.rank] + a.n);
 
   // ---- quantise the local contribution into this rank's arena
   const T* ia = reinterpret_cast<const T*>(a.in_a);
   const T* ib = reinterpret_cast<const T*>(a.in_b);
-  for (long long blk = warp; blk < nblocks; blk += nwarps) {
-    float f[4] = {0.f, 0.f, 0.f, 0.f};
-    if (!a.zero_contribution) {
-      load4<T>(ia + blk * QB + lane * 4, f);
-      if (ib != nullptr) {
-        float g[4];
-        load4<T>(ib + blk * QB + lane * 4, g);
+  for (long long blk0 = warp * BPW; blk0 < nblocks; blk0 += nwarps * BPW) {
+    const long long blk = blk0 + bw;
+    const bool live = blk < nblocks;
+    float f[EPL];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) f[e] -= g[e];
+    for (int e = 0; e < EPL; ++e) f[e] = 0.f;
+    if (live && !a.zero_contribution) {
+      load16<T>(ia + blk * QB + sub * EPL, f);
+      if (ib != nullptr) {
+        float g[EPL];
+        load16<T>(ib + blk * QB + sub * EPL, g);
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) f[e] -= g[e];
       }
     }
-    quantize_block(f, lane, my_codes, my_scales, blk);
+    const float amax = group8_max(absmax16(f));
+    if (live) {
+      const float s = amax > 0.f ? amax / FP8_MAX : 1.f;
+      my_codes[blk * LPB + sub] = encode16(f, 1.f / s);
+      if (sub == 0) my_scales[blk] = s;
+    }
   }
   if (!grid_arrive(tp, 2, &sh_code)) return;
   if (!team_round(tp, 0, 0, &sh_code)) return;
@@ -153,38 +214,43 @@ __device__ __forceinline__ void allreduce_fp8_body(const TeamParams& tp, const Q
   // ---- reduce this rank's slice over all peers, requantise, hand the slice to everybody
   const long long per = nblocks / tp.world;
   const long long lo = per * tp.rank;
-  for (long long b = warp; b < per; b += nwarps) {
-    const long long blk = lo + b;
-    uint32_t bits[MAX_RANKS];
+  for (long long b0 = warp * BPW; b0 < per; b0 += nwarps * BPW) {
+    const long long b = b0 + bw;
+    const bool live = b < per;
+    const long long blk = lo + (live ? b : 0);
+    uint4 bits[MAX_RANKS];
     float sc[MAX_RANKS];
 #pragma unroll
     for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k < tp.world) {
+      if (k < tp.world && live) {
         const int p = (tp.rank + k) % tp.world;
-        bits[k] = reinterpret_cast<const uint32_t*>(a.arena[p])[blk * (QB / 4) + lane];
+        bits[k] = reinterpret_cast<const uint4*>(a.arena[p])[blk * LPB + sub];
         sc[k] = reinterpret_cast<const float*>(a.arena[p] + a.n)[blk];
       }
     }
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) acc[e] = 0.f;
 #pragma unroll
     for (int k = 0; k < MAX_RANKS; ++k) {
-      if (k < tp.world) {
-        float f[4];
-        decode4(bits[k], sc[k], f);
+      if (k < tp.world && live) {
+        float f[EPL];
+        decode16(bits[k], sc[k], f);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[e] += f[e];
+        for (int e = 0; e < EPL; ++e) acc[e] += f[e];
       }
     }
 #pragma unroll
-    for (int e = 0; e < 4; ++e) acc[e] *= a.scale;
-    float amax = fmaxf(fmaxf(fabsf(acc[0]), fabsf(acc[1])), fmaxf(fabsf(acc[2]), fabsf(acc[3])));
-    amax = ftb200::warp_max(amax);
-    const float s = amax > 0.f ? amax / FP8_MAX : 1.f;
-    const uint32_t q = encode4(acc, 1.f / s);
-    for (int k = 0; k < tp.world; ++k) {
-      const int p = (tp.rank + k) % tp.world;
-      reinterpret_cast<uint32_t*>(a.arena[p])[blk * (QB / 4) + lane] = q;
-      if (lane == 0) reinterpret_cast<float*>(a.arena[p] + a.n)[blk] = s;
+    for (int e = 0; e < EPL; ++e) acc[e] *= a.scale;
+    const float amax = group8_max(absmax16(acc));
+    if (live) {
+      const float s = amax > 0.f ? amax / FP8_MAX : 1.f;
+      const uint4 q = encode16(acc, 1.f / s);
+      for (int k = 0; k < tp.world; ++k) {
+        const int p = (tp.rank + k) % tp.world;
+        reinterpret_cast<uint4*>(a.arena[p])[blk * LPB + sub] = q;
+        if (sub == 0) reinterpret_cast<float*>(a.arena[p] + a.n)[blk] = s;
+      }
     }
   }
   if (!grid_arrive(tp, 3, &sh_code)) return;
@@ -192,15 +258,17 @@ __device__ __forceinline__ void allreduce_fp8_body(const TeamParams& tp, const Q
 
   // ---- dequantise the complete result
   T* out = reinterpret_cast<T*>(a.out);
-  for (long long blk = warp; blk < nblocks; blk += nwarps) {
-    float f[4];
-    decode4(my_codes[blk * (QB / 4) + lane], my_scales[blk], f);
-    store4<T>(out + blk * QB + lane * 4, f);
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (long long i = tid; i < nblocks * LPB; i += nthreads) {
+    float f[EPL];
+    decode16(my_codes[i], my_scales[i / LPB], f);
+    store16<T>(out + i * EPL, f);
   }
 }
 
 template <typename T>
-__global__ void __maxnreg__(72) allreduce_fp8_kernel(const TeamParams tp, const QuantAllreduceArgs a) {
+__global__ void __maxnreg__(96) allreduce_fp8_kernel(const TeamParams tp, const QuantAllreduceArgs a) {
   allreduce_fp8_body<T>(tp, a);
 }
 template <typename T>
@@ -240,7 +308,7 @@ __global__ void diloco_outer_kernel(const T* __restrict__ g, float* __restrict__
 }
 
 int grid_for_blocks(long long nblocks) {
-  long long g = (nblocks * 32 + 511) / 512;
+  long long g = (nblocks * 8 + 511) / 512;
   return static_cast<int>(std::max<long long>(1, std::min<long long>(g, ftb200::sm_count() * 4LL)));
 }
 
@@ -253,9 +321,9 @@ FTB200_API int ftb200_quantize_fp8(const void* a, const void* b, void* codes, fl
   const long long nb = n / QB;
   if (dtype == 0)
     quantize_kernel<__nv_bfloat16><<<grid_for_blocks(nb), 512, 0, st>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
-                                                                        (uint32_t*)codes, scales, nb);
+                                                                        (uint4*)codes, scales, nb);
   else
-    quantize_kernel<float><<<grid_for_blocks(nb), 512, 0, st>>>((const float*)a, (const float*)b, (uint32_t*)codes, scales, nb);
+    quantize_kernel<float><<<grid_for_blocks(nb), 512, 0, st>>>((const float*)a, (const float*)b, (uint4*)codes, scales, nb);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
@@ -264,9 +332,9 @@ FTB200_API int ftb200_dequantize_fp8(const void* codes, const float* scales, voi
   if (n <= 0 || n % QB) return FTB200_E_ALIGN;
   const long long nb = n / QB;
   if (dtype == 0)
-    dequantize_kernel<__nv_bfloat16><<<grid_for_blocks(nb), 512, 0, st>>>((const uint32_t*)codes, scales, (__nv_bfloat16*)out, nb);
+    dequantize_kernel<__nv_bfloat16><<<grid_for_blocks(nb), 512, 0, st>>>((const uint4*)codes, scales, (__nv_bfloat16*)out, nb);
   else
-    dequantize_kernel<float><<<grid_for_blocks(nb), 512, 0, st>>>((const uint32_t*)codes, scales, (float*)out, nb);
+    dequantize_kernel<float><<<grid_for_blocks(nb), 512, 0, st>>>((const uint4*)codes, scales, (float*)out, nb);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 

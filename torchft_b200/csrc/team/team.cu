@@ -487,3 +487,35 @@ FTB200_API int ftb200_ipc_export_any(const void* ptr, unsigned char* handle64, u
   *alloc_bytes = size;
   return 0;
 }
+
+// ---- pieces of the GEMM-fused reduce-scatter ------------------------------------------------
+namespace {
+struct StagePeers {
+  void* p[MAX_RANKS];
+};
+// Small fields of a gradient unit (norm weights) that no GEMM produces: copy them into the
+// owners' staging areas with the same addressing as the GEMM's scatter epilogue.
+__global__ void scatter_to_stage_kernel(const ftb200::bf16x8* __restrict__ src, long long n8, long long unit_off,
+                                        long long shard, int src_rank, StagePeers peers) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const long long flat = unit_off + i * 8;
+  const long long owner = flat / shard;
+  const long long rem = flat - owner * shard;
+  __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(peers.p[owner]);
+  *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(src_rank) * shard + rem) = src[i];
+}
+}  // namespace
+
+FTB200_API int ftb200_scatter_to_stage(const void* src, long long n, long long unit_off, long long shard_elems,
+                                       void* const* peers, int world, int src_rank, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if ((n % 8) || (unit_off % 8) || (shard_elems % 8) || (reinterpret_cast<uintptr_t>(src) & 15)) return FTB200_E_ALIGN;
+  if (world < 1 || world > MAX_RANKS || unit_off + n > shard_elems * world) return FTB200_E_BADARG;
+  StagePeers sp;
+  for (int i = 0; i < MAX_RANKS; ++i) sp.p[i] = i < world ? peers[i] : nullptr;
+  const long long n8 = n / 8;
+  scatter_to_stage_kernel<<<static_cast<int>((n8 + 255) / 256), 256, 0, st>>>(
+      reinterpret_cast<const ftb200::bf16x8*>(src), n8, unit_off, shard_elems, src_rank, sp);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}

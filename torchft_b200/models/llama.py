@@ -167,8 +167,10 @@ class LlamaEngine:
         grad_done: Optional[Callable[[int], None]] = None,
         attention: Optional[object] = None,
         logit_chunks: int = 4,
+        grad_fields: Optional[Callable[[int], object]] = None,
     ):
         self.cfg, self.B, self.S, self.device = cfg, batch, seq_len, device
+        self.grad_fields = grad_fields
         self.T = batch * seq_len
         self.param_unit, self.grad_unit = param_unit, grad_unit
         self.before_unit = before_unit or (lambda u, backward: None)
@@ -207,7 +209,13 @@ class LlamaEngine:
     def _p(self, u: int) -> _Fields:
         return _Fields(self.param_unit(u), self.cfg.unit_fields(u))
 
-    def _g(self, u: int) -> _Fields:
+    def _g(self, u: int):
+        """Gradient destinations of unit ``u``: views into its flat gradient buffer, or
+        whatever ``grad_fields`` supplies (e.g. scatter targets of a GEMM-fused reduce-scatter)."""
+        if self.grad_fields is not None:
+            g = self.grad_fields(u)
+            if g is not None:
+                return g
         return _Fields(self.grad_unit(u), self.cfg.unit_fields(u))
 
     # -- forward ---------------------------------------------------------------------------

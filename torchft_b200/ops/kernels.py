@@ -113,6 +113,37 @@ def gemm(
     return out
 
 
+class ScatterField:
+    """Destination of a weight-gradient GEMM whose epilogue performs the reduce-scatter's
+    transfer: a ``[rows, cols]`` field at element offset ``unit_off`` of a flat gradient unit
+    sharded over ``world`` ranks; ``peers`` are the ranks' staging areas (``[world, shard]``)."""
+
+    def __init__(self, peers, world: int, src_rank: int, shard_elems: int, unit_off: int, shape) -> None:
+        self.peers, self.world, self.src_rank = peers, world, src_rank
+        self.shard_elems, self.unit_off, self.shape = shard_elems, unit_off, tuple(shape)
+
+
+def gemm_scatter(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool, b_mn_major: bool, dst: ScatterField) -> None:
+    """``A @ B^T`` written straight into the owners' staging areas (see :class:`ScatterField`)."""
+    _check_2d_bf16(a, "a")
+    _check_2d_bf16(b, "b")
+    K_, M = a.shape if a_mn_major else a.shape[::-1]
+    Kb, Nn = b.shape if b_mn_major else b.shape[::-1]
+    if K_ != Kb or (M, Nn) != dst.shape:
+        raise ValueError(f"shape mismatch: {(M, Nn)} vs field {dst.shape}")
+    rc = N.lib().ftb200_gemm_bf16_scatter(
+        ptr(a), ptr(b), c_int(M), c_int(Nn), c_int(K_), c_int(int(a_mn_major)), c_int(int(b_mn_major)), c_ll(a.stride(0)),
+        c_ll(b.stride(0)), dst.peers, c_int(dst.world), c_int(dst.src_rank), c_ll(dst.shard_elems), c_ll(dst.unit_off),
+        ptr(status_word(a.device)), c_int(0), stream_ptr())
+    N.check(rc, "gemm_bf16_scatter")
+
+
+def scatter_to_stage(src: torch.Tensor, dst: ScatterField) -> None:
+    """Copy a small bf16 field (e.g. a norm-weight gradient) to its owners' staging areas."""
+    N.check(N.lib().ftb200_scatter_to_stage(ptr(src), c_ll(src.numel()), c_ll(dst.unit_off), c_ll(dst.shard_elems), dst.peers,
+                                            c_int(dst.world), c_int(dst.src_rank), stream_ptr()), "scatter_to_stage")
+
+
 def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``y = x @ w^T`` (x ``[T,K]``, w ``[N,K]``)."""
     return gemm(x, w, False, False, out=out)
@@ -126,7 +157,13 @@ def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] 
 
 def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
                  accumulate: bool = False, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
-    """``dw = dy^T @ x`` (dy ``[T,N]``, x ``[T,K]``) -> ``[N,K]``."""
+    """``dw = dy^T @ x`` (dy ``[T,N]``, x ``[T,K]``) -> ``[N,K]``.  ``out`` may be a
+    :class:`ScatterField`: the result then goes straight to the shard owners."""
+    if isinstance(out, ScatterField):
+        if accumulate:
+            raise ValueError("a scattered weight gradient cannot accumulate")
+        gemm_scatter(dy, x, True, True, out)
+        return out  # type: ignore[return-value]
     return gemm(dy, x, True, True, out=out, accumulate=accumulate, out_dtype=out_dtype)
 
 

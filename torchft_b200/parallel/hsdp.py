@@ -46,6 +46,7 @@ class ShardedLlamaTrainer:
         attention=None,
         logit_chunks: int = 4,
         replica_alloc=None,
+        fused_reduce_scatter: bool = True,
     ):
         self.cfg, self.device = cfg, device
         self.comm = shard_comm or LocalShardComm()
@@ -111,9 +112,22 @@ class ShardedLlamaTrainer:
         self.sumsq = torch.zeros(1, dtype=f32, device=device)
         self.clip = torch.ones(1, dtype=f32, device=device)
         self.grad_norm = torch.zeros(1, dtype=f32, device=device)
+        # GEMM-fused reduce-scatter: the weight-gradient GEMMs store their tiles straight into the
+        # shard owners' staging areas (the double-buffered full-unit buffers, viewed as
+        # [world, shard]); what is left of the reduce-scatter is a team round and a local sum.
+        self.fused_rs = bool(
+            fused_reduce_scatter and ws > 1 and self.cuda and getattr(self.comm, "supports_fused_scatter", False)
+            and K.GEMM_IMPL == "2cta" and logit_chunks == 1
+        )
+        self._fused_fields: Dict[int, object] = {}
+        self._vec_tmp: Dict[str, torch.Tensor] = {}
+        if self.fused_rs:
+            for bufs in self._g_bufs.values():
+                for b in bufs:
+                    b.zero_()  # padding of the last shard is never written again
         self.engine = LlamaEngine(
             cfg, batch, seq_len, device, self._param_unit, self._grad_unit, self._before_unit, self._grad_done,
-            attention=attention, logit_chunks=logit_chunks,
+            attention=attention, logit_chunks=logit_chunks, grad_fields=self._grad_fields if self.fused_rs else None,
         )
 
     # ---- unit plumbing -------------------------------------------------------------------
@@ -159,9 +173,53 @@ class ShardedLlamaTrainer:
             if ev is not None:
                 torch.cuda.current_stream().wait_event(ev)
 
+    def _grad_fields(self, u: int):
+        """Scatter targets for the matrices of unit ``u`` (None for the embedding unit, whose
+        gradient is built by atomics in a local buffer and reduce-scattered the plain way)."""
+        if u == 0:
+            return None
+        f = self._fused_fields.get(u)
+        if f is None:
+            import math
+
+            class _F:
+                pass
+
+            f = _F()
+            f.vectors = []
+            stage = self._grad_buf(u)
+            peers = self.comm.stage_peers(stage)
+            off = 0
+            for name, shape in self.cfg.unit_fields(u):
+                field = K.ScatterField(peers, self.comm.size, self.comm.rank, self.shard_numel[u], off, shape)
+                if len(shape) == 2:
+                    setattr(f, name, field)
+                else:
+                    tmp = self._vec_tmp.get(name)
+                    if tmp is None:
+                        tmp = torch.zeros(shape, dtype=torch.bfloat16, device=self.device)
+                        self._vec_tmp[name] = tmp
+                    setattr(f, name, tmp)
+                    f.vectors.append((tmp, field))
+                off += math.prod(shape)
+            self._fused_fields[u] = f
+        return f
+
     def _grad_done(self, u: int) -> None:
         ws = self.comm.size
-        if ws > 1:
+        if ws > 1 and self.fused_rs and u > 0:
+            f = self._grad_fields(u)
+            for tmp, field in f.vectors:
+                K.scatter_to_stage(tmp, field)
+            buf = self._grad_buf(u)
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                self.comm.reduce_stage(buf, self.g_shard[u])
+                self._replica_allreduce(u)
+                ev = torch.cuda.Event()
+                ev.record(self.comm_stream)
+            self._rs_event[buf.data_ptr()] = ev
+        elif ws > 1:
             buf = self._grad_buf(u)
             pad = self.full_numel[u] - self.unit_numel[u]
             if pad:

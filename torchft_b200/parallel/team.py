@@ -238,6 +238,26 @@ class SymmetricTeam:
             "team_reduce_scatter",
         )
 
+    def reduce_local_slices(self, stage_off: int, dst: torch.Tensor, shard_elems: int, dtype: torch.dtype,
+                            scale: float = 1.0, ctas: int = 0) -> None:
+        """Second half of the GEMM-fused reduce-scatter: after a ready round (every peer's
+        GEMM epilogue has stored its contribution into this rank's staging area
+        ``[world, shard_elems]`` at ``stage_off``), sum the ``world`` slices locally into
+        ``dst``; a done round then releases the staging area for reuse."""
+        es = torch.empty((), dtype=dtype).element_size()
+        arr = (ctypes.c_void_p * MAX_RANKS)()
+        lo = shard_elems * self.rank
+        for p in range(self.world):
+            # the kernel reads src[p] + lo + i; make that land on slice p of the local staging area
+            arr[p] = self.arena.base + stage_off + (p * shard_elems - lo) * es
+        d = self._desc()
+        N.check(
+            self.lib.ftb200_team_reduce_scatter(ctypes.byref(d), arr, N.ptr(dst), ctypes.c_longlong(shard_elems),
+                                                ctypes.c_int(_DT[dtype]), ctypes.c_float(scale),
+                                                ctypes.c_int(ctas or DEFAULT_CTAS), N.stream_ptr()),
+            "team_reduce_local_slices",
+        )
+
     def barrier(self) -> None:
         d = self._desc()
         N.check(self.lib.ftb200_team_barrier(ctypes.byref(d), N.stream_ptr()), "team_barrier")
@@ -304,6 +324,16 @@ class PeerShardComm(ShardComm):
 
     def all_reduce_sum_(self, t: torch.Tensor) -> None:
         dist.all_reduce(t, group=self.group)
+
+    # ---- GEMM-fused reduce-scatter ------------------------------------------------------------
+    supports_fused_scatter = True
+
+    def stage_peers(self, stage: torch.Tensor):
+        """Peer pointers of a staging buffer allocated with :meth:`alloc` (same offset in every arena)."""
+        return self.team._peer_ptrs(self._off(stage))
+
+    def reduce_stage(self, stage: torch.Tensor, shard: torch.Tensor) -> None:
+        self.team.reduce_local_slices(self._off(stage), shard, shard.numel(), shard.dtype)
 
     def barrier(self) -> None:
         self.team.barrier()
