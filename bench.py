@@ -43,7 +43,14 @@ def _parse():
     ap.add_argument("--micro-batch", type=int, default=1)
     ap.add_argument("--shard-comm", default="peer", choices=["peer", "nccl"])
     ap.add_argument("--no-ft", action="store_true", help="run without Manager/lighthouse (debug only)")
-    ap.add_argument("--no-fused-rs", action="store_true", help="separate reduce-scatter kernels instead of the GEMM-fused one")
+    ap.add_argument("--attention", default=None, choices=["tcgen05", "sdpa"],
+                    help="attention kernels: hand-written tcgen05 (default where the shape allows) or the library SDPA")
+    ap.add_argument("--fused-rs", action="store_true",
+                    help="store weight-gradient tiles straight into the shard owners' staging from the GEMM epilogue "
+                         "instead of running a separate reduce-scatter kernel (measured slower so far: off by default)")
+    ap.add_argument("--groups", type=int, default=0, help="replica groups (default: 1, 2, 2, 2 for 1, 2, 4, 8 GPUs)")
+    ap.add_argument("--watchdog-s", type=int, default=900,
+                    help="dump every thread's stack and exit if the run has not finished after this many seconds")
     return ap.parse_args()
 
 
@@ -122,6 +129,10 @@ def main() -> int:
     if args.impl == "reference":
         return _reference_arm(args)
 
+    import faulthandler
+
+    faulthandler.dump_traceback_later(args.watchdog_s, exit=True)  # a stuck run says where, then ends
+
     import torch
     import torch.distributed as dist
 
@@ -148,7 +159,8 @@ def main() -> int:
     cfg = CONFIGS[args.model]
     B, S = args.micro_batch, args.seq_len
 
-    n_groups = 1 if world == 1 else 2
+    n_groups = args.groups if args.groups > 0 else (1 if world == 1 else 2)
+    assert world % n_groups == 0, "--groups must divide the number of GPUs"
     shard = world // n_groups
     group_id, group_rank = rank // shard, rank % shard
 
@@ -177,7 +189,8 @@ def main() -> int:
     replica_alloc = manager._pg.alloc if (manager is not None and n_groups > 1) else None
     # one logits chunk: the 2 GB of bf16 logits fit, and the head's wgrad then runs once with the full reduction depth
     trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234,
-                                  replica_alloc=replica_alloc, logit_chunks=1, fused_reduce_scatter=not args.no_fused_rs)
+                                  replica_alloc=replica_alloc, logit_chunks=1, fused_reduce_scatter=args.fused_rs,
+                                  attention=args.attention)
     if manager is not None:
         manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 
@@ -267,6 +280,7 @@ def main() -> int:
                 "l2": "working set per step (>100 GB of weights, optimizer state and activations) is far larger than L2",
                 "fault_tolerance": "off (debug)" if args.no_ft else "Manager quorum + should_commit every step",
                 "shard_comm": args.shard_comm if shard > 1 else "none",
+                "attention": type(trainer.engine.attn).__name__,
                 "reduce_scatter": ("fused into the wgrad GEMM epilogue" if trainer.fused_rs else "separate kernel") if shard > 1 else "none",
             },
             "clocks": clocks,

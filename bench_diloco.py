@@ -1,0 +1,134 @@
+#!/usr/bin/env python
+"""Streaming-DiLoCo benchmark: N replica groups of one GPU each train a Llama-3-style 1B
+decoder (seq 8192, micro-batch 1, bf16 compute, fp32 master weights, AdamW inside) and
+synchronise one of F fragments every H/F inner steps with fp8 pseudo-gradients and a
+Nesterov outer step.
+
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29544 bench_diloco.py --sync-every 100 --fragments 4 --windows 2
+
+Prints one JSON line on rank 0: ``outer_sync_ms`` is the time the training stream loses to
+one fragment synchronisation (quorum, pseudo-gradient exchange, commit vote, outer update,
+bf16 refresh), CUDA-event timed, mean over the timed synchronisations, max over ranks;
+``tokens_per_s`` is the job's aggregate over the timed windows, synchronisations included.
+``--no-quantize`` sends the pseudo-gradients in fp32 instead of fp8.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama3-1b")
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--micro-batch", type=int, default=1)
+    ap.add_argument("--sync-every", type=int, default=100, help="H: inner steps per full round of fragments")
+    ap.add_argument("--fragments", type=int, default=4)
+    ap.add_argument("--delay", type=int, default=0, help="fragment_sync_delay (inner steps of overlap)")
+    ap.add_argument("--alpha", type=float, default=0.0, help="fragment_update_alpha")
+    ap.add_argument("--windows", type=int, default=1, help="timed rounds of H inner steps (after one warm-up round)")
+    ap.add_argument("--no-quantize", action="store_true")
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+
+    from torchft_b200.bench_support import make_ft_manager
+    from torchft_b200.models.llama import CONFIGS
+    from torchft_b200.ops import _native as N
+    from torchft_b200.parallel.diloco import EngineDiLoCo
+    from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    cfg = CONFIGS[args.model]
+    B, S = args.micro_batch, args.seq_len
+    trainer = ShardedLlamaTrainer(cfg, B, S, device, seed=1234, logit_chunks=1)
+    lighthouse, manager = make_ft_manager(rank, world, n_groups=world, shard=1, group_id=rank, group_rank=0,
+                                          device=device, arena_bytes=0, use_async_quorum=False)
+    manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
+    diloco = EngineDiLoCo(trainer, manager, n_fragments=args.fragments, sync_every=args.sync_every,
+                          should_quantize=not args.no_quantize, fragment_sync_delay=args.delay,
+                          fragment_update_alpha=args.alpha, record_timing=True)
+
+    g = torch.Generator(device="cpu").manual_seed(100 + rank)
+    host_tokens = torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g).pin_memory()
+    tokens = torch.empty(B, S + 1, dtype=torch.long, device=device)
+
+    def run_round() -> float:
+        loss = None
+        for _ in range(args.sync_every):
+            tokens.copy_(host_tokens, non_blocking=True)
+            loss = diloco.train_step(tokens[:, :-1], tokens[:, 1:])
+        return float(loss)
+
+    run_round()  # warm-up: every fragment synchronises once
+    diloco.timings.clear()
+    diloco.exchange_timings.clear()
+    commits0 = diloco.commits
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    l0 = N.launch_count
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    last_loss = 0.0
+    for _ in range(args.windows):
+        last_loss = run_round()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    total_ms = e0.elapsed_time(e1)
+    launches = N.launch_count - l0
+    syncs = [sum(a.elapsed_time(b) for a, b in pairs) for pairs in diloco.timings]
+    sync_ms = sum(syncs) / max(1, len(syncs))
+    exch = [a.elapsed_time(b) for a, b in diloco.exchange_timings]
+    exch_ms = sum(exch) / max(1, len(exch))
+    stats = torch.tensor([total_ms, sync_ms, exch_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    total_ms, sync_ms, exch_ms = (float(x) for x in stats.tolist())
+    committed = diloco.commits - commits0
+    steps = args.windows * args.sync_every
+    frag_elems = [sum(trainer.shard_numel[u] for u in f.units) for f in diloco.fragments]
+    if rank == 0:
+        print(json.dumps({
+            "metric": "streaming DiLoCo outer sync ms; tokens/s",
+            "outer_sync_ms": round(sync_ms, 3),
+            "exchange_kernel_ms": round(exch_ms, 3),
+            "tokens_per_s": round(world * B * S * steps / (total_ms / 1e3), 1),
+            "ms_per_inner_step": round((total_ms - sync_ms * len(syncs)) / steps, 3),
+            "n_gpus": world, "inner_steps": steps, "syncs_timed": len(syncs), "syncs_committed": committed,
+            "fragment_melems": [round(n / 1e6, 1) for n in frag_elems],
+            "wire": "fp32" if args.no_quantize else "fp8 e4m3, 128-element blocks",
+            "gpu_launches": launches, "final_loss": round(last_loss, 4), "dtype": "bf16", "data": "synthetic",
+            "config": {"model": args.model, "seq_len": S, "micro_batch": B, "sync_every": args.sync_every,
+                       "fragments": args.fragments, "fragment_sync_delay": args.delay,
+                       "fragment_update_alpha": args.alpha, "parallelism": f"{world} groups x 1 GPU"},
+        }))
+    manager.shutdown(wait=False)
+    if lighthouse is not None:
+        lighthouse.shutdown()
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -195,3 +195,77 @@ def test_diloco_golden_sequence(n_fragments, expected_l0, expected_l1):
     assert seen0 == [float(x) for x in expected_l0]
     assert seen1 == [float(x) for x in expected_l1]
     assert globals_[2] == (-11.0, 1.0) and globals_[5] == (-11.0, -23.0)
+
+
+def _delta_manager(factor=1.0, commit_pattern=None):
+    """Mock manager whose allreduce scales by ``factor`` and whose allreduce_delta is the
+    unfused definition (out = a - b, then allreduce)."""
+    state = {"step": 0, "votes": 0}
+    m = create_autospec(Manager, instance=True)
+    m._use_async_quorum = False
+    m.current_step.side_effect = lambda: state["step"]
+
+    def allreduce(t, should_quantize=False, reduce_op=None):
+        t.mul_(factor)
+        return _DummyWork(t)
+
+    def allreduce_delta(out, a, b, should_quantize=False):
+        torch.sub(a, b, out=out)
+        return allreduce(out)
+
+    def commit():
+        ok = True if commit_pattern is None else commit_pattern[state["votes"] % len(commit_pattern)]
+        state["votes"] += 1
+        if ok:
+            state["step"] += 1
+        return ok
+
+    m.allreduce.side_effect = allreduce
+    m.allreduce_delta.side_effect = allreduce_delta
+    m.should_commit.side_effect = commit
+    return m
+
+
+@pytest.mark.parametrize("delay,alpha", [(0, 0.0), (1, 0.0), (1, 0.3)])
+def test_flat_fragments_match_per_parameter_path(delay, alpha):
+    """Flat-buffer fragments (fused outer step) follow the same trajectory as the
+    per-parameter path with torch.optim.SGD(nesterov) outside, including a failed vote."""
+    def run(flat):
+        torch.manual_seed(3)
+        model = nn.Sequential(nn.Linear(6, 8), nn.Linear(8, 8), nn.Linear(8, 4), nn.Linear(4, 2))
+        frags = [model[:2], model[2:]]
+        inner = optim.AdamW(model.parameters(), lr=1e-2)
+        outers = [optim.SGD(f.parameters(), lr=0.7, momentum=0.9, nesterov=True) for f in frags]
+        m = _delta_manager(factor=0.5, commit_pattern=[True, True, False, True])
+        hooks = {}
+        m.register_state_dict_fn.side_effect = lambda k, load, save: hooks.__setitem__(k, (load, save))
+        g = torch.Generator().manual_seed(11)
+        with DiLoCo(m, frags, inner, outers, sync_every=4, fragment_sync_delay=delay, fragment_update_alpha=alpha,
+                    flat_fragments=flat) as d:
+            assert d.flat_fragments == flat
+            for _ in range(16):
+                inner.zero_grad()
+                model(torch.randn(5, 6, generator=g)).square().mean().backward()
+                inner.step()
+        backups = [f.original_parameters[n].clone() for f in d._fragments for n in sorted(f.original_parameters)]
+        return [p.detach().clone() for p in model.parameters()], backups, hooks
+
+    p_ref, b_ref, _ = run(False)
+    p_flat, b_flat, hooks = run(True)
+    for a, b in zip(p_ref + b_ref, p_flat + b_flat):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    # the healing state of a flat fragment round-trips, momentum included
+    load, save = hooks["StreamingDiLoCoFragment_0"]
+    sd = save()
+    assert set(sd) == {"outer_optimizer", "original_parameters", "outer_momentum", "outer_steps"} and sd["outer_steps"] > 0
+    load(sd)
+
+
+def test_flat_fragments_reject_unsupported_outer_optimizer():
+    model = TinyModel()
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    m = _delta_manager()
+    with pytest.raises(ValueError):
+        DiLoCo(m, [model], inner, optim.Adam(model.parameters(), lr=0.1), sync_every=2, flat_fragments=True)
+    # auto mode quietly keeps the per-parameter path
+    assert not DiLoCo(m, [model], inner, optim.Adam(model.parameters(), lr=0.1), sync_every=2).flat_fragments

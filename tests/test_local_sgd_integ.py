@@ -159,3 +159,52 @@ def test_diloco_upscale_third_replica_joins_late():
         inj.barrier_at(replica=r, step=2 if r < 2 else 0, barrier=barrier)
     res, _ = _run(diloco_loop, n_replicas=3, injector=inj, min_replicas=2, total_syncs=5, n_fragments=2)
     _assert_same_history(res)
+
+
+# ---- streaming DiLoCo on the explicit Llama engine (flat units, fused outer step) ----------
+
+
+def engine_diloco_loop(rank, store_port, runner, total_syncs=4, sync_every=4, n_fragments=2, delay=0, alpha=0.0):
+    from torchft_b200.models.llama import LLAMA_TINY
+    from torchft_b200.parallel.diloco import EngineDiLoCo
+    from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
+
+    cfg, B, S = LLAMA_TINY, 2, 16
+    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), lr=1e-2, seed=5)
+    pg = FakeProcessGroupWrapper(ProcessGroupGloo(timeout=timedelta(seconds=10)))
+    manager = _manager(runner, rank, store_port, pg, tr.load_state_dict, tr.state_dict, use_async_quorum=False)
+    history: Dict[int, Any] = {}
+    try:
+        d = EngineDiLoCo(tr, manager, n_fragments=n_fragments, sync_every=sync_every, fragment_sync_delay=delay,
+                         fragment_update_alpha=alpha)
+        it = 0
+        while manager.current_step() < total_syncs:
+            step = manager.current_step()
+            runner.injector.check(runner.replica_id, rank, step, pg)
+            g = torch.Generator().manual_seed(100 * runner.replica_id + it)
+            tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=g)
+            d.train_step(tokens, torch.roll(tokens, -1, 1))
+            it += 1
+            if manager.current_step() != step:
+                history[manager.current_step()] = {
+                    "global": [{f"unit{u}": b.clone() for u, b in zip(f.units, f.backup)} for f in d.fragments],
+                    "outer": [{u: {"momentum_buffer": m.clone()} for u, m in zip(f.units, f.momentum)} for f in d.fragments],
+                }
+        return {"history": history, "step": manager.current_step()}
+    finally:
+        manager.shutdown(wait=False)
+        pg.shutdown()
+
+
+@pytest.mark.parametrize("n_fragments,delay,alpha", [(2, 0, 0.0), (3, 1, 0.5)])
+def test_engine_diloco_healthy(n_fragments, delay, alpha):
+    res, _ = _run(engine_diloco_loop, n_fragments=n_fragments, delay=delay, alpha=alpha, sync_every=2 * n_fragments)
+    assert all(r[0]["step"] == 4 for r in res)
+    _assert_same_history(res)
+
+
+def test_engine_diloco_recovery():
+    inj = EventInjector().fail_at(replica=1, step=2).gate_until_rejoin(replica=0, step=3)
+    res, inj = _run(engine_diloco_loop, injector=inj, min_replicas=1, total_syncs=5, n_fragments=2, delay=1)
+    assert inj.count == 1
+    _assert_same_history(res)

@@ -19,6 +19,7 @@ torchft/checkpointing/http_transport.py and pg_transport.py.
 from __future__ import annotations
 
 import ctypes
+import time
 import logging
 from dataclasses import dataclass
 from datetime import timedelta
@@ -76,6 +77,8 @@ class P2PTransport(HTTPTransport[T], Generic[T]):
         self._state_dict_fn = state_dict
         self._keepalive: List[torch.Tensor] = []
         self._status = torch.zeros(1, dtype=torch.int32, device=self._device)
+        # what the last recv_checkpoint moved: bytes, device time of the copies, host time of the whole call
+        self.last_recv: Dict[str, float] = {}
 
     def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
         leaves, spec = tree_flatten(state_dict)
@@ -104,6 +107,7 @@ class P2PTransport(HTTPTransport[T], Generic[T]):
         self._keepalive = []
 
     def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
+        t_begin = time.perf_counter()
         remote = self._fetch(f"{metadata}{step}/full", timeout)
         leaves, spec = tree_flatten(remote, is_leaf=lambda x: isinstance(x, _PeerTensorRef))
         inplace: Optional[List[object]] = None
@@ -137,7 +141,13 @@ class P2PTransport(HTTPTransport[T], Generic[T]):
                     result.append(dst)
                     if v.nbytes:
                         segs.append((base + v.offset, dst.data_ptr(), v.nbytes))
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
                 self._pull(segs)
+                ev1.record()
+                ev1.synchronize()
+                self.last_recv = {"bytes": float(sum(nb for _, _, nb in segs)), "copy_ms": ev0.elapsed_time(ev1),
+                                  "total_s": time.perf_counter() - t_begin}
             finally:
                 torch.cuda.current_stream().synchronize()
                 for base in opened.values():

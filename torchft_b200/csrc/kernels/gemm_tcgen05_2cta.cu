@@ -36,6 +36,8 @@ constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+constexpr uint32_t SC_STAGE_WARP_BYTES = 32 * 256;  // scatter epilogue: 32 rows x 128 bf16 per warp
+constexpr uint32_t SMEM_BYTES_SCATTER = SMEM_BYTES + 4 * SC_STAGE_WARP_BYTES;
 constexpr int GROUP_M = 8;  // in 256-row pair tiles
 
 using namespace ftb200::tc;
@@ -280,6 +282,45 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr0 = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      if (p.sc_world > 0) {
+        // Scatter epilogue: the tile goes through a per-warp staging area so that every store
+        // instruction covers two 256-byte row segments; short scattered stores to a peer cost
+        // an NVLink packet each and throttle the whole kernel.
+        uint8_t* stg = smem + STAGES * STAGE_BYTES + 256 + q * SC_STAGE_WARP_BYTES;
+        const int half = lane >> 4, ch = lane & 15;
+#pragma unroll 1
+        for (int cg = 0; cg < BN / 128; ++cg) {
+#pragma unroll 1
+          for (int cc = 0; cc < 4; ++cc) {
+            uint32_t r[32];
+            tmem_ld32(taddr0 + (cg * 4 + cc) * 32, r);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
+              *reinterpret_cast<ftb200::bf16x8*>(stg + lane * 256 + (((cc * 4 + j) ^ (lane & 15)) << 4)) = ftb200::pack8(f);
+            }
+          }
+          __syncwarp();
+          const int gcol = n0 + cg * 128 + ch * 8;
+#pragma unroll 4
+          for (int it = 0; it < 16; ++it) {
+            const int rr = it * 2 + half;
+            const int grow = m0 + q * 32 + rr;
+            const ftb200::bf16x8 v = *reinterpret_cast<const ftb200::bf16x8*>(stg + rr * 256 + ((ch ^ (rr & 15)) << 4));
+            if (grow < p.M && gcol + 8 <= p.N) {
+              const long long flat = p.sc_off + static_cast<long long>(grow) * p.ldc + gcol;
+              const long long owner = flat / p.sc_shard;
+              const long long rem = flat - owner * p.sc_shard;
+              __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.sc_peers[owner]);
+              *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(p.sc_src) * p.sc_shard + rem) = v;
+            }
+          }
+          __syncwarp();
+        }
+      } else
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -312,25 +353,7 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
             }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + col0;
-            if (full && p.sc_world > 0) {
-              // transfer overlaps the math tile by tile: plain 16-byte stores into peer memory
-              const long long flat0 = p.sc_off + static_cast<long long>(row) * p.ldc + col0;
-              long long owner = flat0 / p.sc_shard;
-              long long rem = flat0 - owner * p.sc_shard;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float f[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[8 * j + e]);
-                if (rem >= p.sc_shard) {
-                  rem -= p.sc_shard;
-                  ++owner;
-                }
-                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.sc_peers[owner]);
-                *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(p.sc_src) * p.sc_shard + rem) = ftb200::pack8(f);
-                rem += 8;
-              }
-            } else if (full) {
+            if (full) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 float f[8];
@@ -454,8 +477,8 @@ static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, i
 
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(gemm_bf16_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(gemm_bf16_tcgen05_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SMEM_BYTES_SCATTER) != cudaSuccess)
       return FTB200_E_CUDA;
     attr_set = true;
   }
@@ -486,7 +509,7 @@ static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, i
   int ctas = ftb200::sm_count() & ~1;
   if (max_ctas > 0 && max_ctas < ctas) ctas = std::max(2, max_ctas & ~1);
   if (2 * tiles < ctas) ctas = 2 * tiles;
-  gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+  gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, sc != nullptr ? SMEM_BYTES_SCATTER : SMEM_BYTES, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 

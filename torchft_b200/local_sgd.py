@@ -335,6 +335,133 @@ class _StreamingDiLoCoFragment:
         self._bucketize_and_allreduce(grads, bucket_size_bytes=self.bucket_cap_mb)
 
 
+def _flat_eligible(fragment: nn.Module, outer: optim.Optimizer) -> bool:
+    """Whether a fragment can live in flat buffers: plain tensors of one fp32/bf16 dtype on
+    one device, and an outer optimizer that is momentum SGD without damping or decay."""
+    params = list(fragment.parameters())
+    if not params or not isinstance(outer, optim.SGD) or len(outer.param_groups) != 1:
+        return False
+    g = outer.param_groups[0]
+    if g.get("dampening", 0) != 0 or g.get("weight_decay", 0) != 0 or g.get("maximize", False):
+        return False
+    p0 = params[0]
+    if p0.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    for p in params:
+        if (DTensor is not None and isinstance(p, DTensor)) or p.dtype != p0.dtype or p.device != p0.device:
+            return False
+    return True
+
+
+class _FlatDiLoCoFragment(_StreamingDiLoCoFragment):
+    """A fragment kept in four flat buffers on the parameters' device: the live weights (the
+    module's parameters become views into it), the last global weights, the averaged
+    pseudo-gradient and the fp32 outer momentum.
+
+    A synchronisation is then two kernels instead of several passes per parameter:
+    :meth:`Manager.allreduce_delta` (with fp8 on a peer-memory process group: difference,
+    quantisation, reduction and averaging fused) and :func:`torchft_b200.ops.diloco.outer_step_`
+    (momentum, Nesterov step, new backup, blend with the local weights).  The hyperparameters
+    are read from the outer optimizer's single param group at every step, so LR schedulers on
+    it keep working; its momentum state lives in ``outer_momentum`` of the fragment's state
+    dict.  The scheduling and the state-dict key are those of the per-parameter fragment
+    (torchft/local_sgd.py:176-560).
+    """
+
+    _PAD = 128 * 8  # whole quantisation blocks for every team size up to 8
+
+    def __init__(self, *args: Any, **kwargs: Any) -> None:
+        super().__init__(*args, **kwargs)
+        params = [p for _, p in self._model_fragment.named_parameters()]
+        dtype, dev = params[0].dtype, params[0].device
+        n = sum(p.numel() for p in params)
+        padded = (n + self._PAD - 1) // self._PAD * self._PAD
+        self._flat_param = torch.zeros(padded, dtype=dtype, device=dev)
+        self._flat_backup = torch.zeros(padded, dtype=dtype, device=dev)
+        self._flat_grad = torch.zeros(padded, dtype=dtype, device=dev)
+        self._flat_momentum = torch.zeros(padded, dtype=torch.float32, device=dev)
+        self._outer_steps = 0
+        off = 0
+        with torch.no_grad():
+            for name, p in self._model_fragment.named_parameters():
+                k = p.numel()
+                view = self._flat_param[off : off + k].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                self.original_parameters[name] = self._flat_backup[off : off + k].view(p.shape)
+                off += k
+
+    def register_state_dict_fn(self) -> None:
+        key = f"StreamingDiLoCoFragment_{self._fragment_id}"
+
+        def load_fn(sd: Dict[str, Any]) -> None:
+            for name, value in sd["original_parameters"].items():
+                if name in self.original_parameters:
+                    self.original_parameters[name].copy_(value)
+            self._outer_optimizer.load_state_dict(sd["outer_optimizer"])
+            self._flat_momentum.copy_(sd["outer_momentum"])
+            self._outer_steps = int(sd["outer_steps"])
+
+        def save_fn() -> Dict[str, Any]:
+            return {
+                "outer_optimizer": self._outer_optimizer.state_dict(),
+                "original_parameters": {n: t.clone() for n, t in self.original_parameters.items()},
+                "outer_momentum": self._flat_momentum.clone(),
+                "outer_steps": self._outer_steps,
+            }
+
+        self._manager.register_state_dict_fn(key, load_fn, save_fn)
+
+    def save_parameters(self) -> None:
+        with torch.no_grad():
+            self._flat_backup.copy_(self._flat_param)
+
+    def restore_parameters(self) -> None:
+        with torch.no_grad():
+            self._flat_param.copy_(self._flat_backup)
+
+    def prepare_sync(self) -> None:
+        with torch.profiler.record_function("torchft::local_sgd::prepare_sync"), torch.no_grad():
+            assert not self._allreduce_work
+            early = self._fragment_sync_delay > 0
+            if early:
+                # inner steps go on while the exchange is in flight: take the difference now
+                torch.sub(self._flat_backup, self._flat_param, out=self._flat_grad)
+            if self._stream is not None:
+                self._stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._stream) if self._stream is not None else nullcontext():
+                if early:
+                    work = self._manager.allreduce(self._flat_grad, should_quantize=self.should_quantize)
+                else:
+                    work = self._manager.allreduce_delta(self._flat_grad, self._flat_backup, self._flat_param,
+                                                         should_quantize=self.should_quantize)
+                self._allreduce_work.append(work)
+
+    def perform_sync(self) -> bool:
+        from .ops.diloco import outer_step_
+
+        with torch.profiler.record_function("torchft::local_sgd::perform_sync"), torch.no_grad():
+            assert self._allreduce_work
+            with torch.cuda.stream(self._stream) if self._stream is not None else nullcontext():
+                for w in self._allreduce_work:
+                    w.wait()
+                if self._stream is not None:
+                    self._stop_event = torch.cuda.Event()
+                    self._stop_event.record()
+            self.wait()
+            committed = self._manager.should_commit()
+            if committed:
+                g = self._outer_optimizer.param_groups[0]
+                outer_step_(self._flat_grad, self._flat_momentum, self._flat_backup, self._flat_param, lr=float(g["lr"]),
+                            momentum_coef=float(g.get("momentum", 0.0)), alpha=self._fragment_update_alpha,
+                            nesterov=bool(g.get("nesterov", False)), first_step=self._outer_steps == 0)
+                self._outer_steps += 1
+            else:
+                # back to the last global weights; the manager step did not advance, so the window is retried
+                self._flat_param.copy_(self._flat_backup)
+            return committed
+
+
 class DiLoCo:
     """(Streaming) DiLoCo as a context manager around the inner optimizer.
 
@@ -344,6 +471,11 @@ class DiLoCo:
     ``use_async_quorum=False`` (a healing replica must have its weights before it
     computes a pseudo-gradient).  If a window does not commit, the fragment is reset to
     the last global weights and, the manager step not having advanced, retried.
+
+    ``flat_fragments`` keeps every fragment in flat device buffers and synchronises it with
+    two fused kernels (see :class:`_FlatDiLoCoFragment`); it needs a momentum-SGD outer
+    optimizer without damping or weight decay.  Default: on for CUDA parameters unless ``backup_device`` names
+    the host.
     """
 
     def __init__(
@@ -360,6 +492,7 @@ class DiLoCo:
         should_quantize: bool = False,
         fragment_sync_delay: int = 0,
         fragment_update_alpha: float = 0.0,
+        flat_fragments: Optional[bool] = None,
     ) -> None:
         n = len(model_fragments)
         if isinstance(outer_optimizer, list):
@@ -384,8 +517,18 @@ class DiLoCo:
         self._fragment_sync_delay = fragment_sync_delay
         self._hooks: List[RemovableHandle] = []
         self._local_optimizer = inner_optimizer
+        outers = outer_optimizer if isinstance(outer_optimizer, list) else [outer_optimizer] * n
+        eligible = all(_flat_eligible(f, o) for f, o in zip(model_fragments, outers))
+        if flat_fragments is None:
+            # HBM holds the backup next to the weights unless the caller asked for a host backup
+            on_gpu = all(p.is_cuda for f in model_fragments for p in f.parameters())
+            flat_fragments = eligible and on_gpu and (backup_device is None or backup_device.type == "cuda")
+        elif flat_fragments and not eligible:
+            raise ValueError("flat_fragments needs plain fp32/bf16 parameters and a plain momentum-SGD outer optimizer")
+        self.flat_fragments = bool(flat_fragments)
+        fragment_cls = _FlatDiLoCoFragment if self.flat_fragments else _StreamingDiLoCoFragment
         self._fragments: List[_StreamingDiLoCoFragment] = [
-            _StreamingDiLoCoFragment(
+            fragment_cls(
                 manager,
                 frag,
                 i,

@@ -328,6 +328,39 @@ class Manager:
                 self.report_error(e)
                 return _DummyWork(tensor)
 
+    def allreduce_delta(self, out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, should_quantize: bool = False) -> Work:
+        """``out`` = average over the participating replicas of ``a - b`` (flat tensors of one
+        dtype and size); the pseudo-gradient exchange of LocalSGD/DiLoCo.  On a process group
+        with a fused quantised allreduce (``allreduce_fp8``) and ``should_quantize``, the
+        difference, the quantisation, the reduction and the division are one kernel per rank
+        and ``a - b`` is never written to memory; otherwise this is ``out = a - b`` followed
+        by :meth:`allreduce`.  Error behaviour is that of :meth:`allreduce`.
+        """
+        fused = (should_quantize and out.is_cuda and hasattr(self._pg, "allreduce_fp8")
+                 and out.is_contiguous() and a.is_contiguous() and b.is_contiguous())
+        if fused:
+            if self.errored():
+                return _DummyWork(out)
+            self.wait_quorum()
+            fused = out.numel() % (128 * max(1, self._pg.size())) == 0
+        if not fused:
+            torch.sub(a, b, out=out)
+            return self.allreduce(out, should_quantize=should_quantize)
+        with torch.profiler.record_function("torchft::manager::allreduce_delta"):
+            try:
+                self._pg.allreduce_fp8(  # type: ignore[attr-defined]
+                    a.view(-1), out.view(-1), 1.0 / max(1, self.num_participants()), minus=b.view(-1),
+                    zero_contribution=not self.is_participating())
+                ev = torch.cuda.Event()
+                ev.record()
+                from .collectives import _StreamOrderedWork
+
+                return _ManagedWork(self, _StreamOrderedWork(ev, [out]), out)
+            except Exception as e:
+                self._logger.exception(f"got exception in allreduce_delta -- skipping remaining: {e}")
+                self.report_error(e)
+                return _DummyWork(out)
+
     def report_error(self, e: Exception) -> None:
         """Latch an error: the current step will not commit and the rest of its
         collectives become no-ops.  Cleared by the next :meth:`start_quorum`."""

@@ -21,6 +21,7 @@ RoPE rotates interleaved pairs ``(2i, 2i+1)`` with ``theta = rope_theta``.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Dict, List, Optional, Tuple
 
@@ -146,6 +147,58 @@ class SdpaAttention:
         self._saved.clear()
 
 
+class Tcgen05Attention:
+    """Causal GQA attention on the hand-written tcgen05 kernels.  Q, K and V are read in
+    place from the packed QKV activation and dQ, dK, dV are written in place into the packed
+    dQKV workspace; only the per-row log-sum-exp is saved between the passes."""
+
+    def __init__(self, cfg: LlamaConfig):
+        self.cfg = cfg
+        self._saved: Dict[int, Tuple[torch.Tensor, ...]] = {}
+        self._lse_pool: List[torch.Tensor] = []
+
+    def _views(self, qkv: torch.Tensor):
+        c = self.cfg
+        a, b = c.n_heads * c.head_dim, (c.n_heads + c.n_kv_heads) * c.head_dim
+        return qkv[:, :a], qkv[:, a:b], qkv[:, b:]
+
+    def forward(self, layer: int, qkv: torch.Tensor, batch: int, seq: int, out: torch.Tensor, need_grad: bool) -> None:
+        c = self.cfg
+        q, k, v = self._views(qkv)
+        lse = None
+        if need_grad:
+            lse = self._lse_pool.pop() if self._lse_pool else torch.empty(batch, c.n_heads, seq, dtype=torch.float32,
+                                                                          device=qkv.device)
+            self._saved[layer] = (qkv, out, lse)
+        K.attention_fwd(q, k, v, batch, seq, c.n_heads, c.n_kv_heads, c.head_dim, out, lse, causal=True)
+
+    def backward(self, layer: int, dout: torch.Tensor, batch: int, seq: int, dqkv: torch.Tensor) -> None:
+        c = self.cfg
+        qkv, out, lse = self._saved.pop(layer)
+        q, k, v = self._views(qkv)
+        dq, dk, dv = self._views(dqkv)
+        K.attention_bwd(q, k, v, out, dout, lse, dq, dk, dv, batch, seq, c.n_heads, c.n_kv_heads, c.head_dim, causal=True)
+        self._lse_pool.append(lse)
+
+    def reset(self) -> None:
+        for _, _, lse in self._saved.values():
+            self._lse_pool.append(lse)
+        self._saved.clear()
+
+
+def make_attention(cfg: LlamaConfig, seq_len: int, device: torch.device, kind: Optional[str] = None):
+    """``kind``: "tcgen05" (hand-written kernels; head dim 128, sequence a multiple of 128,
+    CUDA), "sdpa" (library), or None for tcgen05 where it applies.  The environment variable
+    ``FTB200_ATTENTION`` overrides None."""
+    kind = kind or os.environ.get("FTB200_ATTENTION") or "auto"
+    ok = device.type == "cuda" and K.attention_supported(seq_len, cfg.head_dim)
+    if kind == "tcgen05" and not ok:
+        raise ValueError("tcgen05 attention needs CUDA, head_dim 128 and seq_len % 128 == 0")
+    if kind == "tcgen05" or (kind == "auto" and ok):
+        return Tcgen05Attention(cfg)
+    return SdpaAttention(cfg)
+
+
 class LlamaEngine:
     """Forward/backward of a Llama decoder over externally owned parameter/grad units.
 
@@ -175,7 +228,9 @@ class LlamaEngine:
         self.param_unit, self.grad_unit = param_unit, grad_unit
         self.before_unit = before_unit or (lambda u, backward: None)
         self.grad_done = grad_done or (lambda u: None)
-        self.attn = attention if attention is not None else SdpaAttention(cfg)
+        if attention is None or isinstance(attention, str):
+            attention = make_attention(cfg, seq_len, device, attention)
+        self.attn = attention
         self.logit_chunks = max(1, logit_chunks)
         while self.T % self.logit_chunks:
             self.logit_chunks -= 1

@@ -490,3 +490,93 @@ def ref_attention(q, k, v, causal=True):
         s = s.masked_fill(~mask, float("-inf"))
     p = torch.softmax(s, dim=-1)
     return (p @ vf).permute(0, 2, 1, 3).to(q.dtype)
+
+
+def ref_attention_lse(q, k, v, causal=True):
+    """Row-wise ``logsumexp(scale * q k^T)`` ``[B,Hq,S]`` (fp32) of the same problem."""
+    B, S, Hq, Dh = q.shape
+    rep = Hq // k.shape[2]
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(rep, dim=1)
+    s = qf @ kf.transpose(-1, -2) / math.sqrt(Dh)
+    if causal:
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        s = s.masked_fill(~mask, float("-inf"))
+    return torch.logsumexp(s, dim=-1)
+
+
+def attention_supported(seq_len: int, head_dim: int) -> bool:
+    """Shapes the tcgen05 attention kernels take: head dim 128, 128-row blocks."""
+    return head_dim == 128 and seq_len % 128 == 0
+
+
+def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int, seq_len: int, n_heads: int,
+                  n_kv_heads: int, head_dim: int, out: torch.Tensor, lse: Optional[torch.Tensor] = None,
+                  causal: bool = True) -> None:
+    """Causal GQA attention forward.  ``q`` ``[batch*seq, n_heads*head_dim]`` and ``k``/``v``
+    ``[batch*seq, n_kv_heads*head_dim]`` are 2-D bf16 views (column slices of the packed QKV
+    activation are fine), ``out`` ``[batch*seq, n_heads*head_dim]``, ``lse`` ``[batch, n_heads,
+    seq]`` fp32 (saved for the backward pass)."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (out, "out")):
+        _check_2d_bf16(t, name)
+    if not q.is_cuda:
+        B, S = batch, seq_len
+        q4, k4, v4 = (t.reshape(B, S, -1, head_dim) for t in (q, k, v))
+        out.copy_(ref_attention(q4, k4, v4, causal).reshape(B * S, -1))
+        if lse is not None:
+            lse.copy_(ref_attention_lse(q4, k4, v4, causal))
+        return
+    scale = 1.0 / math.sqrt(head_dim)
+    N.check(
+        N.lib().ftb200_attention_fwd(ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(batch), c_int(seq_len), c_int(n_heads),
+                                     c_int(n_kv_heads), c_int(head_dim), c_ll(q.stride(0)), c_ll(k.stride(0)),
+                                     c_ll(v.stride(0)), c_ll(out.stride(0)), c_float(scale), c_int(int(causal)),
+                                     ptr(status_word(q.device)), stream_ptr()),
+        "attention_fwd",
+    )
+
+
+def ref_attention_bwd(q, k, v, d_o, causal=True):
+    """(dq, dk, dv) of :func:`ref_attention` by autograd in fp32; 4-D inputs as there."""
+    q, k, v = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    o = ref_attention(q, k, v, causal)
+    return torch.autograd.grad(o, (q, k, v), d_o.float())
+
+
+_attn_scratch: dict = {}
+
+
+def attention_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
+                  lse: torch.Tensor, dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, batch: int, seq_len: int,
+                  n_heads: int, n_kv_heads: int, head_dim: int, causal: bool = True) -> None:
+    """Backward of :func:`attention_fwd`: writes ``dq``, ``dk``, ``dv`` (2-D bf16 views like
+    ``q``, ``k``, ``v``; column slices of a packed dQKV buffer are fine).  The fp32 dQ
+    accumulator lives in a per-device scratch buffer that is reused across calls on the same
+    stream."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (d_o, "d_o"), (dq, "dq"), (dk, "dk"), (dv, "dv")):
+        _check_2d_bf16(t, name)
+    if not q.is_cuda:
+        B, S = batch, seq_len
+        q4, k4, v4, do4 = (t.reshape(B, S, -1, head_dim) for t in (q, k, v, d_o))
+        gq, gk, gv = ref_attention_bwd(q4, k4, v4, do4, causal)
+        dq.copy_(gq.reshape(B * S, -1))
+        dk.copy_(gk.reshape(B * S, -1))
+        dv.copy_(gv.reshape(B * S, -1))
+        return
+    lib = N.lib()
+    lib.ftb200_attention_bwd_scratch_bytes.restype = ctypes.c_longlong
+    need = int(lib.ftb200_attention_bwd_scratch_bytes(c_int(batch), c_int(seq_len), c_int(n_heads)))
+    key = (q.device.index, torch.cuda.current_stream().cuda_stream)
+    scratch = _attn_scratch.get(key)
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _attn_scratch[key] = scratch
+    scale = 1.0 / math.sqrt(head_dim)
+    N.check(
+        lib.ftb200_attention_bwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(d_o), ptr(lse), ptr(dq), ptr(dk), ptr(dv), ptr(scratch),
+                                 c_int(batch), c_int(seq_len), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+                                 c_ll(q.stride(0)), c_ll(k.stride(0)), c_ll(v.stride(0)), c_ll(o.stride(0)),
+                                 c_ll(d_o.stride(0)), c_ll(dq.stride(0)), c_ll(dk.stride(0)), c_ll(dv.stride(0)),
+                                 c_float(scale), c_int(int(causal)), ptr(status_word(q.device)), stream_ptr()),
+        "attention_bwd", launches=3,
+    )

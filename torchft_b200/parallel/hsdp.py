@@ -46,7 +46,7 @@ class ShardedLlamaTrainer:
         attention=None,
         logit_chunks: int = 4,
         replica_alloc=None,
-        fused_reduce_scatter: bool = True,
+        fused_reduce_scatter: bool = False,
     ):
         self.cfg, self.device = cfg, device
         self.comm = shard_comm or LocalShardComm()
@@ -287,6 +287,13 @@ class ShardedLlamaTrainer:
         if self.manager is None or self.manager.should_commit():
             self.optimizer_step()
         return loss
+
+    def invalidate_gathered(self, units) -> None:
+        """The shards of ``units`` were rewritten outside :meth:`optimizer_step`: gather them
+        again before their next use."""
+        if self.comm.size > 1:
+            for u in units:
+                self._gathered[u] = False
 
     # ---- state dict (heal / durable checkpoints) -------------------------------------------
     def state_dict(self) -> Dict[str, object]:

@@ -502,10 +502,12 @@ class ProcessGroupB200(ProcessGroup):
             pos += m
 
     def allreduce_fp8(self, src: torch.Tensor, dst: torch.Tensor, scale: float = 1.0,
-                      minus: Optional[torch.Tensor] = None) -> None:
+                      minus: Optional[torch.Tensor] = None, zero_contribution: bool = False) -> None:
         """Quantised allreduce of flat ``src`` (or ``src - minus``) into ``dst`` as one fused
         kernel per rank: block-scaled e4m3 on the wire, fp32 accumulation, ``scale`` folded
-        in.  ``numel`` must be a multiple of ``128 * world``; runs on the current stream."""
+        in.  ``numel`` must be a multiple of ``128 * world``; runs on the current stream.
+        With ``zero_contribution`` this rank takes part but adds nothing (a healing or spare
+        replica)."""
         from .. import quantization as Q
 
         n = src.numel()
@@ -520,8 +522,8 @@ class ProcessGroupB200(ProcessGroup):
                 self._team.lib.ftb200_team_allreduce_fp8(
                     ctypes.byref(d), self._team._peer_ptrs(self._staging_off), N.ptr(src[pos : pos + m]),
                     N.ptr(minus[pos : pos + m] if minus is not None else None), N.ptr(dst[pos : pos + m]),
-                    ctypes.c_longlong(m), ctypes.c_int(_DT[src.dtype]), ctypes.c_float(scale), ctypes.c_int(0),
-                    ctypes.c_int(0), N.stream_ptr()),
+                    ctypes.c_longlong(m), ctypes.c_int(_DT[src.dtype]), ctypes.c_float(scale),
+                    ctypes.c_int(int(zero_contribution)), ctypes.c_int(0), N.stream_ptr()),
                 "team_allreduce_fp8",
             )
             pos += m
