@@ -16,7 +16,7 @@
 // whole CTA; dQ^T is drained every tile and added to an fp32 accumulator in global memory with
 // coalesced reductions (one query row, 32 consecutive head-dim elements per warp instruction).
 //
-// Warps: 0 = TMA (K, V once; Q, dO, lse, delta per tile, 2 stages), 1 = MMA issue, 2..9 =
+// Warps: 0 = TMA (K, V once; Q, dO, lse, delta per tile, 2 stages), 1 = MMA issue, 2..17 =
 // softmax / dQ drain / final dK, dV store.  The tail MMAs of tile t-1 are issued after S and dP
 // of tile t, so the tensor cores work under the softmax of tile t.  All waits are bounded.
 #include <cuda.h>
@@ -33,7 +33,10 @@ using namespace ftb200::tc;
 constexpr int D = 128;
 constexpr int BKV = 128;
 constexpr int BQ = 64;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 576;
+constexpr int SOFTMAX_THREADS = 512;
+constexpr int GROUPS = 4;          // threads per key row
+constexpr int CPT = BQ / GROUPS;   // query columns per thread
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 192, COL_DV = 256, COL_DK = 384;
 constexpr uint32_t KV_TILE = BKV * D * 2;      // 32 KB, two slabs of [128 rows x 128 B]
@@ -44,27 +47,29 @@ constexpr uint32_t PT_TILE = BKV * BQ * 2;     // 16 KB, one slab of [128 key ro
 constexpr uint32_t OFF_K = 0, OFF_V = KV_TILE;
 constexpr uint32_t OFF_STAGE = 2 * KV_TILE;    // per stage: Q, dO
 constexpr uint32_t STAGE_BYTES = 2 * Q_TILE;
-constexpr uint32_t OFF_PDS = OFF_STAGE + 2 * STAGE_BYTES;  // per buffer: P^T, dS^T
+constexpr int QDO_STAGES = 3;  // a stage is held until the tile's dV/dK MMAs are done, two tiles after its load began
+constexpr uint32_t OFF_PDS = OFF_STAGE + QDO_STAGES * STAGE_BYTES;  // per buffer: P^T, dS^T
 constexpr uint32_t PDS_BYTES = 2 * PT_TILE;
 constexpr uint32_t OFF_STATS = OFF_PDS + 2 * PDS_BYTES;    // per stage: lse[64], delta[64]
 constexpr uint32_t STATS_BYTES = 2 * BQ * 4;
-constexpr uint32_t OFF_MISC = OFF_STATS + 2 * STATS_BYTES;
+constexpr uint32_t OFF_MISC = OFF_STATS + QDO_STAGES * STATS_BYTES;
 constexpr uint32_t SMEM_BYTES = OFF_MISC + 256 + 1024;
+static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
 
 enum : int {
   BAR_KV = 0,
-  BAR_QDO_FULL = 1,   // +stage
-  BAR_QDO_EMPTY = 3,  // +stage
-  BAR_S_FULL = 5,     // +buf
-  BAR_S_EMPTY = 7,    // +buf
-  BAR_DP_FULL = 9,
-  BAR_DP_EMPTY = 10,
-  BAR_PDS_FULL = 11,  // +buf
-  BAR_PDS_EMPTY = 13, // +buf
-  BAR_DQ_FULL = 15,
-  BAR_DQ_EMPTY = 16,
-  BAR_DKV_DONE = 17,
-  NUM_BARS = 18,
+  BAR_QDO_FULL = 1,   // +stage (3)
+  BAR_QDO_EMPTY = 4,  // +stage (3)
+  BAR_S_FULL = 7,     // +buf
+  BAR_S_EMPTY = 9,    // +buf
+  BAR_DP_FULL = 11,
+  BAR_DP_EMPTY = 12,
+  BAR_PDS_FULL = 13,  // +buf
+  BAR_PDS_EMPTY = 15, // +buf
+  BAR_DQ_FULL = 17,
+  BAR_DQ_EMPTY = 18,
+  BAR_DKV_DONE = 19,
+  NUM_BARS = 20,
 };
 
 struct BwdParams {
@@ -120,18 +125,20 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
   if (threadIdx.x == 0) {
     mbar_init(bar(BAR_KV), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < QDO_STAGES; ++s) {
       mbar_init(bar(BAR_QDO_FULL + s), 1);
       mbar_init(bar(BAR_QDO_EMPTY + s), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_S_FULL + s), 1);
-      mbar_init(bar(BAR_S_EMPTY + s), 256);
-      mbar_init(bar(BAR_PDS_FULL + s), 256);
+      mbar_init(bar(BAR_S_EMPTY + s), SOFTMAX_THREADS);
+      mbar_init(bar(BAR_PDS_FULL + s), SOFTMAX_THREADS);
       mbar_init(bar(BAR_PDS_EMPTY + s), 1);
     }
     mbar_init(bar(BAR_DP_FULL), 1);
-    mbar_init(bar(BAR_DP_EMPTY), 256);
+    mbar_init(bar(BAR_DP_EMPTY), SOFTMAX_THREADS);
     mbar_init(bar(BAR_DQ_FULL), 1);
-    mbar_init(bar(BAR_DQ_EMPTY), 256);
+    mbar_init(bar(BAR_DQ_EMPTY), SOFTMAX_THREADS);
     mbar_init(bar(BAR_DKV_DONE), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -158,8 +165,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tma_load_2d(smem_base + OFF_V + KV_SLAB, &tmV, bar(BAR_KV), hk * D + 64, kv_row0);
       bool ok = true;
       for (int t = 0; t < T && ok; ++t) {
-        const int st = t & 1;
-        const uint32_t use = static_cast<uint32_t>(t >> 1);
+        const int st = t % QDO_STAGES;
+        const uint32_t use = static_cast<uint32_t>(t / QDO_STAGES);
         if (!mbar_wait(bar(BAR_QDO_EMPTY + st), (use & 1u) ^ 1u, abort_flag)) {
           ok = false;
           break;
@@ -196,15 +203,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       bool ok = mbar_wait(bar(BAR_KV), 0, abort_flag);
       for (int t = 0; t <= T && ok; ++t) {
         if (t < T) {
-          const int st = t & 1;
+          const int st = t & 1, qs = t % QDO_STAGES;
           const uint32_t use = static_cast<uint32_t>(t >> 1);
-          if (!mbar_wait(bar(BAR_QDO_FULL + st), use & 1u, abort_flag) ||
+          if (!mbar_wait(bar(BAR_QDO_FULL + qs), static_cast<uint32_t>(t / QDO_STAGES) & 1u, abort_flag) ||
               !mbar_wait(bar(BAR_S_EMPTY + st), (use & 1u) ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sq = smem_base + OFF_STAGE + st * STAGE_BYTES;
+          const uint32_t sq = smem_base + OFF_STAGE + qs * STAGE_BYTES;
           const uint32_t sdo = sq + Q_TILE;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
@@ -227,14 +234,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           umma_commit(bar(BAR_DP_FULL));
         }
         if (t >= 1) {
-          const int u = t - 1, pb = u & 1;
+          const int u = t - 1, pb = u & 1, qs = u % QDO_STAGES;
           const uint32_t use = static_cast<uint32_t>(u >> 1);
           if (!mbar_wait(bar(BAR_PDS_FULL + pb), use & 1u, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sq = smem_base + OFF_STAGE + pb * STAGE_BYTES;
+          const uint32_t sq = smem_base + OFF_STAGE + qs * STAGE_BYTES;
           const uint32_t sdo = sq + Q_TILE;
           const uint32_t spt = smem_base + OFF_PDS + pb * PDS_BYTES;
           const uint32_t sds = spt + PT_TILE;
@@ -248,7 +255,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             umma_bf16(tmem_base + COL_DK, make_smem_desc(sds + kk * 32, 16, 1024),
                       make_smem_desc(sq + kk * 2048, Q_SLAB, 1024), idesc_kv, (u | kk) != 0);
           }
-          umma_commit(bar(BAR_QDO_EMPTY + pb));
+          umma_commit(bar(BAR_QDO_EMPTY + qs));
           if (!mbar_wait(bar(BAR_DQ_EMPTY), (static_cast<uint32_t>(u) & 1u) ^ 1u, abort_flag)) {
             ok = false;
             break;
@@ -267,9 +274,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     __syncwarp();
   } else {
-    // ---------------- softmax, dQ drain, dK/dV store (warps 2..9) ----------------
+    // ---------------- softmax, dQ drain, dK/dV store (warps 2..17) ----------------
     const int quarter = warp & 3;
-    const int g = (warp - 2) >> 2;  // which 32 of the tile's 64 queries (64 of 128 columns at the end)
+    const int g = (warp - 2) >> 2;  // which 16 of the tile's 64 queries (32 of 128 columns at the end)
     const int row = quarter * 32 + lane;  // key within the block; head-dim index when draining dQ^T
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float log2e = 1.4426950408889634f;
@@ -278,19 +285,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     auto drain_dq = [&](int u) -> bool {
       if (!mbar_wait(bar(BAR_DQ_FULL), static_cast<uint32_t>(u) & 1u, abort_flag)) return false;
       tc_fence_after();
-      uint32_t v[32];
-      tmem_ld32(tmem_base + COL_DQ + g * 32 + lane_addr, v);
+      uint32_t v[CPT];
+      tmem_ld16(tmem_base + COL_DQ + g * CPT + lane_addr, v);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(BAR_DQ_EMPTY));
       int h, qt;
       tile_of(u, h, qt);
-      float* dst = p.dq_acc + (static_cast<long long>(b) * p.seq + qt * BQ + g * 32) * (static_cast<long long>(p.n_heads) * D) +
-                   h * D + row;
+      const long long ldq = static_cast<long long>(p.n_heads) * D;
+      float* dst = p.dq_acc + (static_cast<long long>(b) * p.seq + qt * BQ + g * CPT) * ldq + h * D + row;
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        atomicAdd(dst + static_cast<long long>(c) * p.n_heads * D, __uint_as_float(v[c]));
-      }
+      for (int c = 0; c < CPT; ++c) atomicAdd(dst + c * ldq, __uint_as_float(v[c]));
       return true;
     };
 
@@ -304,8 +309,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         break;
       }
       tc_fence_after();
-      uint32_t sv[32], dp[32];
-      tmem_ld32(tmem_base + COL_S + st * BQ + g * 32 + lane_addr, sv);
+      uint32_t sv[CPT], dp[CPT];
+      tmem_ld16(tmem_base + COL_S + st * BQ + g * CPT + lane_addr, sv);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(BAR_S_EMPTY + st));
@@ -314,30 +319,39 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         break;
       }
       tc_fence_after();
-      tmem_ld32(tmem_base + COL_DP + g * 32 + lane_addr, dp);
+      tmem_ld16(tmem_base + COL_DP + g * CPT + lane_addr, dp);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(BAR_DP_EMPTY));
       // the tile's statistics arrived with Q and dO
-      if (!mbar_wait(bar(BAR_QDO_FULL + st), use & 1u, abort_flag)) {
+      const int qs = t % QDO_STAGES;
+      if (!mbar_wait(bar(BAR_QDO_FULL + qs), static_cast<uint32_t>(t / QDO_STAGES) & 1u, abort_flag)) {
         ok = false;
         break;
       }
-      const float* stats = reinterpret_cast<const float*>(smem + OFF_STATS + st * STATS_BYTES);
-      const int key = jb * BKV + row;
-      const int q0 = qt * BQ + g * 32;
-      const bool diag = p.causal && (q0 < jb * BKV + BKV);
-      uint32_t pk[16], dk[16];
+      const float4* stats4 = reinterpret_cast<const float4*>(smem + OFF_STATS + qs * STATS_BYTES);
+      float lse_q[CPT], del_q[CPT];
 #pragma unroll
-      for (int c = 0; c < 16; ++c) {
+      for (int c = 0; c < CPT / 4; ++c) {
+        const float4 a = stats4[g * (CPT / 4) + c];
+        const float4 d4 = stats4[BQ / 4 + g * (CPT / 4) + c];
+        lse_q[4 * c] = a.x; lse_q[4 * c + 1] = a.y; lse_q[4 * c + 2] = a.z; lse_q[4 * c + 3] = a.w;
+        del_q[4 * c] = d4.x; del_q[4 * c + 1] = d4.y; del_q[4 * c + 2] = d4.z; del_q[4 * c + 3] = d4.w;
+      }
+      const int key = jb * BKV + row;
+      const int q0 = qt * BQ + g * CPT;
+      const bool diag = p.causal && (q0 < jb * BKV + BKV);
+      uint32_t pk[CPT / 2], dk[CPT / 2];
+#pragma unroll
+      for (int c = 0; c < CPT / 2; ++c) {
         float pv[2], dv[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          const int qi = g * 32 + 2 * c + e;
-          float pe = exp2f(fmaf(__uint_as_float(sv[2 * c + e]), p.scale_log2, -stats[qi] * log2e));
-          if (diag && key > q0 + 2 * c + e) pe = 0.f;
+          const int qi = 2 * c + e;
+          float pe = exp2f(fmaf(__uint_as_float(sv[qi]), p.scale_log2, -lse_q[qi] * log2e));
+          if (diag && key > q0 + qi) pe = 0.f;
           pv[e] = pe;
-          dv[e] = pe * (__uint_as_float(dp[2 * c + e]) - stats[BQ + qi]) * p.scale;
+          dv[e] = pe * (__uint_as_float(dp[qi]) - del_q[qi]) * p.scale;
         }
         __nv_bfloat162 a = __floats2bfloat162_rn(pv[0], pv[1]);
         __nv_bfloat162 d2 = __floats2bfloat162_rn(dv[0], dv[1]);
@@ -351,8 +365,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       uint8_t* prow = smem + OFF_PDS + st * PDS_BYTES + row * 128;
       uint8_t* drow = prow + PT_TILE;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int chunk = ((g * 4 + c) ^ (row & 7)) << 4;
+      for (int c = 0; c < CPT / 8; ++c) {
+        const int chunk = ((g * (CPT / 8) + c) ^ (row & 7)) << 4;
         *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
       }
@@ -368,22 +382,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + g * 64;
+        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + g * 32;
         __nv_bfloat16* base = which == 0 ? p.dV : p.dK;
         const long long ld = which == 0 ? p.ld_dv : p.ld_dk;
-        __nv_bfloat16* dst = base + static_cast<long long>(kv_row0 + row) * ld + hk * D + g * 64;
+        __nv_bfloat16* dst = base + static_cast<long long>(kv_row0 + row) * ld + hk * D + g * 32;
+        uint32_t v[32];
+        tmem_ld32(tmem_base + col + lane_addr, v);
+        tmem_wait_ld();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t v[32];
-          tmem_ld32(tmem_base + col + half * 32 + lane_addr, v);
-          tmem_wait_ld();
+        for (int c = 0; c < 4; ++c) {
+          float f[8];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * c + e]);
-            reinterpret_cast<ftb200::bf16x8*>(dst + half * 32)[c] = ftb200::pack8(f);
-          }
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * c + e]);
+          reinterpret_cast<ftb200::bf16x8*>(dst)[c] = ftb200::pack8(f);
         }
       }
     }

@@ -9,7 +9,7 @@
 // One CTA owns one (batch, head, 128-query block).  Per 128-key block:
 //   warp 0            TMA: K and V tiles into a 2-stage ring (Q once)
 //   warp 1            tcgen05.mma: S = Q K^T into one of two TMEM buffers, O += P V
-//   warps 2..9        softmax: two threads per query row (64 keys each); scores come from TMEM
+//   warps 2..17       softmax: four threads per query row (32 keys each); scores come from TMEM
 //                     (tcgen05.ld), P goes to shared memory in the 128-byte-swizzled K-major
 //                     layout that the second MMA reads
 // S of block j+1 is issued before P V of block j, so the tensor cores work on the next scores
@@ -36,7 +36,10 @@ constexpr int BKV = 128;     // keys per block
 constexpr uint32_t TILE_BYTES = 128 * 128 * 2;  // every operand tile: 128 x 128 bf16
 constexpr uint32_t SLAB_BYTES = TILE_BYTES / 2;  // 128 rows x 64 elements, one swizzle atom wide
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 320;
+constexpr int NUM_THREADS = 576;
+constexpr int SOFTMAX_THREADS = 512;
+constexpr int GROUPS = 4;   // threads per query row
+constexpr int CPT = BKV / GROUPS;  // score columns per thread
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 256;
 // smem: Q | K0 V0 | K1 V1 | P | barriers + exchange
@@ -44,7 +47,7 @@ constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_KV = TILE_BYTES;
 constexpr uint32_t OFF_P = OFF_KV + KV_STAGES * 2 * TILE_BYTES;
 constexpr uint32_t OFF_MISC = OFF_P + TILE_BYTES;
-constexpr uint32_t MISC_BYTES = 256 + 2 * 2 * BQ * 4;
+constexpr uint32_t MISC_BYTES = 256 + 2 * GROUPS * BQ * 4;
 constexpr uint32_t SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
@@ -63,13 +66,14 @@ enum : int {
   BAR_Q = 0,
   BAR_K_FULL = 1,    // +stage
   BAR_V_FULL = 3,    // +stage
-  BAR_KV_EMPTY = 5,  // +stage
+  BAR_K_EMPTY = 5,   // +stage: K is free once its S MMA is done, long before V
   BAR_S_FULL = 7,    // +buf
   BAR_S_EMPTY = 9,   // +buf
   BAR_P_FULL = 11,
   BAR_O_DONE = 12,
   BAR_XCHG = 13,     // +parity
-  NUM_BARS = 15,
+  BAR_V_EMPTY = 15,  // +stage
+  NUM_BARS = 17,
 };
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -78,8 +82,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_MISC);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 132);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC + 192);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 196);
   float* xchg = reinterpret_cast<float*>(smem + OFF_MISC + 256);  // [parity][group][row]
 
   const int warp = threadIdx.x >> 5;
@@ -103,12 +107,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
       mbar_init(bar(BAR_V_FULL + s), 1);
-      mbar_init(bar(BAR_KV_EMPTY + s), 1);
+      mbar_init(bar(BAR_K_EMPTY + s), 1);
+      mbar_init(bar(BAR_V_EMPTY + s), 1);
       mbar_init(bar(BAR_S_FULL + s), 1);
-      mbar_init(bar(BAR_S_EMPTY + s), 256);
-      mbar_init(bar(BAR_XCHG + s), 256);
+      mbar_init(bar(BAR_S_EMPTY + s), SOFTMAX_THREADS);
+      mbar_init(bar(BAR_XCHG + s), SOFTMAX_THREADS);
     }
-    mbar_init(bar(BAR_P_FULL), 256);
+    mbar_init(bar(BAR_P_FULL), SOFTMAX_THREADS);
     mbar_init(bar(BAR_O_DONE), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -135,7 +140,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j & 1;
         const uint32_t use = static_cast<uint32_t>(j >> 1);
-        if (!mbar_wait(bar(BAR_KV_EMPTY + st), (use & 1u) ^ 1u, abort_flag)) {
+        if (!mbar_wait(bar(BAR_K_EMPTY + st), (use & 1u) ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
@@ -145,6 +150,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         mbar_expect_tx(bar(BAR_K_FULL + st), TILE_BYTES);
         tma_load_2d(sk, &tmK, bar(BAR_K_FULL + st), hk * D, kv_row0);
         tma_load_2d(sk + SLAB_BYTES, &tmK, bar(BAR_K_FULL + st), hk * D + 64, kv_row0);
+        if (!mbar_wait(bar(BAR_V_EMPTY + st), (use & 1u) ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
         mbar_expect_tx(bar(BAR_V_FULL + st), TILE_BYTES);
         tma_load_2d(sv, &tmV, bar(BAR_V_FULL + st), hk * D, kv_row0);
         tma_load_2d(sv + SLAB_BYTES, &tmV, bar(BAR_V_FULL + st), hk * D + 64, kv_row0);
@@ -175,6 +184,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           umma_bf16(d_tmem, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_s, kk != 0);
         }
         umma_commit(bar(BAR_S_FULL + st));
+        umma_commit(bar(BAR_K_EMPTY + st));
       };
       bool ok = mbar_wait(bar(BAR_Q), 0, abort_flag) && mbar_wait(bar(BAR_K_FULL + 0), 0, abort_flag);
       if (ok) {
@@ -210,16 +220,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           const uint64_t bdesc = make_smem_desc(sv + kk * 2048, SLAB_BYTES, 1024);
           umma_bf16(d_tmem, adesc, bdesc, idesc_o, (j | kk) != 0);
         }
-        umma_commit(bar(BAR_KV_EMPTY + st));
+        umma_commit(bar(BAR_V_EMPTY + st));
         umma_commit(bar(BAR_O_DONE));
       }
     }
     __syncwarp();
   } else {
-    // ---------------- softmax + epilogue (warps 2..9) ----------------
+    // ---------------- softmax + epilogue (warps 2..17) ----------------
     const int sw = warp - 2;
     const int quarter = warp & 3;   // TMEM lane quarter this warp may touch
-    const int g = sw >> 2;          // which 64 keys (and, in the epilogue, which 64 output columns)
+    const int g = sw >> 2;          // which 32 keys (and, in the epilogue, which 32 output columns)
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_used = -INFINITY, l_part = 0.f;
@@ -232,36 +242,32 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         break;
       }
       tc_fence_after();
-      uint32_t sv[64];
-      const uint32_t s_addr = tmem_base + COL_S + st * BKV + g * 64 + lane_addr;
-      tmem_ld32(s_addr, sv);
-      tmem_ld32(s_addr + 32, sv + 32);
+      uint32_t sv[CPT];
+      tmem_ld32(tmem_base + COL_S + st * BKV + g * CPT + lane_addr, sv);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(bar(BAR_S_EMPTY + st));
 
-      float mx = -INFINITY;
       if (p.causal && j == qb) {
-        const int key0 = g * 64;
+        const int key0 = g * CPT;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
+        for (int c = 0; c < CPT; ++c)
           if (key0 + c > row) sv[c] = __float_as_uint(-INFINITY);
-          mx = fmaxf(mx, __uint_as_float(sv[c]));
-        }
-      } else {
-#pragma unroll
-        for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sv[c]));
       }
-      float* xc = xchg + (st * 2) * BQ;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < CPT; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      float* xc = xchg + (st * GROUPS) * BQ;
       xc[g * BQ + row] = mx;
       mbar_arrive(bar(BAR_XCHG + st));
       if (!mbar_wait(bar(BAR_XCHG + st), use & 1u, abort_flag)) {
         ok = false;
         break;
       }
-      const float m_new = fmaxf(mx, xc[(g ^ 1) * BQ + row]);
+      const float m_new = fmaxf(fmaxf(xc[row], xc[BQ + row]), fmaxf(xc[2 * BQ + row], xc[3 * BQ + row]));
 
-      // raise the maximum only when it moved far; both threads of a row see the same numbers
+      // raise the maximum only when it moved far; all threads of a row see the same numbers
       float alpha = 1.f;
       const bool raise = (m_new - m_used) * p.scale_log2 > RESCALE_THRESHOLD;
       const bool any_raise = __any_sync(0xffffffffu, raise) && j > 0;
@@ -273,17 +279,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         l_part *= alpha;
       }
       const float neg_m = -m_used * p.scale_log2;
-      uint32_t packed[32];
-      float sum = 0.f;
+      uint32_t packed[CPT / 2];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
+      for (int c = 0; c < CPT / 2; ++c) {
         const float p0 = exp2f(fmaf(__uint_as_float(sv[2 * c]), p.scale_log2, neg_m));
         const float p1 = exp2f(fmaf(__uint_as_float(sv[2 * c + 1]), p.scale_log2, neg_m));
-        sum += p0 + p1;
+        sum4[c & 3] += p0 + p1;
         __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
         packed[c] = *reinterpret_cast<uint32_t*>(&pk);
       }
-      l_part += sum;
+      l_part += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
       // P (and O, if it is rescaled) may only be touched once P V of the previous block is done
       if (j > 0) {
@@ -293,23 +299,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         tc_fence_after();
       }
-      uint8_t* prow = smem + OFF_P + g * SLAB_BYTES + row * 128;
+      uint8_t* prow = smem + OFF_P + (g >> 1) * SLAB_BYTES + row * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(prow + ((((g & 1) * 4 + c) ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       }
       if (any_raise) {
-        const uint32_t o_addr = tmem_base + COL_O + g * 64 + lane_addr;
+        const uint32_t o_addr = tmem_base + COL_O + g * 32 + lane_addr;
+        uint32_t ov[32];
+        tmem_ld32(o_addr, ov);
+        tmem_wait_ld();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t ov[32];
-          tmem_ld32(o_addr + half * 32, ov);
-          tmem_wait_ld();
-#pragma unroll
-          for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
-          tmem_st32(o_addr + half * 32, ov);
-        }
+        for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
+        tmem_st32(o_addr, ov);
         tmem_wait_st();
       }
       fence_async_smem();
@@ -319,28 +322,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
     if (ok && mbar_wait(bar(BAR_O_DONE), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag)) {
       tc_fence_after();
-      // total row sum: the two threads of a row hold partial sums over their keys
+      // total row sum: the threads of a row hold partial sums over their keys
       float* xc = xchg;  // both parities are free again
       xc[g * BQ + row] = l_part;
       const uint32_t xuse = static_cast<uint32_t>((n_kv + 1) >> 1);  // completed phases of XCHG+0 so far
       mbar_arrive(bar(BAR_XCHG + 0));
       if (mbar_wait(bar(BAR_XCHG + 0), xuse & 1u, abort_flag)) {
-        const float l = l_part + xc[(g ^ 1) * BQ + row];
+        const float l = (xc[row] + xc[BQ + row]) + (xc[2 * BQ + row] + xc[3 * BQ + row]);
         const float inv = 1.f / l;
-        const uint32_t o_addr = tmem_base + COL_O + g * 64 + lane_addr;
-        __nv_bfloat16* dst = p.O + static_cast<long long>(q_row0 + row) * p.ld_o + h * D + g * 64;
+        __nv_bfloat16* dst = p.O + static_cast<long long>(q_row0 + row) * p.ld_o + h * D + g * 32;
+        uint32_t ov[32];
+        tmem_ld32(tmem_base + COL_O + g * 32 + lane_addr, ov);
+        tmem_wait_ld();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t ov[32];
-          tmem_ld32(o_addr + half * 32, ov);
-          tmem_wait_ld();
+        for (int c = 0; c < 4; ++c) {
+          float f[8];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[8 * c + e]) * inv;
-            reinterpret_cast<ftb200::bf16x8*>(dst + half * 32)[c] = ftb200::pack8(f);
-          }
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(ov[8 * c + e]) * inv;
+          reinterpret_cast<ftb200::bf16x8*>(dst)[c] = ftb200::pack8(f);
         }
         if (g == 0 && p.lse != nullptr) {
           p.lse[(static_cast<long long>(b) * p.n_heads + h) * p.seq + qb * BQ + row] =

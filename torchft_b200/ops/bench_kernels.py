@@ -90,9 +90,50 @@ def bench_rmsnorm(t: int, d: int, iters: int) -> dict:
     return {"kernel": "rmsnorm_fwd(add+norm)", "t": t, "d": d, "ms": ms, "gbs": gbs, f"frac_of_{how}_copy_bw": gbs / hbm}
 
 
+def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare: bool) -> dict:
+    """Causal GQA attention, head dim 128, forward and backward; FLOPs count the causal half."""
+    import torch.nn.functional as F
+
+    dev, D = "cuda", 128
+    qkv = (torch.randn(batch * seq, (hq + 2 * hkv) * D, device=dev) * 0.5).bfloat16()
+    q, k, v = qkv[:, : hq * D], qkv[:, hq * D : (hq + hkv) * D], qkv[:, (hq + hkv) * D :]
+    out = torch.empty(batch * seq, hq * D, device=dev, dtype=torch.bfloat16)
+    lse = torch.empty(batch, hq, seq, device=dev)
+    d_o = torch.randn_like(out)
+    dqkv = torch.empty_like(qkv)
+    dq, dk, dv = dqkv[:, : hq * D], dqkv[:, hq * D : (hq + hkv) * D], dqkv[:, (hq + hkv) * D :]
+    fwd = timeit(lambda: K.attention_fwd(q, k, v, batch, seq, hq, hkv, D, out, lse), iters)
+    bwd = timeit(lambda: K.attention_bwd(q, k, v, out, d_o, lse, dq, dk, dv, batch, seq, hq, hkv, D), iters)
+    K.check_status(qkv.device)
+    _, tf, how = _peaks()
+    fl_fwd = 4.0 * batch * hq * seq * seq * D / 2
+    fl_bwd = 2.5 * fl_fwd
+    res = {"kernel": "attention_tcgen05", "batch": batch, "seq": seq, "heads": hq, "kv_heads": hkv, "fwd_ms": fwd,
+           "bwd_ms": bwd, "fwd_tflops": fl_fwd / fwd / 1e9, "bwd_tflops": fl_bwd / bwd / 1e9,
+           f"fwd_frac_of_{how}_cublas_peak": fl_fwd / fwd / 1e9 / tf, f"bwd_frac_of_{how}_cublas_peak": fl_bwd / bwd / 1e9 / tf}
+    if compare:
+        q4 = q.reshape(batch, seq, hq, D).transpose(1, 2).detach().requires_grad_(True)
+        k4 = k.reshape(batch, seq, hkv, D).transpose(1, 2).detach().requires_grad_(True)
+        v4 = v.reshape(batch, seq, hkv, D).transpose(1, 2).detach().requires_grad_(True)
+        do4 = d_o.reshape(batch, seq, hq, D).transpose(1, 2)
+
+        def lib_fwd():
+            with torch.no_grad():
+                F.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True)
+
+        o4 = F.scaled_dot_product_attention(q4, k4, v4, is_causal=True, enable_gqa=True)
+        res["sdpa_fwd_ms"] = timeit(lib_fwd, iters)
+        res["sdpa_bwd_ms"] = timeit(lambda: torch.autograd.grad(o4, (q4, k4, v4), do4, retain_graph=True), iters)
+    return res
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "adamw", "rmsnorm", "all"])
+    ap.add_argument("what", choices=["gemm", "adamw", "rmsnorm", "attention", "all"])
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--seq", type=int, default=8192)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -106,6 +147,8 @@ def main() -> None:
             print(json.dumps(bench_gemm(a.m, a.n, a.k, lay, a.iters, not a.no_compare)), flush=True)
     if a.what in ("adamw", "all"):
         print(json.dumps(bench_adamw(1 << 28 if a.what == "all" else a.n, a.iters)), flush=True)
+    if a.what in ("attention", "all"):
+        print(json.dumps(bench_attention(a.batch, a.seq, a.heads, a.kv_heads, a.iters, not a.no_compare)), flush=True)
     if a.what in ("rmsnorm", "all"):
         print(json.dumps(bench_rmsnorm(8192, 4096, a.iters)), flush=True)
 
