@@ -45,11 +45,11 @@ def _parse():
     ap.add_argument("--no-ft", action="store_true", help="run without Manager/lighthouse (debug only)")
     ap.add_argument("--attention", default=None, choices=["tcgen05", "sdpa"],
                     help="attention kernels: hand-written tcgen05 (default where the shape allows) or the library SDPA")
-    ap.add_argument("--fused-rs", action="store_true",
-                    help="store weight-gradient tiles straight into the shard owners' staging from the GEMM epilogue "
-                         "instead of running a separate reduce-scatter kernel (measured slower so far: off by default)")
+    ap.add_argument("--no-fused-rs", action="store_true",
+                    help="run a separate reduce-scatter kernel instead of storing weight-gradient tiles straight into "
+                         "the shard owners' staging from the GEMM epilogue")
     ap.add_argument("--groups", type=int, default=0, help="replica groups (default: 1, 2, 2, 2 for 1, 2, 4, 8 GPUs)")
-    ap.add_argument("--watchdog-s", type=int, default=900,
+    ap.add_argument("--watchdog-s", type=int, default=600,
                     help="dump every thread's stack and exit if the run has not finished after this many seconds")
     return ap.parse_args()
 
@@ -154,6 +154,12 @@ def main() -> int:
             return subprocess.call(cmd)
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
 
+    t_start = time.time()
+
+    def phase(name: str) -> None:
+        # progress on stderr: if the run is ever cut off, the log says how far it got
+        print(f"[bench rank {rank}] {name} (+{time.time() - t_start:.1f}s)", file=sys.stderr, flush=True)
+
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     cfg = CONFIGS[args.model]
@@ -168,8 +174,10 @@ def main() -> int:
     manager = None
     shard_comm = LocalShardComm()
     if world > 1:
+        phase("init_process_group")
         dist.init_process_group("nccl", device_id=dev)
         if shard > 1:
+            phase("shard groups")
             groups = [dist.new_group(list(range(g * shard, (g + 1) * shard))) for g in range(n_groups)]
             if args.shard_comm == "peer":
                 from torchft_b200.parallel.team import PeerShardComm
@@ -182,14 +190,16 @@ def main() -> int:
     if not args.no_ft:
         from torchft_b200.bench_support import make_ft_manager
 
+        phase("manager")
         grad_bytes = sum(cfg.unit_numel(u) for u in range(cfg.n_units)) * 2 // shard
         arena = 0 if n_groups == 1 else grad_bytes + (64 << 20) + 300 * cfg.n_units
         lighthouse, manager = make_ft_manager(rank, world, n_groups, shard, group_id, group_rank, dev, arena_bytes=arena)
 
     replica_alloc = manager._pg.alloc if (manager is not None and n_groups > 1) else None
+    phase("trainer")
     # one logits chunk: the 2 GB of bf16 logits fit, and the head's wgrad then runs once with the full reduction depth
     trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234,
-                                  replica_alloc=replica_alloc, logit_chunks=1, fused_reduce_scatter=args.fused_rs,
+                                  replica_alloc=replica_alloc, logit_chunks=1, fused_reduce_scatter=not args.no_fused_rs,
                                   attention=args.attention)
     if manager is not None:
         manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
@@ -207,12 +217,14 @@ def main() -> int:
         torch.cuda.synchronize()
 
     # ---- warm-up
+    phase("warm-up")
     for i in range(args.warmup):
         t = dev_tok[i]
         loss = trainer.train_step(t[:, :-1], t[:, 1:])
     K.check_status(dev)
 
     # ---- device-resident timed region
+    phase("timed region")
     sampler = ClockSampler(local_rank)
     sync_all()
     if rank == 0:
@@ -234,6 +246,7 @@ def main() -> int:
     final_loss = float(loss.item())
     K.check_status(dev)
 
+    phase("end-to-end region")
     # ---- end-to-end region: pinned host -> device copy of the inputs and loss read-back every step
     stage = torch.empty(B, S + 1, dtype=torch.long, device=dev)
     sync_all()

@@ -101,9 +101,13 @@ def main() -> int:
     exch = [a.elapsed_time(b) for a, b in diloco.exchange_timings]
     exch_ms = sum(exch) / max(1, len(exch))
     stats = torch.tensor([total_ms, sync_ms, exch_ms], dtype=torch.float64, device=device)
+    lo = stats.clone()
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     total_ms, sync_ms, exch_ms = (float(x) for x in stats.tolist())
+    # the rank that reaches a synchronisation last does not wait for anybody: its times are the work alone
+    sync_ms_min, exch_ms_min = float(lo[1]), float(lo[2])
     committed = diloco.commits - commits0
     steps = args.windows * args.sync_every
     frag_elems = [sum(trainer.shard_numel[u] for u in f.units) for f in diloco.fragments]
@@ -112,6 +116,8 @@ def main() -> int:
             "metric": "streaming DiLoCo outer sync ms; tokens/s",
             "outer_sync_ms": round(sync_ms, 3),
             "exchange_kernel_ms": round(exch_ms, 3),
+            "outer_sync_ms_min_over_ranks": round(sync_ms_min, 3),
+            "exchange_kernel_ms_min_over_ranks": round(exch_ms_min, 3),
             "tokens_per_s": round(world * B * S * steps / (total_ms / 1e3), 1),
             "ms_per_inner_step": round((total_ms - sync_ms * len(syncs)) / steps, 3),
             "n_gpus": world, "inner_steps": steps, "syncs_timed": len(syncs), "syncs_committed": committed,

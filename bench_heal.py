@@ -44,7 +44,9 @@ def worker(a) -> int:
     B, S = 1, a.seq_len
     timeout = timedelta(seconds=60)
     store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
-    pg = ProcessGroupB200(timeout=timeout, arena_bytes=1 << 30, device=dev)
+    # gradient shards live in the replica group's arena so that the allreduce runs in place
+    grad_bytes = sum(cfg.unit_numel(u) for u in range(cfg.n_units)) * 2
+    pg = ProcessGroupB200(timeout=timeout, arena_bytes=grad_bytes + (64 << 20) + 300 * cfg.n_units, device=dev)
     # incoming tensors land in place in this replica's own buffers (the state is most of the GPU's memory)
     transport = P2PTransport(timeout=timeout, device=dev, state_dict=lambda: manager._manager_state_dict())
     manager = Manager(

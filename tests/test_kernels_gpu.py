@@ -164,15 +164,19 @@ def test_embedding():
     assert rel_err(dtab, ref) < 2e-2
 
 
-def test_engine_matches_autograd_gpu():
-    from torchft_b200.models.llama import LLAMA_TINY, TorchLlama, _Fields
+@pytest.mark.parametrize("native_attention", [False, True])
+def test_engine_matches_autograd_gpu(native_attention):
+    from torchft_b200.models.llama import LLAMA_TINY, LlamaConfig, SdpaAttention, Tcgen05Attention, TorchLlama, _Fields
     from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
 
     torch.manual_seed(0)
-    cfg = LLAMA_TINY
+    # head dim 128 selects the tcgen05 attention kernels, LLAMA_TINY (head dim 64) the library fallback
+    cfg = (LlamaConfig(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, ffn_dim=512, vocab_size=1024, name="llama-hd128")
+           if native_attention else LLAMA_TINY)
     B, S = 2, 128
     dev = torch.device("cuda")
     tr = ShardedLlamaTrainer(cfg, B, S, dev, logit_chunks=2)
+    assert isinstance(tr.engine.attn, Tcgen05Attention if native_attention else SdpaAttention)
     tokens = torch.randint(0, cfg.vocab_size, (B, S), device=dev)
     targets = torch.randint(0, cfg.vocab_size, (B, S), device=dev)
     loss = tr.forward_backward(tokens, targets)

@@ -291,3 +291,38 @@ def test_state_dict_read_lock(h):
     m.allow_state_dict_read()
     t.join(5)
     assert len(got) == 1
+
+
+def test_managed_future_callbacks_run_in_order_after_normalisation(h):
+    """Callbacks chained on the work's future see the averaged tensor and run in the order
+    they were added, only once the work is waited on."""
+    h.client._quorum.return_value = quorum()
+    h.manager.start_quorum()
+    t = torch.tensor([4.0])
+    order = []
+    work = h.manager.allreduce(t)  # AVG over 2 participants
+    fut = work.get_future()
+
+    def first(f):
+        order.append(("first", float(f.value().item() if isinstance(f.value(), torch.Tensor) else f.value()[0].item())))
+        return f.value()
+
+    def second(f):
+        order.append(("second", None))
+        return f.value()
+
+    fut.then(first).then(second)
+    assert order == []  # nothing runs before the wait
+    work.wait()
+    fut.wait()
+    assert [name for name, _ in order] == ["first", "second"]
+    assert order[0][1] == 2.0 and t.item() == 2.0
+
+
+def test_allreduce_delta_falls_back_to_subtract_then_allreduce(h):
+    h.client._quorum.return_value = quorum()
+    h.manager.start_quorum()
+    a, b, out = torch.tensor([5.0, 3.0]), torch.tensor([1.0, 1.0]), torch.zeros(2)
+    h.manager.allreduce_delta(out, a, b, should_quantize=False).wait()
+    torch.testing.assert_close(out, torch.tensor([2.0, 1.0]))  # (a - b) / 2 participants
+    assert h.pg.allreduce.call_count == 1

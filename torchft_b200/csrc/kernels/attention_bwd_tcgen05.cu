@@ -16,8 +16,9 @@
 // whole CTA; dQ^T is drained every tile and added to an fp32 accumulator in global memory with
 // coalesced reductions (one query row, 32 consecutive head-dim elements per warp instruction).
 //
-// Warps: 0 = TMA (K, V once; Q, dO, lse, delta per tile, 2 stages), 1 = MMA issue, 2..17 =
-// softmax / dQ drain / final dK, dV store.  The tail MMAs of tile t-1 are issued after S and dP
+// Warps: 0 = TMA (K, V once; Q, dO, lse, delta per tile, 3 stages), 1 = MMA issue, 2..17 =
+// softmax and the final dK, dV store, 18..21 = dQ drain (so that the reductions of tile t-1 run
+// beside the softmax of tile t).  The tail MMAs of tile t-1 are issued after S and dP
 // of tile t, so the tensor cores work under the softmax of tile t.  All waits are bounded.
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -30,11 +31,26 @@ namespace {
 
 using namespace ftb200::tc;
 
+// Optional event trace for tuning (compiled in with -DFTB200_ATTN_TRACE): CTA 0 records clock64()
+// at pipeline events of its first tiles into p.trace[role][tile][event].
+#ifdef FTB200_ATTN_TRACE
+#define TRACE(role, tile, ev)                                                                       \
+  do {                                                                                              \
+    if (p.trace != nullptr && blockIdx.x == 0 && (tile) < 32)                                       \
+      p.trace[((role) * 32 + (tile)) * 8 + (ev)] = clock64();                                       \
+  } while (0)
+#else
+#define TRACE(role, tile, ev) \
+  do {                        \
+  } while (0)
+#endif
+
 constexpr int D = 128;
 constexpr int BKV = 128;
 constexpr int BQ = 64;
-constexpr int NUM_THREADS = 576;
+constexpr int NUM_THREADS = 704;
 constexpr int SOFTMAX_THREADS = 512;
+constexpr int DRAIN_THREADS = 128;
 constexpr int GROUPS = 4;          // threads per key row
 constexpr int CPT = BQ / GROUPS;   // query columns per thread
 constexpr uint32_t TMEM_COLS = 512;
@@ -83,6 +99,7 @@ struct BwdParams {
   __nv_bfloat16* dV;
   long long ld_dk, ld_dv;
   int* status;
+  long long* trace;  // tuning aid, null unless built with FTB200_ATTN_TRACE
 };
 
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
@@ -114,7 +131,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int b = bh / p.n_kv_heads, hk = bh % p.n_kv_heads;
   const int rep = p.n_heads / p.n_kv_heads;
   const int n_qtiles = p.seq / BQ;
-  const int first_q = p.causal ? (jb * BKV) / BQ : 0;
+  const int first_q = (p.causal & 1) ? (jb * BKV) / BQ : 0;
   const int tiles_per_head = n_qtiles - first_q;
   const int T = rep * tiles_per_head;
   const int kv_row0 = b * p.seq + jb * BKV;
@@ -138,7 +155,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     mbar_init(bar(BAR_DP_FULL), 1);
     mbar_init(bar(BAR_DP_EMPTY), SOFTMAX_THREADS);
     mbar_init(bar(BAR_DQ_FULL), 1);
-    mbar_init(bar(BAR_DQ_EMPTY), SOFTMAX_THREADS);
+    mbar_init(bar(BAR_DQ_EMPTY), DRAIN_THREADS);
     mbar_init(bar(BAR_DKV_DONE), 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -199,7 +216,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t idesc_st = F | (static_cast<uint32_t>(BQ >> 3) << 17);                             // N = 64, K-major both
       const uint32_t idesc_kv = F | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17);                 // N = 128, B MN-major
       const uint32_t idesc_dq = F | (1u << 15) | (1u << 16) | (static_cast<uint32_t>(BQ >> 3) << 17);   // N = 64, both MN-major
-      const uint32_t sk = smem_base + OFF_K, sv = smem_base + OFF_V;
+      // descriptor bases: one per buffer and operand role, constants per K step (the issue loop
+      // must stay short: these MMAs are too small to hide descriptor arithmetic)
+      constexpr uint32_t HI = smem_desc_hi(1024);
+      const uint32_t k_km = smem_desc_lo(smem_base + OFF_K, 16);        // K as K-major A (S^T)
+      const uint32_t v_km = smem_desc_lo(smem_base + OFF_V, 16);        // V as K-major A (dP^T)
+      const uint32_t k_mn = smem_desc_lo(smem_base + OFF_K, KV_SLAB);   // K as MN-major A (dQ^T)
+      const uint32_t q_km0 = smem_desc_lo(smem_base + OFF_STAGE, 16);             // Q, stage 0, K-major B
+      const uint32_t q_mn0 = smem_desc_lo(smem_base + OFF_STAGE, Q_SLAB);         // Q, stage 0, MN-major B
+      const uint32_t p_km0 = smem_desc_lo(smem_base + OFF_PDS, 16);               // P^T, buffer 0, K-major A
+      const uint32_t ds_mn0 = smem_desc_lo(smem_base + OFF_PDS + PT_TILE, PT_TILE);  // dS^T, buffer 0, MN-major B
+      constexpr uint32_t STAGE16 = STAGE_BYTES >> 4, QT16 = Q_TILE >> 4, PDS16 = PDS_BYTES >> 4, PT16 = PT_TILE >> 4;
       bool ok = mbar_wait(bar(BAR_KV), 0, abort_flag);
       for (int t = 0; t <= T && ok; ++t) {
         if (t < T) {
@@ -211,13 +238,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             break;
           }
           tc_fence_after();
-          const uint32_t sq = smem_base + OFF_STAGE + qs * STAGE_BYTES;
-          const uint32_t sdo = sq + Q_TILE;
+          TRACE(0, t, 0);  // S inputs ready
+          const uint32_t qb_km = q_km0 + qs * STAGE16;
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * KV_SLAB + (kk & 3) * 32, b_off = (kk >> 2) * Q_SLAB + (kk & 3) * 32;
-            umma_bf16(tmem_base + COL_S + st * BQ, make_smem_desc(sk + a_off, 16, 1024),
-                      make_smem_desc(sq + b_off, 16, 1024), idesc_st, kk != 0);
+            const uint32_t a_off = ((kk >> 2) * KV_SLAB + (kk & 3) * 32) >> 4, b_off = ((kk >> 2) * Q_SLAB + (kk & 3) * 32) >> 4;
+            umma_bf16_lh(tmem_base + COL_S + st * BQ, k_km + a_off, HI, qb_km + b_off, HI, idesc_st, kk != 0);
           }
           umma_commit(bar(BAR_S_FULL + st));
           if (!mbar_wait(bar(BAR_DP_EMPTY), (static_cast<uint32_t>(t) & 1u) ^ 1u, abort_flag)) {
@@ -227,11 +253,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < D / 16; ++kk) {
-            const uint32_t a_off = (kk >> 2) * KV_SLAB + (kk & 3) * 32, b_off = (kk >> 2) * Q_SLAB + (kk & 3) * 32;
-            umma_bf16(tmem_base + COL_DP, make_smem_desc(sv + a_off, 16, 1024), make_smem_desc(sdo + b_off, 16, 1024),
-                      idesc_st, kk != 0);
+            const uint32_t a_off = ((kk >> 2) * KV_SLAB + (kk & 3) * 32) >> 4, b_off = ((kk >> 2) * Q_SLAB + (kk & 3) * 32) >> 4;
+            umma_bf16_lh(tmem_base + COL_DP, v_km + a_off, HI, qb_km + QT16 + b_off, HI, idesc_st, kk != 0);
           }
           umma_commit(bar(BAR_DP_FULL));
+          TRACE(0, t, 1);  // S, dP issued
         }
         if (t >= 1) {
           const int u = t - 1, pb = u & 1, qs = u % QDO_STAGES;
@@ -241,19 +267,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             break;
           }
           tc_fence_after();
-          const uint32_t sq = smem_base + OFF_STAGE + qs * STAGE_BYTES;
-          const uint32_t sdo = sq + Q_TILE;
-          const uint32_t spt = smem_base + OFF_PDS + pb * PDS_BYTES;
-          const uint32_t sds = spt + PT_TILE;
+          TRACE(0, u, 2);  // P, dS ready for the tail of tile u
+          const uint32_t qb_mn = q_mn0 + qs * STAGE16;
+          const uint32_t pb_km = p_km0 + pb * PDS16;
+          const uint32_t dsb_mn = ds_mn0 + pb * PDS16;
 #pragma unroll
           for (int kk = 0; kk < BQ / 16; ++kk) {  // dV += P^T dO
-            umma_bf16(tmem_base + COL_DV, make_smem_desc(spt + kk * 32, 16, 1024),
-                      make_smem_desc(sdo + kk * 2048, Q_SLAB, 1024), idesc_kv, (u | kk) != 0);
+            umma_bf16_lh(tmem_base + COL_DV, pb_km + ((kk * 32) >> 4), HI, qb_mn + QT16 + ((kk * 2048) >> 4), HI, idesc_kv,
+                         (u | kk) != 0);
           }
 #pragma unroll
           for (int kk = 0; kk < BQ / 16; ++kk) {  // dK += dS^T Q
-            umma_bf16(tmem_base + COL_DK, make_smem_desc(sds + kk * 32, 16, 1024),
-                      make_smem_desc(sq + kk * 2048, Q_SLAB, 1024), idesc_kv, (u | kk) != 0);
+            umma_bf16_lh(tmem_base + COL_DK, pb_km + PT16 + ((kk * 32) >> 4), HI, qb_mn + ((kk * 2048) >> 4), HI, idesc_kv,
+                         (u | kk) != 0);
           }
           umma_commit(bar(BAR_QDO_EMPTY + qs));
           if (!mbar_wait(bar(BAR_DQ_EMPTY), (static_cast<uint32_t>(u) & 1u) ^ 1u, abort_flag)) {
@@ -263,18 +289,40 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < BKV / 16; ++kk) {  // dQ^T = K^T dS^T
-            umma_bf16(tmem_base + COL_DQ, make_smem_desc(sk + kk * 2048, KV_SLAB, 1024),
-                      make_smem_desc(sds + kk * 2048, PT_TILE, 1024), idesc_dq, kk != 0);
+            umma_bf16_lh(tmem_base + COL_DQ, k_mn + ((kk * 2048) >> 4), HI, dsb_mn + ((kk * 2048) >> 4), HI, idesc_dq, kk != 0);
           }
           umma_commit(bar(BAR_PDS_EMPTY + pb));
           umma_commit(bar(BAR_DQ_FULL));
+          TRACE(0, u, 3);  // tail issued
         }
       }
       if (ok) umma_commit(bar(BAR_DKV_DONE));
     }
     __syncwarp();
+  } else if (warp >= 18) {
+    // ---------------- dQ drain (warps 18..21): TMEM lane = head-dim index ----------------
+    const int quarter = warp & 3;
+    const int dcol = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const long long ldq = static_cast<long long>(p.n_heads) * D;
+    for (int u = 0; u < T; ++u) {
+      if (!mbar_wait(bar(BAR_DQ_FULL), static_cast<uint32_t>(u) & 1u, abort_flag)) break;
+      tc_fence_after();
+      uint32_t v[BQ];
+      tmem_ld32(tmem_base + COL_DQ + lane_addr, v);
+      tmem_ld32(tmem_base + COL_DQ + 32 + lane_addr, v + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_DQ_EMPTY));
+      int h, qt;
+      tile_of(u, h, qt);
+      float* dst = p.dq_acc + (static_cast<long long>(b) * p.seq + qt * BQ) * ldq + h * D + dcol;
+      if (!(p.causal & 2))
+#pragma unroll
+        for (int c = 0; c < BQ; ++c) atomicAdd(dst + c * ldq, __uint_as_float(v[c]));
+    }
   } else {
-    // ---------------- softmax, dQ drain, dK/dV store (warps 2..17) ----------------
+    // ---------------- softmax, dK/dV store (warps 2..17) ----------------
     const int quarter = warp & 3;
     const int g = (warp - 2) >> 2;  // which 16 of the tile's 64 queries (32 of 128 columns at the end)
     const int row = quarter * 32 + lane;  // key within the block; head-dim index when draining dQ^T
@@ -282,47 +330,26 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const float log2e = 1.4426950408889634f;
     bool ok = true;
 
-    auto drain_dq = [&](int u) -> bool {
-      if (!mbar_wait(bar(BAR_DQ_FULL), static_cast<uint32_t>(u) & 1u, abort_flag)) return false;
-      tc_fence_after();
-      uint32_t v[CPT];
-      tmem_ld16(tmem_base + COL_DQ + g * CPT + lane_addr, v);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(BAR_DQ_EMPTY));
-      int h, qt;
-      tile_of(u, h, qt);
-      const long long ldq = static_cast<long long>(p.n_heads) * D;
-      float* dst = p.dq_acc + (static_cast<long long>(b) * p.seq + qt * BQ + g * CPT) * ldq + h * D + row;
-#pragma unroll
-      for (int c = 0; c < CPT; ++c) atomicAdd(dst + c * ldq, __uint_as_float(v[c]));
-      return true;
-    };
-
     for (int t = 0; t < T; ++t) {
       const int st = t & 1;
       const uint32_t use = static_cast<uint32_t>(t >> 1);
       int h, qt;
       tile_of(t, h, qt);
-      if (!mbar_wait(bar(BAR_S_FULL + st), use & 1u, abort_flag)) {
+      if (!mbar_wait(bar(BAR_S_FULL + st), use & 1u, abort_flag) ||
+          !mbar_wait(bar(BAR_DP_FULL), static_cast<uint32_t>(t) & 1u, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after();
+      if (threadIdx.x == 64) TRACE(1, t, 0);  // S and dP complete
       uint32_t sv[CPT], dp[CPT];
       tmem_ld16(tmem_base + COL_S + st * BQ + g * CPT + lane_addr, sv);
-      tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(BAR_S_EMPTY + st));
-      if (!mbar_wait(bar(BAR_DP_FULL), static_cast<uint32_t>(t) & 1u, abort_flag)) {
-        ok = false;
-        break;
-      }
-      tc_fence_after();
       tmem_ld16(tmem_base + COL_DP + g * CPT + lane_addr, dp);
       tmem_wait_ld();
       tc_fence_before();
+      mbar_arrive(bar(BAR_S_EMPTY + st));
       mbar_arrive(bar(BAR_DP_EMPTY));
+      if (threadIdx.x == 64) TRACE(1, t, 1);  // scores in registers
       // the tile's statistics arrived with Q and dO
       const int qs = t % QDO_STAGES;
       if (!mbar_wait(bar(BAR_QDO_FULL + qs), static_cast<uint32_t>(t / QDO_STAGES) & 1u, abort_flag)) {
@@ -340,7 +367,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       const int key = jb * BKV + row;
       const int q0 = qt * BQ + g * CPT;
-      const bool diag = p.causal && (q0 < jb * BKV + BKV);
+      const bool diag = (p.causal & 1) && (q0 < jb * BKV + BKV);
       uint32_t pk[CPT / 2], dk[CPT / 2];
 #pragma unroll
       for (int c = 0; c < CPT / 2; ++c) {
@@ -362,6 +389,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         ok = false;
         break;
       }
+      if (threadIdx.x == 64) TRACE(1, t, 2);  // math done, P/dS buffer free
       uint8_t* prow = smem + OFF_PDS + st * PDS_BYTES + row * 128;
       uint8_t* drow = prow + PT_TILE;
 #pragma unroll
@@ -372,12 +400,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       fence_async_smem();
       mbar_arrive(bar(BAR_PDS_FULL + st));
-      if (t >= 1 && !drain_dq(t - 1)) {
-        ok = false;
-        break;
-      }
+      if (threadIdx.x == 64) TRACE(1, t, 3);  // P/dS published
     }
-    if (ok && T > 0) ok = drain_dq(T - 1);
     if (ok && mbar_wait(bar(BAR_DKV_DONE), 0, abort_flag)) {
       tc_fence_after();
 #pragma unroll
@@ -534,6 +558,10 @@ FTB200_API int ftb200_attention_bwd(const void* q, const void* k, const void* v,
   p.lse = lse; p.delta = delta; p.dq_acc = dq_acc;
   p.dK = reinterpret_cast<__nv_bfloat16*>(dk); p.dV = reinterpret_cast<__nv_bfloat16*>(dv);
   p.ld_dk = ld_dk; p.ld_dv = ld_dv; p.status = status;
+  p.trace = nullptr;
+#ifdef FTB200_ATTN_TRACE
+  p.trace = reinterpret_cast<long long*>(delta + rows * n_heads);  // the caller sized the scratch for it
+#endif
   const long long grid = static_cast<long long>(batch) * n_kv_heads * (seq / BKV);
   if (grid > 0x7fffffffLL) return FTB200_E_TOOBIG;
   attention_bwd_kernel<<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);

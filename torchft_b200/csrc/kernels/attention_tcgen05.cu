@@ -10,8 +10,9 @@
 //   warp 0            TMA: K and V tiles into a 2-stage ring (Q once)
 //   warp 1            tcgen05.mma: S = Q K^T into one of two TMEM buffers, O += P V
 //   warps 2..17       softmax: four threads per query row (32 keys each); scores come from TMEM
-//                     (tcgen05.ld), P goes to shared memory in the 128-byte-swizzled K-major
-//                     layout that the second MMA reads
+//                     (tcgen05.ld) and P goes back into the same TMEM columns as packed bf16
+//                     (tcgen05.st), from where the second MMA takes it as its A operand: P never
+//                     touches shared memory, which halves the operand traffic of P V
 // S of block j+1 is issued before P V of block j, so the tensor cores work on the next scores
 // while the softmax of the current block runs.  The running maximum is only raised (and O in
 // TMEM rescaled, tcgen05.ld/st) when it grows by more than 2^8, which keeps the accumulator
@@ -42,11 +43,10 @@ constexpr int GROUPS = 4;   // threads per query row
 constexpr int CPT = BKV / GROUPS;  // score columns per thread
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_O = 256;
-// smem: Q | K0 V0 | K1 V1 | P | barriers + exchange
+// smem: Q | K0 V0 | K1 V1 | barriers + exchange
 constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_KV = TILE_BYTES;
-constexpr uint32_t OFF_P = OFF_KV + KV_STAGES * 2 * TILE_BYTES;
-constexpr uint32_t OFF_MISC = OFF_P + TILE_BYTES;
+constexpr uint32_t OFF_MISC = OFF_KV + KV_STAGES * 2 * TILE_BYTES;
 constexpr uint32_t MISC_BYTES = 256 + 2 * GROUPS * BQ * 4;
 constexpr uint32_t SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
@@ -68,7 +68,7 @@ enum : int {
   BAR_V_FULL = 3,    // +stage
   BAR_K_EMPTY = 5,   // +stage: K is free once its S MMA is done, long before V
   BAR_S_FULL = 7,    // +buf
-  BAR_S_EMPTY = 9,   // +buf
+  BAR_UNUSED = 9,    // (two slots kept so that the indices below stay put)
   BAR_P_FULL = 11,
   BAR_O_DONE = 12,
   BAR_XCHG = 13,     // +parity
@@ -110,7 +110,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(bar(BAR_K_EMPTY + s), 1);
       mbar_init(bar(BAR_V_EMPTY + s), 1);
       mbar_init(bar(BAR_S_FULL + s), 1);
-      mbar_init(bar(BAR_S_EMPTY + s), SOFTMAX_THREADS);
       mbar_init(bar(BAR_XCHG + s), SOFTMAX_THREADS);
     }
     mbar_init(bar(BAR_P_FULL), SOFTMAX_THREADS);
@@ -173,15 +172,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       // O += P V: A = P K-major (keys contiguous), B = V MN-major (stored [key][d])
       const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17) |
                                (static_cast<uint32_t>(BQ >> 4) << 24);
+      // descriptor bases: one per buffer, constants per K step (the issue loop must stay short)
+      constexpr uint32_t HI = smem_desc_hi(1024);
+      const uint32_t q_lo = smem_desc_lo(smem_base + OFF_Q, 16);
+      const uint32_t k_lo = smem_desc_lo(smem_base + OFF_KV, 16);
+      const uint32_t v_lo = smem_desc_lo(smem_base + OFF_KV + TILE_BYTES, SLAB_BYTES);
+      constexpr uint32_t STAGE16 = (2 * TILE_BYTES) >> 4;
       auto issue_s = [&](int j) {
         const int st = j & 1;
-        const uint32_t sq = smem_base + OFF_Q;
-        const uint32_t sk = smem_base + OFF_KV + st * 2 * TILE_BYTES;
+        const uint32_t kb = k_lo + st * STAGE16;
         const uint32_t d_tmem = tmem_base + COL_S + st * BKV;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * SLAB_BYTES + (kk & 3) * 32;
-          umma_bf16(d_tmem, make_smem_desc(sq + off, 16, 1024), make_smem_desc(sk + off, 16, 1024), idesc_s, kk != 0);
+          const uint32_t off = ((kk >> 2) * SLAB_BYTES + (kk & 3) * 32) >> 4;
+          umma_bf16_lh(d_tmem, q_lo + off, HI, kb + off, HI, idesc_s, kk != 0);
         }
         umma_commit(bar(BAR_S_FULL + st));
         umma_commit(bar(BAR_K_EMPTY + st));
@@ -197,8 +201,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (j + 1 < n_kv) {
           const int st1 = (j + 1) & 1;
           const uint32_t use1 = static_cast<uint32_t>((j + 1) >> 1);
-          if (!mbar_wait(bar(BAR_K_FULL + st1), use1 & 1u, abort_flag) ||
-              !mbar_wait(bar(BAR_S_EMPTY + st1), (use1 & 1u) ^ 1u, abort_flag)) {
+          // S buffer st1 last held P of block j-1: its P V was issued above, and the tensor pipe runs in order
+          if (!mbar_wait(bar(BAR_K_FULL + st1), use1 & 1u, abort_flag)) {
             ok = false;
             break;
           }
@@ -211,14 +215,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           break;
         }
         tc_fence_after();
-        const uint32_t sp = smem_base + OFF_P;
-        const uint32_t sv = smem_base + OFF_KV + st * 2 * TILE_BYTES + TILE_BYTES;
+        const uint32_t vb = v_lo + st * STAGE16;
         const uint32_t d_tmem = tmem_base + COL_O;
+        // P of keys 32g..32g+31 sits, two per column, in the first 16 of the 32 columns its thread group read S from
+        const uint32_t p_tmem = tmem_base + COL_S + st * BKV;
 #pragma unroll
         for (int kk = 0; kk < BKV / 16; ++kk) {
-          const uint64_t adesc = make_smem_desc(sp + (kk >> 2) * SLAB_BYTES + (kk & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sv + kk * 2048, SLAB_BYTES, 1024);
-          umma_bf16(d_tmem, adesc, bdesc, idesc_o, (j | kk) != 0);
+          umma_bf16_tmem_a(d_tmem, p_tmem + (kk >> 1) * CPT + (kk & 1) * 8, vb + ((kk * 2048) >> 4), HI, idesc_o, (j | kk) != 0);
         }
         umma_commit(bar(BAR_V_EMPTY + st));
         umma_commit(bar(BAR_O_DONE));
@@ -245,8 +248,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       uint32_t sv[CPT];
       tmem_ld32(tmem_base + COL_S + st * BKV + g * CPT + lane_addr, sv);
       tmem_wait_ld();
-      tc_fence_before();
-      mbar_arrive(bar(BAR_S_EMPTY + st));
 
       if (p.causal && j == qb) {
         const int key0 = g * CPT;
@@ -291,21 +292,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       l_part += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
-      // P (and O, if it is rescaled) may only be touched once P V of the previous block is done
-      if (j > 0) {
+      // P replaces the scores this thread has just read (its own columns: nobody else touches them)
+      tmem_st16(tmem_base + COL_S + st * BKV + g * CPT + lane_addr, packed);
+      if (any_raise) {
+        // O may only be touched once P V of the previous block is done
         if (!mbar_wait(bar(BAR_O_DONE), static_cast<uint32_t>(j - 1) & 1u, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after();
-      }
-      uint8_t* prow = smem + OFF_P + (g >> 1) * SLAB_BYTES + row * 128;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        *reinterpret_cast<uint4*>(prow + ((((g & 1) * 4 + c) ^ (row & 7)) << 4)) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      }
-      if (any_raise) {
         const uint32_t o_addr = tmem_base + COL_O + g * 32 + lane_addr;
         uint32_t ov[32];
         tmem_ld32(o_addr, ov);
@@ -313,9 +308,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int c = 0; c < 32; ++c) ov[c] = __float_as_uint(__uint_as_float(ov[c]) * alpha);
         tmem_st32(o_addr, ov);
-        tmem_wait_st();
       }
-      fence_async_smem();
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
     }

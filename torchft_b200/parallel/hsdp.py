@@ -46,7 +46,7 @@ class ShardedLlamaTrainer:
         attention=None,
         logit_chunks: int = 4,
         replica_alloc=None,
-        fused_reduce_scatter: bool = False,
+        fused_reduce_scatter: bool = True,
     ):
         self.cfg, self.device = cfg, device
         self.comm = shard_comm or LocalShardComm()
