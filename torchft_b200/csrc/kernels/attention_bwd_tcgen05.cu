@@ -11,8 +11,9 @@
 //   dK  += dS^T Q            [keys x d]      A = dS^T (K-major)     B = Q   (MN-major)
 //   dQ^T = K^T  dS^T         [d x q]         A = K   (MN-major)     B = dS^T (MN-major)
 //
-// P^T and dS^T are written to shared memory once, in the 128-byte-swizzled layout that serves
-// both as a K-major A operand and as an MN-major B operand.  dK and dV stay in TMEM for the
+// P^T and dS^T go back, as packed bf16, into the TMEM columns their scores came from and are the
+// A operands of the dV and dK MMAs straight from tensor memory; dS^T is also written to shared
+// memory (128-byte swizzle) as the MN-major B operand of the dQ^T MMA.  dK and dV stay in TMEM for the
 // whole CTA; dQ^T is drained every tile and added to an fp32 accumulator in global memory with
 // coalesced reductions (one query row, 32 consecutive head-dim elements per warp instruction).
 //
@@ -64,8 +65,8 @@ constexpr uint32_t OFF_K = 0, OFF_V = KV_TILE;
 constexpr uint32_t OFF_STAGE = 2 * KV_TILE;    // per stage: Q, dO
 constexpr uint32_t STAGE_BYTES = 2 * Q_TILE;
 constexpr int QDO_STAGES = 3;  // a stage is held until the tile's dV/dK MMAs are done, two tiles after its load began
-constexpr uint32_t OFF_PDS = OFF_STAGE + QDO_STAGES * STAGE_BYTES;  // per buffer: P^T, dS^T
-constexpr uint32_t PDS_BYTES = 2 * PT_TILE;
+constexpr uint32_t OFF_PDS = OFF_STAGE + QDO_STAGES * STAGE_BYTES;  // per buffer: dS^T
+constexpr uint32_t PDS_BYTES = PT_TILE;        // dS^T only: P^T never leaves tensor memory
 constexpr uint32_t OFF_STATS = OFF_PDS + 2 * PDS_BYTES;    // per stage: lse[64], delta[64]
 constexpr uint32_t STATS_BYTES = 2 * BQ * 4;
 constexpr uint32_t OFF_MISC = OFF_STATS + QDO_STAGES * STATS_BYTES;
@@ -224,9 +225,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       const uint32_t k_mn = smem_desc_lo(smem_base + OFF_K, KV_SLAB);   // K as MN-major A (dQ^T)
       const uint32_t q_km0 = smem_desc_lo(smem_base + OFF_STAGE, 16);             // Q, stage 0, K-major B
       const uint32_t q_mn0 = smem_desc_lo(smem_base + OFF_STAGE, Q_SLAB);         // Q, stage 0, MN-major B
-      const uint32_t p_km0 = smem_desc_lo(smem_base + OFF_PDS, 16);               // P^T, buffer 0, K-major A
-      const uint32_t ds_mn0 = smem_desc_lo(smem_base + OFF_PDS + PT_TILE, PT_TILE);  // dS^T, buffer 0, MN-major B
-      constexpr uint32_t STAGE16 = STAGE_BYTES >> 4, QT16 = Q_TILE >> 4, PDS16 = PDS_BYTES >> 4, PT16 = PT_TILE >> 4;
+      const uint32_t ds_mn0 = smem_desc_lo(smem_base + OFF_PDS, PT_TILE);  // dS^T, buffer 0, MN-major B
+      constexpr uint32_t STAGE16 = STAGE_BYTES >> 4, QT16 = Q_TILE >> 4, PDS16 = PDS_BYTES >> 4;
       bool ok = mbar_wait(bar(BAR_KV), 0, abort_flag);
       for (int t = 0; t <= T && ok; ++t) {
         if (t < T) {
@@ -269,17 +269,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           tc_fence_after();
           TRACE(0, u, 2);  // P, dS ready for the tail of tile u
           const uint32_t qb_mn = q_mn0 + qs * STAGE16;
-          const uint32_t pb_km = p_km0 + pb * PDS16;
           const uint32_t dsb_mn = ds_mn0 + pb * PDS16;
+          // queries 16k..16k+15 of tile u: P^T in columns 16k..16k+7 of its score buffer, dS^T in 16k+8..16k+15
+          const uint32_t pt_tmem = tmem_base + COL_S + pb * BQ;
 #pragma unroll
           for (int kk = 0; kk < BQ / 16; ++kk) {  // dV += P^T dO
-            umma_bf16_lh(tmem_base + COL_DV, pb_km + ((kk * 32) >> 4), HI, qb_mn + QT16 + ((kk * 2048) >> 4), HI, idesc_kv,
-                         (u | kk) != 0);
+            umma_bf16_tmem_a(tmem_base + COL_DV, pt_tmem + kk * 16, qb_mn + QT16 + ((kk * 2048) >> 4), HI, idesc_kv, (u | kk) != 0);
           }
 #pragma unroll
           for (int kk = 0; kk < BQ / 16; ++kk) {  // dK += dS^T Q
-            umma_bf16_lh(tmem_base + COL_DK, pb_km + PT16 + ((kk * 32) >> 4), HI, qb_mn + ((kk * 2048) >> 4), HI, idesc_kv,
-                         (u | kk) != 0);
+            umma_bf16_tmem_a(tmem_base + COL_DK, pt_tmem + kk * 16 + 8, qb_mn + ((kk * 2048) >> 4), HI, idesc_kv, (u | kk) != 0);
           }
           umma_commit(bar(BAR_QDO_EMPTY + qs));
           if (!mbar_wait(bar(BAR_DQ_EMPTY), (static_cast<uint32_t>(u) & 1u) ^ 1u, abort_flag)) {
@@ -390,15 +389,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         break;
       }
       if (threadIdx.x == 64) TRACE(1, t, 2);  // math done, P/dS buffer free
-      uint8_t* prow = smem + OFF_PDS + st * PDS_BYTES + row * 128;
-      uint8_t* drow = prow + PT_TILE;
+      // P^T and dS^T replace the scores this thread has just read (its own 16 columns)
+      uint32_t pds[CPT];
+#pragma unroll
+      for (int c = 0; c < CPT / 2; ++c) {
+        pds[c] = pk[c];
+        pds[CPT / 2 + c] = dk[c];
+      }
+      tmem_st16(tmem_base + COL_S + st * BQ + g * CPT + lane_addr, pds);
+      uint8_t* drow = smem + OFF_PDS + st * PDS_BYTES + row * 128;
 #pragma unroll
       for (int c = 0; c < CPT / 8; ++c) {
         const int chunk = ((g * (CPT / 8) + c) ^ (row & 7)) << 4;
-        *reinterpret_cast<uint4*>(prow + chunk) = make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
         *reinterpret_cast<uint4*>(drow + chunk) = make_uint4(dk[4 * c], dk[4 * c + 1], dk[4 * c + 2], dk[4 * c + 3]);
       }
       fence_async_smem();
+      tmem_wait_st();
+      tc_fence_before();
       mbar_arrive(bar(BAR_PDS_FULL + st));
       if (threadIdx.x == 64) TRACE(1, t, 3);  // P/dS published
     }

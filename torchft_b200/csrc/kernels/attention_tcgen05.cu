@@ -7,7 +7,10 @@
 // QKV projection writes them, so no transposed copies exist on either side.
 //
 // One CTA owns one (batch, head, 128-query block).  Per 128-key block:
-//   warp 0            TMA: K and V tiles into a 2-stage ring (Q once)
+//   warp 0            TMA: K and V tiles into a 2-stage ring
+//   (Q, stationary for the CTA, is loaded by the softmax warps straight into TMEM and is the A
+//   operand of S = Q K^T from there: with both operands in shared memory the MMAs of tiles this
+//   small are bound by operand fetch, not by the tensor pipe)
 //   warp 1            tcgen05.mma: S = Q K^T into one of two TMEM buffers, O += P V
 //   warps 2..17       softmax: four threads per query row (32 keys each); scores come from TMEM
 //                     (tcgen05.ld) and P goes back into the same TMEM columns as packed bf16
@@ -31,6 +34,20 @@ namespace {
 
 using namespace ftb200::tc;
 
+// Optional event trace for tuning (compiled in with -DFTB200_ATTN_TRACE): the CTA with the most
+// key blocks records clock64() at pipeline events of its first blocks into p.trace[role][block][event].
+#ifdef FTB200_ATTN_TRACE
+#define TRACE(role, blk, ev)                                                                        \
+  do {                                                                                              \
+    if (p.trace != nullptr && blockIdx.x == 0 && (blk) < 32)                                        \
+      p.trace[((role) * 32 + (blk)) * 8 + (ev)] = clock64();                                        \
+  } while (0)
+#else
+#define TRACE(role, blk, ev) \
+  do {                       \
+  } while (0)
+#endif
+
 constexpr int D = 128;       // head dim
 constexpr int BQ = 128;      // queries per CTA
 constexpr int BKV = 128;     // keys per block
@@ -42,10 +59,9 @@ constexpr int SOFTMAX_THREADS = 512;
 constexpr int GROUPS = 4;   // threads per query row
 constexpr int CPT = BKV / GROUPS;  // score columns per thread
 constexpr uint32_t TMEM_COLS = 512;
-constexpr uint32_t COL_S = 0, COL_O = 256;
-// smem: Q | K0 V0 | K1 V1 | barriers + exchange
-constexpr uint32_t OFF_Q = 0;
-constexpr uint32_t OFF_KV = TILE_BYTES;
+constexpr uint32_t COL_S = 0, COL_O = 256, COL_Q = 384;  // Q: 128 bf16 per row = 64 columns
+// smem: K0 V0 | K1 V1 | barriers + exchange
+constexpr uint32_t OFF_KV = 0;
 constexpr uint32_t OFF_MISC = OFF_KV + KV_STAGES * 2 * TILE_BYTES;
 constexpr uint32_t MISC_BYTES = 256 + 2 * GROUPS * BQ * 4;
 constexpr uint32_t SMEM_BYTES = OFF_MISC + MISC_BYTES + 1024;
@@ -56,9 +72,12 @@ struct AttnParams {
   int causal;
   float scale_log2;  // softmax scale * log2(e)
   long long ld_o;    // row stride of O in elements
+  const __nv_bfloat16* Q;
+  long long ld_q;
   __nv_bfloat16* O;
   float* lse;        // [batch, n_heads, seq], natural log
   int* status;
+  long long* trace;  // tuning aid, null unless built with FTB200_ATTN_TRACE
 };
 
 // barrier indices
@@ -77,7 +96,7 @@ enum : int {
 };
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+attention_fwd_kernel(const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -103,7 +122,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int q_row0 = b * p.seq + qb * BQ;
 
   if (threadIdx.x == 0) {
-    mbar_init(bar(BAR_Q), 1);
+    mbar_init(bar(BAR_Q), SOFTMAX_THREADS);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(bar(BAR_K_FULL + s), 1);
       mbar_init(bar(BAR_V_FULL + s), 1);
@@ -132,9 +151,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(bar(BAR_Q), TILE_BYTES);
-      tma_load_2d(smem_base + OFF_Q, &tmQ, bar(BAR_Q), h * D, q_row0);
-      tma_load_2d(smem_base + OFF_Q + SLAB_BYTES, &tmQ, bar(BAR_Q), h * D + 64, q_row0);
       bool ok = true;
       for (int j = 0; j < n_kv && ok; ++j) {
         const int st = j & 1;
@@ -174,7 +190,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                                (static_cast<uint32_t>(BQ >> 4) << 24);
       // descriptor bases: one per buffer, constants per K step (the issue loop must stay short)
       constexpr uint32_t HI = smem_desc_hi(1024);
-      const uint32_t q_lo = smem_desc_lo(smem_base + OFF_Q, 16);
       const uint32_t k_lo = smem_desc_lo(smem_base + OFF_KV, 16);
       const uint32_t v_lo = smem_desc_lo(smem_base + OFF_KV + TILE_BYTES, SLAB_BYTES);
       constexpr uint32_t STAGE16 = (2 * TILE_BYTES) >> 4;
@@ -185,7 +200,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * SLAB_BYTES + (kk & 3) * 32) >> 4;
-          umma_bf16_lh(d_tmem, q_lo + off, HI, kb + off, HI, idesc_s, kk != 0);
+          umma_bf16_tmem_a(d_tmem, tmem_base + COL_Q + kk * 8, kb + off, HI, idesc_s, kk != 0);
         }
         umma_commit(bar(BAR_S_FULL + st));
         umma_commit(bar(BAR_K_EMPTY + st));
@@ -207,7 +222,9 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             break;
           }
           tc_fence_after();
+          TRACE(0, j, 0);  // K of block j+1 present
           issue_s(j + 1);
+          TRACE(0, j, 1);  // S of block j+1 issued
         }
         if (!mbar_wait(bar(BAR_P_FULL), static_cast<uint32_t>(j) & 1u, abort_flag) ||
             !mbar_wait(bar(BAR_V_FULL + st), use & 1u, abort_flag)) {
@@ -215,6 +232,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           break;
         }
         tc_fence_after();
+        TRACE(0, j, 2);  // P of block j and V present
         const uint32_t vb = v_lo + st * STAGE16;
         const uint32_t d_tmem = tmem_base + COL_O;
         // P of keys 32g..32g+31 sits, two per column, in the first 16 of the 32 columns its thread group read S from
@@ -225,6 +243,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(bar(BAR_V_EMPTY + st));
         umma_commit(bar(BAR_O_DONE));
+        TRACE(0, j, 3);  // P V of block j issued
       }
     }
     __syncwarp();
@@ -237,6 +256,20 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     float m_used = -INFINITY, l_part = 0.f;
     bool ok = true;
+    {
+      // this thread's quarter of its query row -> TMEM (two head-dim elements per column)
+      const uint4* src = reinterpret_cast<const uint4*>(p.Q + static_cast<long long>(q_row0 + row) * p.ld_q + h * D + g * 32);
+      uint32_t qw[16];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint4 v4 = src[c];
+        qw[4 * c] = v4.x; qw[4 * c + 1] = v4.y; qw[4 * c + 2] = v4.z; qw[4 * c + 3] = v4.w;
+      }
+      tmem_st16(tmem_base + COL_Q + g * 16 + lane_addr, qw);
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_Q));
+    }
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
       const uint32_t use = static_cast<uint32_t>(j >> 1);
@@ -245,9 +278,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         break;
       }
       tc_fence_after();
+      if (threadIdx.x == 64) TRACE(1, j, 0);  // S complete
       uint32_t sv[CPT];
       tmem_ld32(tmem_base + COL_S + st * BKV + g * CPT + lane_addr, sv);
       tmem_wait_ld();
+      if (threadIdx.x == 64) TRACE(1, j, 1);  // scores in registers
 
       if (p.causal && j == qb) {
         const int key0 = g * CPT;
@@ -267,6 +302,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         break;
       }
       const float m_new = fmaxf(fmaxf(xc[row], xc[BQ + row]), fmaxf(xc[2 * BQ + row], xc[3 * BQ + row]));
+      if (threadIdx.x == 64) TRACE(1, j, 2);  // row maximum exchanged
 
       // raise the maximum only when it moved far; all threads of a row see the same numbers
       float alpha = 1.f;
@@ -292,6 +328,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       l_part += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
 
+      if (threadIdx.x == 64) TRACE(1, j, 3);  // exponentials done
       // P replaces the scores this thread has just read (its own columns: nobody else touches them)
       tmem_st16(tmem_base + COL_S + st * BKV + g * CPT + lane_addr, packed);
       if (any_raise) {
@@ -312,6 +349,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL));
+      if (threadIdx.x == 64) TRACE(1, j, 4);  // P published
     }
 
     if (ok && mbar_wait(bar(BAR_O_DONE), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag)) {
@@ -398,10 +436,9 @@ FTB200_API int ftb200_attention_fwd(const void* q, const void* k, const void* v,
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(o) || (ld_q & 7) || (ld_k & 7) || (ld_v & 7) ||
       (ld_o & 7))
     return FTB200_E_ALIGN;
-  CUtensorMap tq, tk, tv;
+  CUtensorMap tk, tv;
   const long long rows = static_cast<long long>(batch) * seq;
-  int rc = encode_rows(&tq, q, rows, static_cast<long long>(n_heads) * D, ld_q, BQ);
-  if (rc == 0) rc = encode_rows(&tk, k, rows, static_cast<long long>(n_kv_heads) * D, ld_k, BKV);
+  int rc = encode_rows(&tk, k, rows, static_cast<long long>(n_kv_heads) * D, ld_k, BKV);
   if (rc == 0) rc = encode_rows(&tv, v, rows, static_cast<long long>(n_kv_heads) * D, ld_v, BKV);
   if (rc != 0) return rc;
   static bool attr_set = false;
@@ -413,9 +450,14 @@ FTB200_API int ftb200_attention_fwd(const void* q, const void* k, const void* v,
   AttnParams p;
   p.batch = batch; p.seq = seq; p.n_heads = n_heads; p.n_kv_heads = n_kv_heads; p.causal = causal;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.Q = reinterpret_cast<const __nv_bfloat16*>(q); p.ld_q = ld_q;
   p.ld_o = ld_o; p.O = reinterpret_cast<__nv_bfloat16*>(o); p.lse = lse; p.status = status;
+  p.trace = nullptr;
+#ifdef FTB200_ATTN_TRACE
+  p.trace = reinterpret_cast<long long*>(lse) + (static_cast<long long>(batch) * n_heads * seq + 1) / 2;  // caller over-allocates lse
+#endif
   const long long grid = static_cast<long long>(batch) * n_heads * (seq / BQ);
   if (grid > 0x7fffffffLL) return FTB200_E_TOOBIG;
-  attention_fwd_kernel<<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, p);
+  attention_fwd_kernel<<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(tk, tv, p);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }

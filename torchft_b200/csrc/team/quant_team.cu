@@ -186,26 +186,38 @@ __device__ __forceinline__ void allreduce_fp8_body(const TeamParams& tp, const Q
   // ---- quantise the local contribution into this rank's arena
   const T* ia = reinterpret_cast<const T*>(a.in_a);
   const T* ib = reinterpret_cast<const T*>(a.in_b);
-  for (long long blk0 = warp * BPW; blk0 < nblocks; blk0 += nwarps * BPW) {
-    const long long blk = blk0 + bw;
-    const bool live = blk < nblocks;
-    float f[EPL];
+  // two block groups per iteration so that twice as many loads are in flight per lane
+  for (long long blk0 = warp * BPW; blk0 < nblocks; blk0 += 2 * nwarps * BPW) {
+    float f[2][EPL];
+    long long blk[2];
+    bool live[2];
 #pragma unroll
-    for (int e = 0; e < EPL; ++e) f[e] = 0.f;
-    if (live && !a.zero_contribution) {
-      load16<T>(ia + blk * QB + sub * EPL, f);
-      if (ib != nullptr) {
-        float g[EPL];
-        load16<T>(ib + blk * QB + sub * EPL, g);
+    for (int u = 0; u < 2; ++u) {
+      blk[u] = blk0 + u * nwarps * BPW + bw;
+      live[u] = blk[u] < nblocks;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) f[e] -= g[e];
+      for (int e = 0; e < EPL; ++e) f[u][e] = 0.f;
+      if (live[u] && !a.zero_contribution) load16<T>(ia + blk[u] * QB + sub * EPL, f[u]);
+    }
+    if (ib != nullptr && !a.zero_contribution) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        if (live[u]) {
+          float g[EPL];
+          load16<T>(ib + blk[u] * QB + sub * EPL, g);
+#pragma unroll
+          for (int e = 0; e < EPL; ++e) f[u][e] -= g[e];
+        }
       }
     }
-    const float amax = group8_max(absmax16(f));
-    if (live) {
-      const float s = amax > 0.f ? amax / FP8_MAX : 1.f;
-      my_codes[blk * LPB + sub] = encode16(f, 1.f / s);
-      if (sub == 0) my_scales[blk] = s;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const float amax = group8_max(absmax16(f[u]));
+      if (live[u]) {
+        const float s = amax > 0.f ? amax / FP8_MAX : 1.f;
+        my_codes[blk[u] * LPB + sub] = encode16(f[u], 1.f / s);
+        if (sub == 0) my_scales[blk[u]] = s;
+      }
     }
   }
   if (!grid_arrive(tp, 2, &sh_code)) return;
@@ -260,10 +272,28 @@ __device__ __forceinline__ void allreduce_fp8_body(const TeamParams& tp, const Q
   T* out = reinterpret_cast<T*>(a.out);
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = tid; i < nblocks * LPB; i += nthreads) {
-    float f[EPL];
-    decode16(my_codes[i], my_scales[i / LPB], f);
-    store16<T>(out + i * EPL, f);
+  // four pieces in flight per thread: the loop is a pure stream and latency-bound otherwise
+  const long long npieces = nblocks * LPB;
+  for (long long i0 = tid; i0 < npieces; i0 += 4 * nthreads) {
+    uint4 q[4];
+    float sc[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < npieces) {
+        q[u] = my_codes[i];
+        sc[u] = my_scales[i / LPB];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < npieces) {
+        float f[EPL];
+        decode16(q[u], sc[u], f);
+        store16<T>(out + i * EPL, f);
+      }
+    }
   }
 }
 

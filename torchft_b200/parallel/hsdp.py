@@ -71,9 +71,19 @@ class ShardedLlamaTrainer:
             self.g_shard = [replica_alloc(n, bf) for n in self.shard_numel]
         else:
             self.g_shard = [torch.empty(n, dtype=bf, device=device) for n in self.shard_numel]
-        self.master = [torch.empty(n, dtype=f32, device=device) for n in self.shard_numel]
-        self.m = [torch.zeros(n, dtype=f32, device=device) for n in self.shard_numel]
-        self.v = [torch.zeros(n, dtype=f32, device=device) for n in self.shard_numel]
+        # fp32 master weights and AdamW moments: one allocation each, units are views.  A peer that
+        # heals from this rank then maps three allocations instead of three per unit.
+        def carve(flat: torch.Tensor) -> List[torch.Tensor]:
+            out, off = [], 0
+            for n in self.shard_numel:
+                out.append(flat[off : off + n])
+                off += n
+            return out
+
+        total = sum(self.shard_numel)
+        self.master = carve(torch.empty(total, dtype=f32, device=device))
+        self.m = carve(torch.zeros(total, dtype=f32, device=device))
+        self.v = carve(torch.zeros(total, dtype=f32, device=device))
         if ws == 1:
             self.p_full = self.p_shard
             self._g_bufs: Dict[int, List[torch.Tensor]] = {}
