@@ -41,7 +41,7 @@ def run_multi_recovery(init_transport, world=3):
             meta_box[rank] = metadata
             barrier.wait(10)
             md = meta_box[0]
-            # round 1: rank 0 -> ranks 1, 2
+            # first exchange: rank 0 -> ranks 1, 2
             if rank == 0:
                 transport.send_checkpoint([1, 2], step=1, state_dict=want, timeout=timeout)
             else:
@@ -49,14 +49,14 @@ def run_multi_recovery(init_transport, world=3):
                 assert_state_equal(got, want)
             barrier.wait(10)
             transport.disallow_checkpoint()
-            # round 2: rank 0 -> rank 1
+            # second exchange: rank 0 -> rank 1
             if rank == 0:
                 transport.send_checkpoint([1], step=2, state_dict=want, timeout=timeout)
             elif rank == 1:
                 assert_state_equal(transport.recv_checkpoint(0, md, step=2, timeout=timeout), want)
             barrier.wait(10)
             transport.disallow_checkpoint()
-            # round 3: nobody sends; the receiver must give up quickly
+            # third exchange: nobody sends; the receiver must give up quickly
             if rank == 2:
                 with pytest.raises(Exception):
                     transport.recv_checkpoint(0, md, step=3, timeout=timedelta(milliseconds=10))

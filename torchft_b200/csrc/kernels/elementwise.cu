@@ -91,18 +91,19 @@ __global__ void rmsnorm_bwd_kernel(const bf16x8* __restrict__ dy, const bf16x8* 
   for (int64_t row = blockIdx.x; row < T; row += gridDim.x) {
     const float r = rstd[row];
     float dot = 0.f;
+    float a[MAXV][8], b[MAXV][8];  // dy and x of this row stay in registers across the reduction
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
       if (i < D8) {
-        float a[8], b[8], c[8];
-        unpack8(dy[row * D8 + i], a);
-        unpack8(x[row * D8 + i], b);
+        float c[8];
+        unpack8(dy[row * D8 + i], a[v]);
+        unpack8(x[row * D8 + i], b[v]);
         unpack8(w[i], c);
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
-          dot += a[e] * c[e] * b[e];
-          dw_acc[v][e] += a[e] * b[e] * r;
+          dot += a[v][e] * c[e] * b[v][e];
+          dw_acc[v][e] += a[v][e] * b[v][e] * r;
         }
       }
     }
@@ -112,12 +113,10 @@ __global__ void rmsnorm_bwd_kernel(const bf16x8* __restrict__ dy, const bf16x8* 
     for (int v = 0; v < MAXV; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
       if (i < D8) {
-        float a[8], b[8], c[8], o[8];
-        unpack8(dy[row * D8 + i], a);
-        unpack8(x[row * D8 + i], b);
+        float c[8], o[8];
         unpack8(w[i], c);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = r * c[e] * a[e] - b[e] * coef;
+        for (int e = 0; e < 8; ++e) o[e] = r * c[e] * a[v][e] - b[v][e] * coef;
         if (dres != nullptr) {
           float d[8];
           unpack8(dres[row * D8 + i], d);
@@ -405,7 +404,7 @@ FTB200_API int ftb200_rmsnorm_bwd(const void* dy, const void* x, const void* w, 
                                   cudaStream_t st) {
   if (D % 8) return FTB200_E_ALIGN;
   const int D8 = D / 8;
-  const int threads = 256;
+  const int threads = D8 > 256 ? 512 : 256;  // wide rows: 16 warps per block, two blocks per SM
   const int nblk = min(T, ftb200::sm_count() * 2);
   const int maxv = (D8 + threads - 1) / threads;
   if (maxv <= 1)
@@ -530,7 +529,7 @@ FTB200_API int ftb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const v
   }
   float* scratch = g_noalloc_scratch_addr[dev];
   const int D8 = D / 8;
-  const int threads = 256;
+  const int threads = D8 > 256 ? 512 : 256;  // wide rows: 16 warps per block, two blocks per SM
   const int maxv = (D8 + threads - 1) / threads;
   if (maxv <= 1)
     rmsnorm_bwd_kernel<1><<<nblk, threads, 0, st>>>((const bf16x8*)dy, (const bf16x8*)x, (const bf16x8*)w, rstd,

@@ -90,6 +90,65 @@ def bench_rmsnorm(t: int, d: int, iters: int) -> dict:
     return {"kernel": "rmsnorm_fwd(add+norm)", "t": t, "d": d, "ms": ms, "gbs": gbs, f"frac_of_{how}_copy_bw": gbs / hbm}
 
 
+def bench_elementwise(iters: int) -> list:
+    """The memory-bound kernels of one Llama-3 8B layer / head at seq 8192: each is timed on tensors of the real
+    shape, several of them cycled so that consecutive launches do not hit L2, and reported as algorithmic bytes
+    over the measured copy bandwidth."""
+    dev = "cuda"
+    hbm, _, how = _peaks()
+    T, D, Fd, V, QKV, H = 8192, 4096, 14336, 128256, 6144, 40
+    out = []
+
+    def row(name, nbytes, ms):
+        gbs = nbytes / ms / 1e6
+        out.append({"kernel": name, "ms": ms, "gbs": gbs, f"frac_of_{how}_copy_bw": gbs / hbm})
+
+    def cycle(make, n=4):
+        bufs = [make() for _ in range(n)]
+        state = {"i": 0}
+
+        def nxt():
+            state["i"] = (state["i"] + 1) % n
+            return bufs[state["i"]]
+
+        return nxt
+
+    # RMSNorm backward (dx and dw): reads dy, x, dres, writes dx
+    xs = cycle(lambda: torch.randn(T, D, device=dev).bfloat16())
+    w = torch.ones(D, device=dev).bfloat16()
+    rstd = torch.rand(T, device=dev) + 0.5
+    dx, dw = torch.empty(T, D, device=dev, dtype=torch.bfloat16), torch.zeros(D, device=dev, dtype=torch.bfloat16)
+    row("rmsnorm_bwd", T * D * 2 * 4, timeit(lambda: K.rmsnorm_bwd(xs(), xs(), w, rstd, dres=xs(), dx=dx, dw=dw), iters))
+    # RoPE in place on the packed QKV activation (Q and K heads)
+    qkvs = cycle(lambda: torch.randn(T, QKV, device=dev).bfloat16(), 6)
+    table = K.rope_table(T, 128, 500000.0, torch.device(dev))
+    row("rope", T * H * 128 * 2 * 2, timeit(lambda: K.rope_(qkvs(), table, T, H, 128), iters))
+    # SwiGLU backward in place on the gate/up activation: reads ds, gu, writes dgu
+    gus = cycle(lambda: torch.randn(T, 2 * Fd, device=dev).bfloat16(), 3)
+    dss = cycle(lambda: torch.randn(T, Fd, device=dev).bfloat16(), 3)
+
+    def swiglu():
+        g = gus()
+        K.swiglu_bwd(dss(), g, dgu=g)
+
+    row("swiglu_bwd", T * Fd * 2 * 5, timeit(swiglu, iters))
+    # cross-entropy with in-place gradient over the full vocabulary: reads and writes the logits once
+    logits = torch.randn(T, V, device=dev).bfloat16()
+    tgt = torch.randint(0, V, (T,), device=dev)
+    loss = torch.empty(T, device=dev)
+    row("cross_entropy", T * V * 2 * 2, timeit(lambda: K.cross_entropy_(logits, tgt, 1.0 / T, loss), max(2, iters // 2), warmup=1))
+    del logits
+    # embedding gather
+    table_e = torch.randn(V, D, device=dev).bfloat16()
+    eo = torch.empty(T, D, device=dev, dtype=torch.bfloat16)
+    row("embedding_fwd", T * D * 2 * 2, timeit(lambda: K.embedding_fwd(tgt, table_e, out=eo), iters))
+    # sum of squares (gradient norm) over a 218 M-element layer gradient
+    gsq = cycle(lambda: torch.randn(218112000, device=dev).bfloat16(), 2)
+    acc = torch.zeros(1, device=dev)
+    row("sumsq", 218112000 * 2, timeit(lambda: K.sumsq_(gsq(), acc), iters))
+    return out
+
+
 def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare: bool) -> dict:
     """Causal GQA attention, head dim 128, forward and backward; FLOPs count the causal half."""
     import torch.nn.functional as F
@@ -129,7 +188,7 @@ def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "adamw", "rmsnorm", "attention", "all"])
+    ap.add_argument("what", choices=["gemm", "adamw", "rmsnorm", "attention", "elementwise", "all"])
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=32)
@@ -149,6 +208,9 @@ def main() -> None:
         print(json.dumps(bench_adamw(1 << 28 if a.what == "all" else a.n, a.iters)), flush=True)
     if a.what in ("attention", "all"):
         print(json.dumps(bench_attention(a.batch, a.seq, a.heads, a.kv_heads, a.iters, not a.no_compare)), flush=True)
+    if a.what in ("elementwise", "all"):
+        for r in bench_elementwise(a.iters):
+            print(json.dumps(r), flush=True)
     if a.what in ("rmsnorm", "all"):
         print(json.dumps(bench_rmsnorm(8192, 4096, a.iters)), flush=True)
 
