@@ -34,6 +34,7 @@ LIB_DIR = PKG_DIR / "_lib"
 BUILD_DIR = REPO_DIR / "build"
 
 KERNEL_LIB = LIB_DIR / "libftb200_kernels.so"
+KERNEL_LIB_CHECKED = LIB_DIR / "libftb200_kernels_checked.so"  # -DFT_BOUNDS_CHECK=1 debug build
 CONTROL_MOD = PKG_DIR / ("_ftcp" + sysconfig.get_config_var("EXT_SUFFIX"))
 
 NVCC_FLAGS = [
@@ -118,27 +119,32 @@ def _needs_link(target: Path, objs: Sequence[Path]) -> bool:
     return any(o.stat().st_mtime > t for o in objs)
 
 
-def build_kernels(verbose: bool = False) -> Path:
-    """Compile every ``csrc/kernels/*.cu`` and ``csrc/team/*.cu`` for sm_100a."""
+def build_kernels(verbose: bool = False, checked: bool = False) -> Path:
+    """Compile every ``csrc/kernels/*.cu`` and ``csrc/team/*.cu`` for sm_100a.  ``checked``
+    (or ``FTB200_BOUNDS_CHECK=1``) builds the checked-index debug variant next to the normal
+    library instead: ``FTB_IN_RANGE`` then records out-of-range indices in a status word that
+    ``ftb200_bounds_status_*`` report, and the guarded access is skipped."""
+    checked = checked or bool(os.environ.get("FTB200_BOUNDS_CHECK"))
+    target = KERNEL_LIB_CHECKED if checked else KERNEL_LIB
     with _lock:
         sources = sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "team").glob("*.cu"))
         headers = []
         for d in ("kernels", "team"):
             headers += sorted((CSRC / d).glob("*.cuh")) + sorted((CSRC / d).glob("*.h"))
         flags = NVCC_FLAGS + [f"-I{CSRC / 'kernels'}", f"-I{CSRC / 'team'}"]
-        if os.environ.get("FTB200_BOUNDS_CHECK"):
+        if checked:
             flags = flags + ["-DFT_BOUNDS_CHECK=1"]
         if verbose:
             flags = flags + ["-Xptxas", "-v"]
-        objs = _compile_objects(sources, headers, [_nvcc()], flags, "k")
+        objs = _compile_objects(sources, headers, [_nvcc()], flags, "kc" if checked else "k")
         LIB_DIR.mkdir(parents=True, exist_ok=True)
-        if _needs_link(KERNEL_LIB, objs):
+        if _needs_link(target, objs):
             _run(
                 [
                     _nvcc(),
                     "-shared",
                     "-o",
-                    str(KERNEL_LIB),
+                    str(target),
                     *map(str, objs),
                     "-gencode",
                     "arch=compute_100a,code=sm_100a",
@@ -146,7 +152,7 @@ def build_kernels(verbose: bool = False) -> Path:
                     "shared",
                 ]
             )
-        return KERNEL_LIB
+        return target
 
 
 def build_control() -> Path:
@@ -171,6 +177,7 @@ def build_control() -> Path:
 
 def build_all(verbose: bool = False) -> None:
     build_kernels(verbose=verbose)
+    build_kernels(checked=True)  # the checked-index debug variant, used by tests/test_bounds_check_build.py
     build_control()
 
 

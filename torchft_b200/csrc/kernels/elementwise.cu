@@ -18,7 +18,7 @@ __global__ void embedding_fwd_kernel(const int64_t* __restrict__ tok, const bf16
   const int t = blockIdx.x;
   if (t >= T) return;
   int64_t id = tok[t];
-  if (id < 0 || id >= V) id = 0;
+  if (!FTB_IN_RANGE(id, V) || id < 0 || id >= V) id = 0;  // an id outside the vocabulary reads row 0
   const bf16x8* src = table + id * D8;
   bf16x8* dst = out + static_cast<int64_t>(t) * D8;
   for (int i = threadIdx.x; i < D8; i += blockDim.x) dst[i] = src[i];
@@ -29,7 +29,7 @@ __global__ void embedding_bwd_kernel(const int64_t* __restrict__ tok, const __nv
   const int t = blockIdx.x;
   if (t >= T) return;
   int64_t id = tok[t];
-  if (id < 0 || id >= V) return;
+  if (!FTB_IN_RANGE(id, V) || id < 0 || id >= V) return;
   const __nv_bfloat162* src = dout + static_cast<int64_t>(t) * D2;
   __nv_bfloat162* dst = dtable + id * D2;
   for (int i = threadIdx.x; i < D2; i += blockDim.x) atomicAdd(dst + i, src[i]);
@@ -166,6 +166,7 @@ __global__ void rope_kernel(bf16x8* __restrict__ buf, const float4* __restrict__
   const float4 c0 = c[0], c1 = c[1];
   const float cosv[4] = {c0.x, c0.z, c1.x, c1.z};
   const float sinv[4] = {c0.y * sin_sign, c0.w * sin_sign, c1.y * sin_sign, c1.w * sin_sign};
+  if (!FTB_IN_RANGE(r, row_stride8)) return;  // rotated heads must fit inside a row
   bf16x8* p = buf + t * row_stride8 + r;
   float f[8];
   unpack8(*p, f);
@@ -246,6 +247,8 @@ __global__ void cross_entropy_kernel(bf16x8* __restrict__ logits, const int64_t*
   sum *= __expf(mx - gmx);
   const float gsum = ftb200::block_sum(sum, scratch);
   const int64_t tgt = target[row];
+  if (tgt >= 0) (void)FTB_IN_RANGE(tgt, 8 * static_cast<int64_t>(V8));  // negative targets mean "ignore"
+  (void)FTB_IN_RANGE(V8 - 1, ld8);                                        // a row must fit inside its stride
   const float inv = 1.f / gsum;
   if (threadIdx.x == 0) {
     const __nv_bfloat16* flat = reinterpret_cast<const __nv_bfloat16*>(lr);
@@ -543,3 +546,16 @@ FTB200_API int ftb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const v
   colsum_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
+
+// ---- checked-index debug build: status query and a self-test that records an out-of-range
+// index without touching memory (a launch of one thread evaluating FTB_IN_RANGE(5, 4))
+#ifdef FT_BOUNDS_CHECK
+namespace {
+__global__ void bounds_selftest_kernel(int i, int n, int* ok) { *ok = FTB_IN_RANGE(i, n) ? 1 : 0; }
+}  // namespace
+FTB200_API int ftb200_bounds_selftest(int i, int n, int* ok_dev, cudaStream_t st) {
+  bounds_selftest_kernel<<<1, 1, 0, st>>>(i, n, ok_dev);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+#endif
+FTB_DEFINE_BOUNDS_QUERY(elementwise)

@@ -29,6 +29,43 @@
 #define FTB200_ST_EPOCH 3
 #define FTB200_ST_BOUNDS 4
 
+// Checked-index debug build (-DFT_BOUNDS_CHECK=1, FTB200_BOUNDS_CHECK=1 for the build driver):
+// FTB_IN_RANGE(i, n) is true for 0 <= i < n; otherwise it records FTB200_ST_BOUNDS and the
+// offending index in a per-translation-unit device word and is false, and the caller skips
+// the access.  In the normal build it is the constant `true` and costs nothing.  Used where an
+// index derives from data or from caller-supplied strides (token ids, targets, row strides,
+// shard owners, copy tables); loops bounded by their own extent are not decorated.
+// FTB_DEFINE_BOUNDS_QUERY(tag) exports `ftb200_bounds_status_<tag>(long long* index)`, which
+// returns the recorded code and clears it.
+#ifdef FT_BOUNDS_CHECK
+namespace ftb200 {
+namespace dbg {
+static __device__ int g_bounds_status;
+static __device__ long long g_bounds_index;
+__device__ __forceinline__ bool in_range(long long i, long long n) {
+  if (i >= 0 && i < n) return true;
+  if (atomicCAS(&g_bounds_status, 0, FTB200_ST_BOUNDS) == 0) g_bounds_index = i;
+  return false;
+}
+}  // namespace dbg
+}  // namespace ftb200
+#define FTB_IN_RANGE(i, n) ftb200::dbg::in_range(static_cast<long long>(i), static_cast<long long>(n))
+#define FTB_DEFINE_BOUNDS_QUERY(tag)                                                                     \
+  FTB200_API int ftb200_bounds_status_##tag(long long* index) {                                          \
+    int st = 0;                                                                                          \
+    long long idx = 0;                                                                                   \
+    if (cudaMemcpyFromSymbol(&st, ftb200::dbg::g_bounds_status, sizeof(st)) != cudaSuccess) return -5;   \
+    if (cudaMemcpyFromSymbol(&idx, ftb200::dbg::g_bounds_index, sizeof(idx)) != cudaSuccess) return -5;  \
+    const int zero = 0;                                                                                  \
+    if (cudaMemcpyToSymbol(ftb200::dbg::g_bounds_status, &zero, sizeof(zero)) != cudaSuccess) return -5; \
+    if (index != nullptr) *index = idx;                                                                  \
+    return st;                                                                                           \
+  }
+#else
+#define FTB_IN_RANGE(i, n) true
+#define FTB_DEFINE_BOUNDS_QUERY(tag)
+#endif
+
 namespace ftb200 {
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {

@@ -314,6 +314,7 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
               const long long flat = p.sc_off + static_cast<long long>(grow) * p.ldc + gcol;
               const long long owner = flat / p.sc_shard;
               const long long rem = flat - owner * p.sc_shard;
+              if (!FTB_IN_RANGE(owner, p.sc_world)) continue;
               __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.sc_peers[owner]);
               *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(p.sc_src) * p.sc_shard + rem) = v;
             }
@@ -547,3 +548,5 @@ FTB200_API int ftb200_gemm_bf16_scatter(const void* A, const void* B, int M, int
   sc.world = world; sc.src = src_rank; sc.shard = shard_elems; sc.off = unit_off; sc.peers = peers;
   return gemm_2cta_impl(A, B, nullptr, M, N, K, a_mn_major, b_mn_major, lda, ldb, N, 0, status, max_ctas, nullptr, 0, stream, &sc);
 }
+
+FTB_DEFINE_BOUNDS_QUERY(gemm_2cta)

@@ -502,6 +502,7 @@ __global__ void scatter_to_stage_kernel(const ftb200::bf16x8* __restrict__ src, 
   const long long flat = unit_off + i * 8;
   const long long owner = flat / shard;
   const long long rem = flat - owner * shard;
+  if (!FTB_IN_RANGE(owner, MAX_RANKS)) return;
   __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(peers.p[owner]);
   *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(src_rank) * shard + rem) = src[i];
 }
@@ -519,3 +520,5 @@ FTB200_API int ftb200_scatter_to_stage(const void* src, long long n, long long u
       reinterpret_cast<const ftb200::bf16x8*>(src), n8, unit_off, shard_elems, src_rank, sp);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
+
+FTB_DEFINE_BOUNDS_QUERY(team)

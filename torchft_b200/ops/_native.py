@@ -51,13 +51,31 @@ def lib() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        path = _build.KERNEL_LIB
+        checked = os.environ.get("FTB200_KERNEL_LIB", "") == "checked"
+        path = _build.KERNEL_LIB_CHECKED if checked else _build.KERNEL_LIB
         if not path.exists():
             if os.environ.get("FTB200_NO_AUTOBUILD"):
                 raise KernelError(f"{path} is missing; run `python -m torchft_b200._build`")
-            _build.build_kernels()
+            _build.build_kernels(checked=checked)
         _lib = ctypes.CDLL(str(path))
         return _lib
+
+
+def bounds_status() -> tuple:
+    """``(code, index)`` recorded by the checked-index debug build (``FTB200_KERNEL_LIB=checked``)
+    since the last call: ``(0, 0)`` when every guarded index was in range, ``(4, i)`` with the
+    first offending index otherwise.  Always ``(0, 0)`` on the normal library, which has no checks."""
+    code, index = 0, 0
+    library = lib()
+    for tag in ("elementwise", "team", "gemm_2cta"):
+        fn = getattr(library, f"ftb200_bounds_status_{tag}", None)
+        if fn is None:
+            continue
+        idx = ctypes.c_longlong(0)
+        st = int(fn(ctypes.byref(idx)))
+        if st and not code:
+            code, index = st, int(idx.value)
+    return code, index
 
 
 launch_count = 0  # kernels launched through this library since import (bench.py reports the delta)
