@@ -282,10 +282,11 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = m0 + q * 32 + lane;
       const uint32_t taddr0 = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      if (p.sc_world > 0) {
-        // Scatter epilogue: the tile goes through a per-warp staging area so that every store
-        // instruction covers two 256-byte row segments; short scattered stores to a peer cost
-        // an NVLink packet each and throttle the whole kernel.
+      if (p.sc_world > 0 || (!p.out_fp32 && !p.accumulate && vec_ok && (p.N & 7) == 0)) {
+        // Staged epilogue (bf16 output, local or scattered to peers): the tile goes through a
+        // per-warp staging area so that every store instruction covers two 256-byte row segments.
+        // One 16-byte piece per thread and row would touch 32 rows per instruction: half-filled
+        // sectors locally, and an NVLink packet each towards a peer, which throttles the kernel.
         uint8_t* stg = smem + STAGES * STAGE_BYTES + 256 + q * SC_STAGE_WARP_BYTES;
         const int half = lane >> 4, ch = lane & 15;
 #pragma unroll 1
@@ -311,12 +312,31 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
             const int grow = m0 + q * 32 + rr;
             const ftb200::bf16x8 v = *reinterpret_cast<const ftb200::bf16x8*>(stg + rr * 256 + ((ch ^ (rr & 15)) << 4));
             if (grow < p.M && gcol + 8 <= p.N) {
-              const long long flat = p.sc_off + static_cast<long long>(grow) * p.ldc + gcol;
-              const long long owner = flat / p.sc_shard;
-              const long long rem = flat - owner * p.sc_shard;
-              if (!FTB_IN_RANGE(owner, p.sc_world)) continue;
-              __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.sc_peers[owner]);
-              *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(p.sc_src) * p.sc_shard + rem) = v;
+              if (p.sc_world > 0) {
+                const long long flat = p.sc_off + static_cast<long long>(grow) * p.ldc + gcol;
+                const long long owner = flat / p.sc_shard;
+                const long long rem = flat - owner * p.sc_shard;
+                if (!FTB_IN_RANGE(owner, p.sc_world)) continue;
+                __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(p.sc_peers[owner]);
+                *reinterpret_cast<ftb200::bf16x8*>(base + static_cast<long long>(p.sc_src) * p.sc_shard + rem) = v;
+              } else {
+                __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(grow) * p.ldc;
+                *reinterpret_cast<ftb200::bf16x8*>(crow + gcol) = v;
+                if (p.aux != nullptr) {
+                  // activation of the rounded values, so that a later recompute from C agrees
+                  float g[8];
+                  ftb200::unpack8(v, g);
+                  float sv[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) sv[e] = g[2 * e] / (1.f + __expf(-g[2 * e])) * g[2 * e + 1];
+                  __nv_bfloat162 lo = __floats2bfloat162_rn(sv[0], sv[1]), hi = __floats2bfloat162_rn(sv[2], sv[3]);
+                  uint2 o2;
+                  o2.x = *reinterpret_cast<uint32_t*>(&lo);
+                  o2.y = *reinterpret_cast<uint32_t*>(&hi);
+                  *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.aux) + static_cast<long long>(grow) * p.ld_aux +
+                                            (gcol >> 1)) = o2;
+                }
+              }
             }
           }
           __syncwarp();
@@ -510,7 +530,7 @@ static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, i
   int ctas = ftb200::sm_count() & ~1;
   if (max_ctas > 0 && max_ctas < ctas) ctas = std::max(2, max_ctas & ~1);
   if (2 * tiles < ctas) ctas = 2 * tiles;
-  gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, sc != nullptr ? SMEM_BYTES_SCATTER : SMEM_BYTES, stream>>>(tmA, tmB, p);
+  gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, SMEM_BYTES_SCATTER, stream>>>(tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
