@@ -134,3 +134,78 @@ def test_runner_environment_and_punisher(tmp_path):
     assert env["REPLICA_GROUP_ID"] == "1" and env["NUM_REPLICA_GROUPS"] == "2" and env["CUDA_VISIBLE_DEVICES"] == "4,5,6,7"
     (tmp_path / "p.json").write_text(json.dumps({"0": None, "1": None}))
     assert Punisher(str(tmp_path / "p.json")).kill_one() is None
+
+
+# ---- pieces added with the engine-native DiLoCo and the attention kernels -------------------
+
+
+def test_split_units_is_contiguous_balanced_and_total():
+    from torchft_b200.parallel.diloco import split_units
+
+    numels = [500, 10, 10, 10, 10, 10, 10, 10, 10, 520]
+    parts = split_units(numels, 4)
+    assert [u for p in parts for u in p] == list(range(len(numels)))  # contiguous cover
+    assert all(parts)
+    assert parts[0] == [0] and parts[-1][-1] == 9
+    assert split_units([1, 1, 1], 3) == [[0], [1], [2]]
+    import pytest as _pytest
+
+    with _pytest.raises(ValueError):
+        split_units([1, 2], 3)
+
+
+def test_engine_diloco_argument_validation():
+    from unittest.mock import MagicMock
+
+    import pytest as _pytest
+    import torch as _torch
+
+    from torchft_b200.models.llama import LLAMA_TINY
+    from torchft_b200.parallel.diloco import EngineDiLoCo
+    from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
+
+    tr = ShardedLlamaTrainer(LLAMA_TINY, 1, 16, _torch.device("cpu"))
+    m = MagicMock()
+    m._use_async_quorum = True
+    with _pytest.raises(ValueError):
+        EngineDiLoCo(tr, m, n_fragments=2, sync_every=4)  # needs a synchronous quorum
+    m._use_async_quorum = False
+    with _pytest.raises(ValueError):
+        EngineDiLoCo(tr, m, n_fragments=3, sync_every=4)  # not a multiple
+    with _pytest.raises(ValueError):
+        EngineDiLoCo(tr, m, n_fragments=2, sync_every=4, fragment_sync_delay=2)  # delay >= interval
+    with _pytest.raises(ValueError):
+        EngineDiLoCo(tr, m, n_fragments=2, sync_every=4, fragment_update_alpha=1.5)
+    d = EngineDiLoCo(tr, m, n_fragments=2, sync_every=4)
+    assert len(d.fragments) == 2 and m.register_state_dict_fn.call_count == 2
+    tr2 = ShardedLlamaTrainer(LLAMA_TINY, 1, 16, _torch.device("cpu"), manager=m)
+    with _pytest.raises(ValueError):
+        EngineDiLoCo(tr2, m, n_fragments=2, sync_every=4)  # the trainer must not allreduce every step
+
+
+def test_attention_selection_and_cpu_wrappers():
+    import pytest as _pytest
+    import torch as _torch
+
+    from torchft_b200.models.llama import LLAMA3_8B, LLAMA_TINY, SdpaAttention, make_attention
+    from torchft_b200.ops import kernels as K
+
+    cpu = _torch.device("cpu")
+    assert isinstance(make_attention(LLAMA3_8B, 8192, cpu), SdpaAttention)  # no CUDA: library/CPU path
+    assert isinstance(make_attention(LLAMA_TINY, 128, cpu, "sdpa"), SdpaAttention)
+    with _pytest.raises(ValueError):
+        make_attention(LLAMA_TINY, 128, cpu, "tcgen05")
+    assert K.attention_supported(8192, 128) and not K.attention_supported(8192, 64) and not K.attention_supported(100, 128)
+    # the CPU restatement behind the wrappers: forward + backward agree with autograd of the reference
+    B, S, Hq, Hkv, D = 1, 8, 2, 1, 4
+    g = _torch.Generator().manual_seed(0)
+    qkv = _torch.randn(B * S, (Hq + 2 * Hkv) * D, generator=g).bfloat16()
+    q, k, v = qkv[:, : Hq * D], qkv[:, Hq * D : (Hq + Hkv) * D], qkv[:, (Hq + Hkv) * D :]
+    out = _torch.empty(B * S, Hq * D, dtype=_torch.bfloat16)
+    lse = _torch.empty(B, Hq, S)
+    K.attention_fwd(q, k, v, B, S, Hq, Hkv, D, out, lse)
+    assert _torch.isfinite(out.float()).all() and _torch.isfinite(lse).all()
+    dqkv = _torch.zeros_like(qkv)
+    K.attention_bwd(q, k, v, out, _torch.ones_like(out), lse, dqkv[:, : Hq * D], dqkv[:, Hq * D : (Hq + Hkv) * D],
+                    dqkv[:, (Hq + Hkv) * D :], B, S, Hq, Hkv, D)
+    assert dqkv.float().abs().sum() > 0

@@ -33,12 +33,19 @@ def make_ft_manager(rank: int, world: int, n_groups: int, shard: int, group_id: 
         dist.broadcast_object_list(addr, src=0)
     lighthouse_addr = addr[0]
 
-    base_port = int(os.environ.get("MASTER_PORT", "29500")) + 101 + group_id
+    # one store per replica group on an ephemeral port (fixed offsets from MASTER_PORT collide when two
+    # jobs run back to back on neighbouring ports); the port travels over the job's process group
     store = None
+    mine = None
     if group_rank == 0:
-        store = TCPStore(host_name="127.0.0.1", port=base_port, is_master=True, wait_for_workers=False)
+        store = TCPStore(host_name="127.0.0.1", port=0, is_master=True, wait_for_workers=False)
+        mine = (group_id, store.port)
     if world > 1:
-        dist.barrier()
+        ports = [None] * world
+        dist.all_gather_object(ports, mine)
+        base_port = dict(p for p in ports if p is not None)[group_id]
+    else:
+        base_port = store.port
 
     pg = ProcessGroupB200(timeout=timeout, arena_bytes=arena_bytes, device=device)
     manager = Manager(
