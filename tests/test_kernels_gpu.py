@@ -58,7 +58,7 @@ def test_linear_trio_matches_autograd():
     assert rel_err(K.linear_wgrad(dy, x), dy.float().t() @ x.float()) < 1e-2
 
 
-@pytest.mark.parametrize("T,D", [(64, 256), (33, 4096), (7, 1024)])
+@pytest.mark.parametrize("T,D", [(64, 256), (33, 4096), (7, 1024), (701, 4096), (613, 8192)])
 def test_rmsnorm(T, D):
     torch.manual_seed(4)
     x = torch.randn(T, D, device=DEV).bfloat16()

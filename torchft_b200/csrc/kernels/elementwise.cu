@@ -77,53 +77,83 @@ __global__ void rmsnorm_fwd_kernel(const bf16x8* __restrict__ x, const bf16x8* _
 // dx = dres + rstd*w*dy - x*rstd^3/D * sum(dy*w*x);  dw partial sums per block.
 // Each thread owns fixed 8-column groups so dw accumulates in registers across rows.
 template <int MAXV>
-__global__ void rmsnorm_bwd_kernel(const bf16x8* __restrict__ dy, const bf16x8* __restrict__ x,
+__global__ void __launch_bounds__(512, MAXV == 1 ? 2 : 1) rmsnorm_bwd_kernel(const bf16x8* __restrict__ dy, const bf16x8* __restrict__ x,
                                    const bf16x8* __restrict__ w, const float* __restrict__ rstd,
                                    const bf16x8* __restrict__ dres, bf16x8* __restrict__ dx,
                                    float* __restrict__ dw_partial, int T, int D8) {
-  __shared__ float scratch[33];
+  __shared__ float scratch[66];
   float dw_acc[MAXV][8];
 #pragma unroll
   for (int v = 0; v < MAXV; ++v)
 #pragma unroll
     for (int e = 0; e < 8; ++e) dw_acc[v][e] = 0.f;
 
-  for (int64_t row = blockIdx.x; row < T; row += gridDim.x) {
-    const float r = rstd[row];
-    float dot = 0.f;
-    float a[MAXV][8], b[MAXV][8];  // dy and x of this row stay in registers across the reduction
+  // Two rows per iteration: their loads (dy, x and the residual gradient) are all in flight before the one
+  // block-wide reduction they share, and the rows stay in registers (packed) across it.
+  for (int64_t row0 = blockIdx.x; row0 < T; row0 += 2 * static_cast<int64_t>(gridDim.x)) {
+    const int64_t rows[2] = {row0, row0 + gridDim.x};
+    const bool live[2] = {true, rows[1] < T};
+    float r[2] = {rstd[rows[0]], live[1] ? rstd[rows[1]] : 0.f};
+    bf16x8 a[2][MAXV], b[2][MAXV], d[2][MAXV];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+#pragma unroll
+      for (int v = 0; v < MAXV; ++v) {
+        const int i = threadIdx.x + v * blockDim.x;
+        if (live[k] && i < D8) {
+          a[k][v] = dy[rows[k] * D8 + i];
+          b[k][v] = x[rows[k] * D8 + i];
+          if (dres != nullptr) d[k][v] = dres[rows[k] * D8 + i];
+        }
+      }
+    }
+    float dot[2] = {0.f, 0.f};
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
       if (i < D8) {
         float c[8];
-        unpack8(dy[row * D8 + i], a[v]);
-        unpack8(x[row * D8 + i], b[v]);
         unpack8(w[i], c);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) {
-          dot += a[v][e] * c[e] * b[v][e];
-          dw_acc[v][e] += a[v][e] * b[v][e] * r;
+        for (int k = 0; k < 2; ++k) {
+          if (live[k]) {
+            float fa[8], fb[8];
+            unpack8(a[k][v], fa);
+            unpack8(b[k][v], fb);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              dot[k] += fa[e] * c[e] * fb[e];
+              dw_acc[v][e] += fa[e] * fb[e] * r[k];
+            }
+          }
         }
       }
     }
-    dot = ftb200::block_sum(dot, scratch);
-    const float coef = dot * r * r * r / (8.f * D8);
+    const float2 dots = ftb200::block_sum2(dot[0], dot[1], scratch);
+    const float coef[2] = {dots.x * r[0] * r[0] * r[0] / (8.f * D8), dots.y * r[1] * r[1] * r[1] / (8.f * D8)};
 #pragma unroll
     for (int v = 0; v < MAXV; ++v) {
       const int i = threadIdx.x + v * blockDim.x;
       if (i < D8) {
-        float c[8], o[8];
+        float c[8];
         unpack8(w[i], c);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = r * c[e] * a[v][e] - b[v][e] * coef;
-        if (dres != nullptr) {
-          float d[8];
-          unpack8(dres[row * D8 + i], d);
+        for (int k = 0; k < 2; ++k) {
+          if (live[k]) {
+            float fa[8], fb[8], o[8];
+            unpack8(a[k][v], fa);
+            unpack8(b[k][v], fb);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) o[e] += d[e];
+            for (int e = 0; e < 8; ++e) o[e] = r[k] * c[e] * fa[e] - fb[e] * coef[k];
+            if (dres != nullptr) {
+              float fd[8];
+              unpack8(d[k][v], fd);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o[e] += fd[e];
+            }
+            dx[rows[k] * D8 + i] = pack8(o);
+          }
         }
-        dx[row * D8 + i] = pack8(o);
       }
     }
   }

@@ -104,6 +104,32 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return scratch[32];
 }
 
+// Two block-wide sums for the price of one (same barriers).  `scratch` must hold 66 floats.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  a = warp_sum(a);
+  b = warp_sum(b);
+  __syncthreads();
+  if (lane == 0) {
+    scratch[warp] = a;
+    scratch[33 + warp] = b;
+  }
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float ra = (threadIdx.x < nw) ? scratch[threadIdx.x] : 0.f;
+  float rb = (threadIdx.x < nw) ? scratch[33 + threadIdx.x] : 0.f;
+  if (warp == 0) {
+    ra = warp_sum(ra);
+    rb = warp_sum(rb);
+    if (lane == 0) {
+      scratch[32] = ra;
+      scratch[65] = rb;
+    }
+  }
+  __syncthreads();
+  return make_float2(scratch[32], scratch[65]);
+}
+
 __device__ __forceinline__ float block_max(float v, float* scratch) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   v = warp_max(v);
