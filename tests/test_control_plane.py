@@ -330,3 +330,63 @@ def test_connect_timeout_raises_timeout_error():
     with pytest.raises(TimeoutError):
         C.ManagerClient("localhost:1", timedelta(milliseconds=300))
     assert time.time() - t0 < 3.0
+
+
+def test_lighthouse_join_during_shrink_only_round():
+    """A replica that asks to join while the others shrink waits through the shrink-only round and
+    is admitted in the next one: participant counts 2, 2, 3 (src/lighthouse.rs:1114-1225)."""
+    lh = C.LighthouseServer("[::]:0", 2, join_timeout_ms=100, quorum_tick_ms=10)
+    try:
+        clients = {r: C.LighthouseClient(lh.address(), timedelta(seconds=5)) for r in "abc"}
+
+        def ask(rid, out, **kw):
+            out[rid] = clients[rid].quorum(rid, timedelta(seconds=10), **kw)
+
+        def round_(specs):
+            out, threads = {}, []
+            for rid, kw in specs.items():
+                t = threading.Thread(target=ask, args=(rid, out), kwargs=kw)
+                t.start()
+                threads.append(t)
+            return out, threads
+
+        out1, th = round_({"a": {}, "b": {}})
+        for t in th:
+            t.join()
+        assert {len(q.participants) for q in out1.values()} == {2}
+        # a and b shrink; c asks to join in the same round and has to wait
+        out2, th2 = round_({"a": {"shrink_only": True}, "b": {"shrink_only": True}})
+        joiner_out = {}
+        tc = threading.Thread(target=ask, args=("c", joiner_out))
+        tc.start()
+        for t in th2:
+            t.join()
+        assert all(sorted(p.replica_id for p in q.participants) == ["a", "b"] for q in out2.values())
+        assert "c" not in joiner_out  # still blocked
+        out3, th3 = round_({"a": {}, "b": {}})
+        for t in th3:
+            t.join()
+        tc.join()
+        assert all(len(q.participants) == 3 for q in list(out3.values()) + [joiner_out["c"]])
+    finally:
+        lh.shutdown()
+
+
+def test_commit_failures_reported_by_a_member_bump_the_quorum_id():
+    """Same membership, but a member reports failed commits: the lighthouse issues a new quorum id so
+    that every group reconfigures its process group (src/lighthouse.rs:1263-1293)."""
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    mgr = _manager(lh)
+    try:
+        cl = C.ManagerClient(mgr.address(), timedelta(seconds=5))
+        ids = []
+        for failures in (0, 0, 2, 0):
+            r = cl._quorum(group_rank=0, step=1, checkpoint_metadata="m", shrink_only=False, timeout=timedelta(seconds=5),
+                           init_sync=False, commit_failures=failures)
+            ids.append((r.quorum_id, r.commit_failures))
+        assert ids[0][0] == ids[1][0]
+        assert ids[2][0] == ids[1][0] + 1 and ids[2][1] == 2
+        assert ids[3][0] == ids[2][0]
+    finally:
+        mgr.shutdown()
+        lh.shutdown()
