@@ -390,3 +390,37 @@ def test_commit_failures_reported_by_a_member_bump_the_quorum_id():
     finally:
         mgr.shutdown()
         lh.shutdown()
+
+
+def test_manager_retries_until_the_lighthouse_answers():
+    """The lighthouse goes away and comes back on the same port while a quorum request is in flight:
+    with quorum_retries the manager reconnects and the request succeeds (the role MockLighthouse plays
+    in src/manager.rs:1109-1217)."""
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    port = lh.address().rsplit(":", 1)[1]
+    ms = C.ManagerServer(replica_id="late", lighthouse_addr=lh.address(), hostname="localhost", bind="[::]:0",
+                         store_addr="store:1", world_size=1, heartbeat_interval=timedelta(milliseconds=50),
+                         connect_timeout=timedelta(seconds=1), quorum_retries=8)
+    try:
+        c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+        first = c._quorum(group_rank=0, step=4, checkpoint_metadata="m", shrink_only=False, timeout=timedelta(seconds=10),
+                          init_sync=False, commit_failures=0)
+        assert first.max_step == 4
+        lh.shutdown()
+        lh = None
+        out = {}
+
+        def ask():
+            out["r"] = c._quorum(group_rank=0, step=5, checkpoint_metadata="m", shrink_only=False,
+                                 timeout=timedelta(seconds=30), init_sync=False, commit_failures=0)
+
+        t = threading.Thread(target=ask)
+        t.start()
+        time.sleep(0.5)  # the first attempts fail: nothing listens
+        lh = C.LighthouseServer(f"[::]:{port}", 1, join_timeout_ms=100, quorum_tick_ms=10)
+        t.join(30)
+        assert not t.is_alive() and out["r"].max_step == 5 and out["r"].replica_world_size == 1
+    finally:
+        ms.shutdown()
+        if lh is not None:
+            lh.shutdown()

@@ -119,3 +119,18 @@ def test_pg_transport_gloo(inplace):
     finally:
         for pg in pgs:
             pg.shutdown()
+
+
+def test_transport_benchmark_smoke(capsys):
+    """The transport benchmark with a few hundred bytes, as a smoke test of its HTTP path
+    (torchft/checkpointing/http_transport_test.py:138-146 does the same with the reference's bench)."""
+    import sys as _sys
+    from unittest.mock import patch as _patch
+
+    from torchft_b200.checkpointing import bench_transports as B
+
+    for chunks in ("0", "2"):
+        with _patch.object(_sys, "argv", ["bench_transports", "--transport", "http", "--total-mb", "0.0004", "--chunk-mb",
+                                          "0.0001", "--num-chunks", chunks, "--timeout", "10"]):
+            assert B.main() == 0
+    assert '"transport": "http"' in capsys.readouterr().out
