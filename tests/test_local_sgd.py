@@ -269,3 +269,54 @@ def test_flat_fragments_reject_unsupported_outer_optimizer():
         DiLoCo(m, [model], inner, optim.Adam(model.parameters(), lr=0.1), sync_every=2, flat_fragments=True)
     # auto mode quietly keeps the per-parameter path
     assert not DiLoCo(m, [model], inner, optim.Adam(model.parameters(), lr=0.1), sync_every=2).flat_fragments
+
+
+def _simulate_streaming_diloco(n_frag, sync_every, delay, alpha, steps, inner_lr=1.0, grad=2.0, outer_lr=2.0):
+    """Independent restatement of streaming DiLoCo for scalar weights, constant gradient and plain SGD
+    inside and outside; returns the local weights after every inner step and the global weights."""
+    local = [1.0] * n_frag
+    glob = [1.0] * n_frag
+    every = sync_every // n_frag
+    trace, manager_step, local_step, pending = [], 0, 0, None
+    for _ in range(steps):
+        local = [w - inner_lr * grad for w in local]
+        local_step += 1
+        if local_step == every - delay:
+            f = manager_step % n_frag
+            pending = (f, glob[f] - local[f])
+        if local_step == every:
+            f, pseudo = pending
+            new_global = glob[f] - outer_lr * pseudo
+            local[f] = new_global + alpha * (local[f] - new_global)
+            glob[f] = new_global
+            manager_step += 1
+            local_step = 0
+        trace.append((list(local), list(glob)))
+    return trace
+
+
+@pytest.mark.parametrize("flat", [False, True])
+@pytest.mark.parametrize("n_frag,sync_every,delay,alpha", [
+    (1, 3, 0, 0.0), (2, 6, 0, 0.0), (2, 6, 1, 0.0), (2, 8, 2, 0.5), (3, 9, 1, 1.0), (3, 12, 3, 0.25),
+])
+def test_streaming_diloco_matches_independent_simulation(flat, n_frag, sync_every, delay, alpha):
+    layers = [_MockLayer() for _ in range(n_frag)]
+    model = nn.Sequential(*layers)
+    inner = _MockOptimizer(model.parameters(), lr=1.0)
+    # the flat path needs torch's SGD outside; without momentum it is the same update as the mock optimizer
+    outers = ([optim.SGD(l.parameters(), lr=2.0) for l in layers] if flat
+              else [_MockOptimizer(l.parameters(), lr=2.0) for l in layers])
+    m = _delta_manager()
+    steps = 3 * sync_every
+    want = _simulate_streaming_diloco(n_frag, sync_every, delay, alpha, steps)
+    with DiLoCo(m, layers, inner, outers, sync_every=sync_every, fragment_sync_delay=delay, fragment_update_alpha=alpha,
+                flat_fragments=flat) as d:
+        for k in range(steps):
+            for p in model.parameters():
+                p.grad = torch.full_like(p, 2.0)
+            inner.step()
+            got_local = [l.weight.item() for l in layers]
+            got_global = [f.original_parameters["weight"].item() for f in d._fragments]
+            assert got_local == pytest.approx(want[k][0]), (k, got_local, want[k][0])
+            assert got_global == pytest.approx(want[k][1]), (k, got_global, want[k][1])
+    assert m.should_commit.call_count == 3 * n_frag
