@@ -1,6 +1,7 @@
 """Process-group conformance: every collective on world-size-1 groups, numeric checks on
 multi-rank gloo groups (ranks are threads sharing one store), reconfiguration, and the
 resiliency contract (a peer that goes away makes the survivors' collectives fail fast)."""
+import os
 import time
 from concurrent.futures import ThreadPoolExecutor
 from datetime import timedelta
@@ -231,3 +232,35 @@ def test_create_store_client_and_base_class_contract():
         base.group_name
     base._set_group_name("x")
     assert base.group_name == "x"
+
+
+def test_registered_pg_serves_functional_collectives_and_device_mesh():
+    """A registered process group resolves for torch's functional collectives and DeviceMesh.from_group
+    (torchft/process_group_test.py:732-774).  Runs in a child: it initialises torch.distributed."""
+    import subprocess
+    import sys
+
+    child = r'''
+import sys, torch, torch.distributed as dist
+from datetime import timedelta
+from torch.distributed import TCPStore
+from torch.distributed import _functional_collectives as fc
+from torch.distributed.device_mesh import DeviceMesh
+from torchft_b200.process_group import ProcessGroupGloo
+store = TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+dist.init_process_group("gloo", store=dist.PrefixStore("default", store), rank=0, world_size=1)
+pg = ProcessGroupGloo(timeout=timedelta(seconds=10))
+pg.configure(f"127.0.0.1:{store.port}/ft", "rep0", 0, 1)
+pg.register("ftb200_functional")
+t = torch.arange(10, dtype=torch.float32)
+out = fc.wait_tensor(fc.all_reduce(t, "sum", pg))
+assert torch.equal(out, t)
+mesh = DeviceMesh.from_group(pg, "cpu")
+assert mesh.size() == 1 and mesh.get_group() is not None
+pg.unregister()
+print("ok")
+'''
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=120,
+                       env=dict(os.environ, PYTHONPATH=root))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
