@@ -40,3 +40,12 @@ __all__ = (
     "ProcessGroupGloo",
     "ProcessGroupBabyGloo",
 )
+
+
+def __getattr__(name):
+    # the peer-memory group pulls in the kernel library bindings: resolved on first use
+    if name == "ProcessGroupB200":
+        from .parallel.team import ProcessGroupB200
+
+        return ProcessGroupB200
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
