@@ -209,3 +209,29 @@ def test_attention_selection_and_cpu_wrappers():
     K.attention_bwd(q, k, v, out, _torch.ones_like(out), lse, dqkv[:, : Hq * D], dqkv[:, Hq * D : (Hq + Hkv) * D],
                     dqkv[:, (Hq + Hkv) * D :], B, S, Hq, Hkv, D)
     assert dqkv.float().abs().sum() > 0
+
+
+def test_open_group_store():
+    """Every rank of a replica group learns the ephemeral port of its group's store; groups get
+    different stores (4 gloo ranks = 2 groups of 2)."""
+    import json
+    import os
+    import socket
+    import subprocess
+    import sys
+
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_group_store_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "4", "2", str(port)], stdout=subprocess.PIPE,
+                              stderr=subprocess.PIPE, text=True) for r in range(4)]
+    res = []
+    for p in procs:
+        out, err = p.communicate(timeout=120)
+        assert p.returncode == 0, err[-2000:]
+        res.append(json.loads([l for l in out.splitlines() if l.startswith("{")][-1]))
+    res.sort(key=lambda r: r["rank"])
+    assert res[0]["port"] == res[1]["port"] and res[2]["port"] == res[3]["port"] and res[0]["port"] != res[2]["port"]
+    assert [r["who"] for r in res] == ["group0", "group0", "group1", "group1"]

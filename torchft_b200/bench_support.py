@@ -16,6 +16,24 @@ from ._ftcp import LighthouseServer
 from .manager import Manager
 
 
+def open_group_store(world: int, group_id: int, group_rank: int) -> Tuple[Optional[TCPStore], int]:
+    """One TCPStore per replica group, hosted by the group's rank 0 on an ephemeral port (fixed offsets
+    from MASTER_PORT collide when two jobs run back to back on neighbouring ports); the port travels
+    over the job's default process group.  Returns ``(server or None, port)``.  Collective: every rank
+    of the job calls it."""
+    store = None
+    mine = None
+    if group_rank == 0:
+        store = TCPStore(host_name="127.0.0.1", port=0, is_master=True, wait_for_workers=False)
+        mine = (group_id, store.port)
+    if world > 1:
+        ports = [None] * world
+        dist.all_gather_object(ports, mine)
+        return store, dict(p for p in ports if p is not None)[group_id]
+    assert store is not None
+    return store, store.port
+
+
 def make_ft_manager(rank: int, world: int, n_groups: int, shard: int, group_id: int, group_rank: int,
                     device: torch.device, arena_bytes: int = 1 << 30, min_replica_size: Optional[int] = None,
                     timeout: timedelta = timedelta(seconds=120), use_async_quorum: bool = True,
@@ -33,19 +51,7 @@ def make_ft_manager(rank: int, world: int, n_groups: int, shard: int, group_id: 
         dist.broadcast_object_list(addr, src=0)
     lighthouse_addr = addr[0]
 
-    # one store per replica group on an ephemeral port (fixed offsets from MASTER_PORT collide when two
-    # jobs run back to back on neighbouring ports); the port travels over the job's process group
-    store = None
-    mine = None
-    if group_rank == 0:
-        store = TCPStore(host_name="127.0.0.1", port=0, is_master=True, wait_for_workers=False)
-        mine = (group_id, store.port)
-    if world > 1:
-        ports = [None] * world
-        dist.all_gather_object(ports, mine)
-        base_port = dict(p for p in ports if p is not None)[group_id]
-    else:
-        base_port = store.port
+    store, base_port = open_group_store(world, group_id, group_rank)
 
     pg = ProcessGroupB200(timeout=timeout, arena_bytes=arena_bytes, device=device)
     manager = Manager(
