@@ -235,3 +235,18 @@ def test_open_group_store():
     res.sort(key=lambda r: r["rank"])
     assert res[0]["port"] == res[1]["port"] and res[2]["port"] == res[3]["port"] and res[0]["port"] != res[2]["port"]
     assert [r["who"] for r in res] == ["group0", "group0", "group1", "group1"]
+
+
+def test_bench_reference_arm_reports_unavailable():
+    """`bench.py --impl reference` prints one JSON line saying why the reference cannot run here."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                        "--warmup", "3"], capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-1000:]
+    line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["impl"] == "reference" and "unavailable" in line and "maturin" in line["unavailable"]
