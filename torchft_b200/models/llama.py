@@ -221,9 +221,13 @@ class LlamaEngine:
         attention: Optional[object] = None,
         logit_chunks: int = 4,
         grad_fields: Optional[Callable[[int], object]] = None,
+        grad_scale: float = 1.0,
     ):
         self.cfg, self.B, self.S, self.device = cfg, batch, seq_len, device
         self.grad_fields = grad_fields
+        # multiplies every gradient (not the reported loss): 1/shard-group size when the group's
+        # gradients are summed, so that the result is the mean over all of the group's tokens
+        self.grad_scale = float(grad_scale)
         self.T = batch * seq_len
         self.param_unit, self.grad_unit = param_unit, grad_unit
         self.before_unit = before_unit or (lambda u, backward: None)
@@ -321,7 +325,7 @@ class LlamaEngine:
         for ci in range(self.logit_chunks):
             sl = slice(ci * rows, (ci + 1) * rows)
             K.linear_fwd(self.ws_n[sl], W.lm_head, out=self.logits)
-            K.cross_entropy_(self.logits, tgt[sl], 1.0 / T, loss=self.loss_rows[sl])
+            K.cross_entropy_(self.logits, tgt[sl], self.grad_scale / T, loss=self.loss_rows[sl])
             if train:
                 K.linear_wgrad(self.logits, self.ws_n[sl], out=G.lm_head, accumulate=ci > 0)
                 K.linear_dgrad(self.logits, W.lm_head, out=self.ws_dn[sl])

@@ -138,6 +138,7 @@ class ShardedLlamaTrainer:
         self.engine = LlamaEngine(
             cfg, batch, seq_len, device, self._param_unit, self._grad_unit, self._before_unit, self._grad_done,
             attention=attention, logit_chunks=logit_chunks, grad_fields=self._grad_fields if self.fused_rs else None,
+            grad_scale=1.0 / ws,  # the shard group sums its gradients: scale so that the sum is the mean over the group
         )
 
     # ---- unit plumbing -------------------------------------------------------------------
