@@ -33,6 +33,7 @@ def main() -> None:
     ap.add_argument("--exit-at-step", type=int, default=-1)
     ap.add_argument("--hold-step", type=int, default=10 ** 9)
     ap.add_argument("--seed", type=int, default=3)
+    ap.add_argument("--async-quorum", type=int, default=0)
     a = ap.parse_args()
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{a.init_port}", rank=a.rank, world_size=2)
     store = TCPStore("127.0.0.1", a.store_port, is_master=(a.rank == 0), wait_for_workers=False)
@@ -42,7 +43,7 @@ def main() -> None:
         pg=pg, min_replica_size=1, load_state_dict=None, state_dict=None, replica_id=f"hsdp_cpu_{a.group}",
         store_addr="127.0.0.1", store_port=a.store_port, rank=a.rank, world_size=2, lighthouse_addr=a.lighthouse, port=0,
         hostname="127.0.0.1", timeout=timeout, quorum_timeout=timedelta(seconds=40), connect_timeout=timedelta(seconds=20),
-        use_async_quorum=False, init_sync=False)
+        use_async_quorum=bool(a.async_quorum), init_sync=False)
     cfg, B, S = LLAMA_TINY, 1, 16
     tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), shard_comm=TorchShardComm(dist.group.WORLD), manager=manager,
                              seed=a.seed, lr=1e-2)

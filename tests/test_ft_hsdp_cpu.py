@@ -25,12 +25,12 @@ def _free_port() -> int:
     return p
 
 
-def _spawn_group(group, lighthouse, steps, exit_at=-1, hold=10 ** 9, seed=3):
+def _spawn_group(group, lighthouse, steps, exit_at=-1, hold=10 ** 9, seed=3, async_quorum=False):
     init_port, store_port = _free_port(), _free_port()
     return [subprocess.Popen(
         [sys.executable, WORKER, "--group", str(group), "--rank", str(r), "--init-port", str(init_port), "--store-port",
          str(store_port), "--lighthouse", lighthouse, "--steps", str(steps), "--exit-at-step", str(exit_at), "--hold-step",
-         str(hold), "--seed", str(seed)],
+         str(hold), "--seed", str(seed), "--async-quorum", str(int(async_quorum))],
         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
 
 
@@ -67,17 +67,19 @@ def test_ft_hsdp_two_groups_healthy():
         lh.shutdown()
 
 
-def test_ft_hsdp_group_leaves_and_heals():
+@pytest.mark.parametrize("async_quorum", [False, True])
+def test_ft_hsdp_group_leaves_and_heals(async_quorum):
     lh = LighthouseServer("[::]:0", 1, join_timeout_ms=300, quorum_tick_ms=20, heartbeat_timeout_ms=1000)
     addr = "http://127.0.0.1:" + lh.address().rsplit(":", 1)[1]
     procs = []
     try:
-        g0 = _spawn_group(0, addr, 10, hold=5)
-        g1 = _spawn_group(1, addr, 10, exit_at=3)
+        g0 = _spawn_group(0, addr, 10, hold=5, async_quorum=async_quorum)
+        g1 = _spawn_group(1, addr, 10, exit_at=3, async_quorum=async_quorum)
         procs = g0 + g1
         assert [p.wait(timeout=180) for p in g1] == [17, 17]  # left between steps
         time.sleep(0.5)
-        g1b = _spawn_group(1, addr, 10, hold=0, seed=99)  # fresh weights: only healing can make them agree
+        # fresh weights: only healing can make them agree
+        g1b = _spawn_group(1, addr, 10, hold=0, seed=99, async_quorum=async_quorum)
         procs += g1b
         r0, r1 = _results(g0), _results(g1b)
         assert r0[0]["step"] == r1[0]["step"] >= 10
