@@ -34,6 +34,7 @@ def main() -> None:
     ap.add_argument("--hold-step", type=int, default=10 ** 9)
     ap.add_argument("--seed", type=int, default=3)
     ap.add_argument("--async-quorum", type=int, default=0)
+    ap.add_argument("--diloco", type=int, default=0, help="streaming DiLoCo over the engine: number of fragments")
     a = ap.parse_args()
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{a.init_port}", rank=a.rank, world_size=2)
     store = TCPStore("127.0.0.1", a.store_port, is_master=(a.rank == 0), wait_for_workers=False)
@@ -45,9 +46,31 @@ def main() -> None:
         hostname="127.0.0.1", timeout=timeout, quorum_timeout=timedelta(seconds=40), connect_timeout=timedelta(seconds=20),
         use_async_quorum=bool(a.async_quorum), init_sync=False)
     cfg, B, S = LLAMA_TINY, 1, 16
-    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), shard_comm=TorchShardComm(dist.group.WORLD), manager=manager,
-                             seed=a.seed, lr=1e-2)
+    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), shard_comm=TorchShardComm(dist.group.WORLD),
+                             manager=None if a.diloco else manager, seed=a.seed, lr=1e-2)
     manager.register_state_dict_fn("trainer", tr.load_state_dict, tr.state_dict)
+    if a.diloco:
+        from torchft_b200.parallel.diloco import EngineDiLoCo
+
+        d = EngineDiLoCo(tr, manager, n_fragments=a.diloco, sync_every=2 * a.diloco, fragment_sync_delay=1,
+                         fragment_update_alpha=0.5)
+        it = 0
+        while manager.current_step() < a.steps:
+            g = torch.Generator().manual_seed(10000 * a.group + 100 * a.rank + it)
+            tok = torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g)
+            d.train_step(tok[:, :-1], tok[:, 1:])
+            it += 1
+        sums = []
+        for f in d.fragments:  # the global (backup) weights are what the groups must agree on
+            for b in f.backup:
+                full = [torch.empty_like(b) for _ in range(2)]
+                dist.all_gather(full, b)
+                sums.append(float(torch.cat(full).double().sum()))
+        print(json.dumps({"group": a.group, "rank": a.rank, "step": manager.current_step(), "unit_sums": sums,
+                          "max_participants": manager.num_participants(), "errored": str(pg.errored()),
+                          "commits": d.commits}), flush=True)
+        manager.shutdown(wait=False)
+        os._exit(0)
 
     max_participants, rejoined_at, t_hold = 0, None, time.time()
     while True:

@@ -25,12 +25,12 @@ def _free_port() -> int:
     return p
 
 
-def _spawn_group(group, lighthouse, steps, exit_at=-1, hold=10 ** 9, seed=3, async_quorum=False):
+def _spawn_group(group, lighthouse, steps, exit_at=-1, hold=10 ** 9, seed=3, async_quorum=False, diloco=0):
     init_port, store_port = _free_port(), _free_port()
     return [subprocess.Popen(
         [sys.executable, WORKER, "--group", str(group), "--rank", str(r), "--init-port", str(init_port), "--store-port",
          str(store_port), "--lighthouse", lighthouse, "--steps", str(steps), "--exit-at-step", str(exit_at), "--hold-step",
-         str(hold), "--seed", str(seed), "--async-quorum", str(int(async_quorum))],
+         str(hold), "--seed", str(seed), "--async-quorum", str(int(async_quorum)), "--diloco", str(diloco)],
         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
 
 
@@ -84,6 +84,27 @@ def test_ft_hsdp_group_leaves_and_heals(async_quorum):
         r0, r1 = _results(g0), _results(g1b)
         assert r0[0]["step"] == r1[0]["step"] >= 10
         assert all(r["errored"] == "None" and r["max_participants"] == 2 for r in r0 + r1)
+        _assert_same(r0[0], r1[0])
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+        lh.shutdown()
+
+
+def test_engine_diloco_on_sharded_groups():
+    """Streaming DiLoCo on the engine with two sharded groups: every rank exchanges the pseudo-gradient of its
+    own shard with the same-numbered rank of the other group; after four fragment synchronisations the global
+    weights of the two groups are identical."""
+    lh = LighthouseServer("[::]:0", 2, join_timeout_ms=500, quorum_tick_ms=20, heartbeat_timeout_ms=2000)
+    addr = "http://127.0.0.1:" + lh.address().rsplit(":", 1)[1]
+    procs = []
+    try:
+        g0, g1 = _spawn_group(0, addr, 4, diloco=2), _spawn_group(1, addr, 4, diloco=2)
+        procs = g0 + g1
+        r0, r1 = _results(g0), _results(g1)
+        assert all(r["step"] == 4 and r["commits"] == 4 and r["errored"] == "None" for r in r0 + r1)
+        _assert_same(r0[0], r0[1])
         _assert_same(r0[0], r1[0])
     finally:
         for p in procs:
