@@ -117,7 +117,7 @@ class Runner:
         raise RuntimeError("ran out of attempts")
 
 
-def run_replicas(runners: List[Runner]) -> List[List[Dict[str, Any]]]:
+def run_replicas(runners: List[Runner], timeout: float = 180) -> List[List[Dict[str, Any]]]:
     with ThreadPoolExecutor(max_workers=len(runners)) as ex:
         futs = [ex.submit(r.run_replica) for r in runners]
-        return [f.result(timeout=180) for f in futs]
+        return [f.result(timeout=timeout) for f in futs]
