@@ -424,3 +424,26 @@ def test_manager_retries_until_the_lighthouse_answers():
         ms.shutdown()
         if lh is not None:
             lh.shutdown()
+
+
+def test_should_commit_declines_when_ranks_vote_for_different_steps():
+    """Two ranks of one group that drifted to different steps must not commit together (the reference's
+    barrier ignores `step`); the round after, with matching steps, commits again."""
+    lh = C.LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10)
+    ms = _manager(lh, world_size=2)
+    try:
+        def vote(rank, step, out):
+            c = C.ManagerClient(ms.address(), timedelta(seconds=5))
+            out[rank] = c.should_commit(rank, step, True, timedelta(seconds=5))
+
+        for steps, want in (((7, 8), False), ((9, 9), True)):
+            out = {}
+            ts = [threading.Thread(target=vote, args=(r, steps[r], out)) for r in range(2)]
+            for t in ts:
+                t.start()
+            for t in ts:
+                t.join()
+            assert out == {0: want, 1: want}, (steps, out)
+    finally:
+        ms.shutdown()
+        lh.shutdown()

@@ -169,6 +169,18 @@ ManagerQuorumResponse ManagerServer::handle_quorum(const ManagerQuorumRequest& r
 
 bool ManagerServer::handle_should_commit(const ShouldCommitRequest& req, TimePoint deadline) {
   std::unique_lock<std::mutex> lk(mu_);
+  // Votes of one round must be about one step.  The reference merges whatever arrives
+  // (src/manager.rs:440-478 never looks at `step`); ranks that drifted apart would then commit
+  // different steps together.  Here a vote for another step than the round's first vote counts
+  // as a failure, so the whole group declines and retries.
+  if (commit_votes_.empty()) {
+    commit_step_ = req.step;
+  } else if (req.step != commit_step_) {
+    log_warn("manager", "[Replica " + short_id(replica_id_) + "] should_commit: group_rank " + std::to_string(req.group_rank) +
+                            " votes for step " + std::to_string(req.step) + " while the round is about step " +
+                            std::to_string(commit_step_) + "; declining the commit");
+    commit_failures_.insert(req.group_rank);
+  }
   if (!req.should_commit) commit_failures_.insert(req.group_rank);
   commit_votes_.insert(req.group_rank);
   const uint64_t my_round = commit_round_ + 1;

@@ -57,6 +57,7 @@ class ManagerServer {
   std::set<int64_t> commit_votes_, commit_failures_;
   uint64_t commit_round_ = 0, commit_done_round_ = 0;
   bool commit_decision_ = false;
+  int64_t commit_step_ = 0;  // step the current should_commit round is about (set by its first vote)
 
   std::unique_ptr<Server> server_;
   std::thread heartbeat_thread_;
