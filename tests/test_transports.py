@@ -134,3 +134,52 @@ def test_transport_benchmark_smoke(capsys):
                                           "0.0001", "--num-chunks", chunks, "--timeout", "10"]):
             assert B.main() == 0
     assert '"transport": "http"' in capsys.readouterr().out
+
+
+def test_durable_checkpointer_roundtrip_prune_and_incomplete(tmp_path):
+    """Durable checkpoints: atomic per-rank files, a step is usable only when every rank wrote it, old steps are
+    pruned, and a fresh process restores model, optimizer and the manager's step from the newest complete one."""
+    from unittest.mock import MagicMock
+
+    from torchft_b200.checkpointing.durable import DurableCheckpointer
+
+    def fake_manager(step):
+        m = MagicMock()
+        state = {"step": step, "batches_committed": 2 * step}
+        m.current_step.side_effect = lambda: state["step"]
+        m.state_dict.side_effect = lambda: dict(state)
+        m.load_state_dict.side_effect = lambda sd: state.update(sd)
+        m._user_state_dicts = {}
+        m._load_state_dict_fns = {}
+        m._state = state
+        return m
+
+    w = torch.arange(6, dtype=torch.float32)
+    m0 = fake_manager(0)
+    m0._user_state_dicts["trainer"] = lambda: {"w": w.clone()}
+    ck0 = DurableCheckpointer(m0, str(tmp_path), rank=0, world_size=2, every=2, keep=2)
+    ck1 = DurableCheckpointer(m0, str(tmp_path), rank=1, world_size=2, every=2, keep=2)
+    assert ck0.maybe_save() is None and ck0.load_latest() is None  # step 0: nothing to do, nothing to load
+    for step in (1, 2, 3, 4, 5, 6):
+        m0._state.update(step=step, batches_committed=2 * step)
+        w.add_(1)
+        wrote = ck0.maybe_save(extra={"loader_pos": 10 * step})
+        assert (wrote is not None) == (step % 2 == 0)
+        if step != 6:
+            ck1.maybe_save()  # rank 1 never writes step 6: that step stays incomplete
+        assert ck0.maybe_save() is None  # once per step
+    assert ck0.complete_steps() == [2, 4]
+    ck0.save()  # re-saving by rank 0 prunes by complete steps only
+    assert not list(tmp_path.glob("**/*.tmp*"))
+
+    got = {}
+    m1 = fake_manager(0)
+    m1._load_state_dict_fns["trainer"] = lambda sd: got.update(sd)
+    extra = DurableCheckpointer(m1, str(tmp_path), rank=0, world_size=2).load_latest()
+    assert extra == {"loader_pos": 40} and m1._state == {"step": 4, "batches_committed": 8}
+    torch.testing.assert_close(got["w"], torch.arange(6, dtype=torch.float32) + 4)
+    # pruning keeps the newest `keep` complete steps
+    m0._state.update(step=8, batches_committed=16)
+    ck1.save()
+    ck0.save()
+    assert ck0.complete_steps() == [4, 8]

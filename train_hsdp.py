@@ -9,7 +9,9 @@ AdamW state are sharded (FSDP style, NVLink peer-memory all-gather / reduce-scat
 across groups gradients are averaged through the fault-tolerant Manager.  A group that
 disappears (``--kill-group G --kill-step S`` makes group G exit at step S to demonstrate)
 is dropped from the quorum within the heartbeat timeout and the others continue; relaunch
-its ranks with ``--rejoin`` and they heal from a surviving group over NVLink.
+its ranks and they heal from a surviving group over NVLink.  ``--ckpt-dir D --ckpt-every N`` writes
+a durable checkpoint every N committed steps (replica group 0 only: the groups hold identical
+state) and resumes from the newest complete one when the whole job is started again.
 The reference reaches the same layout through torchtitan + torchft; here the trainer is
 part of the framework (:mod:`torchft_b200.parallel.hsdp`).
 """
@@ -41,6 +43,8 @@ def main() -> None:
     ap.add_argument("--lr", type=float, default=3e-4)
     ap.add_argument("--kill-group", type=int, default=-1)
     ap.add_argument("--kill-step", type=int, default=-1)
+    ap.add_argument("--ckpt-dir", default="")
+    ap.add_argument("--ckpt-every", type=int, default=0)
     a = ap.parse_args()
 
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
@@ -67,6 +71,15 @@ def main() -> None:
     manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 
     g = torch.Generator().manual_seed(1234 + rank)
+    ckpt = None
+    if a.ckpt_dir:
+        from torchft_b200.checkpointing.durable import DurableCheckpointer
+
+        ckpt = DurableCheckpointer(manager, a.ckpt_dir, rank=group_rank, world_size=shard, every=a.ckpt_every)
+        extra = ckpt.load_latest()
+        if extra is not None:
+            g.set_state(extra["data_rng"])
+            print(f"[rank {rank}] resumed from step {manager.current_step()}", flush=True)
     t0 = time.time()
     while manager.current_step() < a.steps:
         step = manager.current_step()
@@ -75,6 +88,8 @@ def main() -> None:
             os._exit(1)
         tok = torch.randint(0, cfg.vocab_size, (a.micro_batch, a.seq_len + 1), generator=g).to(dev)
         loss = trainer.train_step(tok[:, :-1], tok[:, 1:])
+        if ckpt is not None and group_id == 0:
+            ckpt.maybe_save(extra={"data_rng": g.get_state()})
         if rank == 0 and step % 5 == 0:
             print(f"step {step} loss {loss.item():.4f} participants {manager.num_participants()} "
                   f"{(time.time() - t0):.1f}s", flush=True)
