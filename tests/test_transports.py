@@ -1,5 +1,6 @@
 """Checkpoint transport contract: 1->2 fan-out, 1->1, then a tiny timeout must raise."""
 import threading
+import time
 import urllib.error
 import urllib.request
 from concurrent.futures import ThreadPoolExecutor
@@ -183,3 +184,60 @@ def test_durable_checkpointer_roundtrip_prune_and_incomplete(tmp_path):
     ck1.save()
     ck0.save()
     assert ck0.complete_steps() == [4, 8]
+
+
+def test_durable_checkpoint_resumes_a_real_trainer(tmp_path):
+    """Train a few fault-tolerant steps, checkpoint, start over in a fresh manager + trainer, resume: the weights,
+    the optimizer state and the manager's step come back and the next step matches an uninterrupted run."""
+    from torch.distributed import TCPStore
+
+    from torchft_b200 import Manager, ProcessGroupGloo
+    from torchft_b200._ftcp import LighthouseServer
+    from torchft_b200.checkpointing.durable import DurableCheckpointer
+    from torchft_b200.models.llama import LLAMA_TINY
+    from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
+
+    lh = LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10, heartbeat_timeout_ms=500)
+    cfg, B, S = LLAMA_TINY, 1, 16
+
+    def make(replica_id):
+        store = TCPStore("localhost", 0, is_master=True, wait_for_workers=False)
+        manager = Manager(pg=ProcessGroupGloo(timeout=timedelta(seconds=10)), min_replica_size=1, load_state_dict=None,
+                          state_dict=None, replica_id=replica_id, store_addr="localhost", store_port=store.port, rank=0,
+                          world_size=1, lighthouse_addr=lh.address(), port=0, timeout=timedelta(seconds=10),
+                          quorum_timeout=timedelta(seconds=20), connect_timeout=timedelta(seconds=10), hostname="localhost")
+        tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), manager=manager, seed=3, lr=1e-2)
+        manager.register_state_dict_fn("trainer", tr.load_state_dict, tr.state_dict)
+        return store, manager, tr
+
+    def batch(step):
+        g = torch.Generator().manual_seed(step)
+        t = torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g)
+        return t[:, :-1], t[:, 1:]
+
+    managers = []
+    try:
+        _, m_a, tr_a = make("durable_a")
+        managers.append(m_a)
+        ck = DurableCheckpointer(m_a, str(tmp_path), rank=0, world_size=1, every=2)
+        for step in range(4):
+            tr_a.train_step(*batch(step))
+            ck.maybe_save(extra={"next_batch": step + 1})
+        assert ck.complete_steps() == [2, 4]
+        tr_a.train_step(*batch(4))  # the uninterrupted run goes one step further
+        m_a.shutdown(wait=False)  # the whole job goes away (its heartbeats must stop before a new one can form a quorum)
+        time.sleep(0.3)
+
+        _, m_b, tr_b = make("durable_b")
+        managers.append(m_b)
+        extra = DurableCheckpointer(m_b, str(tmp_path), rank=0, world_size=1).load_latest()
+        assert extra == {"next_batch": 4} and m_b.current_step() == 4 and tr_b.opt_step == 4
+        tr_b.train_step(*batch(extra["next_batch"]))
+        assert m_b.current_step() == 5
+        for u in range(cfg.n_units):
+            torch.testing.assert_close(tr_b.master[u], tr_a.master[u])
+            torch.testing.assert_close(tr_b.v[u], tr_a.v[u])
+    finally:
+        for m in managers:
+            m.shutdown(wait=False)
+        lh.shutdown()
