@@ -241,3 +241,73 @@ def test_durable_checkpoint_resumes_a_real_trainer(tmp_path):
         for m in managers:
             m.shutdown(wait=False)
         lh.shutdown()
+
+
+def test_streaming_serialisation_roundtrip_and_framing():
+    """The transports' stream format: nested containers, every dtype incl. bf16, scalars, empty and
+    non-contiguous tensors, Python leaves; reads from a stream that returns short reads; rejects garbage."""
+    import io
+
+    from torch.utils._pytree import tree_flatten
+
+    from torchft_b200.checkpointing._serialization import streaming_load, streaming_save
+
+    sd = {
+        "model": {"w": torch.randn(5, 7), "b": torch.randn(7).bfloat16(), "idx": torch.arange(10)[::2],
+                  "half": torch.randn(3, 3).half(), "flag": torch.tensor(True), "empty": torch.empty(0, 4)},
+        "optim": [torch.tensor(3.5), {"step": 7, "name": "adamw", "nested": (1, 2.0, None)}],
+        "param": torch.nn.Parameter(torch.ones(2, 2)),
+    }
+    buf = io.BytesIO()
+    streaming_save(sd, buf)
+
+    class Dribble(io.RawIOBase):  # a socket that hands out at most 1000 bytes at a time
+        def __init__(self, data):
+            self.data, self.pos = data, 0
+
+        def readable(self):
+            return True
+
+        def readinto(self, b):
+            n = min(len(b), 1000, len(self.data) - self.pos)
+            b[:n] = self.data[self.pos : self.pos + n]
+            self.pos += n
+            return n
+
+    for stream in (io.BytesIO(buf.getvalue()), io.BufferedReader(Dribble(buf.getvalue()), 4096), Dribble(buf.getvalue())):
+        got = streaming_load(stream)
+        a, spec_a = tree_flatten(sd)
+        b, spec_b = tree_flatten(got)
+        assert spec_a == spec_b
+        for x, y in zip(a, b):
+            if isinstance(x, torch.Tensor):
+                assert x.dtype == y.dtype and x.shape == y.shape and torch.equal(x.detach(), y)
+            else:
+                assert x == y
+    with pytest.raises(ValueError):
+        streaming_load(io.BytesIO(b"garbage-garbage-garbage"))
+    with pytest.raises(EOFError):
+        streaming_load(io.BytesIO(buf.getvalue()[:-5]))
+
+
+@pytest.mark.parametrize("num_chunks", [0, 3])
+def test_http_transport_receives_in_place(num_chunks):
+    """With a `state_dict` callable the HTTP transport fills matching tensors in place (and falls back to new
+    tensors where shape or dtype differ)."""
+    timeout = timedelta(seconds=10)
+    src = {"a": torch.arange(12, dtype=torch.float32).reshape(3, 4), "b": torch.ones(5).bfloat16(), "n": 7,
+           "c": torch.full((2, 2), 3.0), "d": torch.arange(4)}
+    dst = {"a": torch.zeros(3, 4), "b": torch.zeros(5).bfloat16(), "n": 0, "c": torch.zeros(3, 3), "d": torch.zeros(4)}
+    send = HTTPTransport(timeout, num_chunks=num_chunks)
+    recv = HTTPTransport(timeout, num_chunks=num_chunks, state_dict=lambda: dst)
+    try:
+        send.send_checkpoint([1], step=3, state_dict=src, timeout=timeout)
+        got = recv.recv_checkpoint(0, send.metadata(), 3, timeout)
+        assert got["a"] is dst["a"] and got["b"] is dst["b"]  # filled in place
+        assert got["c"] is not dst["c"] and got["d"] is not dst["d"]  # shape / dtype mismatch: fresh tensors
+        for k in ("a", "b", "c", "d"):
+            assert torch.equal(got[k], src[k])
+        assert got["n"] == 7
+    finally:
+        send.shutdown()
+        recv.shutdown()

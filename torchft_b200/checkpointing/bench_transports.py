@@ -43,7 +43,8 @@ def bench_http(a) -> dict:
     sd = _state(a.total_mb, a.chunk_mb, dev)
     timeout = timedelta(seconds=a.timeout)
     send = HTTPTransport(timeout, num_chunks=a.num_chunks)
-    recv = HTTPTransport(timeout, num_chunks=a.num_chunks)
+    dst = _state(a.total_mb, a.chunk_mb, dev) if a.inplace else None
+    recv = HTTPTransport(timeout, num_chunks=a.num_chunks, state_dict=(lambda: dst) if a.inplace else None)
     try:
         t0 = time.perf_counter()
         send.send_checkpoint([1], step=1, state_dict=sd, timeout=timeout)
@@ -55,7 +56,7 @@ def bench_http(a) -> dict:
         send.shutdown()
         recv.shutdown()
     b = _nbytes(sd)
-    return {"transport": "http", "num_chunks": a.num_chunks, "device": a.device, "gb": b / 1e9, "stage_s": t1 - t0,
+    return {"transport": "http", "num_chunks": a.num_chunks, "device": a.device, "inplace": a.inplace, "gb": b / 1e9, "stage_s": t1 - t0,
             "recv_s": t2 - t1, "recv_gbs": b / 1e9 / (t2 - t1)}
 
 
@@ -135,7 +136,7 @@ def main() -> int:
     ap.add_argument("--total-mb", type=float, default=12000.0)
     ap.add_argument("--chunk-mb", type=float, default=3.0)
     ap.add_argument("--num-chunks", type=int, default=0, help="http: parallel chunk streams (0 = one stream)")
-    ap.add_argument("--inplace", action="store_true", help="pg/p2p: receive into existing tensors")
+    ap.add_argument("--inplace", action="store_true", help="receive into existing tensors")
     ap.add_argument("--timeout", type=float, default=600.0)
     a = ap.parse_args()
     if a.transport == "p2p":

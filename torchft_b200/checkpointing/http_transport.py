@@ -24,7 +24,7 @@ import urllib.request
 from concurrent.futures import ThreadPoolExecutor
 from datetime import timedelta
 from http.server import BaseHTTPRequestHandler, ThreadingHTTPServer
-from typing import Generic, List, Optional, TypeVar
+from typing import Callable, Generic, List, Optional, TypeVar
 
 import torch
 from torch.utils._pytree import TreeSpec, tree_flatten, tree_unflatten
@@ -64,8 +64,13 @@ def _leaf_to_cpu(v: object, pin: bool) -> object:
 
 
 class HTTPTransport(CheckpointTransport[T], Generic[T]):
-    def __init__(self, timeout: timedelta, num_chunks: int = 0, pin_memory: bool = False) -> None:
+    def __init__(self, timeout: timedelta, num_chunks: int = 0, pin_memory: bool = False,
+                 state_dict: Optional[Callable[[], T]] = None) -> None:
+        """``state_dict``: optional callable returning the receiver's current state dict; tensors whose shape
+        and dtype match are then filled in place instead of being allocated (as the process-group and
+        peer-memory transports do)."""
         self._timeout = timeout
+        self._state_dict_fn = state_dict
         self._num_chunks = num_chunks
         self._pin = pin_memory and torch.cuda.is_available()
         self._lock = RWLock(timeout=timeout.total_seconds())
@@ -82,6 +87,10 @@ class HTTPTransport(CheckpointTransport[T], Generic[T]):
 
         class Handler(BaseHTTPRequestHandler):
             timeout = sock_timeout
+            # The serialiser emits a small header before every tensor's bytes.  Unbuffered, each is its own
+            # TCP segment and Nagle's algorithm against delayed ACKs stalls ~10-40 ms per tensor.
+            wbufsize = 4 << 20
+            disable_nagle_algorithm = True
 
             def log_message(self, fmt, *args):  # keep stderr quiet
                 logger.debug(fmt, *args)
@@ -166,22 +175,29 @@ class HTTPTransport(CheckpointTransport[T], Generic[T]):
         self.allow_checkpoint(step)
 
     @staticmethod
-    def _fetch(url: str, timeout: timedelta) -> object:
+    def _fetch(url: str, timeout: timedelta, into: Optional[List[object]] = None) -> object:
         # resolve our own hostname locally: containers often cannot resolve it via DNS
         host = socket.gethostname()
         if f"//{host}:" in url:
             url = url.replace(f"//{host}:", "//localhost:")
+        # Deserialise straight from the socket through a large read buffer.  Reading the whole body first
+        # (`f.read()` on a response of unknown length) goes through 8 KB receives and a growing byte string:
+        # 60 MB/s on a 1.2 GB state dict; streaming reaches the speed of the loopback/NIC.
         with urllib.request.urlopen(url, timeout=timeout.total_seconds()) as f:
-            data = f.read()
-        return streaming_load(io.BytesIO(data))
+            return streaming_load(io.BufferedReader(f, buffer_size=4 << 20), into=into)
 
     def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
         base = f"{metadata}{step}"
+        into: Optional[List[object]] = None
+        if self._state_dict_fn is not None:
+            into, _ = tree_flatten(self._state_dict_fn())
         if self._num_chunks == 0:
-            return self._fetch(f"{base}/full", timeout)  # type: ignore[return-value]
+            return self._fetch(f"{base}/full", timeout, into)  # type: ignore[return-value]
         spec = self._fetch(f"{base}/metadata", timeout)
-        with ThreadPoolExecutor(max_workers=self._num_chunks, thread_name_prefix="torchft_b200_ckpt_fetch") as ex:
-            chunks = list(ex.map(lambda i: self._fetch(f"{base}/{i}", timeout), range(self._num_chunks)))
+        n_chunks = self._num_chunks
+        with ThreadPoolExecutor(max_workers=n_chunks, thread_name_prefix="torchft_b200_ckpt_fetch") as ex:
+            chunks = list(ex.map(lambda i: self._fetch(f"{base}/{i}", timeout, into[i::n_chunks] if into is not None else None),
+                                 range(n_chunks)))
         n = sum(len(c) for c in chunks)
         leaves: List[object] = [None] * n
         for i, c in enumerate(chunks):
