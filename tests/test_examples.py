@@ -1,0 +1,145 @@
+"""The example trainers run as a user would start them: a lighthouse, then one ``torchrun`` per
+replica group (train_ddp.py / train_diloco.py in the reference are started the same way,
+README.md "Example Training Loop (DDP)").  CPU, Gloo."""
+
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import psutil
+import pytest
+
+from torchft_b200.coordination import LighthouseServer
+
+REPO = Path(__file__).resolve().parent.parent
+
+
+def _launch(script: str, group: int, lighthouse: str, port: int, **env) -> subprocess.Popen:
+    full = dict(os.environ, TORCHFT_LIGHTHOUSE=lighthouse, REPLICA_GROUP_ID=str(group), NUM_REPLICA_GROUPS="2",
+                PYTHONPATH=str(REPO), OMP_NUM_THREADS="2", **env)  # two trainers share the cores: no oversubscription
+    return subprocess.Popen(
+        [sys.executable, "-m", "torch.distributed.run", "--standalone", "--local-addr", "127.0.0.1", "--nproc-per-node", "1",
+         "--master-port", str(port), str(REPO / script)],
+        env=full, cwd=REPO, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, start_new_session=True)
+
+
+def _kill_tree(pid: int) -> None:
+    """SIGKILL a launcher and everything it started.  torchrun puts its workers into sessions of their own,
+    so the launcher's process group does not reach them; the children are looked up by pid instead."""
+    try:
+        root = psutil.Process(pid)
+    except psutil.NoSuchProcess:
+        return
+    procs = root.children(recursive=True) + [root]
+    for q in procs:
+        try:
+            q.kill()
+        except psutil.NoSuchProcess:
+            pass
+    psutil.wait_procs(procs, timeout=10)
+
+
+def _finish(p: subprocess.Popen, timeout: float = 240) -> str:
+    try:
+        out, _ = p.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        _kill_tree(p.pid)
+        out, _ = p.communicate()
+        pytest.fail("example did not finish:\n" + out[-3000:])
+    return out
+
+
+@pytest.mark.timeout(600)
+def test_train_ddp_two_groups_cpu():
+    lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=1000)
+    try:
+        procs = [_launch("train_ddp.py", g, lh.address(), 29720 + g, STEPS="6") for g in range(2)]
+        outs = [_finish(p) for p in procs]
+        for p, out in zip(procs, outs):
+            assert p.returncode == 0, out[-3000:]
+            assert "step 5] should_commit=True" in out, out[-3000:]
+    finally:
+        lh.shutdown()
+
+
+class _Tail:
+    """Collects a process's output on a thread so that a test can wait for a line to appear."""
+
+    def __init__(self, p: subprocess.Popen) -> None:
+        self.p, self.lines, self._lock = p, [], threading.Lock()
+        self._t = threading.Thread(target=self._pump, daemon=True)
+        self._t.start()
+
+    def _pump(self) -> None:
+        for line in self.p.stdout:
+            with self._lock:
+                self.lines.append(line)
+
+    def text(self) -> str:
+        with self._lock:
+            return "".join(self.lines)
+
+    def wait_for_count(self, needle: str, count: int, timeout: float) -> None:
+        end = time.monotonic() + timeout
+        while self.text().count(needle) < count:
+            if time.monotonic() > end or self.p.poll() is not None:
+                pytest.fail(f"{needle!r} did not appear {count} times:\n" + self.text()[-3000:])
+            time.sleep(0.2)
+
+    def finish(self, timeout: float) -> str:
+        try:
+            self.p.wait(timeout)
+        except subprocess.TimeoutExpired:
+            _kill_tree(self.p.pid)
+            self.p.wait()
+            pytest.fail("example did not finish:\n" + self.text()[-3000:])
+        self._t.join(10)
+        return self.text()
+
+
+@pytest.mark.timeout(900)
+def test_train_ddp_restarted_group_heals_cpu():
+    """Group 1 is killed mid-run and started again: it rejoins, copies the state from group 0 and both
+    reach the last step; group 0 never stops."""
+    lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=1000, heartbeat_timeout_ms=1000)
+    steps = 1500
+    t0 = t1 = t1b = None
+    try:
+        t0 = _Tail(_launch("train_ddp.py", 0, lh.address(), 29730, STEPS=str(steps)))
+        t1 = _Tail(_launch("train_ddp.py", 1, lh.address(), 29731, STEPS=str(steps)))
+        t1.wait_for_count("should_commit=True", 20, 120)  # (it may have healed past any particular step number)
+        _kill_tree(t1.p.pid)
+        t1.p.wait()
+        t1b = _Tail(_launch("train_ddp.py", 1, lh.address(), 29732, STEPS=str(steps)))
+        out0, out1 = t0.finish(600), t1b.finish(600)
+        assert t0.p.returncode == 0, out0[-3000:]
+        assert t1b.p.returncode == 0, out1[-3000:]
+        last = f"step {steps - 1}] should_commit=True"
+        assert last in out0 and last in out1
+        # the restarted group did not start from step 0: it healed to the survivor's step
+        assert "healing required" in out1, out1[:3000]
+        assert "step 1] should_commit" not in out1
+        assert "peers need recovery from us" in out0
+    finally:
+        for t in (t0, t1, t1b):
+            if t is not None:
+                _kill_tree(t.p.pid)
+        lh.shutdown()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("streaming", ["0", "1"])
+def test_train_diloco_two_groups_cpu(streaming):
+    lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=1000)
+    try:
+        procs = [_launch("train_diloco.py", g, lh.address(), 29740 + g + 4 * int(streaming), STEPS="45", USE_STREAMING=streaming)
+                 for g in range(2)]
+        outs = [_finish(p) for p in procs]
+        for p, out in zip(procs, outs):
+            assert p.returncode == 0, out[-3000:]
+            assert "should_commit=True" in out and "local_step=40" in out, out[-3000:]
+    finally:
+        lh.shutdown()

@@ -11,7 +11,8 @@ Start a lighthouse, then one process (group) per replica:
 
 Kill either trainer and restart it: it rejoins the quorum, copies the weights from the
 surviving replica and continues; the survivor never stops.  ``USE_PEER=1`` on GPUs of one
-NVSwitch domain selects the NVLink peer-memory process group and state transfer.
+NVSwitch domain selects the NVLink peer-memory process group and state transfer; ``USE_NCCL=0``
+selects Gloo for the replica dimension on GPUs (the default is NCCL on GPUs, Gloo on CPU).
 Counterpart of the reference's train_ddp.py (CIFAR-10 replaced by seeded synthetic data).
 """
 
@@ -77,7 +78,9 @@ def main() -> None:
         pg = ProcessGroupB200(timeout=timeout, device=device)
         transport = P2PTransport(timeout=timeout, device=device, state_dict=state_dict)
     else:
-        pg = ProcessGroupNCCL(timeout=timeout) if use_cuda else ProcessGroupGloo(timeout=timeout)
+        # USE_NCCL=0 keeps the tensors on the GPU but moves the replica dimension to Gloo
+        use_nccl = use_cuda and os.environ.get("USE_NCCL", "1").lower() not in ("0", "false")
+        pg = ProcessGroupNCCL(timeout=timeout) if use_nccl else ProcessGroupGloo(timeout=timeout)
         transport = PGTransport(pg, timeout=timeout, device=device)
 
     manager = Manager(

@@ -68,7 +68,9 @@ def main() -> None:
 
         pg = ProcessGroupB200(timeout=timeout, device=device)
     else:
-        pg = ProcessGroupNCCL(timeout=timeout) if use_cuda else ProcessGroupGloo(timeout=timeout)
+        # USE_NCCL=0 keeps the tensors on the GPU but moves the replica dimension to Gloo
+        use_nccl = use_cuda and os.environ.get("USE_NCCL", "1").lower() not in ("0", "false")
+        pg = ProcessGroupNCCL(timeout=timeout) if use_nccl else ProcessGroupGloo(timeout=timeout)
     manager = Manager(
         pg=pg,
         min_replica_size=1,
