@@ -264,3 +264,37 @@ print("ok")
     r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=120,
                        env=dict(os.environ, PYTHONPATH=root))
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+def test_baby_gloo_on_thread_backed_context(monkeypatch):
+    """The subprocess-backed group runs unchanged with its worker on a thread (DummyContext): two ranks in
+    one interpreter, allreduce, reconfigure, an injected worker death."""
+    from torchft_b200.multiprocessing_dummy_context import DummyContext, ThreadProcess
+
+    monkeypatch.setattr(ProcessGroupBabyGloo, "_mp_context", staticmethod(DummyContext))
+    world = 2
+    store = _store()
+    pgs = [ProcessGroupBabyGloo(timeout=timedelta(seconds=20)) for _ in range(world)]
+    try:
+        for gen in ("a", "b"):
+            with ThreadPoolExecutor(max_workers=world) as ex:
+                list(ex.map(lambda r: pgs[r].configure(f"localhost:{store.port}/thr{gen}", "rep", r, world), range(world)))
+            assert all(isinstance(pg._proc, ThreadProcess) for pg in pgs)
+
+            def allreduce(r, pg):
+                t = torch.full((4,), float(r + 1))
+                pg.allreduce([t], ReduceOp.SUM).wait()
+                return t
+            for t in _run(pgs, allreduce):
+                assert torch.equal(t, torch.full((4,), 3.0))
+            assert pgs[0].num_active_work() == 0
+        # the worker "dies": outstanding and later work fails instead of hanging
+        proc = pgs[1]._proc
+        proc.kill()
+        proc.join(5)
+        assert not proc.is_alive()
+        with pytest.raises(Exception):
+            pgs[1].allreduce([torch.ones(1)], ReduceOp.SUM).wait(timedelta(seconds=5))
+    finally:
+        for pg in pgs:
+            pg.shutdown()

@@ -250,3 +250,50 @@ def test_bench_reference_arm_reports_unavailable():
     assert r.returncode == 0, r.stderr[-1000:]
     line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
     assert line["impl"] == "reference" and "unavailable" in line and "maturin" in line["unavailable"]
+
+
+def test_thread_backed_mp_context_pipe_and_process():
+    """DummyContext: pipes with timeouts and EOF, a 'process' that is a thread, fd-like sharing of an endpoint."""
+    import threading
+    from datetime import timedelta
+
+    from torchft_b200.multiprocessing import _MonitoredPipe
+    from torchft_b200.multiprocessing_dummy_context import DummyContext, get_context
+
+    ctx = get_context("spawn")
+    assert isinstance(ctx, DummyContext) and ctx.get_start_method() == "thread"
+    parent, child = ctx.Pipe()
+
+    def echo(conn, tag):
+        try:
+            while True:
+                conn.send((tag, conn.recv()))
+        except (EOFError, OSError):
+            pass
+
+    p = ctx.Process(target=echo, args=(child, "x"), daemon=True)
+    p.start()
+    child.close()  # the parent's copy, as after a fork: the worker's stays open
+    mon = _MonitoredPipe(parent)
+    mon.send(41)
+    assert mon.recv(timedelta(seconds=5)) == ("x", 41)
+    with pytest.raises(TimeoutError):
+        mon.recv(timedelta(milliseconds=50))
+    assert p.is_alive() and p.pid is not None
+    payload = object()
+    mon.send(payload)
+    assert mon.recv(timedelta(seconds=5))[1] is payload  # by reference, nothing is pickled
+    mon.close()  # EOF for the worker
+    p.join(5)
+    assert not p.is_alive() and p.exitcode == 0
+
+    # kill() unblocks a worker that waits on its endpoint
+    a, b = ctx.Pipe()
+    q = ctx.Process(target=echo, args=(b, "y"))
+    q.start()
+    q.kill()
+    q.join(5)
+    assert not q.is_alive()
+    with pytest.raises((EOFError, OSError)):
+        a.recv()
+    assert isinstance(ctx.Lock(), type(threading.Lock())) and ctx.Queue().empty() and not ctx.Event().is_set()

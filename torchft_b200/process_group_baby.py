@@ -194,7 +194,7 @@ def _worker(cls, store_addr: str, rank: int, world_size: int, req, fut, timeout:
                     req.send(active["n"])
             elif kind == "stop":
                 break
-    except EOFError:
+    except (EOFError, OSError):  # the parent closed the pipe (or "killed" a thread-backed worker)
         pass
     finally:
         pending.put(None)
@@ -221,12 +221,18 @@ class ProcessGroupBaby(ProcessGroup):
     def _create_pg(cls, store: Store, rank: int, world_size: int, timeout: timedelta) -> BaseProcessGroup:
         raise NotImplementedError
 
+    @staticmethod
+    def _mp_context():
+        """The context that provides ``Process`` and ``Pipe``.  Tests may replace it by
+        ``multiprocessing_dummy_context.DummyContext`` to run the worker on a thread."""
+        return mp.get_context("spawn")
+
     # ---- lifecycle ------------------------------------------------------------------------
     def configure(self, store_addr: str, replica_id: str, rank: int, world_size: int) -> None:
         self.shutdown()
         self._errored = None
         self._rank, self._world_size = rank, world_size
-        ctx = mp.get_context("spawn")
+        ctx = self._mp_context()
         req_parent, req_child = ctx.Pipe()
         fut_parent, fut_child = ctx.Pipe()
         device = torch.cuda.current_device() if torch.cuda.is_available() else None
