@@ -143,3 +143,60 @@ def test_train_diloco_two_groups_cpu(streaming):
             assert "should_commit=True" in out and "local_step=40" in out, out[-3000:]
     finally:
         lh.shutdown()
+
+
+@pytest.mark.timeout(900)
+def test_runner_and_punisher_with_real_trainers(tmp_path):
+    """The job runner supervises two real train_ddp.py groups; the punisher injects a communication failure
+    (the process survives, the step is discarded, the group is rebuilt), then kills a group (every process of
+    it, no orphaned trainer stays in the job), which the runner restarts; both groups finish."""
+    from torchft_b200.launch.runner import Punisher, Runner, _descendants
+
+    pid_file, logs = str(tmp_path / "pids.json"), tmp_path / "logs"
+    steps = 1500
+    runner = Runner([str(REPO / "train_ddp.py")], num_groups=2, base_port=29760, max_restarts=3, pid_file=pid_file,
+                    poll_secs=0.2, log_dir=str(logs), extra_env={"STEPS": str(steps), "OMP_NUM_THREADS": "2", "PYTHONPATH": str(REPO)})
+    result = {}
+    th = threading.Thread(target=lambda: result.setdefault("rc", runner.run()), daemon=True)
+    th.start()
+
+    def log(g, restart=0):
+        f = logs / f"group_{g}.{restart}.log"
+        return f.read_text() if f.exists() else ""
+
+    def wait(cond, timeout, what):
+        end = time.monotonic() + timeout
+        while not cond():
+            assert time.monotonic() < end and th.is_alive(), f"{what}:\n{log(0)[-1500:]}\n{log(1)[-1500:]}"
+            time.sleep(0.2)
+
+    try:
+        wait(lambda: log(0).count("should_commit=True") > 20 and log(1).count("should_commit=True") > 20, 180, "never stepped")
+        pun = Punisher(pid_file)
+        assert pun.inject("comms", group=1) == 1
+        wait(lambda: "injected communication failure" in log(1), 30, "no injection seen")
+        before = log(1).count("should_commit=True")
+        wait(lambda: log(1).count("should_commit=True") > before + 20, 120, "group 1 did not recover from the comms fault")
+        assert "should_commit=False" in log(1)
+        assert not (logs / "group_1.1.log").exists()  # it was never restarted: the process survived
+
+        with open(pid_file) as f:
+            import json
+            launcher = json.load(f)["1"]
+        victims = [launcher] + _descendants(launcher)
+        assert len(victims) >= 2
+        assert pun.inject("kill", group=1) == 1
+        wait(lambda: all(not os.path.exists(f"/proc/{q}") or open(f"/proc/{q}/stat").read().split(")")[-1].split()[0] == "Z"
+                         for q in victims), 30, "killed group left processes behind")
+        wait(lambda: "healing required" in log(1, 1), 180, "restarted group did not heal")
+        th.join(600)
+        assert not th.is_alive() and result.get("rc") == 0, (result, log(0)[-1500:], log(1, 1)[-1500:])
+        assert f"step {steps - 1}] should_commit=True" in log(0)
+        assert f"step {steps - 1}] should_commit=True" in log(1, 1)
+        assert "participants=3" not in log(0)  # the dead group's trainer did not linger as a third replica
+        with pytest.raises(ValueError):
+            pun.inject("meteor")
+    finally:
+        for gp in runner._groups:
+            if gp.proc is not None:
+                _kill_tree(gp.proc.pid)

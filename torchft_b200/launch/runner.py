@@ -7,11 +7,17 @@ when it exits, up to ``max_restarts`` times -- what the reference does with Slur
 torchft/examples/slurm/runner.py:112-143 and with actors in
 examples/monarch/train_distributed.py:67-312.  ``Punisher`` is the chaos side
 (torchft/examples/slurm/punisher.py:15-45): ``kill_one``, ``kill_all`` and ``kill_loop``
-with a mean time between failures; it signals the groups' process groups, i.e. failures
-are always injected on the host.
+with a mean time between failures, plus ``inject`` with the failure kinds of the reference's
+actor-based failure controller (examples/monarch/utils/failure.py:25-136): ``kill`` (SIGKILL),
+``segfault`` (SIGSEGV), ``hang`` (SIGSTOP, then SIGKILL after a while: a process that stops
+answering) and ``comms`` (SIGUSR1: a trainer that called :func:`install_fault_handlers` aborts
+its replica process group and latches an error, so the step fails and the group is rebuilt
+without the process dying).  Failures are always injected on the host, by signalling the
+launcher and every process below it.
 
     python -m torchft_b200.launch.runner --groups 2 --gpus-per-group 4 -- train_hsdp.py --model llama3-1b
     python -m torchft_b200.launch.runner punish --pid-file /tmp/ftb200_runner.json kill_loop --mtbf-secs 30
+    python -m torchft_b200.launch.runner punish --pid-file /tmp/ftb200_runner.json inject --kind comms --group 1
 """
 
 from __future__ import annotations
@@ -28,6 +34,62 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 from .._ftcp import LighthouseServer
+
+
+FAILURE_KINDS = ("kill", "segfault", "hang", "comms")
+
+
+def _descendants(pid: int, max_depth: Optional[int] = None) -> List[int]:
+    """Every live process below ``pid`` (down to ``max_depth`` generations), children before grandchildren.
+    ``torchrun`` starts its workers in sessions of their own, so a launcher's process group does not reach
+    them; the tree is read from /proc."""
+    parent_of: Dict[int, int] = {}
+    for name in os.listdir("/proc"):
+        if not name.isdigit():
+            continue
+        try:
+            with open(f"/proc/{name}/stat") as f:
+                stat = f.read()
+            parent_of[int(name)] = int(stat[stat.rindex(")") + 2:].split()[1])  # the command may hold spaces
+        except (OSError, ValueError, IndexError):
+            continue
+    out, frontier, depth = [], [pid], 0
+    while frontier and (max_depth is None or depth < max_depth):
+        nxt = [c for c, p in parent_of.items() if p in frontier]
+        out += nxt
+        frontier = nxt
+        depth += 1
+    return out
+
+
+def signal_tree(pid: int, sig: int, include_root: bool = True) -> List[int]:
+    """Send ``sig`` to the processes below ``pid`` (deepest last) and then, if asked, to ``pid``; returns the
+    pids that were signalled."""
+    hit = []
+    for q in _descendants(pid) + ([pid] if include_root else []):
+        try:
+            os.kill(q, sig)
+            hit.append(q)
+        except ProcessLookupError:
+            pass
+    return hit
+
+
+def install_fault_handlers(manager) -> None:
+    """Call once from a trainer's main thread: SIGUSR1 then injects a communication failure into this
+    process -- the replica process group is aborted and an error is latched in ``manager``, so the
+    current step does not commit and the next quorum rebuilds the group.  The process keeps running."""
+
+    def on_comms_fault(signum, frame) -> None:
+        err = RuntimeError("injected communication failure")
+        try:
+            manager.report_error(err)
+            manager._pg.abort()
+        except Exception as e:  # never let an injection take the trainer down
+            print(f"[fault] injection failed: {e}", flush=True)
+        print("[fault] injected communication failure", flush=True)
+
+    signal.signal(signal.SIGUSR1, on_comms_fault)
 
 
 @dataclass
@@ -50,6 +112,7 @@ class Runner:
     pid_file: Optional[str] = None
     poll_secs: float = 1.0
     extra_env: Dict[str, str] = field(default_factory=dict)
+    log_dir: Optional[str] = None  # group output goes to <log_dir>/group_<g>.<restart>.log instead of this process's stdout
 
     def __post_init__(self) -> None:
         self._lighthouse: Optional[LighthouseServer] = None
@@ -68,7 +131,14 @@ class Runner:
     def _launch(self, gp: GroupProc) -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={self.gpus_per_group}",
                "--master-addr", "127.0.0.1", "--master-port", str(self.base_port + gp.group_id), *self.script_args]
-        gp.proc = subprocess.Popen(cmd, env=self._env(gp.group_id), start_new_session=True)
+        out = None
+        if self.log_dir:
+            os.makedirs(self.log_dir, exist_ok=True)
+            out = open(os.path.join(self.log_dir, f"group_{gp.group_id}.{gp.restarts}.log"), "w")
+        gp.proc = subprocess.Popen(cmd, env=self._env(gp.group_id), start_new_session=True, stdout=out,
+                                   stderr=subprocess.STDOUT if out else None)
+        if out is not None:
+            out.close()  # the child holds its own descriptor
         gp.started = time.time()
         self._write_pids()
 
@@ -94,6 +164,7 @@ class Runner:
                     rc = gp.proc.poll()
                     if rc is None:
                         continue
+                    signal_tree(gp.proc.pid, signal.SIGKILL, include_root=False)  # workers a dead launcher left behind
                     if rc == 0:
                         done[gp.group_id] = 0
                     elif gp.restarts < self.max_restarts:
@@ -105,7 +176,7 @@ class Runner:
         finally:
             for gp in self._groups:
                 if gp.proc is not None and gp.proc.poll() is None:
-                    os.killpg(gp.proc.pid, signal.SIGTERM)
+                    signal_tree(gp.proc.pid, signal.SIGTERM)
             if self._lighthouse is not None:
                 self._lighthouse.shutdown()
         return max(done.values()) if done else 1
@@ -126,13 +197,38 @@ class Punisher:
         if not pids:
             return None
         g = group if group is not None else random.choice(sorted(pids))
-        os.killpg(pids[g], signal.SIGKILL)
-        print(f"[punisher] killed group {g} (pgid {pids[g]})", flush=True)
+        signal_tree(pids[g], signal.SIGKILL)
+        print(f"[punisher] killed group {g} (launcher pid {pids[g]})", flush=True)
         return g
 
     def kill_all(self) -> None:
         for g, pid in self._pids().items():
-            os.killpg(pid, signal.SIGKILL)
+            signal_tree(pid, signal.SIGKILL)
+
+    def inject(self, kind: str, group: Optional[int] = None, hang_secs: float = 30.0) -> Optional[int]:
+        """Inject one failure of ``kind`` (see :data:`FAILURE_KINDS`) into ``group`` (random when None).
+        ``segfault``, ``hang`` and ``comms`` go to the trainer processes only, not to their launcher; a hung
+        group is killed after ``hang_secs`` so that its launcher's supervisor can replace it."""
+        if kind not in FAILURE_KINDS:
+            raise ValueError(f"unknown failure kind {kind!r}; expected one of {FAILURE_KINDS}")
+        if kind == "kill":
+            return self.kill_one(group)
+        pids = self._pids()
+        if not pids:
+            return None
+        g = group if group is not None else random.choice(sorted(pids))
+        workers = _descendants(pids[g], max_depth=1)  # the launcher's children are the trainers
+        sig = {"segfault": signal.SIGSEGV, "hang": signal.SIGSTOP, "comms": signal.SIGUSR1}[kind]
+        for q in workers:
+            try:
+                os.kill(q, sig)
+            except ProcessLookupError:
+                pass
+        print(f"[punisher] {kind} -> group {g} (pids {workers})", flush=True)
+        if kind == "hang":
+            time.sleep(hang_secs)
+            signal_tree(pids[g], signal.SIGKILL)
+        return g
 
     def kill_loop(self, num_failures: int, mtbf_secs: float) -> None:
         """``num_failures`` kills, exponentially distributed gaps with mean ``mtbf_secs``."""
@@ -149,12 +245,16 @@ def main(argv: Optional[List[str]] = None) -> int:
     if argv and argv[0] == "punish":
         ap = argparse.ArgumentParser(prog="runner punish")
         ap.add_argument("--pid-file", required=True)
-        ap.add_argument("action", choices=["kill_one", "kill_all", "kill_loop"])
+        ap.add_argument("action", choices=["kill_one", "kill_all", "kill_loop", "inject"])
         ap.add_argument("--num-failures", type=int, default=10)
         ap.add_argument("--mtbf-secs", type=float, default=30.0)
+        ap.add_argument("--kind", choices=FAILURE_KINDS, default="kill")
+        ap.add_argument("--group", type=int, default=None)
+        ap.add_argument("--hang-secs", type=float, default=30.0)
         a = ap.parse_args(argv[1:])
         p = Punisher(a.pid_file)
-        {"kill_one": p.kill_one, "kill_all": p.kill_all, "kill_loop": lambda: p.kill_loop(a.num_failures, a.mtbf_secs)}[a.action]()
+        {"kill_one": p.kill_one, "kill_all": p.kill_all, "kill_loop": lambda: p.kill_loop(a.num_failures, a.mtbf_secs),
+         "inject": lambda: p.inject(a.kind, a.group, a.hang_secs)}[a.action]()
         return 0
     ap = argparse.ArgumentParser(prog="runner")
     ap.add_argument("--groups", type=int, default=2)
@@ -164,10 +264,12 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--min-replicas", type=int, default=1)
     ap.add_argument("--lighthouse", default=None)
     ap.add_argument("--pid-file", default="/tmp/ftb200_runner.json")
+    ap.add_argument("--log-dir", default=None)
     ap.add_argument("script", nargs=argparse.REMAINDER)
     a = ap.parse_args(argv)
     script = [s for s in a.script if s != "--"]
-    return Runner(script, a.groups, a.gpus_per_group, a.base_port, a.max_restarts, a.min_replicas, a.lighthouse, a.pid_file).run()
+    return Runner(script, a.groups, a.gpus_per_group, a.base_port, a.max_restarts, a.min_replicas, a.lighthouse, a.pid_file,
+                  log_dir=a.log_dir).run()
 
 
 if __name__ == "__main__":

@@ -28,6 +28,7 @@ sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
 
 from torchft_b200 import DistributedDataParallel, DistributedSampler, Manager, Optimizer, ProcessGroupGloo, ProcessGroupNCCL
 from torchft_b200.checkpointing.pg_transport import PGTransport
+from torchft_b200.launch.runner import install_fault_handlers
 from torchft_b200.models.lenet import LeNet
 
 logging.basicConfig(level=logging.INFO)
@@ -92,6 +93,7 @@ def main() -> None:
         timeout=timeout,
         checkpoint_transport=transport,
     )
+    install_fault_handlers(manager)  # lets the punisher inject a communication failure (SIGUSR1)
     ddp = DistributedDataParallel(manager, model)
     optimizer = Optimizer(manager, opt)
     criterion = nn.CrossEntropyLoss()
