@@ -447,3 +447,35 @@ def test_should_commit_declines_when_ranks_vote_for_different_steps():
     finally:
         ms.shutdown()
         lh.shutdown()
+
+
+def test_control_plane_threads_are_named():
+    """Server threads carry names (visible in ps -L / top -H / debuggers), as the reference names its runtime
+    threads torchft-lighths / torchft-manager (src/lib.rs:105,337)."""
+    import os
+    import time as _time
+    from datetime import timedelta as _td
+
+    from torchft_b200.coordination import LighthouseServer, ManagerServer
+
+    def names():
+        out = []
+        for t in os.listdir("/proc/self/task"):
+            try:
+                out.append(open(f"/proc/self/task/{t}/comm").read().strip())
+            except OSError:
+                pass
+        return out
+
+    lh = LighthouseServer(bind="[::]:0", min_replicas=1)
+    ms = ManagerServer(replica_id="named", lighthouse_addr=lh.address(), hostname="localhost", bind="[::]:0",
+                       store_addr="localhost:1", world_size=1, heartbeat_interval=_td(milliseconds=50),
+                       connect_timeout=_td(seconds=5))
+    try:
+        _time.sleep(0.3)
+        got = names()
+        for want in ("ftb-lighths-acc", "ftb-lighths-tic", "ftb-manager-acc", "ftb-manager-hb", "ftb-lighths-con"):
+            assert want in got, (want, got)
+    finally:
+        ms.shutdown()
+        lh.shutdown()

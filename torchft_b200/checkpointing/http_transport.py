@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import io
 import logging
+import time
 import socket
 import threading
 import urllib.request
@@ -187,6 +188,13 @@ class HTTPTransport(CheckpointTransport[T], Generic[T]):
             return streaming_load(io.BufferedReader(f, buffer_size=4 << 20), into=into)
 
     def recv_checkpoint(self, src_rank: int, metadata: str, step: int, timeout: timedelta) -> T:
+        t0 = time.perf_counter()
+        try:
+            return self._recv_checkpoint(metadata, step, timeout)
+        finally:
+            logger.info("recv_checkpoint of step %d from rank %d took %.3fs", step, src_rank, time.perf_counter() - t0)
+
+    def _recv_checkpoint(self, metadata: str, step: int, timeout: timedelta) -> T:
         base = f"{metadata}{step}"
         into: Optional[List[object]] = None
         if self._state_dict_fn is not None:

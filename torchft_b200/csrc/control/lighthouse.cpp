@@ -52,6 +52,7 @@ Lighthouse::Lighthouse(LighthouseOpt opt) : opt_(std::move(opt)) {
   server_ = std::make_unique<Server>(
       opt_.bind, [this](uint8_t m, const std::string& b, TimePoint d) { return rpc(m, b, d); },
       [this](const HttpRequest& r) { return http(r); });
+  server_->set_thread_tag("ftb-lighths");
   server_->start();
   tick_thread_ = std::thread([this] { tick_loop(); });
   log_info("lighthouse", "listening on " + address());
@@ -73,6 +74,7 @@ void Lighthouse::shutdown() {
 }
 
 void Lighthouse::tick_loop() {
+  set_thread_name("ftb-lighths-tick");
   std::unique_lock<std::mutex> lk(mu_);
   while (!stop_) {
     tick_locked();

@@ -9,6 +9,8 @@
 #include <cstring>
 #include <string>
 
+#include <pthread.h>
+
 namespace ftcp {
 
 inline int log_level() {
@@ -31,6 +33,9 @@ inline void log_at(int lvl, const char* name, const std::string& who, const std:
   const double t = std::chrono::duration<double>(now).count();
   fprintf(stderr, "[%.3f %s torchft_b200::%s] %s\n", t, name, who.c_str(), msg.c_str());
 }
+
+// Names the calling thread (shown by ps -L, top -H, gdb and py-spy); the kernel keeps 15 characters.
+inline void set_thread_name(const std::string& name) { pthread_setname_np(pthread_self(), name.substr(0, 15).c_str()); }
 
 inline void log_error(const std::string& who, const std::string& msg) { log_at(0, "ERROR", who, msg); }
 inline void log_warn(const std::string& who, const std::string& msg) { log_at(1, "WARN", who, msg); }

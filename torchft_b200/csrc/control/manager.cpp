@@ -29,6 +29,7 @@ ManagerServer::ManagerServer(std::string replica_id, std::string lighthouse_addr
   // fail early (TimeoutError) when the lighthouse is unreachable
   { Client probe(lighthouse_addr_, connect_timeout_); }
   server_ = std::make_unique<Server>(bind, [this](uint8_t m, const std::string& b, TimePoint d) { return rpc(m, b, d); });
+  server_->set_thread_tag("ftb-manager");
   server_->start();
   heartbeat_thread_ = std::thread([this] { heartbeat_loop(); });
   log_info("manager", "[Replica " + short_id(replica_id_) + "] Manager listening on " + address());
@@ -57,6 +58,7 @@ void ManagerServer::shutdown() {
 }
 
 void ManagerServer::heartbeat_loop() {
+  set_thread_name("ftb-manager-hb");
   std::unique_ptr<Client> client;
   std::unique_lock<std::mutex> lk(mu_);
   while (!stop_) {

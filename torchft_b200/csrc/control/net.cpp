@@ -1,5 +1,7 @@
 #include "net.h"
 
+#include "log.h"
+
 #include <arpa/inet.h>
 #include <errno.h>
 #include <fcntl.h>
@@ -252,7 +254,12 @@ Server::Server(const std::string& bind, RpcHandler rpc, HttpHandler http) : rpc_
 
 Server::~Server() { shutdown(); }
 
-void Server::start() { accept_thread_ = std::thread([this] { accept_loop(); }); }
+void Server::start() {
+  accept_thread_ = std::thread([this] {
+    set_thread_name(tag_ + "-acc");
+    accept_loop();
+  });
+}
 
 void Server::shutdown() {
   if (stop_.exchange(true)) {
@@ -287,6 +294,7 @@ void Server::accept_loop() {
     }
     active_.fetch_add(1);
     std::thread([this, fd] {
+      set_thread_name(tag_ + "-conn");
       try {
         serve(fd);
       } catch (...) {

@@ -68,6 +68,8 @@ class Server {
   void shutdown();
   int port() const { return port_; }
   bool stopping() const { return stop_.load(); }
+  // Prefix of the names of the accept and connection threads; call before start().
+  void set_thread_tag(std::string tag) { tag_ = std::move(tag); }
 
  private:
   void accept_loop();
@@ -83,6 +85,7 @@ class Server {
   std::mutex mu_;
   std::set<int> conns_;
   std::atomic<int> active_{0};
+  std::string tag_ = "ftb-rpc";
 };
 
 // One reusable connection; calls are serialised.  A call that times out or fails closes

@@ -188,7 +188,7 @@ class Manager:
         if checkpoint_transport is None:
             checkpoint_transport = HTTPTransport[Dict[str, T]](timeout=self._timeout, num_chunks=0)
         self._checkpoint_transport = checkpoint_transport
-        self._executor = ThreadPoolExecutor(max_workers=1, thread_name_prefix="async_quorum")
+        self._executor = ThreadPoolExecutor(max_workers=1, thread_name_prefix="torchft_quorum")
         self._quorum_future: Optional[concurrent.futures.Future] = None
 
         self._store = TCPStore(host_name=store_addr, port=store_port, is_master=False, wait_for_workers=False)
@@ -418,6 +418,10 @@ class Manager:
             self._quorum_future.result()
 
     def _async_quorum(self, allow_heal: bool, shrink_only: bool, quorum_timeout: timedelta, curr_device: int) -> None:
+        with torch.profiler.record_function("torchft::manager::_async_quorum"):
+            self._async_quorum_impl(allow_heal, shrink_only, quorum_timeout, curr_device)
+
+    def _async_quorum_impl(self, allow_heal: bool, shrink_only: bool, quorum_timeout: timedelta, curr_device: int) -> None:
         threading.current_thread().name = "torchft_quorum"
         if curr_device >= 0 and torch.cuda.is_available():
             torch.cuda.set_device(curr_device)

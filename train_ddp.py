@@ -98,6 +98,16 @@ def main() -> None:
     optimizer = Optimizer(manager, opt)
     criterion = nn.CrossEntropyLoss()
 
+    # PROFILE_DIR=<dir>: trace a few steps with torch.profiler (the manager's record_function scopes such as
+    # torchft::manager::allreduce and ::should_commit show up in it) and write chrome traces there
+    prof = None
+    if os.environ.get("PROFILE_DIR"):
+        acts = [torch.profiler.ProfilerActivity.CPU] + ([torch.profiler.ProfilerActivity.CUDA] if use_cuda else [])
+        prof = torch.profiler.profile(
+            activities=acts, schedule=torch.profiler.schedule(wait=5, warmup=2, active=6, repeat=1),
+            on_trace_ready=torch.profiler.tensorboard_trace_handler(os.path.join(os.environ["PROFILE_DIR"], f"group{replica_group}")))
+        prof.start()
+
     while manager.current_step() < steps:
         sampler.set_epoch(manager.current_step())
         for x, y in loader:
@@ -109,9 +119,13 @@ def main() -> None:
             if manager.current_step() % 10 == 0:
                 print(f"[{replica_group}] step={manager.current_step()} batches={manager.batches_committed()} "
                       f"participants={manager.num_participants()} loss={loss.item():.4f}", flush=True)
+            if prof is not None:
+                prof.step()
             # a durable checkpoint would save state_dict(), manager.state_dict() and the loader position here
             if manager.current_step() >= steps:
                 break
+    if prof is not None:
+        prof.stop()
     manager.shutdown()
 
 
