@@ -229,7 +229,19 @@ PYBIND11_MODULE(_ftcp, m) {
     }
   });
 
-  py::class_<ManagerQuorumResponse>(m, "QuorumResult")
+  py::class_<ManagerQuorumResponse>(m, "QuorumResult", R"doc(What one rank learns from a quorum round.
+
+Args (all read/write attributes; the constructor takes none):
+    quorum_id: changes whenever the set of replica groups changes or a member reported failed commits
+    replica_rank, replica_world_size: this group's index among the quorum's groups and their number
+    recover_src_manager_address, recover_src_replica_rank: where a group that is behind fetches its state
+    recover_dst_replica_ranks: groups this rank must serve state to
+    store_address: store on which the replica process group of this quorum rendezvouses
+    max_step, max_replica_rank, max_world_size: the most advanced step, this group's index among the groups
+        at that step (None when behind) and their number
+    heal: True when this group must fetch state before it can contribute
+    commit_failures: largest number of consecutive failed commits reported by a member
+)doc")
       .def(py::init<>())
       .def_readwrite("quorum_id", &ManagerQuorumResponse::quorum_id)
       .def_readwrite("replica_rank", &ManagerQuorumResponse::replica_rank)
@@ -244,7 +256,18 @@ PYBIND11_MODULE(_ftcp, m) {
       .def_readwrite("heal", &ManagerQuorumResponse::heal)
       .def_readwrite("commit_failures", &ManagerQuorumResponse::commit_failures);
 
-  py::class_<PyQuorumMember>(m, "QuorumMember")
+  py::class_<PyQuorumMember>(m, "QuorumMember", R"doc(One replica group as the lighthouse sees it.
+
+Args:
+    replica_id: unique name of the group (a fresh suffix per process start)
+    address: address of the group's manager server
+    store_address: address of the group's store
+    step: committed steps of the group
+    world_size: ranks in the group
+    shrink_only: the group asks that the next quorum does not grow
+    data: free-form dict that is carried through the quorum as JSON
+    commit_failures: consecutive failed commits the group reports
+)doc")
       .def(py::init([](std::string replica_id, std::string address, std::string store_address, int64_t step,
                        uint64_t world_size, bool shrink_only, py::object data, int64_t commit_failures) {
              PyQuorumMember q;
@@ -270,18 +293,36 @@ PYBIND11_MODULE(_ftcp, m) {
       .def_readwrite("commit_failures", &PyQuorumMember::commit_failures)
       .def_readwrite("data", &PyQuorumMember::data);
 
-  py::class_<PyTimestamp>(m, "Timestamp")
+  py::class_<PyTimestamp>(m, "Timestamp", R"doc(Wall-clock time of an event.
+
+Args (attributes):
+    seconds: seconds since the Unix epoch
+    nanos: nanoseconds within the second
+)doc")
       .def(py::init<>())
       .def_readwrite("seconds", &PyTimestamp::seconds)
       .def_readwrite("nanos", &PyTimestamp::nanos);
 
-  py::class_<PyQuorum>(m, "Quorum")
+  py::class_<PyQuorum>(m, "Quorum", R"doc(A quorum as issued by the lighthouse.
+
+Args (attributes):
+    quorum_id: identifier of the quorum
+    participants: list of QuorumMember, sorted by replica_id
+    created: Timestamp of the decision
+)doc")
       .def(py::init<>())
       .def_readwrite("quorum_id", &PyQuorum::quorum_id)
       .def_readwrite("participants", &PyQuorum::participants)
       .def_readwrite("created", &PyQuorum::created);
 
-  py::class_<PyManagerClient>(m, "ManagerClient")
+  py::class_<PyManagerClient>(m, "ManagerClient", R"doc(Client of a replica group's manager server, one per rank.
+
+Args:
+    addr: address of the manager server, e.g. http://host:port
+    connect_timeout: timedelta bound on establishing the connection
+
+A call whose deadline passes raises TimeoutError, any other failure RuntimeError; the GIL is released while a call blocks.
+)doc")
       .def(py::init<const std::string&, std::chrono::duration<double>>(), py::arg("addr"), py::arg("connect_timeout"))
       .def("_quorum", &PyManagerClient::quorum, py::arg("group_rank"), py::arg("step"), py::arg("checkpoint_metadata"),
            py::arg("shrink_only"), py::arg("timeout"), py::arg("init_sync") = true, py::arg("commit_failures") = 0)
@@ -290,7 +331,21 @@ PYBIND11_MODULE(_ftcp, m) {
            py::arg("should_commit"), py::arg("timeout"))
       .def("_kill", &PyManagerClient::kill, py::arg("msg"), py::arg("timeout"));
 
-  py::class_<ManagerServer>(m, "ManagerServer")
+  py::class_<ManagerServer>(m, "ManagerServer", R"doc(The per-group manager server (hosted by the group's rank 0): gathers the quorum requests of the group's
+ranks into one lighthouse request, hands each rank its share of the answer, runs the commit barrier, keeps the ranks'
+checkpoint metadata and sends heartbeats.
+
+Args:
+    replica_id: name of the replica group
+    lighthouse_addr: address of the lighthouse
+    hostname: host name other groups use to reach this server
+    bind: address to listen on, e.g. [::]:0
+    store_addr: address of the group's store, published to the other groups
+    world_size: ranks in the group
+    heartbeat_interval: timedelta between heartbeats to the lighthouse
+    connect_timeout: timedelta bound on connecting to the lighthouse
+    quorum_retries: extra attempts at the lighthouse inside one quorum call
+)doc")
       .def(py::init([](const std::string& replica_id, const std::string& lighthouse_addr, const std::string& hostname,
                        const std::string& bind, const std::string& store_addr, uint64_t world_size,
                        std::chrono::duration<double> heartbeat_interval, std::chrono::duration<double> connect_timeout,
@@ -304,7 +359,15 @@ PYBIND11_MODULE(_ftcp, m) {
       .def("address", &ManagerServer::address)
       .def("shutdown", &ManagerServer::shutdown, py::call_guard<py::gil_scoped_release>());
 
-  py::class_<Lighthouse>(m, "LighthouseServer")
+  py::class_<Lighthouse>(m, "LighthouseServer", R"doc(The job-wide quorum service, with the dashboard on the same port.
+
+Args:
+    bind: address to listen on, e.g. [::]:29510
+    min_replicas: smallest number of groups a quorum may have
+    join_timeout_ms: how long a quorum waits for healthy groups that have not asked yet (default 100)
+    quorum_tick_ms: period of the background quorum check (default 100)
+    heartbeat_timeout_ms: silence after which a group no longer counts as healthy (default 5000)
+)doc")
       .def(py::init([](const std::string& bind, uint64_t min_replicas, std::optional<int64_t> join_timeout_ms,
                        std::optional<int64_t> quorum_tick_ms, std::optional<int64_t> heartbeat_timeout_ms) {
              LighthouseOpt opt;
@@ -321,7 +384,12 @@ PYBIND11_MODULE(_ftcp, m) {
       .def("address", &Lighthouse::address)
       .def("shutdown", &Lighthouse::shutdown, py::call_guard<py::gil_scoped_release>());
 
-  py::class_<PyLighthouseClient>(m, "LighthouseClient")
+  py::class_<PyLighthouseClient>(m, "LighthouseClient", R"doc(Direct client of the lighthouse, for launchers and tools that take part in quorums without a manager.
+
+Args:
+    addr: address of the lighthouse, e.g. http://host:29510
+    connect_timeout: timedelta bound on establishing the connection
+)doc")
       .def(py::init<const std::string&, std::chrono::duration<double>>(), py::arg("addr"), py::arg("connect_timeout"))
       .def("quorum", &PyLighthouseClient::quorum, py::arg("replica_id"), py::arg("timeout"),
            py::arg("address") = py::none(), py::arg("store_address") = py::none(), py::arg("step") = py::none(),
@@ -338,7 +406,13 @@ PYBIND11_MODULE(_ftcp, m) {
         py::gil_scoped_release nogil;
         return lighthouse_main(args);
       },
-      py::arg("argv") = py::none());
+      py::arg("argv") = py::none(),
+      R"doc(Run a lighthouse until it is interrupted; returns the process exit code.
+
+Args:
+    argv: program name followed by --bind, --min_replicas, --join_timeout_ms, --quorum_tick_ms,
+        --heartbeat_timeout_ms (sys.argv when None)
+)doc");
 
   // ---- pure functions, exposed for table-driven tests of the quorum mathematics ----
   m.def(
