@@ -115,6 +115,65 @@ def test_reduce_scatter_quantized_gloo():
             pg.shutdown()
 
 
+def _factorisations(n):
+    return [(a, n // a) for a in range(1, n + 1) if n % a == 0]
+
+
+def _simulated_allreduce(per_rank, scale):
+    """The quantised allreduce for ranks that live in one process: quantise each rank's flat data, hand slice r of
+    every rank to rank r, reduce there, gather the reduced slices, dequantise (the data flow of allreduce_quantized
+    with the collectives replaced by slicing)."""
+    ws = len(per_rank)
+    n = Q.padded_numel(per_rank[0].numel(), ws)
+    per = n // ws
+    qbufs = []
+    for x in per_rank:
+        flat = torch.zeros(n, dtype=x.dtype)
+        flat[: x.numel()] = x.reshape(-1)
+        b = torch.empty(Q.quantized_nbytes(n), dtype=torch.uint8)
+        Q.quantize_into(flat, b)
+        qbufs.append(b)
+    full = torch.empty(Q.quantized_nbytes(n), dtype=torch.uint8)
+    fc, fs = Q.split_quantized(full, n)
+    nb = per // Q.BLOCK
+    for r in range(ws):
+        parts = []
+        for k in range(ws):
+            c, sc = Q.split_quantized(qbufs[(r + k) % ws], n)
+            b = torch.empty(Q.quantized_nbytes(per), dtype=torch.uint8)
+            bc, bs = Q.split_quantized(b, per)
+            bc.copy_(c[r * per : (r + 1) * per])
+            bs.copy_(sc[r * nb : (r + 1) * nb])
+            parts.append(b)
+        red = torch.empty(Q.quantized_nbytes(per), dtype=torch.uint8)
+        Q.reduce_quantized(parts, per, scale, red)
+        rc, rs = Q.split_quantized(red, per)
+        fc[r * per : (r + 1) * per].copy_(rc)
+        fs[r * nb : (r + 1) * nb].copy_(rs)
+    out = torch.empty(n, dtype=per_rank[0].dtype)
+    Q.dequantize_from(full, out)
+    return out[: per_rank[0].numel()]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("avg", [False, True])
+def test_simulated_two_rank_allreduce_matrix(dtype, avg):
+    """Sizes x multipliers x every 2-D factorisation of the size, two simulated ranks, against the exact
+    reduction; mean relative error <= 0.05 (the matrix of torchft/quantization_test.py:35-131)."""
+    ws = 2
+    g = torch.Generator().manual_seed(5)
+    for size in (128, 512, 4096):
+        for mult in (1.0, 100.0, 1000.0):
+            if dtype == torch.float16 and mult == 1000.0 and not avg:
+                mult = 500.0  # keep the exact sum inside fp16's range
+            for rows, cols in _factorisations(size):
+                xs = [(torch.rand(rows, cols, generator=g) * mult).to(dtype) for _ in range(ws)]
+                want = sum(x.float() for x in xs) * (1.0 / ws if avg else 1.0)
+                got = _simulated_allreduce(xs, 1.0 / ws if avg else 1.0).view(rows, cols)
+                assert got.dtype == dtype
+                assert mean_rel_err(got, want) <= 0.05, (size, mult, rows, cols)
+
+
 # ------------------------------------------------------------------------------------ GPU
 
 
