@@ -1,5 +1,6 @@
 """End-to-end fault tolerance on CPU/gloo: replica groups train a LeNet with FT-DDP; one
 is killed and heals from its peer; pass criterion is identical final weights."""
+import threading
 from datetime import timedelta
 from typing import Any, Dict
 
@@ -14,13 +15,20 @@ from torchft_b200.models.lenet import LeNet, synthetic_batch
 from torchft_b200.process_group import FakeProcessGroupWrapper, ProcessGroupGloo
 
 
+_INIT_LOCK = threading.Lock()
+
+
 def ddp_train_loop(rank: int, store_port: int, runner: Runner, total_steps: int = 100, batch: int = 64,
                    use_async_quorum: bool = True, model_fn=LeNet, init_sync: bool = True) -> Dict[str, Any]:
-    torch.manual_seed(42 if not init_sync else runner.replica_id)  # init_sync must equalise different inits
-    model = model_fn()
+    with _INIT_LOCK:  # replica groups are threads here: the global generator must not be shared while seeding
+        torch.manual_seed(42 if not init_sync else runner.replica_id)  # init_sync must equalise different inits
+        model = model_fn()
     opt = optim.SGD(model.parameters(), lr=1e-3, momentum=0.9)
 
+    loads = []
+
     def load_state_dict(sd):
+        loads.append(manager.current_step())
         model.load_state_dict(sd["model"])
         opt.load_state_dict(sd["optim"])
 
@@ -48,7 +56,7 @@ def ddp_train_loop(rank: int, store_port: int, runner: Runner, total_steps: int 
             loss.backward()
             optimizer.step()
         return {"state": {k: v.clone() for k, v in model.state_dict().items()}, "step": manager.current_step(),
-                "batches": manager.batches_committed()}
+                "batches": manager.batches_committed(), "loads": len(loads)}
     finally:
         manager.shutdown(wait=False)
         pg.shutdown()
@@ -96,6 +104,23 @@ def test_ddp_recovery_kill_and_heal(use_async_quorum):
         assert inj.count == 1
         _assert_same(res)
         assert all(r[0]["step"] == 30 for r in res)
+    finally:
+        lh.shutdown()
+
+
+@pytest.mark.parametrize("init_sync", [True, False])
+def test_ddp_init_sync(init_sync):
+    """init_sync=True: differently initialised groups are equalised at step 0 (every group but the primary loads
+    state once).  init_sync=False: the user vouches for identical initialisation, nothing is transferred."""
+    lh = LighthouseServer("[::]:0", 2, join_timeout_ms=100)
+    try:
+        runners = [Runner(i, lh.address(), EventInjector(), None) for i in range(2)]  # type: ignore[arg-type]
+        for r in runners:
+            r.train_loop = lambda rank, store_port, runner: ddp_train_loop(rank, store_port, runner, total_steps=5,
+                                                                          init_sync=init_sync)
+        res = run_replicas(runners)
+        _assert_same(res)
+        assert sum(r[0]["loads"] for r in res) == (1 if init_sync else 0)
     finally:
         lh.shutdown()
 
