@@ -53,3 +53,52 @@ def test_managed_device_mesh_gloo():
     world = 2
     port = 29000 + os.getpid() % 2000
     mp.spawn(_worker, args=(world, port), nprocs=world, join=True)
+
+
+def _fsdp_worker(rank: int, world: int, port: int) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torch.distributed.fsdp import fully_shard
+
+        from torchft_b200.device_mesh import ft_init_device_mesh
+        from torchft_b200.manager import Manager
+        from torchft_b200.process_group import ProcessGroupGloo
+        from torchft_b200.work import _DummyWork
+
+        manager = MagicMock(spec=Manager)
+        manager._pg = ProcessGroupGloo()
+        manager.num_participants.return_value = 1
+        seen = []
+
+        def allreduce(t, should_quantize=False, reduce_op=None):
+            seen.append(t.numel())
+            return _DummyWork(t)
+
+        manager.allreduce.side_effect = allreduce
+        mesh = ft_init_device_mesh(device_type="cpu", mesh_shape=(1, world), mesh_dim_names=("dp_replicate", "dp_shard"),
+                                   replicate_dim=0, manager=manager)
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
+        ref = pickle.loads(pickle.dumps(model))
+        fully_shard(model, mesh=mesh)
+        x = torch.randn(4 * world, 8)  # the same global batch everywhere; each rank takes its rows
+        mine = x[rank * 4:(rank + 1) * 4]
+        model(mine).sum().backward()
+        ref(x).sum().backward()
+        # the shard-sized gradients went through the manager (the replicate dimension) exactly once
+        assert len(seen) == 1 and seen[0] > 0
+        for p, q in zip(model.parameters(), ref.parameters()):
+            # FSDP shards dim 0 over the group and averages over it: this rank holds its rows of the mean gradient
+            want = (q.grad / world).chunk(world, dim=0)[rank]
+            torch.testing.assert_close(p.grad.to_local(), want, rtol=1e-5, atol=1e-6)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fully_shard_on_managed_mesh_gloo():
+    """HSDP as the reference wires it (torchft/fsdp_test.py:82-92): FSDP2 shards inside the group over a real
+    process group and reduces over the replicate dimension through the manager."""
+    world = 2
+    port = 31000 + os.getpid() % 2000
+    mp.spawn(_fsdp_worker, args=(world, port), nprocs=world, join=True)
