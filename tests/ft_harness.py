@@ -8,17 +8,14 @@ from scratch, or the next allreduce's future is made to fail.
 from __future__ import annotations
 
 import threading
-import traceback
 from concurrent.futures import ThreadPoolExecutor, as_completed
 from dataclasses import dataclass, field
-from datetime import timedelta
 from typing import Any, Callable, Dict, List, Optional, Set, Tuple
 
 import torch
 import torch.distributed as dist
 
-from torchft_b200._ftcp import LighthouseServer
-from torchft_b200.process_group import FakeProcessGroupWrapper, ProcessGroupGloo
+from torchft_b200.process_group import FakeProcessGroupWrapper
 
 
 class InjectedFailure(Exception):

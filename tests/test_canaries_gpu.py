@@ -1,5 +1,4 @@
 """Every kernel family once, with guard zones around everything it writes (tests/canary.py)."""
-import math
 
 import pytest
 import torch

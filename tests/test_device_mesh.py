@@ -4,7 +4,6 @@ import os
 import pickle
 from unittest.mock import MagicMock
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp

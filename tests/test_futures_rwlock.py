@@ -4,7 +4,6 @@ from datetime import timedelta
 from unittest.mock import patch
 
 import pytest
-import torch
 from torch.futures import Future
 
 from torchft_b200 import futures as F

@@ -1,5 +1,4 @@
 """The explicit forward/backward engine must match autograd on the same weights."""
-import pytest
 import torch
 
 from torchft_b200.models.llama import LLAMA_TINY, TorchLlama

@@ -1,8 +1,7 @@
 """LocalSGD / DiLoCo unit tests against a mocked Manager, and the analytic golden sequence:
 inner lr 1 with constant gradient 2, outer lr 2, 2 fragments, sync_every 6 gives local
 weights 1,-1,-3,-11,... for fragment 0 and global updates -11, -23, -35, -47."""
-from typing import Dict, List
-from unittest.mock import MagicMock, create_autospec
+from unittest.mock import create_autospec
 
 import pytest
 import torch

@@ -4,13 +4,13 @@ Pass criterion: the replicas' global state (backup weights, outer optimizer) is 
 import copy
 import threading
 from datetime import timedelta
-from typing import Any, Dict, List
+from typing import Any, Dict
 
 import pytest
 import torch
 from torch import nn, optim
 
-from ft_harness import EventInjector, InjectedFailure, Runner, run_replicas
+from ft_harness import EventInjector, Runner, run_replicas
 from torchft_b200 import Manager
 from torchft_b200._ftcp import LighthouseServer
 from torchft_b200.local_sgd import DiLoCo, LocalSGD

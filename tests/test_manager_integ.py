@@ -8,7 +8,7 @@ import pytest
 import torch
 from torch import nn, optim
 
-from ft_harness import EventInjector, InjectedFailure, Runner, run_replicas
+from ft_harness import EventInjector, Runner, run_replicas
 from torchft_b200 import DistributedDataParallel, Manager, Optimizer
 from torchft_b200._ftcp import LighthouseServer
 from torchft_b200.models.lenet import LeNet, synthetic_batch

@@ -12,9 +12,16 @@ import torch.distributed as dist
 from torch.distributed.distributed_c10d import (AllgatherOptions, AllreduceOptions, AllToAllOptions, BarrierOptions,
                                                 BroadcastOptions, ReduceOp, ReduceScatterOptions)
 
-from torchft_b200.process_group import (ErrorSwallowingProcessGroupWrapper, FakeProcessGroupWrapper, ManagedProcessGroup,
-                                         ProcessGroup, ProcessGroupBabyGloo, ProcessGroupDummy, ProcessGroupGloo,
-                                         ProcessGroupWrapper, create_store_client)
+from torchft_b200.process_group import (
+    ErrorSwallowingProcessGroupWrapper,
+    FakeProcessGroupWrapper,
+    ManagedProcessGroup,
+    ProcessGroup,
+    ProcessGroupBabyGloo,
+    ProcessGroupDummy,
+    ProcessGroupGloo,
+    create_store_client,
+)
 from torchft_b200.work import _DummyWork
 
 

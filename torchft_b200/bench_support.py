@@ -4,7 +4,6 @@ global rank 0), one TCPStore per replica group (hosted by the group's rank 0), o
 
 from __future__ import annotations
 
-import os
 from datetime import timedelta
 from typing import Optional, Tuple
 

@@ -6,18 +6,14 @@ communicator.
 """
 
 
-import os
-import sys
-from typing import TYPE_CHECKING, Optional
-from unittest.mock import patch
+from typing import TYPE_CHECKING
 
 import torch
 import torch.distributed as dist
 from torch import nn
-from torch.distributed.algorithms.join import Joinable
 from torch.nn import parallel
 
-from .process_group import ProcessGroup, ProcessGroupDummy
+from .process_group import ProcessGroupDummy
 
 if TYPE_CHECKING:
     from .manager import Manager

@@ -17,7 +17,6 @@ import argparse
 import random
 import shlex
 import subprocess
-import sys
 import time
 from typing import List, Set
 

@@ -20,7 +20,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _native as N
-from ._native import c_float, c_int, c_ll, c_void_p, ptr, stream_ptr
+from ._native import c_float, c_int, c_ll, ptr, stream_ptr
 
 # --------------------------------------------------------------------------- status word
 

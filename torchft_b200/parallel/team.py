@@ -19,12 +19,12 @@ import logging
 import os
 import threading
 from datetime import timedelta
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
 from torch.distributed import Store
-from torch.distributed.distributed_c10d import AllreduceOptions, ReduceOp, Work
+from torch.distributed.distributed_c10d import ReduceOp, Work
 from torch.futures import Future
 
 from .._pg_base import ProcessGroup, _reduce_op, create_store_client

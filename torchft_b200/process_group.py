@@ -29,20 +29,13 @@ from __future__ import annotations
 
 import logging
 import os
-import threading
-from contextlib import contextmanager, nullcontext
+from contextlib import contextmanager
 from datetime import timedelta
-from typing import TYPE_CHECKING, Callable, Dict, Generator, List, Optional, Tuple, Union
+from typing import TYPE_CHECKING, Callable, Generator, List, Optional
 
 import torch
 import torch.distributed as dist
-from torch.distributed import (
-    PrefixStore,
-    ProcessGroup as BaseProcessGroup,
-    ProcessGroupGloo as BaseProcessGroupGloo,
-    Store,
-    TCPStore,
-)
+from torch.distributed import ProcessGroup as BaseProcessGroup, ProcessGroupGloo as BaseProcessGroupGloo, Store
 from torch.distributed.distributed_c10d import (
     AllgatherOptions,
     AllreduceCoalescedOptions,

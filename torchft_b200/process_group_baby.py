@@ -24,7 +24,6 @@ from datetime import timedelta
 from typing import Dict, List, Optional, Tuple
 
 import torch
-import torch.distributed as dist
 import torch.multiprocessing as mp
 from torch.distributed import ProcessGroup as BaseProcessGroup
 from torch.distributed import ProcessGroupGloo as BaseProcessGroupGloo
