@@ -3,6 +3,7 @@ console scripts, and an installed copy works away from the source tree (the refe
 maturin-built wheel with a ``torchft_lighthouse`` script, pyproject.toml:43-48)."""
 
 import os
+import shutil
 import subprocess
 import sys
 import zipfile
@@ -19,8 +20,19 @@ def _pip(*args, tmp):
                           cwd=REPO, env=env, capture_output=True, text=True, timeout=1200)
 
 
+@pytest.fixture
+def clean_setuptools_leftovers():
+    """``pip wheel .`` builds in the source tree; remove what setuptools leaves next to the native build's objects."""
+    yield
+    for d in (REPO / "build").glob("lib.*"):
+        shutil.rmtree(d, ignore_errors=True)
+    for d in (REPO / "build").glob("bdist.*"):
+        shutil.rmtree(d, ignore_errors=True)
+    shutil.rmtree(REPO / "torchft_b200.egg-info", ignore_errors=True)
+
+
 @pytest.mark.timeout(1500)
-def test_wheel_builds_installs_and_runs(tmp_path):
+def test_wheel_builds_installs_and_runs(tmp_path, clean_setuptools_leftovers):
     out = tmp_path / "wheel"
     r = _pip("wheel", ".", "--no-build-isolation", "-w", str(out), tmp=tmp_path)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
