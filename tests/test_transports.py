@@ -311,3 +311,66 @@ def test_http_transport_receives_in_place(num_chunks):
     finally:
         send.shutdown()
         recv.shutdown()
+
+
+def test_transports_carry_dtensor_leaves():
+    """A state dict with DTensor leaves (what FSDP2 / tensor-parallel models hold) survives the HTTP and the
+    process-group transport: the local shard travels, the receiver gets a DTensor on its own mesh again
+    (the reference's transport tests include a DTensor leaf, torchft/checkpointing/transport_test.py:45-155).
+    Runs in a child because it initialises torch.distributed."""
+    import subprocess
+    import sys
+
+    child = r'''
+import threading, torch, torch.distributed as dist
+from concurrent.futures import ThreadPoolExecutor
+from datetime import timedelta
+from torch.distributed.device_mesh import init_device_mesh
+from torch.distributed.tensor import DTensor, Shard, distribute_tensor
+from torchft_b200.checkpointing.http_transport import HTTPTransport
+from torchft_b200.checkpointing.pg_transport import PGTransport
+from torchft_b200.process_group import ProcessGroupGloo
+
+store = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+dist.init_process_group("gloo", store=dist.PrefixStore("w", store), rank=0, world_size=1)
+mesh = init_device_mesh("cpu", (1,))
+full = torch.arange(12, dtype=torch.float32).reshape(4, 3)
+sd = {"dt": distribute_tensor(full, mesh, [Shard(0)]), "plain": torch.ones(2), "s": "x", "i": 3}
+timeout = timedelta(seconds=10)
+
+def check(got):
+    assert isinstance(got["dt"], DTensor), type(got["dt"])
+    assert got["dt"].placements == sd["dt"].placements and tuple(got["dt"].shape) == (4, 3)
+    torch.testing.assert_close(got["dt"].to_local(), full)
+    torch.testing.assert_close(got["plain"], torch.ones(2))
+    assert got["s"] == "x" and got["i"] == 3
+
+send, recv = HTTPTransport(timeout, num_chunks=0), HTTPTransport(timeout, num_chunks=0)
+send.send_checkpoint([1], 1, sd, timeout)
+check(recv.recv_checkpoint(0, send.metadata(), 1, timeout))
+send.shutdown(); recv.shutdown()
+
+pgs = [ProcessGroupGloo(timeout=timeout) for _ in range(2)]
+with ThreadPoolExecutor(2) as ex:
+    list(ex.map(lambda r: pgs[r].configure(f"127.0.0.1:{store.port}/t", "rep", r, 2), range(2)))
+trs = [PGTransport(pgs[r], timeout, torch.device("cpu")) for r in range(2)]
+with ThreadPoolExecutor(2) as ex:
+    f0 = ex.submit(trs[0].send_checkpoint, [1], 1, sd, timeout)
+    f1 = ex.submit(trs[1].recv_checkpoint, 0, trs[0].metadata(), 1, timeout)
+    f0.result(30); check(f1.result(30))
+# in place: the receiver's own DTensor gets the values
+mine = {"dt": distribute_tensor(torch.zeros(4, 3), mesh, [Shard(0)]), "plain": torch.zeros(2), "s": "", "i": 0}
+trs[1] = PGTransport(pgs[1], timeout, torch.device("cpu"), state_dict=lambda: mine)
+with ThreadPoolExecutor(2) as ex:
+    f0 = ex.submit(trs[0].send_checkpoint, [1], 2, sd, timeout)
+    f1 = ex.submit(trs[1].recv_checkpoint, 0, trs[0].metadata(), 2, timeout)
+    f0.result(30); check(f1.result(30))
+torch.testing.assert_close(mine["dt"].to_local(), full)
+for pg in pgs: pg.shutdown()
+print("dtensor ok")
+'''
+    import os as _os
+    repo = _os.path.dirname(_os.path.dirname(_os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=240,
+                       env=dict(_os.environ, PYTHONPATH=repo))
+    assert r.returncode == 0 and "dtensor ok" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
