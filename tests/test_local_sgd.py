@@ -319,3 +319,74 @@ def test_streaming_diloco_matches_independent_simulation(flat, n_frag, sync_ever
             assert got_local == pytest.approx(want[k][0]), (k, got_local, want[k][0])
             assert got_global == pytest.approx(want[k][1]), (k, got_global, want[k][1])
     assert m.should_commit.call_count == 3 * n_frag
+
+
+def test_local_sgd_and_diloco_with_dtensor_parameters():
+    """Models sharded by FSDP2 hold DTensor parameters: LocalSGD and DiLoCo (both fragment layouts) work on the
+    local shards and follow the same trajectory as the unsharded model; what reaches the manager's allreduce is a
+    plain tensor (torchft/local_sgd.py:33-43 extract_local_tensor).  Child process: it initialises torch.distributed."""
+    import os
+    import subprocess
+    import sys
+
+    child = r'''
+import torch, torch.distributed as dist
+from torch import nn, optim
+from unittest.mock import create_autospec
+from torch.distributed.device_mesh import init_device_mesh
+from torch.distributed.fsdp import fully_shard
+from torch.distributed.tensor import DTensor
+from torchft_b200.local_sgd import DiLoCo, LocalSGD
+from torchft_b200.manager import Manager
+from torchft_b200.work import _DummyWork
+store = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+dist.init_process_group("gloo", store=dist.PrefixStore("w", store), rank=0, world_size=1)
+mesh = init_device_mesh("cpu", (1,))
+def mk():
+    state = {"step": 0}
+    m = create_autospec(Manager, instance=True)
+    m._use_async_quorum = False
+    m.current_step.side_effect = lambda: state["step"]
+    def ar(t, should_quantize=False, reduce_op=None):
+        assert not isinstance(t, DTensor); t.mul_(0.5); return _DummyWork(t)
+    def ard(out, a, b, should_quantize=False):
+        torch.sub(a, b, out=out); return ar(out)
+    def commit(): state["step"] += 1; return True
+    m.allreduce.side_effect = ar; m.allreduce_delta.side_effect = ard; m.should_commit.side_effect = commit
+    return m
+def run(shard, flat):
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(4, 8), nn.Linear(8, 2))
+    if shard:
+        for l in model: fully_shard(l, mesh=mesh)
+        fully_shard(model, mesh=mesh)
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    outer = optim.SGD(model.parameters(), lr=0.7, momentum=0.9, nesterov=True)
+    g = torch.Generator().manual_seed(1)
+    with DiLoCo(mk(), [model], inner, outer, sync_every=3, flat_fragments=flat) as d:
+        for _ in range(9):
+            inner.zero_grad(); model(torch.randn(5, 4, generator=g)).square().mean().backward(); inner.step()
+    return [ (p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()]
+ref = run(False, False)
+for flat in (False, None):
+    got = run(True, flat)
+    for a, b in zip(ref, got): torch.testing.assert_close(a, b)
+    print("ok flat=", flat)
+# LocalSGD
+def run_l(shard):
+    torch.manual_seed(0)
+    model = nn.Sequential(nn.Linear(4, 8), nn.Linear(8, 2))
+    if shard:
+        fully_shard(model, mesh=mesh)
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    g = torch.Generator().manual_seed(1)
+    with LocalSGD(mk(), model, inner, sync_every=2):
+        for _ in range(6):
+            inner.zero_grad(); model(torch.randn(5, 4, generator=g)).square().mean().backward(); inner.step()
+    return [ (p.to_local() if isinstance(p, DTensor) else p).detach().clone() for p in model.parameters()]
+for a, b in zip(run_l(False), run_l(True)): torch.testing.assert_close(a, b)
+print("localsgd ok")
+'''
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=240, env=dict(os.environ, PYTHONPATH=repo))
+    assert r.returncode == 0 and "localsgd ok" in r.stdout and "ok flat= None" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
