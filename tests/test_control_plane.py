@@ -1,6 +1,7 @@
 """Control-plane tests: the quorum mathematics on hand-built states (the vectors come from
 the behaviour the reference's Rust unit tests pin down, src/lighthouse.rs:627-1112 and
 src/manager.rs:880-1107) and end-to-end runs over real sockets in-process."""
+import os
 import threading
 import time
 import urllib.request
@@ -478,4 +479,49 @@ def test_control_plane_threads_are_named():
             assert want in got, (want, got)
     finally:
         ms.shutdown()
+        lh.shutdown()
+
+
+def test_dashboard_kill_button_ends_the_replica_process():
+    """POST /replica/<id>/kill on the lighthouse reaches the replica's manager server, which exits the
+    process with status 1 (src/lighthouse.rs:454-479, src/manager.rs:481-486); an unknown id is an error."""
+    import subprocess
+    import sys
+    import urllib.error
+    import urllib.parse
+    import urllib.request
+
+    from torchft_b200.coordination import LighthouseServer
+
+    lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=100)
+    port = lh.address().rsplit(":", 1)[1]
+    base = f"http://127.0.0.1:{port}"
+    child = f'''
+import time
+from datetime import timedelta
+from torchft_b200.coordination import ManagerClient, ManagerServer
+ms = ManagerServer(replica_id="victim:1", lighthouse_addr="{base}", hostname="127.0.0.1", bind="[::]:0",
+                   store_addr="127.0.0.1:1", world_size=1, heartbeat_interval=timedelta(milliseconds=50),
+                   connect_timeout=timedelta(seconds=5))
+c = ManagerClient(ms.address(), timedelta(seconds=5))
+c._quorum(group_rank=0, step=0, checkpoint_metadata="", shrink_only=False, timeout=timedelta(seconds=10),
+          init_sync=False, commit_failures=0)
+print("joined", flush=True)
+time.sleep(60)
+'''
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    p = subprocess.Popen([sys.executable, "-c", child], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True,
+                         env=dict(os.environ, PYTHONPATH=repo))
+    try:
+        assert p.stdout.readline().strip() == "joined"
+        with pytest.raises(urllib.error.HTTPError) as e:
+            urllib.request.urlopen(urllib.request.Request(f"{base}/replica/nobody/kill", method="POST"), timeout=5)
+        assert e.value.code == 500
+        assert p.poll() is None
+        url = f"{base}/replica/{urllib.parse.quote('victim:1', safe='')}/kill"
+        assert urllib.request.urlopen(urllib.request.Request(url, method="POST"), timeout=15).read() == b"ok"
+        assert p.wait(timeout=15) == 1
+    finally:
+        if p.poll() is None:
+            p.kill()
         lh.shutdown()
