@@ -2,8 +2,18 @@
 // -fsanitize=address: one lighthouse, three replica groups of two ranks each running quorum +
 // should_commit rounds from their own threads, a fourth group that joins and leaves in the
 // middle, dashboard requests and heartbeats in the background.  Exits non-zero when the ranks of
-// one step disagree on the quorum or on the commit decision.
+// one step disagree on the quorum or on the commit decision.  A last stage throws malformed input
+// (garbage, truncated frames, absurd lengths, random bodies for every method) at both servers,
+// which must keep answering; under the sanitizers any bad read in the decoders shows up there.
+#include <arpa/inet.h>
+#include <netinet/in.h>
+#include <sys/socket.h>
+#include <sys/time.h>
+#include <unistd.h>
+
 #include <atomic>
+#include <cstdint>
+#include <cstring>
 #include <cstdio>
 #include <map>
 #include <mutex>
@@ -53,6 +63,67 @@ void rank_loop(const std::string& replica, const std::string& manager_addr, int 
     if (decision != expect) fail("commit decision", step);
     (void)decode_str1(c.call(kManagerCheckpointMetadata, encode_i64_1(1 - rank), Millis(5000)));
   }
+}
+
+// ---- malformed input ------------------------------------------------------------------------
+uint32_t g_lcg = 12345;
+uint32_t rnd() { return g_lcg = g_lcg * 1664525u + 1013904223u; }
+
+void poke(int port, const std::string& payload) {
+  int fd = ::socket(AF_INET, SOCK_STREAM, 0);
+  if (fd < 0) return;
+  sockaddr_in a{};
+  a.sin_family = AF_INET;
+  a.sin_port = htons(static_cast<uint16_t>(port));
+  a.sin_addr.s_addr = htonl(INADDR_LOOPBACK);
+  timeval tv{0, 20000};
+  ::setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof(tv));
+  if (::connect(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) == 0) {
+    if (!payload.empty()) (void)!::send(fd, payload.data(), payload.size(), MSG_NOSIGNAL);
+    char buf[512];
+    (void)!::recv(fd, buf, sizeof(buf), 0);
+  }
+  ::close(fd);
+}
+
+std::string frame(uint8_t method, const std::string& body, uint32_t announced) {
+  std::string f = "FTB2";
+  for (int i = 0; i < 4; ++i) f.push_back(static_cast<char>((announced >> (8 * i)) & 0xff));
+  f.push_back(static_cast<char>(method));
+  const uint64_t timeout_ms = 30;
+  for (int i = 0; i < 8; ++i) f.push_back(static_cast<char>((timeout_ms >> (8 * i)) & 0xff));
+  return f + body;
+}
+
+std::string random_bytes(size_t n) {
+  std::string s(n, '\0');
+  for (auto& c : s) c = static_cast<char>(rnd() >> 24);
+  return s;
+}
+
+void malformed_input(int port) {
+  poke(port, "");
+  poke(port, random_bytes(3));
+  poke(port, random_bytes(64));
+  poke(port, "FTB2" + random_bytes(5));
+  poke(port, frame(1, "", 0xFFFFFFFFu));
+  poke(port, frame(1, "abc", 1u << 20));
+  poke(port, "GET /" + std::string(70000, 'a') + " HTTP/1.1\r\n\r\n");
+  poke(port, "POST /replica/%zz/kill HTTP/1.1\r\nContent-Length: 99999999999\r\n\r\n");
+  const size_t sizes[] = {0, 1, 2, 7, 33, 200, 4096};
+  for (int method = 0; method < 12; ++method)
+    for (int k = 0; k < 8; ++k) {
+      const std::string body = random_bytes(sizes[rnd() % 7]);
+      poke(port, frame(static_cast<uint8_t>(method), body, static_cast<uint32_t>(body.size())));
+    }
+  ManagerQuorumRequest good;
+  good.group_rank = 1;
+  good.step = 7;
+  good.checkpoint_metadata = "some metadata";
+  const std::string enc = good.encode();
+  for (size_t cut = 0; cut < enc.size(); ++cut)
+    for (int method = 1; method <= 6; ++method)
+      poke(port, frame(static_cast<uint8_t>(method), enc.substr(0, cut), static_cast<uint32_t>(cut)));
 }
 
 }  // namespace
@@ -113,6 +184,27 @@ int main() {
   churn.join();
   stop.store(true);
   pinger.join();
+  // malformed input against the lighthouse and one manager; both must still answer afterwards
+  {
+    ManagerServer probe("probe", lh_addr, "127.0.0.1", "[::]:0", "storeP:1", 1, Millis(20), Millis(5000), 0);
+    const std::string paddr = probe.address();
+    malformed_input(lh.port());
+    malformed_input(std::stoi(paddr.substr(paddr.rfind(':') + 1)));
+    try {
+      Client c(lh_addr, Millis(2000));
+      (void)c.call(kLighthouseHeartbeat, encode_str1("observer"), Millis(2000));
+      Client m(paddr, Millis(2000));
+      ShouldCommitRequest v;  // a group of one rank: the vote returns at once
+      v.group_rank = 0;
+      v.step = 0;
+      v.should_commit = true;
+      if (decode_i64_1(m.call(kManagerShouldCommit, v.encode(), Millis(2000))) == 0) fail("vote after malformed input", 0);
+    } catch (const std::exception& e) {
+      std::fprintf(stderr, "MISMATCH: server unusable after malformed input: %s\n", e.what());
+      g_failures.fetch_add(1);
+    }
+    probe.shutdown();
+  }
   for (auto& m : managers) m->shutdown();
   lh.shutdown();
   if (g_failures.load() != 0) return 1;

@@ -525,3 +525,74 @@ time.sleep(60)
         if p.poll() is None:
             p.kill()
         lh.shutdown()
+
+
+def test_servers_survive_malformed_input():
+    """Garbage, truncated frames, oversized length fields and random bodies for every method id leave the
+    lighthouse and a manager server running and still answering.  In a child process: a crash of the native
+    code must fail this test, not the test runner."""
+    import subprocess
+    import sys
+
+    child = r'''
+import os, random, socket, struct, time
+from datetime import timedelta
+from torchft_b200.coordination import LighthouseServer, ManagerClient, ManagerServer
+
+lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=50, heartbeat_timeout_ms=300)
+lport = int(lh.address().rsplit(":", 1)[1])
+ms = ManagerServer(replica_id="fuzz", lighthouse_addr=f"http://127.0.0.1:{lport}", hostname="127.0.0.1", bind="[::]:0",
+                   store_addr="127.0.0.1:1", world_size=1, heartbeat_interval=timedelta(milliseconds=50),
+                   connect_timeout=timedelta(seconds=5))
+mport = int(ms.address().rsplit(":", 1)[1])
+rnd = random.Random(1234)
+
+def poke(port, payload, linger=0.02):
+    s = socket.create_connection(("127.0.0.1", port), timeout=2)
+    try:
+        s.sendall(payload)
+        s.settimeout(linger)
+        try:
+            s.recv(4096)
+        except (socket.timeout, ConnectionError):
+            pass
+    finally:
+        s.close()
+
+def frame(method, body, timeout_ms=50, length=None):
+    return b"FTB2" + struct.pack("<IBQ", len(body) if length is None else length, method, timeout_ms) + body
+
+cases = 0
+for port in (lport, mport):
+    poke(port, b"")                                        # connect and leave
+    poke(port, os.urandom(3))                              # less than a magic
+    poke(port, os.urandom(64))                             # garbage (treated as a broken HTTP request)
+    poke(port, b"FTB2" + os.urandom(5))                    # truncated header
+    poke(port, frame(1, b"", length=0xFFFFFFFF))           # absurd length field
+    poke(port, frame(1, b"abc", length=1 << 20))           # body shorter than announced
+    poke(port, b"GET /" + b"a" * 70000 + b" HTTP/1.1\r\n\r\n")   # oversized request line
+    poke(port, b"POST /replica/%zz/kill HTTP/1.1\r\nContent-Length: 99999999999\r\n\r\n")
+    for method in range(0, 12):
+        for _ in range(12):
+            n = rnd.choice([0, 1, 2, 7, 33, 200, 4096])
+            poke(port, frame(method, bytes(rnd.getrandbits(8) for _ in range(n))))
+            cases += 1
+    # valid prefix of a real message, cut at every length
+    good = b"\x0a\x05hello\x10\x01\x18\x02\x22\x03abc"
+    for cut in range(len(good)):
+        poke(port, frame(1, good[:cut]))
+        poke(port, frame(2, good[:cut]))
+
+# Random bodies that happen to decode as heartbeats or quorum requests register phantom replicas (the protocol has no
+# authentication); they stop counting once their heartbeats are older than the timeout.
+time.sleep(0.6)
+# both servers still work: the manager's quorum goes through the lighthouse
+r = ManagerClient(ms.address(), timedelta(seconds=5))._quorum(group_rank=0, step=0, checkpoint_metadata="", shrink_only=False,
+        timeout=timedelta(seconds=10), init_sync=False, commit_failures=0)
+assert r.replica_world_size == 1 and r.quorum_id >= 1
+ms.shutdown(); lh.shutdown()
+print("survived", cases)
+'''
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=280, env=dict(os.environ, PYTHONPATH=repo))
+    assert r.returncode == 0 and "survived" in r.stdout, f"rc={r.returncode}\n{r.stdout[-1500:]}\n{r.stderr[-3000:]}"
