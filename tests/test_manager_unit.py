@@ -326,3 +326,77 @@ def test_allreduce_delta_falls_back_to_subtract_then_allreduce(h):
     h.manager.allreduce_delta(out, a, b, should_quantize=False).wait()
     torch.testing.assert_close(out, torch.tensor([2.0, 1.0]))  # (a - b) / 2 participants
     assert h.pg.allreduce.call_count == 1
+
+
+def test_heal_async_not_enough_participants(h):
+    """A healing replica does not count: with only one up-to-date replica and min_replica_size 2 the step must not
+    commit, although this replica still receives its state (torchft/manager_test.py test_quorum_heal_async_not_enough_participants)."""
+    h.client._quorum.return_value = quorum(heal=True, max_step=20, recover_src_replica_rank=0, max_replica_rank=None,
+                                           max_world_size=1)
+    h.client._checkpoint_metadata.return_value = "src_meta"
+    h.client.should_commit.side_effect = lambda rank, step, vote, timeout: vote
+    h.transport.recv_checkpoint.return_value = {"user": {"default": {"w": 9}}, "torchft": {"step": 20, "batches_committed": 40}}
+    m = h.manager
+    m.start_quorum()
+    m.wait_quorum()
+    assert m.num_participants() == 1 and not m.is_participating()
+    m.allreduce(torch.ones(2)).wait()
+    assert not m.should_commit()  # 1 participant < min_replica_size 2
+    assert h.client.should_commit.call_args.args[2] is False or h.client.should_commit.call_args.kwargs.get("should_commit") is False
+    assert h.loaded == [{"w": 9}]  # the fetched state is applied all the same
+    assert m.current_step() == 20  # healed to the peers' step, nothing committed on top
+
+
+def test_checkpoint_errors_are_latched_not_raised(h):
+    """A failing state transfer (fetching as well as serving) ends in the error latch and a step that does not commit."""
+    h.client.should_commit.side_effect = lambda rank, step, vote, timeout: vote
+    m = h.manager
+    # fetching
+    h.client._quorum.return_value = quorum(heal=True, max_step=20, recover_src_replica_rank=0, max_replica_rank=None,
+                                           max_world_size=1)
+    h.client._checkpoint_metadata.return_value = "src_meta"
+    h.transport.recv_checkpoint.side_effect = RuntimeError("peer went away")
+    m.start_quorum()
+    m.wait_quorum()
+    assert "peer went away" in str(m.errored())
+    assert not m.should_commit() and h.loaded == []
+    # serving
+    h.transport.recv_checkpoint.side_effect = None
+    h.transport.send_checkpoint.side_effect = RuntimeError("disk on fire")
+    h.client._quorum.return_value = quorum(recover_dst_replica_ranks=[0], max_step=5)
+    m.start_quorum()
+    m.wait_quorum()
+    assert "disk on fire" in str(m.errored())
+    assert not m.should_commit()
+    # the latch is cleared by the next quorum
+    h.transport.send_checkpoint.side_effect = None
+    h.client._quorum.return_value = quorum()
+    m.start_quorum()
+    m.wait_quorum()
+    assert m.errored() is None
+
+
+def test_state_dict_lock_concurrent_readers_and_writer(h):
+    """Readers of the state (healing peers) and the writer (the optimizer step) exclude each other; readers run
+    concurrently with each other."""
+    m = h.manager
+    order = []
+    barrier = threading.Barrier(3)
+
+    def reader(i):
+        barrier.wait(5)
+        sd = m._manager_state_dict()
+        order.append(("read", i, sd["user"]["default"]))
+
+    ts = [threading.Thread(target=reader, args=(i,)) for i in range(2)]
+    m.disallow_state_dict_read()  # the optimizer is about to mutate the weights
+    for t in ts:
+        t.start()
+    barrier.wait(5)
+    time.sleep(0.2)
+    assert order == []  # both readers are held back
+    order.append(("write",))
+    m.allow_state_dict_read()
+    for t in ts:
+        t.join(5)
+    assert order[0] == ("write",) and sorted(o[1] for o in order[1:]) == [0, 1]
