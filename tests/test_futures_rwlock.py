@@ -103,3 +103,39 @@ def test_rwlock_writer_preference():
     t.join()
     r.join()
     assert got == ["w", "r"]
+
+
+def test_stream_timeout_logic_with_a_fake_event(monkeypatch):
+    """stream_timeout: the callback runs only when the recorded event has not completed by the deadline, and the event
+    is handed to the deletion queue instead of being destroyed on the timer thread (torchft/futures_test.py
+    test_stream_timeout; the CUDA event is faked so that the logic runs on CPU)."""
+    import threading
+    import time
+    from datetime import timedelta
+
+    import torch
+
+    from torchft_b200 import futures as F
+
+    class FakeEvent:
+        done = False
+        recorded = 0
+
+        def record(self):
+            FakeEvent.recorded += 1
+
+        def query(self):
+            return FakeEvent.done
+
+    monkeypatch.setattr(torch.cuda, "is_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "Event", FakeEvent)
+    fired = threading.Event()
+    FakeEvent.done = False
+    F.stream_timeout(fired.set, timedelta(milliseconds=30))
+    assert fired.wait(5) and FakeEvent.recorded == 1
+    fired.clear()
+    FakeEvent.done = True  # the stream finished in time
+    F.stream_timeout(fired.set, timedelta(milliseconds=30))
+    time.sleep(0.3)
+    assert not fired.is_set() and FakeEvent.recorded == 2
+    assert F._TIMEOUT_MANAGER._drain_del_queue() >= 1  # parked events are released by a later caller

@@ -390,3 +390,36 @@ print("localsgd ok")
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=240, env=dict(os.environ, PYTHONPATH=repo))
     assert r.returncode == 0 and "localsgd ok" in r.stdout and "ok flat= None" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
+
+
+def test_diloco_pseudo_gradient_is_what_the_outer_optimizer_sees():
+    """At a sync the outer optimizer steps on grad = (last synchronised weights - local weights), averaged by the
+    manager, applied to the last synchronised weights (torchft/local_sgd_test.py test_gradient_correctness)."""
+    seen = []
+
+    class Recording(optim.SGD):
+        def step(self, closure=None):
+            seen.append([(p.detach().clone(), p.grad.detach().clone()) for g in self.param_groups for p in g["params"]])
+            return super().step(closure)
+
+    torch.manual_seed(0)
+    model = TinyModel()
+    start = [p.detach().clone() for p in model.parameters()]
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    outer = Recording(model.parameters(), lr=0.5)
+    m = _delta_manager(factor=0.5)
+    g = torch.Generator().manual_seed(3)
+    with DiLoCo(m, [model], inner, outer, sync_every=2, flat_fragments=False):
+        local = None
+        for k in range(2):
+            inner.zero_grad()
+            model(torch.randn(4, 3, generator=g)).square().mean().backward()
+            if k == 1:  # what the local weights will be right before the sync
+                local = [p.detach() - 0.1 * p.grad for p in model.parameters()]
+            inner.step()
+    assert len(seen) == 1
+    for (p_at_step, grad), s0, l in zip(seen[0], start, local):
+        torch.testing.assert_close(p_at_step, s0)               # the outer step starts from the global weights
+        torch.testing.assert_close(grad, 0.5 * (s0 - l))         # pseudo-gradient, scaled by the (mock) average
+    for p, s0, l in zip(model.parameters(), start, local):
+        torch.testing.assert_close(p.detach(), s0 - 0.5 * 0.5 * (s0 - l))
