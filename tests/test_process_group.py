@@ -307,3 +307,18 @@ def test_baby_gloo_on_thread_backed_context(monkeypatch):
     finally:
         for pg in pgs:
             pg.shutdown()
+
+
+@pytest.mark.parametrize("cls", [ProcessGroupGloo, ProcessGroupBabyGloo])
+def test_configure_times_out_when_peers_never_arrive(cls):
+    """configure() for a world of two with nobody else joining gives up after the group's timeout instead of hanging
+    (torchft/process_group_test.py test_gloo_timeout / test_baby_gloo_timeout)."""
+    store = _store()
+    # the subprocess-backed group also needs time to start its child, so it gets a longer timeout
+    secs = 0.5 if cls is ProcessGroupGloo else 12.0
+    pg = cls(timeout=timedelta(seconds=secs))
+    t0 = time.time()
+    with pytest.raises(Exception):
+        pg.configure(f"localhost:{store.port}/lonely", "rep", 0, 2)
+    assert time.time() - t0 < secs + 20
+    pg.shutdown()
