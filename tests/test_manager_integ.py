@@ -40,8 +40,9 @@ def ddp_train_loop(rank: int, store_port: int, runner: Runner, total_steps: int 
         pg=pg, min_replica_size=1, load_state_dict=load_state_dict, state_dict=state_dict,
         replica_id=str(runner.replica_id), store_addr="localhost", store_port=store_port, rank=rank,
         world_size=runner.world_size, lighthouse_addr=runner.lighthouse_address, port=0,
-        timeout=timedelta(seconds=10), quorum_timeout=timedelta(seconds=20), connect_timeout=timedelta(seconds=10),
-        use_async_quorum=use_async_quorum, init_sync=init_sync, hostname="localhost", **runner.manager_args,
+        quorum_timeout=timedelta(seconds=20), connect_timeout=timedelta(seconds=10),
+        use_async_quorum=use_async_quorum, init_sync=init_sync, hostname="localhost",
+        **{"timeout": timedelta(seconds=10), **runner.manager_args},
     )
     try:
         m = DistributedDataParallel(manager, model)
@@ -148,6 +149,25 @@ def test_ddp_multi_rank_groups():
             r.train_loop = lambda rank, store_port, runner: ddp_train_loop(rank, store_port, runner, total_steps=4)
         res = run_replicas(runners)
         _assert_same(res)
+    finally:
+        lh.shutdown()
+
+
+def test_ddp_recovery_multi_rank_groups():
+    """Groups of two ranks: rank 0 of group 1 fails, the whole group restarts (its other rank runs into the commit
+    barrier's timeout), heals rank by rank from group 0 and all columns end identical
+    (torchft/manager_integ_test.py test_ddp_recovery_multi_rank)."""
+    lh = LighthouseServer("[::]:0", 1, join_timeout_ms=100, heartbeat_timeout_ms=1000)
+    try:
+        inj = EventInjector().fail_at(replica=1, step=4, rank=0).gate_until_rejoin(replica=0, step=6)
+        runners = [Runner(i, lh.address(), inj, None, world_size=2, manager_args={"timeout": timedelta(seconds=3)})  # type: ignore[arg-type]
+                   for i in range(2)]
+        for r in runners:
+            r.train_loop = lambda rank, store_port, runner: ddp_train_loop(rank, store_port, runner, total_steps=12)
+        res = run_replicas(runners)
+        assert inj.count == 1
+        _assert_same(res)
+        assert all(r[k]["step"] == 12 for r in res for k in range(2))
     finally:
         lh.shutdown()
 
