@@ -23,10 +23,24 @@ import struct
 from typing import IO, List, Optional, Tuple
 
 import torch
-from torch.utils._pytree import tree_flatten, tree_unflatten
+from torch.utils._pytree import TreeSpec, tree_flatten, tree_unflatten, treespec_dumps, treespec_loads
 
 MAGIC = b"FTB2SD01"
 _CHUNK = 64 << 20  # upper bound of one write / readinto call
+
+
+def pack_treespec(spec: TreeSpec) -> object:
+    """A tree spec in the form it travels in: torch's JSON form for the standard containers (stable across torch
+    versions), the object itself (to be pickled) for specs that contain types without a registered serialiser."""
+    try:
+        return ("json", treespec_dumps(spec))
+    except Exception:
+        return ("obj", spec)
+
+
+def unpack_treespec(packed: object) -> TreeSpec:
+    kind, value = packed  # type: ignore[misc]
+    return treespec_loads(value) if kind == "json" else value
 
 
 def _is_plain_tensor(x: object) -> bool:
@@ -60,7 +74,7 @@ def streaming_save(obj: object, f: IO[bytes]) -> None:
             metas.append(("S", buf.getvalue()))
         else:
             metas.append(("O", leaf))
-    header = pickle.dumps((spec, metas), protocol=pickle.HIGHEST_PROTOCOL)
+    header = pickle.dumps((pack_treespec(spec), metas), protocol=pickle.HIGHEST_PROTOCOL)
     f.write(MAGIC + struct.pack("<Q", len(header)))
     f.write(header)
     for t in tensors:
@@ -107,7 +121,8 @@ def streaming_load(f: IO[bytes], into: Optional[List[object]] = None) -> object:
     if head[: len(MAGIC)] != MAGIC:
         raise ValueError("not a torchft_b200 state-dict stream")
     (hlen,) = struct.unpack("<Q", head[len(MAGIC) :])
-    spec, metas = pickle.loads(_read_exact(f, hlen))
+    packed_spec, metas = pickle.loads(_read_exact(f, hlen))
+    spec = unpack_treespec(packed_spec)
     leaves: List[object] = []
     for i, m in enumerate(metas):
         if m[0] == "T":

@@ -18,9 +18,9 @@ from __future__ import annotations
 
 import io
 import logging
-import time
 import socket
 import threading
+import time
 import urllib.request
 from concurrent.futures import ThreadPoolExecutor
 from datetime import timedelta
@@ -31,7 +31,7 @@ import torch
 from torch.utils._pytree import TreeSpec, tree_flatten, tree_unflatten
 
 from ._rwlock import RWLock
-from ._serialization import streaming_load, streaming_save
+from ._serialization import pack_treespec, streaming_load, streaming_save, unpack_treespec
 from .transport import CheckpointTransport
 
 logger = logging.getLogger(__name__)
@@ -119,7 +119,7 @@ class HTTPTransport(CheckpointTransport[T], Generic[T]):
                         if key == "full":
                             self._reply(transport._state)
                         elif key == "metadata":
-                            self._reply(transport._spec)
+                            self._reply(pack_treespec(transport._spec))
                         else:
                             assert transport._chunks is not None, "checkpoint was not staged in chunks"
                             self._reply(transport._chunks[int(key)])
@@ -201,7 +201,7 @@ class HTTPTransport(CheckpointTransport[T], Generic[T]):
             into, _ = tree_flatten(self._state_dict_fn())
         if self._num_chunks == 0:
             return self._fetch(f"{base}/full", timeout, into)  # type: ignore[return-value]
-        spec = self._fetch(f"{base}/metadata", timeout)
+        spec = unpack_treespec(self._fetch(f"{base}/metadata", timeout))
         n_chunks = self._num_chunks
         with ThreadPoolExecutor(max_workers=n_chunks, thread_name_prefix="torchft_b200_ckpt_fetch") as ex:
             chunks = list(ex.map(lambda i: self._fetch(f"{base}/{i}", timeout, into[i::n_chunks] if into is not None else None),

@@ -20,8 +20,9 @@ from datetime import timedelta
 from typing import Callable, Generator, Generic, List, Optional, Tuple, TypeVar, Union
 
 import torch
-from torch.utils._pytree import TreeSpec, tree_flatten, tree_unflatten
+from torch.utils._pytree import tree_flatten, tree_unflatten
 
+from ._serialization import pack_treespec, unpack_treespec
 from .transport import CheckpointTransport
 
 try:
@@ -48,7 +49,7 @@ class _TensorLeaf:
 @dataclass
 class _Header:
     step: int
-    treespec: TreeSpec
+    treespec: object  # packed with _serialization.pack_treespec
     leaves: List[Union[_TensorLeaf, object]] = field(default_factory=list)  # _TensorLeaf or the literal leaf
     is_tensor: List[bool] = field(default_factory=list)
 
@@ -93,7 +94,7 @@ class PGTransport(CheckpointTransport[T], Generic[T]):
     def send_checkpoint(self, dst_ranks: List[int], step: int, state_dict: T, timeout: timedelta) -> None:
         with _timed("preparing state_dict"):
             leaves, spec = tree_flatten(state_dict)
-            hdr = _Header(step=step, treespec=spec)
+            hdr = _Header(step=step, treespec=pack_treespec(spec))
             payloads: List[torch.Tensor] = []
             for v in leaves:
                 if isinstance(v, torch.Tensor):
@@ -201,4 +202,4 @@ class PGTransport(CheckpointTransport[T], Generic[T]):
             if len(pending) >= _RECV_WINDOW or staged[0] >= _RECV_WINDOW_BYTES:
                 drain()
         drain()
-        return tree_unflatten(out, hdr.treespec)
+        return tree_unflatten(out, unpack_treespec(hdr.treespec))
