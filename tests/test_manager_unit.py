@@ -400,3 +400,34 @@ def test_state_dict_lock_concurrent_readers_and_writer(h):
     for t in ts:
         t.join(5)
     assert order[0] == ("write",) and sorted(o[1] for o in order[1:]) == [0, 1]
+
+
+def test_managed_future_chain_may_change_types_and_failures_are_latched(h):
+    """Each callback receives what the previous one returned (tensor -> float -> str); a callback that raises does
+    not raise out of wait(): the error is latched and the future resolves to the default
+    (torchft/_test/managed_work_test.py test_callbacks_changing_return_types)."""
+    h.client._quorum.return_value = quorum()
+    h.client.should_commit.side_effect = lambda rank, step, vote, timeout: vote
+    m = h.manager
+    m.start_quorum()
+    t = torch.tensor([6.0])
+    work = m.allreduce(t)
+    seen = []
+    fut = work.get_future().then(lambda f: float(f.value()[0].item() if not isinstance(f.value(), torch.Tensor) else f.value().item()))
+    fut = fut.then(lambda f: seen.append(f.value()) or f"value={f.value()}")
+    fut = fut.then(lambda f: seen.append(f.value()) or len(f.value()))
+    assert seen == []
+    work.wait()
+    assert fut.wait() == len("value=3.0") and seen == [3.0, "value=3.0"]
+    assert m.errored() is None
+
+    work = m.allreduce(torch.tensor([1.0]))
+
+    def boom(f):
+        raise ValueError("callback failed")
+
+    fut = work.get_future().then(boom)
+    work.wait()
+    fut.wait()  # does not raise
+    assert "callback failed" in str(m.errored())
+    assert not m.should_commit()
