@@ -139,3 +139,27 @@ def test_stream_timeout_logic_with_a_fake_event(monkeypatch):
     time.sleep(0.3)
     assert not fired.is_set() and FakeEvent.recorded == 2
     assert F._TIMEOUT_MANAGER._drain_del_queue() >= 1  # parked events are released by a later caller
+
+
+def test_timer_wakes_for_earlier_deadlines_and_sweeps_cancelled_timers():
+    """A timer armed after a later one still fires on time (the timer thread is woken because the new deadline is the
+    earliest), and cancelled timers do not pile up in the heap."""
+    import threading
+    import time
+    from datetime import timedelta
+
+    from torchft_b200 import futures as F
+
+    tm = F._TIMEOUT_MANAGER
+    late, early = threading.Event(), threading.Event()
+    h_late = tm.call_later(timedelta(seconds=30), late.set)
+    t0 = time.monotonic()
+    tm.call_later(timedelta(milliseconds=50), early.set)
+    assert early.wait(2) and time.monotonic() - t0 < 1.0
+    assert not late.is_set()
+    h_late.cancel()
+    handles = [tm.call_later(timedelta(seconds=60), lambda: None) for _ in range(F._COMPACT_ABOVE + 200)]
+    for h in handles:
+        h.cancel()
+    tm.call_later(timedelta(seconds=60), lambda: None).cancel()  # this push sweeps the cancelled ones
+    assert len(tm._heap) < 300

@@ -32,6 +32,9 @@ T = TypeVar("T")
 WATCHDOG_TIMEOUT_SEC = "TORCHFT_WATCHDOG_TIMEOUT_SEC"
 
 
+_COMPACT_ABOVE = 4096  # timers in the heap above which cancelled ones are swept out
+
+
 class _TimerHandle:
     __slots__ = ("_cancelled", "_lock")
 
@@ -141,9 +144,19 @@ class _TimeoutManager:
         self._ensure_started()
         self._drain_del_queue()
         handle = _TimerHandle()
+        deadline = time.monotonic() + timeout.total_seconds()
         with self._cond:
-            heapq.heappush(self._heap, (time.monotonic() + timeout.total_seconds(), next(self._seq), handle, cb))
-            self._cond.notify_all()
+            # the timer thread only has to be woken when this deadline becomes the earliest one: almost every timer
+            # is cancelled long before it is due, and a wake-up per armed timer is a context switch per collective
+            wake = not self._heap or deadline < self._heap[0][0]
+            heapq.heappush(self._heap, (deadline, next(self._seq), handle, cb))
+            if len(self._heap) > _COMPACT_ABOVE:
+                live = [e for e in self._heap if not e[2]._cancelled]
+                if len(live) < len(self._heap) // 2:  # cancelled timers otherwise stay until their deadline
+                    heapq.heapify(live)
+                    self._heap = live
+            if wake:
+                self._cond.notify_all()
         return handle
 
     def register(self, fut: Future, timeout: timedelta) -> Future:
