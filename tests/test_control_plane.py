@@ -596,3 +596,32 @@ print("survived", cases)
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=280, env=dict(os.environ, PYTHONPATH=repo))
     assert r.returncode == 0 and "survived" in r.stdout, f"rc={r.returncode}\n{r.stdout[-1500:]}\n{r.stderr[-3000:]}"
+
+
+def test_lighthouse_metrics_endpoint():
+    """GET /metrics: Prometheus text exposition of the quorum state (an addition; the reference exposes no metrics)."""
+    from torchft_b200.coordination import LighthouseClient, LighthouseServer
+
+    lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=50)
+    try:
+        port = lh.address().rsplit(":", 1)[1]
+        cl = LighthouseClient(f"http://127.0.0.1:{port}", timedelta(seconds=5))
+        cl.quorum(replica_id="m0", timeout=timedelta(seconds=5), step=7)
+        cl.heartbeat('odd"name')  # afterwards: a second heartbeating replica that never joins would block the quorum
+        text = urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5).read().decode()
+        values = {}
+        for line in text.splitlines():
+            if line and not line.startswith("#"):
+                name, value = line.rsplit(" ", 1)
+                values[name] = float(value)
+        assert values["torchft_lighthouse_quorum_id"] == 1
+        assert values["torchft_lighthouse_quorum_participants"] == 1
+        assert values["torchft_lighthouse_quorums_issued_total"] == 1
+        assert values["torchft_lighthouse_quorum_requests_total"] == 1
+        assert values["torchft_lighthouse_heartbeats_total"] == 1
+        assert values["torchft_lighthouse_healthy_replicas"] == 2
+        assert values['torchft_lighthouse_replica_step{replica="m0"}'] == 7
+        assert values['torchft_lighthouse_heartbeat_age_seconds{replica="odd\\"name"}'] < 5
+        assert "# TYPE torchft_lighthouse_quorums_issued_total counter" in text
+    finally:
+        lh.shutdown()

@@ -82,7 +82,20 @@ void Lighthouse::tick_loop() {
   }
 }
 
+// Replica ids are fresh on every process start, so a long job with many restarts would otherwise collect an
+// unbounded number of dead entries.  Entries stay long enough for the dashboard to show them as stale.
+void Lighthouse::prune_heartbeats_locked(TimePoint now) {
+  const auto keep = std::max<int64_t>(600000, 100 * static_cast<int64_t>(opt_.heartbeat_timeout_ms));
+  for (auto it = state_.heartbeats.begin(); it != state_.heartbeats.end();) {
+    if (now - it->second > Millis(keep) && state_.participants.find(it->first) == state_.participants.end())
+      it = state_.heartbeats.erase(it);
+    else
+      ++it;
+  }
+}
+
 void Lighthouse::tick_locked() {
+  if ((++ticks_ & 1023) == 0) prune_heartbeats_locked(Clock::now());
   auto [members, reason] = quorum_compute(Clock::now(), state_, opt_);
   if (reason != last_reason_) {
     log_info("lighthouse", "Quorum status: " + reason);
@@ -115,6 +128,7 @@ void Lighthouse::tick_locked() {
 Quorum Lighthouse::handle_quorum(const QuorumMember& requester, TimePoint deadline) {
   std::unique_lock<std::mutex> lk(mu_);
   const std::string& id = requester.replica_id;
+  ++quorum_requests_;
   log_info("lighthouse", "Received quorum request for replica " + id);
   auto join = [&] {
     const TimePoint now = Clock::now();
@@ -143,6 +157,7 @@ Quorum Lighthouse::handle_quorum(const QuorumMember& requester, TimePoint deadli
 
 void Lighthouse::handle_heartbeat(const std::string& replica_id) {
   std::lock_guard<std::mutex> g(mu_);
+  ++heartbeats_received_;
   state_.heartbeats[replica_id] = Clock::now();
 }
 
@@ -203,6 +218,59 @@ std::string Lighthouse::render_status() {
   return o.str();
 }
 
+namespace {
+std::string label_escape(const std::string& v) {
+  std::string o;
+  for (char c : v) {
+    if (c == '\\' || c == '"') o += '\\';
+    if (c == '\n') {
+      o += "\\n";
+      continue;
+    }
+    o += c;
+  }
+  return o;
+}
+}  // namespace
+
+std::string Lighthouse::render_metrics() {
+  std::lock_guard<std::mutex> g(mu_);
+  const TimePoint now = Clock::now();
+  size_t healthy = 0;
+  for (const auto& [id, last] : state_.heartbeats)
+    if (now - last < Millis(opt_.heartbeat_timeout_ms)) ++healthy;
+  std::ostringstream o;
+  auto gauge = [&](const char* name, const char* help, double v) {
+    o << "# HELP " << name << ' ' << help << "\n# TYPE " << name << " gauge\n" << name << ' ' << v << "\n";
+  };
+  auto counter = [&](const char* name, const char* help, uint64_t v) {
+    o << "# HELP " << name << ' ' << help << "\n# TYPE " << name << " counter\n" << name << ' ' << v << "\n";
+  };
+  gauge("torchft_lighthouse_quorum_id", "Identifier of the latest quorum.", static_cast<double>(state_.quorum_id));
+  gauge("torchft_lighthouse_quorum_participants", "Replica groups in the latest quorum.",
+        state_.prev_quorum ? static_cast<double>(state_.prev_quorum->participants.size()) : 0.0);
+  gauge("torchft_lighthouse_pending_participants", "Replica groups that have asked for the next quorum.",
+        static_cast<double>(state_.participants.size()));
+  gauge("torchft_lighthouse_healthy_replicas", "Replica groups with a heartbeat younger than the timeout.",
+        static_cast<double>(healthy));
+  gauge("torchft_lighthouse_known_replicas", "Replica ids with a recorded heartbeat.", static_cast<double>(state_.heartbeats.size()));
+  counter("torchft_lighthouse_quorums_issued_total", "Quorums issued since start.", seq_);
+  counter("torchft_lighthouse_quorum_requests_total", "Quorum requests received since start.", quorum_requests_);
+  counter("torchft_lighthouse_heartbeats_total", "Explicit heartbeats received since start.", heartbeats_received_);
+  if (state_.prev_quorum) {
+    o << "# HELP torchft_lighthouse_replica_step Step reported by each member of the latest quorum.\n"
+      << "# TYPE torchft_lighthouse_replica_step gauge\n";
+    for (const auto& p : state_.prev_quorum->participants)
+      o << "torchft_lighthouse_replica_step{replica=\"" << label_escape(p.replica_id) << "\"} " << p.step << "\n";
+  }
+  o << "# HELP torchft_lighthouse_heartbeat_age_seconds Seconds since each replica was last heard from.\n"
+    << "# TYPE torchft_lighthouse_heartbeat_age_seconds gauge\n";
+  for (const auto& [id, last] : state_.heartbeats)
+    o << "torchft_lighthouse_heartbeat_age_seconds{replica=\"" << label_escape(id) << "\"} "
+      << std::chrono::duration<double>(now - last).count() << "\n";
+  return o.str();
+}
+
 HttpResponse Lighthouse::http(const HttpRequest& req) {
   HttpResponse resp;
   if (req.method == "GET" && (req.path == "/" || req.path == "/index.html")) {
@@ -211,6 +279,11 @@ HttpResponse Lighthouse::http(const HttpRequest& req) {
   }
   if (req.method == "GET" && req.path == "/status") {
     resp.body = render_status();
+    return resp;
+  }
+  if (req.method == "GET" && req.path == "/metrics") {
+    resp.body = render_metrics();
+    resp.content_type = "text/plain; version=0.0.4";
     return resp;
   }
   const std::string prefix = "/replica/", suffix = "/kill";

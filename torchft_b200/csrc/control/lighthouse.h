@@ -34,6 +34,8 @@ class Lighthouse {
   void tick_locked();
   void tick_loop();
   std::string render_status();
+  std::string render_metrics();  // Prometheus text exposition, served at /metrics
+  void prune_heartbeats_locked(TimePoint now);
 
   LighthouseOpt opt_;
   std::mutex mu_;
@@ -41,6 +43,9 @@ class Lighthouse {
   LighthouseState state_;
   std::deque<std::pair<uint64_t, Quorum>> history_;  // recently issued quorums (seq, quorum)
   uint64_t seq_ = 0;
+  uint64_t quorum_requests_ = 0;  // counters for /metrics
+  uint64_t heartbeats_received_ = 0;
+  uint64_t ticks_ = 0;
   std::string last_reason_;
   bool stop_ = false;
   std::unique_ptr<Server> server_;
