@@ -3,6 +3,7 @@ replica group (train_ddp.py / train_diloco.py in the reference are started the s
 README.md "Example Training Loop (DDP)").  CPU, Gloo."""
 
 import os
+import socket
 import subprocess
 import sys
 import threading
@@ -17,7 +18,14 @@ from torchft_b200.coordination import LighthouseServer
 REPO = Path(__file__).resolve().parent.parent
 
 
-def _launch(script: str, group: int, lighthouse: str, port: int, **env) -> subprocess.Popen:
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _launch(script: str, group: int, lighthouse: str, port: int = 0, **env) -> subprocess.Popen:
+    port = port or _free_port()
     full = dict(os.environ, TORCHFT_LIGHTHOUSE=lighthouse, REPLICA_GROUP_ID=str(group), NUM_REPLICA_GROUPS="2",
                 PYTHONPATH=str(REPO), OMP_NUM_THREADS="2", **env)  # two trainers share the cores: no oversubscription
     return subprocess.Popen(
@@ -56,7 +64,7 @@ def _finish(p: subprocess.Popen, timeout: float = 240) -> str:
 def test_train_ddp_two_groups_cpu():
     lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=1000)
     try:
-        procs = [_launch("train_ddp.py", g, lh.address(), 29720 + g, STEPS="6") for g in range(2)]
+        procs = [_launch("train_ddp.py", g, lh.address(), STEPS="6") for g in range(2)]
         outs = [_finish(p) for p in procs]
         for p, out in zip(procs, outs):
             assert p.returncode == 0, out[-3000:]
@@ -108,12 +116,12 @@ def test_train_ddp_restarted_group_heals_cpu():
     steps = 1500
     t0 = t1 = t1b = None
     try:
-        t0 = _Tail(_launch("train_ddp.py", 0, lh.address(), 29730, STEPS=str(steps)))
-        t1 = _Tail(_launch("train_ddp.py", 1, lh.address(), 29731, STEPS=str(steps)))
+        t0 = _Tail(_launch("train_ddp.py", 0, lh.address(), STEPS=str(steps)))
+        t1 = _Tail(_launch("train_ddp.py", 1, lh.address(), STEPS=str(steps)))
         t1.wait_for_count("should_commit=True", 20, 120)  # (it may have healed past any particular step number)
         _kill_tree(t1.p.pid)
         t1.p.wait()
-        t1b = _Tail(_launch("train_ddp.py", 1, lh.address(), 29732, STEPS=str(steps)))
+        t1b = _Tail(_launch("train_ddp.py", 1, lh.address(), STEPS=str(steps)))
         out0, out1 = t0.finish(600), t1b.finish(600)
         assert t0.p.returncode == 0, out0[-3000:]
         assert t1b.p.returncode == 0, out1[-3000:]
@@ -135,7 +143,7 @@ def test_train_ddp_restarted_group_heals_cpu():
 def test_train_diloco_two_groups_cpu(streaming):
     lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=1000)
     try:
-        procs = [_launch("train_diloco.py", g, lh.address(), 29740 + g + 4 * int(streaming), STEPS="45", USE_STREAMING=streaming)
+        procs = [_launch("train_diloco.py", g, lh.address(), STEPS="45", USE_STREAMING=streaming)
                  for g in range(2)]
         outs = [_finish(p) for p in procs]
         for p, out in zip(procs, outs):
@@ -154,7 +162,7 @@ def test_runner_and_punisher_with_real_trainers(tmp_path):
 
     pid_file, logs = str(tmp_path / "pids.json"), tmp_path / "logs"
     steps = 1500
-    runner = Runner([str(REPO / "train_ddp.py")], num_groups=2, base_port=29760, max_restarts=3, pid_file=pid_file,
+    runner = Runner([str(REPO / "train_ddp.py")], num_groups=2, base_port=_free_port(), max_restarts=3, pid_file=pid_file,
                     poll_secs=0.2, log_dir=str(logs), extra_env={"STEPS": str(steps), "OMP_NUM_THREADS": "2", "PYTHONPATH": str(REPO)})
     result = {}
     th = threading.Thread(target=lambda: result.setdefault("rc", runner.run()), daemon=True)
