@@ -3,6 +3,7 @@ replica group (train_ddp.py / train_diloco.py in the reference are started the s
 README.md "Example Training Loop (DDP)").  CPU, Gloo."""
 
 import os
+import random
 import socket
 import subprocess
 import sys
@@ -18,14 +19,24 @@ from torchft_b200.coordination import LighthouseServer
 REPO = Path(__file__).resolve().parent.parent
 
 
-def _free_port() -> int:
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        return s.getsockname()[1]
+def _free_port_pair() -> int:
+    """A port P below the ephemeral range such that P and P+1 can both be bound right now (the runner gives group g
+    the port base+g; ports inside the ephemeral range can be taken by an outgoing connection at any moment)."""
+    rnd = random.Random(os.getpid() ^ int(time.time() * 1000))
+    for _ in range(200):
+        p = rnd.randrange(20000, 30000, 2)
+        try:
+            with socket.socket() as a, socket.socket() as b:
+                a.bind(("127.0.0.1", p))
+                b.bind(("127.0.0.1", p + 1))
+            return p
+        except OSError:
+            continue
+    raise RuntimeError("no free port pair found")
 
 
 def _launch(script: str, group: int, lighthouse: str, port: int = 0, **env) -> subprocess.Popen:
-    port = port or _free_port()
+    port = port or _free_port_pair()
     full = dict(os.environ, TORCHFT_LIGHTHOUSE=lighthouse, REPLICA_GROUP_ID=str(group), NUM_REPLICA_GROUPS="2",
                 PYTHONPATH=str(REPO), OMP_NUM_THREADS="2", **env)  # two trainers share the cores: no oversubscription
     return subprocess.Popen(
@@ -162,7 +173,7 @@ def test_runner_and_punisher_with_real_trainers(tmp_path):
 
     pid_file, logs = str(tmp_path / "pids.json"), tmp_path / "logs"
     steps = 1500
-    runner = Runner([str(REPO / "train_ddp.py")], num_groups=2, base_port=_free_port(), max_restarts=3, pid_file=pid_file,
+    runner = Runner([str(REPO / "train_ddp.py")], num_groups=2, base_port=_free_port_pair(), max_restarts=3, pid_file=pid_file,
                     poll_secs=0.2, log_dir=str(logs), extra_env={"STEPS": str(steps), "OMP_NUM_THREADS": "2", "PYTHONPATH": str(REPO)})
     result = {}
     th = threading.Thread(target=lambda: result.setdefault("rc", runner.run()), daemon=True)
