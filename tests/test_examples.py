@@ -219,3 +219,28 @@ def test_runner_and_punisher_with_real_trainers(tmp_path):
         for gp in runner._groups:
             if gp.proc is not None:
                 _kill_tree(gp.proc.pid)
+
+
+@pytest.mark.timeout(600)
+def test_train_hsdp_cpu_with_durable_checkpoint_resume(tmp_path):
+    """train_hsdp.py on CPU (Gloo): two replica groups of two shard ranks under one torchrun; the job writes durable
+    checkpoints, is started again and resumes from the newest complete one."""
+    ckpt = tmp_path / "ckpt"
+
+    def run(steps):
+        port = _free_port_pair()
+        env = dict(os.environ, PYTHONPATH=str(REPO), OMP_NUM_THREADS="1")
+        return subprocess.run(
+            [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "4", "--master-addr", "127.0.0.1",
+             "--master-port", str(port), str(REPO / "train_hsdp.py"), "--model", "llama-tiny", "--seq-len", "16", "--steps", str(steps),
+             "--replica-groups", "2", "--ckpt-dir", str(ckpt), "--ckpt-every", "5"],
+            cwd=REPO, env=env, capture_output=True, text=True, timeout=280)
+
+    r = run(10)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "participants 2" in r.stdout
+    done = sorted(p.name for p in ckpt.iterdir())
+    assert "step_00000010" in done and all((ckpt / "step_00000010" / f"rank_{k}.pt").is_file() for k in range(2))
+    r = run(15)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    assert "resumed from step 10" in r.stdout and "step 10 loss" in r.stdout and "step 0 loss" not in r.stdout

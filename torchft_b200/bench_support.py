@@ -37,9 +37,9 @@ def make_ft_manager(rank: int, world: int, n_groups: int, shard: int, group_id: 
                     device: torch.device, arena_bytes: int = 1 << 30, min_replica_size: Optional[int] = None,
                     timeout: timedelta = timedelta(seconds=120), use_async_quorum: bool = True,
                     checkpoint_transport=None) -> Tuple[Optional[LighthouseServer], Manager]:
-    """Returns ``(lighthouse or None, manager)``.  All ranks of the job must call this."""
-    from .parallel.team import ProcessGroupB200
-
+    """Returns ``(lighthouse or None, manager)``.  All ranks of the job must call this.  On a CUDA device the
+    replica dimension is a :class:`ProcessGroupB200` (NVLink peer memory); on CPU it is Gloo, which lets the same
+    scripts run without GPUs."""
     lighthouse = None
     addr = [None]
     if rank == 0:
@@ -52,7 +52,14 @@ def make_ft_manager(rank: int, world: int, n_groups: int, shard: int, group_id: 
 
     store, base_port = open_group_store(world, group_id, group_rank)
 
-    pg = ProcessGroupB200(timeout=timeout, arena_bytes=arena_bytes, device=device)
+    if device.type == "cuda":
+        from .parallel.team import ProcessGroupB200
+
+        pg = ProcessGroupB200(timeout=timeout, arena_bytes=arena_bytes, device=device)
+    else:
+        from .process_group import ProcessGroupGloo
+
+        pg = ProcessGroupGloo(timeout=timeout)
     manager = Manager(
         pg=pg,
         load_state_dict=None,

@@ -13,7 +13,8 @@ its ranks and they heal from a surviving group over NVLink.  ``--ckpt-dir D --ck
 a durable checkpoint every N committed steps (replica group 0 only: the groups hold identical
 state) and resumes from the newest complete one when the whole job is started again.
 The reference reaches the same layout through torchtitan + torchft; here the trainer is
-part of the framework (:mod:`torchft_b200.parallel.hsdp`).
+part of the framework (:mod:`torchft_b200.parallel.hsdp`).  Without a GPU the same script runs on CPU
+over Gloo (use ``--model llama-tiny --seq-len 16``), which is how the test suite exercises it.
 """
 
 import argparse
@@ -48,26 +49,35 @@ def main() -> None:
     a = ap.parse_args()
 
     rank, world, local = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1)), int(os.environ.get("LOCAL_RANK", 0))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
+    use_cuda = torch.cuda.is_available()
+    if use_cuda:
+        torch.cuda.set_device(local)
+    dev = torch.device("cuda", local) if use_cuda else torch.device("cpu")  # CPU: Gloo everywhere, for trying things out
     cfg = CONFIGS[a.model]
     n_groups = min(a.replica_groups, world)
     shard = world // n_groups
     group_id, group_rank = rank // shard, rank % shard
     shard_comm = LocalShardComm()
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        if use_cuda:
+            dist.init_process_group("nccl", device_id=dev)
+        else:
+            dist.init_process_group("gloo")
         groups = [dist.new_group(list(range(g * shard, (g + 1) * shard))) for g in range(n_groups)]
-        if shard > 1:
+        if shard > 1 and use_cuda:
             from torchft_b200.parallel.team import PeerShardComm
 
             pbytes = sum(cfg.unit_numel(u) for u in range(cfg.n_units)) * 2
             shard_comm = PeerShardComm(groups[group_id], dev, arena_bytes=pbytes // shard + (5 << 30))
+        elif shard > 1:
+            from torchft_b200.parallel.shard_comm import TorchShardComm
+
+            shard_comm = TorchShardComm(groups[group_id])
     grad_bytes = sum(cfg.unit_numel(u) for u in range(cfg.n_units)) * 2 // shard
     lighthouse, manager = make_ft_manager(rank, world, n_groups, shard, group_id, group_rank, dev,
                                           arena_bytes=grad_bytes + (64 << 20), min_replica_size=1)
     trainer = ShardedLlamaTrainer(cfg, a.micro_batch, a.seq_len, dev, shard_comm=shard_comm, manager=manager, lr=a.lr,
-                                  replica_alloc=manager._pg.alloc if n_groups > 1 else None)
+                                  replica_alloc=manager._pg.alloc if n_groups > 1 and use_cuda else None)
     manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 
     g = torch.Generator().manual_seed(1234 + rank)
@@ -93,7 +103,8 @@ def main() -> None:
         if rank == 0 and step % 5 == 0:
             print(f"step {step} loss {loss.item():.4f} participants {manager.num_participants()} "
                   f"{(time.time() - t0):.1f}s", flush=True)
-    K.check_status(dev)
+    if use_cuda:
+        K.check_status(dev)
     manager.shutdown(wait=False)
     if lighthouse is not None:
         lighthouse.shutdown()
