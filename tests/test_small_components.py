@@ -299,3 +299,26 @@ def test_thread_backed_mp_context_pipe_and_process():
     with pytest.raises((EOFError, OSError)):
         a.recv()
     assert isinstance(ctx.Lock(), type(threading.Lock())) and ctx.Queue().empty() and not ctx.Event().is_set()
+
+
+def test_optimizer_wrapper_reports_commit_and_works_with_lr_schedulers():
+    manager = create_autospec(Manager, instance=True)
+    model = nn.Linear(2, 2)
+    inner = optim.SGD(model.parameters(), lr=1.0)
+    opt = OptimizerWrapper(manager, inner)
+    assert opt.last_step_committed is None and "SGD" in repr(opt)
+    sched = torch.optim.lr_scheduler.StepLR(opt, step_size=1, gamma=0.5)  # schedulers accept the wrapper
+    for commit in (True, False, True):
+        manager.should_commit.return_value = commit
+        opt.zero_grad()
+        model(torch.ones(1, 2)).sum().backward()
+        opt.step()
+        assert opt.last_step_committed is commit
+        sched.step()
+    assert inner.param_groups[0]["lr"] == 0.125 and opt.defaults is inner.defaults
+    seen = []
+    handle = opt.register_step_post_hook(lambda o, a, k: seen.append(type(o).__name__))  # hooks live on the real optimizer
+    manager.should_commit.return_value = True
+    opt.step()
+    handle.remove()
+    assert seen == ["SGD"]
