@@ -34,19 +34,26 @@ class DistributedDataParallel(parallel.DistributedDataParallel):
     """
 
     def __init__(self, manager: "Manager", module: nn.Module, **kwargs: object) -> None:
-        pg = ProcessGroupDummy(0, 1)
-        super().__init__(module, process_group=pg, find_unused_parameters=True, **kwargs)  # type: ignore[arg-type]
-        self.register_comm_hook(manager, self._comm_hook)
+        if "process_group" in kwargs or "find_unused_parameters" in kwargs:
+            raise TypeError("process_group and find_unused_parameters are fixed by the fault-tolerant wrapper")
+        super().__init__(
+            module,
+            process_group=ProcessGroupDummy(0, 1),  # swallows construction-time collectives
+            find_unused_parameters=True,  # keeps the bucket layout fixed, see above
+            **kwargs,  # type: ignore[arg-type]
+        )
+        self.register_comm_hook(manager, _average_bucket)
 
-    @staticmethod
-    def _comm_hook(state: "Manager", bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
-        work = state.allreduce(bucket.buffer())
-        work.wait()
-        fut = work.get_future()
-        # the reducer needs a plain torch future resolving to the bucket tensor
-        out: torch.futures.Future[torch.Tensor] = torch.futures.Future()
-        out.set_result(bucket.buffer())
-        return out
+
+def _average_bucket(manager: "Manager", bucket: dist.GradBucket) -> torch.futures.Future[torch.Tensor]:
+    """DDP communication hook: average one gradient bucket over the participating replica groups.  The manager's
+    work is waited here (errors are latched inside the manager, never raised), and the reducer gets an already
+    completed plain future holding the bucket."""
+    flat = bucket.buffer()
+    manager.allreduce(flat).wait()
+    done: torch.futures.Future[torch.Tensor] = torch.futures.Future()
+    done.set_result(flat)
+    return done
 
 
 class PureDistributedDataParallel(nn.Module):
@@ -57,13 +64,16 @@ class PureDistributedDataParallel(nn.Module):
     def __init__(self, manager: "Manager", module: nn.Module) -> None:
         super().__init__()
         self.module = module
+        self._hooks = [p.register_post_accumulate_grad_hook(self._make_hook(manager)) for p in module.parameters()]
 
-        def post_grad_hook(p: torch.Tensor) -> None:
-            if p.grad is not None:
-                manager.allreduce(p.grad).wait()
+    @staticmethod
+    def _make_hook(manager: "Manager"):
+        def average(param: torch.Tensor) -> None:
+            grad = param.grad
+            if grad is not None:
+                manager.allreduce(grad).wait()
 
-        for p in module.parameters():
-            p.register_post_accumulate_grad_hook(post_grad_hook)
+        return average
 
-    def forward(self, *args: object) -> object:
-        return self.module(*args)
+    def forward(self, *args: object, **kwargs: object) -> object:
+        return self.module(*args, **kwargs)

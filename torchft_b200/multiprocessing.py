@@ -3,32 +3,35 @@
 from __future__ import annotations
 
 from datetime import timedelta
-from multiprocessing.connection import Connection
 from typing import Union
 
 
-class _MonitoredPipe:
-    """Wraps a ``multiprocessing`` connection: ``recv`` gives up with ``TimeoutError``
-    after a deadline and re-raises exceptions that the peer sent as payload
-    (role of torchft/multiprocessing.py:10-32)."""
+def _seconds(t: Union[float, timedelta]) -> float:
+    return t.total_seconds() if isinstance(t, timedelta) else float(t)
 
-    def __init__(self, pipe: "Connection[object, object]") -> None:
+
+class _MonitoredPipe:
+    """One end of a ``multiprocessing`` pipe (or anything with ``send/recv/poll/close``) whose ``recv`` gives up
+    with ``TimeoutError`` after a deadline and re-raises exceptions that the peer sent as payload, so that a
+    child's failure surfaces in the parent as the same exception (role of torchft/multiprocessing.py:10-32)."""
+
+    def __init__(self, pipe) -> None:
         self._pipe = pipe
 
     def send(self, obj: object) -> None:
         self._pipe.send(obj)
 
     def recv(self, timeout: Union[float, timedelta]) -> object:
-        secs = timeout.total_seconds() if isinstance(timeout, timedelta) else float(timeout)
-        if not self._pipe.poll(secs):
-            raise TimeoutError(f"pipe.recv() timed out after {secs} seconds")
-        out = self._pipe.recv()
-        if isinstance(out, Exception):
-            raise out
-        return out
+        wait = _seconds(timeout)
+        if not self._pipe.poll(wait):
+            raise TimeoutError(f"pipe.recv() timed out after {wait} seconds")
+        payload = self._pipe.recv()
+        if isinstance(payload, BaseException):
+            raise payload
+        return payload
 
     def close(self) -> None:
         self._pipe.close()
 
     def closed(self) -> bool:
-        return self._pipe.closed
+        return bool(self._pipe.closed)
