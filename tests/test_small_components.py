@@ -322,3 +322,44 @@ def test_optimizer_wrapper_reports_commit_and_works_with_lr_schedulers():
     opt.step()
     handle.remove()
     assert seen == ["SGD"]
+
+
+def test_extension_stub_matches_the_module():
+    """torchft_b200/_ftcp.pyi names exactly the classes, methods, attributes and functions the extension module has,
+    with the same parameter names."""
+    import ast
+    import inspect
+    import re
+    from pathlib import Path
+
+    from torchft_b200 import _ftcp as C
+
+    tree = ast.parse((Path(C.__file__).parent / "_ftcp.pyi").read_text())
+    stub_classes = {n.name: n for n in tree.body if isinstance(n, ast.ClassDef)}
+    stub_funcs = {n.name: n for n in tree.body if isinstance(n, ast.FunctionDef)}
+    real_classes = {n: o for n, o in vars(C).items() if inspect.isclass(o)}
+    real_funcs = {n: o for n, o in vars(C).items() if callable(o) and not inspect.isclass(o) and not n.startswith("__")}
+    assert set(stub_classes) == set(real_classes)
+    assert set(stub_funcs) == set(real_funcs)
+
+    def params(doc):  # "name(self: X, a: int, b: str = '') -> R" -> ["a", "b"]
+        inside = doc.strip().splitlines()[0]
+        inside = inside[inside.index("(") + 1:inside.rindex(")")]
+        names = re.findall(r"(?:^|, )(\w+): ", inside)
+        return [n for n in names if n != "self"]
+
+    for name, node in stub_classes.items():
+        real = real_classes[name]
+        stub_members = {m.name for m in node.body if isinstance(m, ast.FunctionDef)} | {
+            m.target.id for m in node.body if isinstance(m, ast.AnnAssign)}
+        real_members = {m for m in vars(real) if not m.startswith("__") and "pybind11" not in m} | {"__init__"}
+        assert stub_members == real_members, (name, stub_members ^ real_members)
+        for m in node.body:
+            if isinstance(m, ast.FunctionDef):
+                want = params(getattr(real, m.name).__doc__)
+                got = [a.arg for a in m.args.args if a.arg != "self"]
+                assert got == want, (name, m.name, got, want)
+    for name, node in stub_funcs.items():
+        want = params(real_funcs[name].__doc__)
+        got = [a.arg for a in node.args.args]
+        assert got == want or name == "quorum_changed", (name, got, want)
