@@ -423,3 +423,39 @@ def test_diloco_pseudo_gradient_is_what_the_outer_optimizer_sees():
         torch.testing.assert_close(grad, 0.5 * (s0 - l))         # pseudo-gradient, scaled by the (mock) average
     for p, s0, l in zip(model.parameters(), start, local):
         torch.testing.assert_close(p.detach(), s0 - 0.5 * 0.5 * (s0 - l))
+
+
+def test_local_sgd_bucketed_average_matches_per_parameter():
+    """bucket_cap_mb packs the parameter copies into flat buffers: same averaged weights, fewer collectives."""
+    def run(cap_mb):
+        torch.manual_seed(0)
+        model = TinyModel()
+        inner = optim.SGD(model.parameters(), lr=0.1)
+        m = mock_manager(commit=True, factor=0.5)
+        g = torch.Generator().manual_seed(1)
+        with LocalSGD(m, model, inner, sync_every=2, bucket_cap_mb=cap_mb):
+            for _ in range(2):
+                inner.zero_grad()
+                model(torch.randn(4, 3, generator=g)).square().mean().backward()
+                inner.step()
+        return m.allreduce.call_count, [p.detach().clone() for p in model.parameters()]
+
+    calls_each, each = run(None)
+    calls_packed, packed = run(1)
+    assert (calls_each, calls_packed) == (4, 1)
+    for a, b in zip(each, packed):
+        torch.testing.assert_close(a, b)
+
+
+def test_local_sgd_bucket_cap_splits_and_oversized_parameter():
+    big = nn.Linear(600, 600, bias=True)  # weight 1.44 MB > 1 MB cap, bias small
+    small = nn.Linear(4, 4)
+    model = nn.Sequential(small, big)
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    m = mock_manager(commit=True, factor=1.0)
+    before = [p.detach().clone() for p in model.parameters()]
+    LocalSGD(m, model, inner, sync_every=1, bucket_cap_mb=1).sync()
+    sizes = sorted(c.args[0].numel() for c in m.allreduce.call_args_list)
+    assert sizes == sorted([4 * 4 + 4, 600 * 600, 600])  # small layer together | big weight alone | big bias
+    for p, b in zip(model.parameters(), before):
+        torch.testing.assert_close(p.detach(), b)

@@ -64,12 +64,20 @@ def _assign(p: torch.Tensor, value: torch.Tensor, non_blocking: bool = False) ->
 class LocalSGD:
     """Context manager: every ``sync_every`` optimizer steps the parameters are averaged
     across replicas (quorum -> allreduce -> commit vote -> copy back).  If the window
-    fails to commit, local weights are kept and the next window tries again."""
+    fails to commit, local weights are kept and the next window tries again.
 
-    def __init__(self, manager: Manager, model: nn.Module, optimizer: optim.Optimizer, sync_every: int) -> None:
+    ``bucket_cap_mb``: when given, the parameter copies of one dtype and device are packed into flat buffers of at most
+    that size and each buffer is one allreduce (a model with hundreds of small parameters then costs a handful of
+    collectives instead of hundreds); ``None`` keeps one allreduce per parameter, as the reference does
+    (torchft/local_sgd.py:160-173).  The averaged values are the same either way."""
+
+    def __init__(self, manager: Manager, model: nn.Module, optimizer: optim.Optimizer, sync_every: int,
+                 bucket_cap_mb: Optional[int] = None) -> None:
         assert sync_every >= 1, "sync_every must be greater than or equal to 1"
+        assert bucket_cap_mb is None or bucket_cap_mb > 0, "bucket_cap_mb must be positive"
         self._manager, self._model, self._local_optimizer = manager, model, optimizer
         self._sync_every = sync_every
+        self._bucket_cap_bytes = None if bucket_cap_mb is None else bucket_cap_mb * 1024 * 1024
         self._local_step = 0
         self._hooks: List[RemovableHandle] = []
 
@@ -109,11 +117,43 @@ class LocalSGD:
                     _assign(p, avg)
 
     def _average(self) -> List[torch.Tensor]:
+        if self._bucket_cap_bytes is not None:
+            return self._average_bucketed(self._bucket_cap_bytes)
         copies = [extract_local_tensor(p.data) for p in self._model.parameters()]
         works = [self._manager.allreduce(c) for c in copies]
         for w in works:
             w.wait()
         return copies
+
+    def _average_bucketed(self, cap_bytes: int) -> List[torch.Tensor]:
+        """Pack the local values into flat buffers per (dtype, device), allreduce each buffer once and return views
+        into the buffers in parameter order.  A parameter larger than the cap gets a buffer of its own."""
+        locals_ = [_local_view(p.data) for p in self._model.parameters()]
+        out: List[Optional[torch.Tensor]] = [None] * len(locals_)
+        groups: Dict[Tuple[torch.dtype, torch.device], List[int]] = {}
+        for i, t in enumerate(locals_):
+            groups.setdefault((t.dtype, t.device), []).append(i)
+        works = []
+        for (dtype, device), idxs in groups.items():
+            start = 0
+            while start < len(idxs):
+                end, nbytes = start, 0
+                while end < len(idxs) and (end == start or nbytes + locals_[idxs[end]].numel() * locals_[idxs[end]].element_size() <= cap_bytes):
+                    nbytes += locals_[idxs[end]].numel() * locals_[idxs[end]].element_size()
+                    end += 1
+                flat = torch.empty(sum(locals_[i].numel() for i in idxs[start:end]), dtype=dtype, device=device)
+                off = 0
+                for i in idxs[start:end]:
+                    n = locals_[i].numel()
+                    view = flat[off:off + n].view(locals_[i].shape)
+                    view.copy_(locals_[i])
+                    out[i] = view
+                    off += n
+                works.append(self._manager.allreduce(flat))
+                start = end
+        for w in works:
+            w.wait()
+        return out  # type: ignore[return-value]
 
 
 class _StreamingDiLoCoFragment:
