@@ -83,6 +83,12 @@ def main() -> None:
     )
     criterion = nn.CrossEntropyLoss()
     g = torch.Generator().manual_seed(1000 + replica_group)
+    # RUN=<name>: TensorBoard scalars (loss, committed outer steps, participants) under runs/<name>_group<g>
+    writer = None
+    if os.environ.get("RUN"):
+        from torch.utils.tensorboard import SummaryWriter
+
+        writer = SummaryWriter(os.path.join("runs", f"{os.environ['RUN']}_group{replica_group}"))
     with DiLoCo(manager, fragments, inner, outers, sync_every=20 if streaming else 20,
                 fragment_sync_delay=5 if streaming else 0, should_quantize=quantize,
                 backup_device=device if use_cuda else None) as diloco:
@@ -93,9 +99,14 @@ def main() -> None:
             loss = criterion(model(x), y)
             loss.backward()
             inner.step()  # DiLoCo's hooks run the quorum / allreduce / outer step when due
+            if writer is not None:
+                writer.add_scalar("loss", loss.item(), step)
+                writer.add_scalar("manager_step", manager.current_step(), step)
             if step % 20 == 0:
                 print(f"[{replica_group}] local_step={step} manager_step={manager.current_step()} loss={loss.item():.4f}",
                       flush=True)
+    if writer is not None:
+        writer.close()
     manager.shutdown()
 
 
