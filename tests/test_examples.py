@@ -172,7 +172,7 @@ def test_runner_and_punisher_with_real_trainers(tmp_path):
     from torchft_b200.launch.runner import Punisher, Runner, _descendants
 
     pid_file, logs = str(tmp_path / "pids.json"), tmp_path / "logs"
-    steps = 1500
+    steps = 3000  # long enough that group 0 is still training when the killed group is back, even on a loaded host
     runner = Runner([str(REPO / "train_ddp.py")], num_groups=2, base_port=_free_port_pair(), max_restarts=3, pid_file=pid_file,
                     poll_secs=0.2, log_dir=str(logs), extra_env={"STEPS": str(steps), "OMP_NUM_THREADS": "2", "PYTHONPATH": str(REPO)})
     result = {}
