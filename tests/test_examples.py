@@ -124,7 +124,7 @@ def test_train_ddp_restarted_group_heals_cpu():
     """Group 1 is killed mid-run and started again: it rejoins, copies the state from group 0 and both
     reach the last step; group 0 never stops."""
     lh = LighthouseServer(bind="[::]:0", min_replicas=1, join_timeout_ms=1000, heartbeat_timeout_ms=1000)
-    steps = 1500
+    steps = 2500  # the survivor must still be training when the restarted group is back
     t0 = t1 = t1b = None
     try:
         t0 = _Tail(_launch("train_ddp.py", 0, lh.address(), STEPS=str(steps)))
