@@ -391,7 +391,7 @@ class Manager:
         """Begin a step: join the quorum (asynchronously when configured so) and clear the
         error latch.  Call before the forward pass.  ``allow_heal=False`` keeps a behind
         replica from fetching state (all replicas must pass the same value);
-        ``shrink_only`` forbids the quorum to grow this round."""
+        ``shrink_only`` forbids this quorum to grow."""
         if self._quorum_future is not None:
             self._quorum_future.result()  # previous round must be over
         self._errored = None
