@@ -244,3 +244,42 @@ def test_train_hsdp_cpu_with_durable_checkpoint_resume(tmp_path):
     r = run(15)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
     assert "resumed from step 10" in r.stdout and "step 10 loss" in r.stdout and "step 0 loss" not in r.stdout
+
+
+@pytest.mark.timeout(600)
+def test_runner_detects_a_hung_group(tmp_path, capfd):
+    """A trainer that is alive but stuck (SIGSTOP here) stops voting on commits; the runner notices through the
+    managers' progress files, kills the group's processes and starts it again."""
+    import signal
+
+    from torchft_b200.launch.runner import Runner, _descendants
+
+    logs = tmp_path / "logs"
+    runner = Runner([str(REPO / "train_ddp.py")], num_groups=1, base_port=_free_port_pair(), max_restarts=2,
+                    pid_file=str(tmp_path / "pids.json"), poll_secs=0.2, log_dir=str(logs), hang_timeout_secs=12.0,
+                    progress_dir=str(tmp_path / "progress"),
+                    extra_env={"STEPS": "800", "OMP_NUM_THREADS": "2", "PYTHONPATH": str(REPO)})
+    result = {}
+    th = threading.Thread(target=lambda: result.setdefault("rc", runner.run()), daemon=True)
+    th.start()
+    try:
+        first = logs / "group_0.0.log"
+        end = time.monotonic() + 120
+        while not (first.exists() and first.read_text().count("should_commit=True") > 10):
+            assert time.monotonic() < end and th.is_alive(), first.read_text()[-1500:] if first.exists() else "no log"
+            time.sleep(0.2)
+        assert (tmp_path / "progress" / "group0.rank0").is_file()
+        trainers = _descendants(runner._groups[0].proc.pid, max_depth=1)
+        assert trainers
+        for pid in trainers:
+            os.kill(pid, signal.SIGSTOP)
+        th.join(300)
+        assert not th.is_alive() and result.get("rc") == 0, result
+        assert "made no progress" in capfd.readouterr().out
+        second = (logs / "group_0.1.log").read_text()
+        assert "step 799] should_commit=True" in second
+        assert "step 799] should_commit=True" not in first.read_text()
+    finally:
+        for gp in runner._groups:
+            if gp.proc is not None:
+                _kill_tree(gp.proc.pid)

@@ -113,6 +113,13 @@ class Runner:
     poll_secs: float = 1.0
     extra_env: Dict[str, str] = field(default_factory=dict)
     log_dir: Optional[str] = None  # group output goes to <log_dir>/group_<g>.<restart>.log instead of this process's stdout
+    # A group whose trainers have not voted on a commit for this long is killed (and then restarted like any group that
+    # exits): catches processes that are alive but stuck.  The trainers' managers write a progress file per rank at
+    # every commit vote (FTB200_PROGRESS_DIR, set by the runner); None disables the check.  Choose it longer than the
+    # slowest step, LocalSGD/DiLoCo window or state transfer.
+    hang_timeout_secs: Optional[float] = None
+    startup_grace_secs: float = 120.0  # a (re)started group gets this long for its first vote (imports, rendezvous, healing)
+    progress_dir: Optional[str] = None
 
     def __post_init__(self) -> None:
         self._lighthouse: Optional[LighthouseServer] = None
@@ -124,9 +131,33 @@ class Runner:
         env["REPLICA_GROUP_ID"] = str(g)
         env["NUM_REPLICA_GROUPS"] = str(self.num_groups)
         env["TORCHFT_LIGHTHOUSE"] = self.lighthouse_addr or ""
+        if self.hang_timeout_secs is not None:
+            env["FTB200_PROGRESS_DIR"] = self._progress_dir()
         first = g * self.gpus_per_group
         env["CUDA_VISIBLE_DEVICES"] = ",".join(str(first + i) for i in range(self.gpus_per_group))
         return env
+
+    def _progress_dir(self) -> str:
+        if self.progress_dir is None:
+            import tempfile
+
+            self.progress_dir = tempfile.mkdtemp(prefix="ftb200_progress_")
+        return self.progress_dir
+
+    def _is_hung(self, gp: GroupProc, now: float) -> bool:
+        """No commit vote for ``hang_timeout_secs``; before the first vote of this incarnation the (longer) start-up
+        grace applies instead."""
+        assert self.hang_timeout_secs is not None
+        newest = 0.0
+        d = self._progress_dir()
+        for r in range(self.gpus_per_group):
+            try:
+                newest = max(newest, os.path.getmtime(os.path.join(d, f"group{gp.group_id}.rank{r}")))
+            except OSError:
+                pass
+        if newest <= gp.started:  # nothing written since this incarnation started
+            return now - gp.started > max(self.startup_grace_secs, self.hang_timeout_secs)
+        return now - newest > self.hang_timeout_secs
 
     def _launch(self, gp: GroupProc) -> None:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={self.gpus_per_group}",
@@ -163,6 +194,9 @@ class Runner:
                         continue
                     rc = gp.proc.poll()
                     if rc is None:
+                        if self.hang_timeout_secs is not None and self._is_hung(gp, time.time()):
+                            print(f"[runner] group {gp.group_id} made no progress for {self.hang_timeout_secs} s; killing it", flush=True)
+                            signal_tree(gp.proc.pid, signal.SIGKILL)
                         continue
                     signal_tree(gp.proc.pid, signal.SIGKILL, include_root=False)  # workers a dead launcher left behind
                     if rc == 0:
@@ -265,11 +299,13 @@ def main(argv: Optional[List[str]] = None) -> int:
     ap.add_argument("--lighthouse", default=None)
     ap.add_argument("--pid-file", default="/tmp/ftb200_runner.json")
     ap.add_argument("--log-dir", default=None)
+    ap.add_argument("--hang-timeout-secs", type=float, default=None,
+                    help="kill and restart a group whose trainers have not voted on a commit for this long")
     ap.add_argument("script", nargs=argparse.REMAINDER)
     a = ap.parse_args(argv)
     script = [s for s in a.script if s != "--"]
     return Runner(script, a.groups, a.gpus_per_group, a.base_port, a.max_restarts, a.min_replicas, a.lighthouse, a.pid_file,
-                  log_dir=a.log_dir).run()
+                  log_dir=a.log_dir, hang_timeout_secs=a.hang_timeout_secs).run()
 
 
 if __name__ == "__main__":

@@ -53,6 +53,7 @@ REPLICA_ID_KEY: str = "replica_id"
 
 # Environment overrides (they win over constructor arguments).
 TIMEOUT_SEC_ENV: str = "TORCHFT_TIMEOUT_SEC"
+PROGRESS_DIR_ENV: str = "FTB200_PROGRESS_DIR"
 QUORUM_TIMEOUT_SEC_ENV: str = "TORCHFT_QUORUM_TIMEOUT_SEC"
 CONNECT_TIMEOUT_SEC_ENV: str = "TORCHFT_CONNECT_TIMEOUT_SEC"
 QUORUM_RETRIES_ENV: str = "TORCHFT_QUORUM_RETRIES"
@@ -222,6 +223,13 @@ class Manager:
         replica_id = self._store.get(REPLICA_ID_KEY).decode("utf-8")
         self._replica_id = replica_id
         self._logger = _ManagerLogger(manager=self, replica_id=replica_id or "", group_rank=self._group_rank)
+        # Progress beacon for a supervisor (launch/runner.py): a file rewritten at every commit vote.  Heartbeats
+        # come from the manager server's own thread and keep flowing while a trainer is stuck; this does not.
+        self._progress_file: Optional[str] = None
+        progress_dir = os.environ.get(PROGRESS_DIR_ENV)
+        if progress_dir:
+            group = os.environ.get("REPLICA_GROUP_ID", (replica_id or "replica").split(":")[0])
+            self._progress_file = os.path.join(progress_dir, f"group{group}.rank{self._group_rank}")
 
         self._step = 0
         self._quorum_id = -1
@@ -573,7 +581,18 @@ class Manager:
                            f"exceeding max_retries={self._max_retries}")
                     self._logger.exception(msg)
                     raise RuntimeError(msg)
+            self._write_progress()
             return decision
+
+    def _write_progress(self) -> None:
+        if self._progress_file is None:
+            return
+        try:
+            os.makedirs(os.path.dirname(self._progress_file), exist_ok=True)
+            with open(self._progress_file, "w") as f:
+                f.write(f"{self._step}\n")
+        except OSError:  # a beacon must never take training down
+            pass
 
     # ------------------------------------------------------------------ state
     def load_state_dict(self, state_dict: Dict[str, int]) -> None:
