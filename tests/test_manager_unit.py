@@ -431,3 +431,17 @@ def test_managed_future_chain_may_change_types_and_failures_are_latched(h):
     fut.wait()  # does not raise
     assert "callback failed" in str(m.errored())
     assert not m.should_commit()
+
+
+def test_unreachable_store_fails_within_connect_timeout():
+    import socket as _socket
+
+    with _socket.socket() as s:  # a port nobody listens on
+        s.bind(("127.0.0.1", 0))
+        dead_port = s.getsockname()[1]
+    pg = create_autospec(ProcessGroup, instance=True)
+    t0 = time.monotonic()
+    with pytest.raises(Exception):
+        Manager(pg=pg, min_replica_size=1, load_state_dict=None, state_dict=None, store_addr="127.0.0.1", store_port=dead_port,
+                rank=1, world_size=2, connect_timeout=timedelta(seconds=2), timeout=timedelta(seconds=5))
+    assert time.monotonic() - t0 < 30

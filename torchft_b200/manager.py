@@ -191,7 +191,10 @@ class Manager:
         self._executor = ThreadPoolExecutor(max_workers=1, thread_name_prefix="torchft_quorum")
         self._quorum_future: Optional[concurrent.futures.Future] = None
 
-        self._store = TCPStore(host_name=store_addr, port=store_port, is_master=False, wait_for_workers=False)
+        # connect_timeout bounds reaching the group's store and, below, waiting for rank 0 to publish the manager
+        # address (torch's default of five minutes turns a wrong address into a very long silence)
+        self._store = TCPStore(host_name=store_addr, port=store_port, is_master=False, wait_for_workers=False,
+                               timeout=self._connect_timeout)
         self._pg = pg
         self._manager: Optional[ManagerServer] = None
         self._recovery_stream: Optional[torch.cuda.Stream] = torch.cuda.Stream() if torch.cuda.is_available() else None
