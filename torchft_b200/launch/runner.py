@@ -94,6 +94,8 @@ def install_fault_handlers(manager) -> None:
 
 @dataclass
 class GroupProc:
+    """One replica group as the runner tracks it: its launcher process, restart count and start time."""
+
     group_id: int
     proc: Optional[subprocess.Popen] = None
     restarts: int = 0
@@ -102,6 +104,12 @@ class GroupProc:
 
 @dataclass
 class Runner:
+    """Supervisor of ``num_groups`` replica groups on one box.  ``run()`` hosts a lighthouse (unless
+    ``lighthouse_addr`` names one), starts one ``torchrun`` per group with ``gpus_per_group`` workers on rendezvous port
+    ``base_port + group``, restarts a group that exits with a non-zero status (up to ``max_restarts`` times each) or that
+    stops voting on commits (``hang_timeout_secs``), and returns when every group has exited with status 0 or has run out
+    of restarts.  ``pid_file`` is where the punisher finds the launchers."""
+
     script_args: List[str]
     num_groups: int = 2
     gpus_per_group: int = 1
