@@ -30,6 +30,9 @@ _STEP_RE = re.compile(r"^step_(\d{8})$")
 
 
 class DurableCheckpointer:
+    """Writes and restores on-disk checkpoints of everything registered with a :class:`Manager` (user state, step and
+    batch counters, caller-supplied extras); see the module docstring for the layout."""
+
     def __init__(self, manager: Manager, directory: str, rank: int, world_size: int, every: int = 0, keep: int = 2) -> None:
         """``rank`` / ``world_size``: this rank's position inside its replica group.  ``every``:
         :meth:`maybe_save` writes when the committed step is a multiple of it (0 = never).

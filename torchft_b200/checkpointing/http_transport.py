@@ -65,6 +65,12 @@ def _leaf_to_cpu(v: object, pin: bool) -> object:
 
 
 class HTTPTransport(CheckpointTransport[T], Generic[T]):
+    """Checkpoint transport over HTTP: every rank runs a small threaded server; a healthy rank stages a snapshot of
+    its state (``send_checkpoint``) and recovering ranks download it (``recv_checkpoint``) from
+    ``/checkpoint/<step>/full``, or in ``num_chunks`` parallel streams from ``/checkpoint/<step>/<i>``.  Nothing is served
+    before the first ``send_checkpoint`` or after ``disallow_checkpoint``; a request for another step gets HTTP 400.
+    Works between any two hosts that can reach each other (torchft/checkpointing/http_transport.py:39-267)."""
+
     def __init__(self, timeout: timedelta, num_chunks: int = 0, pin_memory: bool = False,
                  state_dict: Optional[Callable[[], T]] = None) -> None:
         """``state_dict``: optional callable returning the receiver's current state dict; tensors whose shape

@@ -37,6 +37,8 @@ def _submit(replica: int, replicas: int, nodes: int, gpus: int, lighthouse: str,
 
 
 def runner(replicas: int, nodes: int, gpus: int, lighthouse: str, script: List[str], poll_secs: float = 10.0) -> None:
+    """Keep one Slurm job per replica group (``ft_<g>``) in the queue: every ``poll_secs`` submit the ones that are
+    missing.  Runs until interrupted."""
     while True:
         alive = _running()
         for r in range(replicas):
@@ -47,6 +49,7 @@ def runner(replicas: int, nodes: int, gpus: int, lighthouse: str, script: List[s
 
 
 def kill_one() -> None:
+    """``scancel`` one randomly chosen replica-group job."""
     jobs = sorted(_running())
     if jobs:
         victim = random.choice(jobs)
@@ -55,11 +58,13 @@ def kill_one() -> None:
 
 
 def kill_all() -> None:
+    """``scancel`` every replica-group job."""
     for j in _running():
         subprocess.run(["scancel", f"--name={j}"], check=True)
 
 
 def kill_loop(num_failures: int, mtbf_secs: float) -> None:
+    """``num_failures`` times: sleep an exponentially distributed time with mean ``mtbf_secs``, then ``kill_one``."""
     for _ in range(num_failures):
         time.sleep(random.expovariate(1.0 / mtbf_secs))
         kill_one()

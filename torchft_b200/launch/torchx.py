@@ -17,6 +17,9 @@ from typing import Dict, Optional
 def hsdp(*script_args: str, replicas: int = 2, workers_per_replica: int = 1, max_restarts: int = 10,
          script: str = "train_ddp.py", env: Optional[Dict[str, str]] = None, image: str = "", h: Optional[str] = None,
          cpu: int = 2, gpu: int = 0, memMB: int = 1024):
+    """torchx component: an ``AppDef`` with one ``torchrun`` role per replica group (``replicas`` groups of
+    ``workers_per_replica`` workers), each with ``REPLICA_GROUP_ID``, ``NUM_REPLICA_GROUPS`` and ``TORCHFT_LIGHTHOUSE`` in
+    its environment, its own ``--master_port`` (29600 + group) and ``--max_restarts`` (torchft/torchx.py:11-83)."""
     try:
         import torchx.specs as specs
     except ImportError as e:  # pragma: no cover - torchx is not a dependency

@@ -81,6 +81,9 @@ class WorldSizeMode(Enum):
 
 
 class ExceptionWithTraceback(Exception):
+    """What :meth:`Manager.errored` returns: the latched exception (``original_exception``) with the stack trace of
+    the place where it was reported (``stack_trace``)."""
+
     def __init__(self, e: Exception) -> None:
         self.original_exception = e
         self.stack_trace: str = traceback.format_exc()

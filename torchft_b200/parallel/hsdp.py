@@ -29,6 +29,13 @@ def _round_up(x: int, m: int) -> int:
 
 
 class ShardedLlamaTrainer:
+    """Llama trainer on the explicit engine with FSDP-style sharding inside the replica group and an optional managed
+    replica dimension.  Parameters, gradients and AdamW state live as one shard per rank and unit (a unit is the
+    embedding, one decoder layer, or the head); ``shard_comm`` gathers a unit's parameters ahead of its GEMMs and
+    reduce-scatters its gradients; with ``manager`` the shard-sized gradients are averaged over the replica groups and
+    the optimizer runs only when the step commits.  ``train_step(tokens, targets)`` is one complete step and returns
+    the loss; ``state_dict()`` / ``load_state_dict()`` expose this rank's shards for healing and checkpoints."""
+
     def __init__(
         self,
         cfg: LlamaConfig,

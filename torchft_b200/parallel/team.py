@@ -102,7 +102,8 @@ class Arena:
 
 
 class TeamError(RuntimeError):
-    pass
+    """A peer-memory collective ended with a status other than OK (timeout, abort, epoch mismatch) or the team could
+    not be set up."""
 
 
 class SymmetricTeam:

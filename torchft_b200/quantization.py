@@ -47,6 +47,8 @@ def split_quantized(buf: torch.Tensor, n: int) -> Tuple[torch.Tensor, torch.Tens
 
 
 def ref_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """PyTorch restatement of the block quantiser: ``(codes uint8 [n], scales fp32 [n/128])`` with
+    ``scale = amax / 448`` per 128 elements (1 for an all-zero block) and ``code = e4m3(x / scale)``."""
     xf = x.float().reshape(-1, BLOCK)
     amax = xf.abs().amax(dim=1)
     scale = torch.where(amax > 0, amax / FP8_MAX, torch.ones_like(amax))
@@ -55,6 +57,7 @@ def ref_quantize(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
 
 
 def ref_dequantize(codes: torch.Tensor, scales: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Inverse of :func:`ref_quantize`: ``code * scale`` per block, cast to ``dtype``."""
     vals = codes.view(torch.float8_e4m3fn).float().reshape(-1, BLOCK) * scales[:, None]
     return vals.reshape(-1).to(dtype)
 
@@ -79,6 +82,7 @@ def quantize_into(x: torch.Tensor, out: torch.Tensor, minus: Optional[torch.Tens
 
 
 def dequantize_from(buf: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Dequantise the quantised buffer ``buf`` into flat ``out`` (whose length is a multiple of the block size)."""
     n = out.numel()
     assert n % BLOCK == 0
     codes, scales = split_quantized(buf, n)
