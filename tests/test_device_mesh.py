@@ -81,6 +81,14 @@ def _fsdp_worker(rank: int, world: int, port: int) -> None:
         model = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.ReLU(), torch.nn.Linear(16, 4))
         ref = pickle.loads(pickle.dumps(model))
         fully_shard(model, mesh=mesh)
+        # gathering works on the managed mesh too: DTensor.full_tensor() and torch's full state dict
+        from torch.distributed.checkpoint.state_dict import StateDictOptions, get_model_state_dict
+
+        for p, q in zip(model.parameters(), ref.parameters()):
+            torch.testing.assert_close(p.full_tensor(), q.detach())
+        full_sd = get_model_state_dict(model, options=StateDictOptions(full_state_dict=True))
+        for k, v in ref.state_dict().items():
+            torch.testing.assert_close(full_sd[k], v)
         x = torch.randn(4 * world, 8)  # the same global batch everywhere; each rank takes its rows
         mine = x[rank * 4:(rank + 1) * 4]
         model(mine).sum().backward()

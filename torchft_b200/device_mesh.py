@@ -181,6 +181,23 @@ class ManagedDeviceMesh(DeviceMesh):
         coord.insert(self.replicate_dim, get_rank(self.replicate_pg))
         return coord
 
+    # DTensor's redistribution code (full_tensor(), state-dict gathering) asks the mesh these two questions through
+    # private members of torch's DeviceMesh; answer them from the managed view.
+    @property
+    def _coordinate_on_dim(self) -> Optional[List[int]]:  # type: ignore[override]
+        return self.get_coordinate()
+
+    def _is_current_rank_part_of_mesh(self) -> bool:
+        return self.get_coordinate() is not None
+
+    @property
+    def _dim_group_names(self) -> List[str]:  # type: ignore[override]
+        """Registered group name per mesh dimension: the real mesh's names with the managed group's name inserted at
+        the replicate dimension (functional collectives resolve ``(mesh, dim)`` through this list)."""
+        names = list(self._mesh._dim_group_names) if self._mesh is not None else []
+        names.insert(self.replicate_dim, self.replicate_pg.group_name)
+        return names
+
     def get_all_groups(self) -> List[BaseProcessGroup]:
         raise NotImplementedError
 
