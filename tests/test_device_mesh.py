@@ -54,7 +54,7 @@ def test_managed_device_mesh_gloo():
     mp.spawn(_worker, args=(world, port), nprocs=world, join=True)
 
 
-def _fsdp_worker(rank: int, world: int, port: int) -> None:
+def _fsdp_worker(rank: int, world: int, port: int, ckpt_dir: str) -> None:
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -89,6 +89,16 @@ def _fsdp_worker(rank: int, world: int, port: int) -> None:
         full_sd = get_model_state_dict(model, options=StateDictOptions(full_state_dict=True))
         for k, v in ref.state_dict().items():
             torch.testing.assert_close(full_sd[k], v)
+        # ... and so does torch.distributed.checkpoint: sharded save, wipe, sharded load
+        import torch.distributed.checkpoint as dcp
+
+        dcp.save({"model": model.state_dict()}, checkpoint_id=ckpt_dir)
+        with torch.no_grad():
+            for p in model.parameters():
+                p.to_local().zero_()
+        dcp.load({"model": model.state_dict()}, checkpoint_id=ckpt_dir)
+        for p, q in zip(model.parameters(), ref.parameters()):
+            torch.testing.assert_close(p.full_tensor(), q.detach())
         x = torch.randn(4 * world, 8)  # the same global batch everywhere; each rank takes its rows
         mine = x[rank * 4:(rank + 1) * 4]
         model(mine).sum().backward()
@@ -103,9 +113,9 @@ def _fsdp_worker(rank: int, world: int, port: int) -> None:
         dist.destroy_process_group()
 
 
-def test_fully_shard_on_managed_mesh_gloo():
+def test_fully_shard_on_managed_mesh_gloo(tmp_path):
     """HSDP as the reference wires it (torchft/fsdp_test.py:82-92): FSDP2 shards inside the group over a real
     process group and reduces over the replicate dimension through the manager."""
     world = 2
     port = 31000 + os.getpid() % 2000
-    mp.spawn(_fsdp_worker, args=(world, port), nprocs=world, join=True)
+    mp.spawn(_fsdp_worker, args=(world, port, str(tmp_path / "dcp")), nprocs=world, join=True)
