@@ -119,3 +119,38 @@ def test_fully_shard_on_managed_mesh_gloo(tmp_path):
     world = 2
     port = 31000 + os.getpid() % 2000
     mp.spawn(_fsdp_worker, args=(world, port, str(tmp_path / "dcp")), nprocs=world, join=True)
+
+
+def _tp_worker(rank: int, world: int, port: int) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torch.distributed.tensor.parallel import ColwiseParallel, RowwiseParallel, parallelize_module
+
+        from torchft_b200.device_mesh import ft_init_device_mesh
+        from torchft_b200.manager import Manager
+        from torchft_b200.process_group import ProcessGroupGloo
+
+        manager = MagicMock(spec=Manager)
+        manager._pg = ProcessGroupGloo()
+        manager.num_participants.return_value = 1
+        mesh = ft_init_device_mesh(device_type="cpu", mesh_shape=(1, 2, 2), mesh_dim_names=("dp_replicate", "dp_shard", "tp"),
+                                   replicate_dim=0, manager=manager)
+        assert mesh.shape == (1, 2, 2) and mesh["tp"].size() == 2
+        torch.manual_seed(0)
+        model = torch.nn.Sequential(torch.nn.Linear(8, 16, bias=False), torch.nn.ReLU(), torch.nn.Linear(16, 8, bias=False))
+        w0, w1 = [p.detach().clone() for p in model.parameters()]
+        x = torch.randn(4, 8)
+        want = torch.relu(x @ w0.t()) @ w1.t()
+        parallelize_module(model, mesh["tp"], {"0": ColwiseParallel(), "2": RowwiseParallel()})
+        torch.testing.assert_close(model(x), want, rtol=1e-5, atol=1e-5)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_on_a_submesh_of_the_managed_mesh():
+    """A 3-D managed mesh (replicate x shard x tp): the tp dimension is a real sub-mesh on which torch's tensor-parallel
+    styles work (the reference exercises ColwiseParallel the same way, torchft/fsdp_test.py:84-90)."""
+    world = 4
+    port = 33000 + os.getpid() % 2000
+    mp.spawn(_tp_worker, args=(world, port), nprocs=world, join=True)
