@@ -144,13 +144,27 @@ def _tp_worker(rank: int, world: int, port: int) -> None:
         want = torch.relu(x @ w0.t()) @ w1.t()
         parallelize_module(model, mesh["tp"], {"0": ColwiseParallel(), "2": RowwiseParallel()})
         torch.testing.assert_close(model(x), want, rtol=1e-5, atol=1e-5)
+        # FSDP2 on top of the tensor-parallel parameters, over the managed (replicate, shard) part of the mesh
+        from torch.distributed.fsdp import fully_shard
+
+        from torchft_b200.work import _DummyWork
+
+        seen = []
+        manager.allreduce.side_effect = lambda t, should_quantize=False, reduce_op=None: seen.append(t.numel()) or _DummyWork(t)
+        fully_shard(model, mesh=mesh["dp_replicate", "dp_shard"])
+        out = model(x)
+        torch.testing.assert_close(out, want, rtol=1e-5, atol=1e-5)
+        out.sum().backward()
+        assert len(seen) == 1  # the replicate-dimension reduction of the (shard x tp)-sized gradients went through the manager
+        assert all(p.grad is not None for p in model.parameters())
     finally:
         dist.destroy_process_group()
 
 
-def test_tensor_parallel_on_a_submesh_of_the_managed_mesh():
+def test_tensor_parallel_and_fsdp2_on_a_3d_managed_mesh():
     """A 3-D managed mesh (replicate x shard x tp): the tp dimension is a real sub-mesh on which torch's tensor-parallel
-    styles work (the reference exercises ColwiseParallel the same way, torchft/fsdp_test.py:84-90)."""
+    styles work, and FSDP2 composes with them over the managed (replicate, shard) part
+    (the reference's fsdp_test.py:84-92 builds the same (1, 2, 2) layout)."""
     world = 4
     port = 33000 + os.getpid() % 2000
     mp.spawn(_tp_worker, args=(world, port), nprocs=world, join=True)

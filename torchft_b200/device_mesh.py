@@ -11,6 +11,7 @@ Counterpart of torchft/device_mesh.py:22-340.
 
 from __future__ import annotations
 
+import warnings
 from typing import TYPE_CHECKING, Any, Dict, List, Optional, Tuple, Union
 
 import torch
@@ -57,9 +58,6 @@ class ManagedDeviceMesh(DeviceMesh):
         src = mesh if mesh is not None else parent
         assert src is not None
         self._device_type: str = src.device_type
-        for attr in ("_layout", "_rank_map"):  # internals newer torch versions consult
-            if hasattr(src, attr):
-                setattr(self, attr, getattr(src, attr))
         self._flatten_mesh_list: Tuple[DeviceMesh, ...] = tuple()
         self._flatten_mapping: Dict[str, DeviceMesh] = {}
         self._thread_id: Optional[int] = None
@@ -97,7 +95,9 @@ class ManagedDeviceMesh(DeviceMesh):
                 sub = ManagedDeviceMesh(self._mesh[rest], mesh_dim_names, self.replicate_pg,
                                         mesh_dim_names.index(self.replicate_dim_name), parent=self)
         try:
-            sub._root_mesh = _mesh_resources.get_root_mesh(self)  # type: ignore[attr-defined]
+            with warnings.catch_warnings():
+                warnings.simplefilter("ignore")  # torch announces the removal of this lookup; there is no public successor yet
+                sub._root_mesh = _mesh_resources.get_root_mesh(self)  # type: ignore[attr-defined]
         except Exception:
             pass
         return sub
@@ -197,6 +197,40 @@ class ManagedDeviceMesh(DeviceMesh):
         names = list(self._mesh._dim_group_names) if self._mesh is not None else []
         names.insert(self.replicate_dim, self.replicate_pg.group_name)
         return names
+
+    # FSDP2 on parameters that are already tensor-parallel DTensors concatenates the data-parallel mesh (this object)
+    # with the tensor-parallel mesh (torch's ``DeviceMesh._concatenate``), which reads the members below.  The managed
+    # dimension is described as a dimension of size one: its real size lives in the quorum, no rank layout exists for
+    # it, and the only collective FSDP runs over it (the gradient all-reduce) goes through ``get_group``, not through
+    # the concatenated mesh.
+    @property
+    def _layout(self):  # type: ignore[override]
+        from torch.distributed._mesh_layout import _MeshLayout
+
+        if self._mesh is None:  # the replicate dimension on its own
+            return _MeshLayout((1,), (0,))
+        real = self._mesh._layout
+        sizes = [real[i].sizes for i in range(len(real))]
+        strides = [real[i].strides for i in range(len(real))]
+        sizes.insert(self.replicate_dim, 1)
+        strides.insert(self.replicate_dim, 0)
+        return _MeshLayout(tuple(sizes), tuple(strides))
+
+    def _real_source(self) -> DeviceMesh:
+        src = self._mesh if self._mesh is not None else (self.parent._mesh if self.parent is not None else None)
+        assert src is not None
+        return src
+
+    @property
+    def _flatten_rank_map(self):  # type: ignore[override]
+        return self._real_source()._flatten_rank_map
+
+    @property
+    def _rank_map(self):  # type: ignore[override]
+        return self._real_source()._rank_map
+
+    def _get_root_mesh(self) -> DeviceMesh:
+        return self._real_source()._get_root_mesh()
 
     def get_all_groups(self) -> List[BaseProcessGroup]:
         raise NotImplementedError
