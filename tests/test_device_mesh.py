@@ -168,3 +168,40 @@ def test_tensor_parallel_and_fsdp2_on_a_3d_managed_mesh():
     world = 4
     port = 33000 + os.getpid() % 2000
     mp.spawn(_tp_worker, args=(world, port), nprocs=world, join=True)
+
+
+def test_extend_device_mesh_inserts_a_registered_group():
+    """The older helper: a registered reconfigurable group becomes an extra mesh dimension of size one; an unregistered
+    group is refused with a message that says what to do (torchft/process_group_test.py test_device_mesh).  Child
+    process: it initialises torch.distributed."""
+    import subprocess
+    import sys
+
+    child = r'''
+import os, sys
+import torch, torch.distributed as dist
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29972", RANK="0", WORLD_SIZE="1")
+dist.init_process_group("gloo", rank=0, world_size=1)
+from torch.distributed.device_mesh import init_device_mesh
+from torchft_b200.device_mesh import extend_device_mesh
+from torchft_b200.process_group import ProcessGroupGloo
+store = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
+pg = ProcessGroupGloo(); pg.configure(f"127.0.0.1:{store.port}/x", "r", 0, 1)
+mesh = init_device_mesh("cpu", (1,), mesh_dim_names=("fsdp",))
+try:
+    extend_device_mesh(mesh, pg); raise SystemExit("expected an error")
+except ValueError as e:
+    assert "register" in str(e)
+pg.register("ext_probe")
+ext = extend_device_mesh(mesh, pg)
+assert ext.mesh_dim_names == ("dp", "fsdp") and tuple(ext.mesh.shape) == (1, 1), (ext.mesh_dim_names, ext.mesh.shape)
+assert ext.get_group("dp").size() == 1
+t = torch.ones(3)
+dist.all_reduce(t, group=ext.get_group("dp"))
+assert torch.equal(t, torch.ones(3))
+pg.unregister()
+print("extend ok")
+'''
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=240, env=dict(os.environ, PYTHONPATH=repo))
+    assert r.returncode == 0 and "extend ok" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]

@@ -28,7 +28,12 @@ if TYPE_CHECKING:
 def extend_device_mesh(mesh: DeviceMesh, pg: ProcessGroup, name: str = "dp", dim: int = 0) -> DeviceMesh:
     """Older helper: insert ``pg`` into ``mesh`` as a new dimension ``name`` of size 1.
     DeviceMesh believes the dimension has one member; the scaling by the real number of
-    replicas happens inside ``pg``."""
+    replicas happens inside ``pg``.  ``pg`` must have been registered (``pg.register(name)``) so that torch can
+    resolve it by name."""
+    try:
+        pg.group_name
+    except ValueError as e:
+        raise ValueError("extend_device_mesh needs a registered process group: call pg.register(<name>) first") from e
     groups = mesh.get_all_groups()
     groups.insert(dim, pg)
     names = list(mesh.mesh_dim_names or [])
