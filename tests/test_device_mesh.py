@@ -34,6 +34,8 @@ def _worker(rank: int, world: int, port: int) -> None:
         rep = mesh["dp_replicate"]
         assert isinstance(rep, ManagedDeviceMesh) and rep.size() == 2
         assert mesh.get_group("dp_replicate") is mesh.replicate_pg
+        groups = mesh.get_all_groups()
+        assert len(groups) == 2 and groups[0] is mesh.replicate_pg and groups[1] is mesh.get_group("dp_shard")
         both = mesh[("dp_replicate", "dp_shard")]
         assert both.size() == 2 * world
         flat = mesh._flatten("dp")

@@ -238,7 +238,10 @@ class ManagedDeviceMesh(DeviceMesh):
         return self._real_source()._get_root_mesh()
 
     def get_all_groups(self) -> List[BaseProcessGroup]:
-        raise NotImplementedError
+        """One process group per dimension: the real mesh's groups with the managed group at the replicate dimension."""
+        groups: List[BaseProcessGroup] = list(self._mesh.get_all_groups()) if self._mesh is not None else []
+        groups.insert(self.replicate_dim, self.replicate_pg)
+        return groups
 
     def __repr__(self) -> str:
         return f"ManagedDeviceMesh(mesh={self._mesh})"
