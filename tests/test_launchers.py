@@ -110,3 +110,40 @@ def test_stream_helpers_are_noops_without_an_accelerator():
         pass
     assert record_event() is None
     synchronize()
+
+
+def test_runner_restarts_a_group_after_an_injected_segfault(tmp_path):
+    """Punisher.inject("segfault") sends SIGSEGV to a group's trainer processes (not to its launcher); the launcher
+    reports the failure by exiting non-zero and the runner starts the group again."""
+    import threading
+    import time
+    from pathlib import Path
+
+    from torchft_b200.launch.runner import Punisher, Runner, _descendants
+
+    repo = Path(__file__).resolve().parent.parent
+    pid_file = str(tmp_path / "pids.json")
+    runner = Runner([str(repo / "tests" / "_sleepy_worker.py")], num_groups=1, base_port=24000 + os.getpid() % 4000,
+                    max_restarts=2, pid_file=pid_file, poll_secs=0.2, log_dir=str(tmp_path / "logs"),
+                    extra_env={"SLEEPY_DIR": str(tmp_path)})
+    result = {}
+    th = threading.Thread(target=lambda: result.setdefault("rc", runner.run()), daemon=True)
+    th.start()
+    try:
+        log0 = tmp_path / "logs" / "group_0.0.log"
+        end = time.monotonic() + 120
+        while not (log0.exists() and "incarnation 1" in log0.read_text()):
+            assert time.monotonic() < end and th.is_alive()
+            time.sleep(0.2)
+        assert Punisher(pid_file).inject("segfault", group=0) == 0
+        th.join(180)
+        assert not th.is_alive() and result.get("rc") == 0, result
+        assert "incarnation 2" in (tmp_path / "logs" / "group_0.1.log").read_text()
+    finally:
+        for gp in runner._groups:
+            if gp.proc is not None and gp.proc.poll() is None:
+                for q in _descendants(gp.proc.pid) + [gp.proc.pid]:
+                    try:
+                        os.kill(q, 9)
+                    except ProcessLookupError:
+                        pass
