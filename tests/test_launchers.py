@@ -147,3 +147,52 @@ def test_runner_restarts_a_group_after_an_injected_segfault(tmp_path):
                         os.kill(q, 9)
                     except ProcessLookupError:
                         pass
+
+
+def test_punisher_hang_stops_then_kills_the_group(tmp_path):
+    """Punisher.inject("hang"): the trainers are stopped (alive but silent) and, after ``hang_secs``, the whole group is
+    killed so that the runner replaces it."""
+    import threading
+    import time
+    from pathlib import Path
+
+    from torchft_b200.launch.runner import Punisher, Runner, _descendants
+
+    repo = Path(__file__).resolve().parent.parent
+    pid_file = str(tmp_path / "pids.json")
+    runner = Runner([str(repo / "tests" / "_sleepy_worker.py")], num_groups=1, base_port=20000 + os.getpid() % 4000,
+                    max_restarts=2, pid_file=pid_file, poll_secs=0.2, log_dir=str(tmp_path / "logs"),
+                    extra_env={"SLEEPY_DIR": str(tmp_path)})
+    result = {}
+    th = threading.Thread(target=lambda: result.setdefault("rc", runner.run()), daemon=True)
+    th.start()
+    try:
+        log0 = tmp_path / "logs" / "group_0.0.log"
+        end = time.monotonic() + 120
+        while not (log0.exists() and "incarnation 1" in log0.read_text()):
+            assert time.monotonic() < end and th.is_alive()
+            time.sleep(0.2)
+        trainer = _descendants(runner._groups[0].proc.pid, max_depth=1)[0]
+        stopper = threading.Thread(target=lambda: Punisher(pid_file).inject("hang", group=0, hang_secs=2.0), daemon=True)
+        stopper.start()
+        end = time.monotonic() + 10
+        state = ""
+        while time.monotonic() < end and state != "T":
+            try:
+                state = open(f"/proc/{trainer}/stat").read().rsplit(")", 1)[1].split()[0]
+            except OSError:
+                break
+            time.sleep(0.05)
+        assert state == "T"  # stopped, not dead
+        stopper.join(30)
+        th.join(180)
+        assert not th.is_alive() and result.get("rc") == 0, result
+        assert "incarnation 2" in (tmp_path / "logs" / "group_0.1.log").read_text()
+    finally:
+        for gp in runner._groups:
+            if gp.proc is not None and gp.proc.poll() is None:
+                for q in _descendants(gp.proc.pid) + [gp.proc.pid]:
+                    try:
+                        os.kill(q, 9)
+                    except ProcessLookupError:
+                        pass
