@@ -49,6 +49,35 @@ def _assert_same(a, b):
         assert abs(x - y) <= 1e-5 * max(1.0, abs(x)), (a["sums"], b["sums"])
 
 
+def _single_process_reference(steps):
+    """The same model, data and optimizer as tests/_fsdp_ft_worker.py without any parallelism: the mean gradient over
+    the batches of all (group, rank) pairs, SGD with momentum.  Initial weights are what init_sync leaves behind: the
+    recovery source rotates with the rank inside the group, so rank 0's shards (the first half of every parameter's
+    rows) are group 0's initial values and rank 1's shards are group 1's."""
+    import torch
+    from torch import nn
+
+    def init(seed):
+        torch.manual_seed(seed)
+        return nn.Sequential(nn.Linear(16, 32), nn.ReLU(), nn.Linear(32, 32), nn.ReLU(), nn.Linear(32, 8))
+
+    model, other = init(100), init(101)
+    with torch.no_grad():
+        for p, q in zip(model.parameters(), other.parameters()):
+            half = p.shape[0] // 2
+            p[half:].copy_(q[half:])
+    opt = torch.optim.SGD(model.parameters(), lr=0.05, momentum=0.9)
+    for step in range(steps):
+        opt.zero_grad()
+        for group in range(2):
+            for rank in range(2):
+                g = torch.Generator().manual_seed(1000 * group + 10 * rank + step)
+                x, y = torch.randn(8, 16, generator=g), torch.randn(8, 8, generator=g)
+                ((model(x) - y).square().mean() / 4).backward()
+        opt.step()
+    return [p.detach() for p in model.parameters()]
+
+
 @pytest.mark.timeout(400)
 def test_fsdp2_groups_agree_after_init_sync_and_training():
     lh = LighthouseServer("[::]:0", 2, join_timeout_ms=500, quorum_tick_ms=20, heartbeat_timeout_ms=2000)
@@ -63,6 +92,13 @@ def test_fsdp2_groups_agree_after_init_sync_and_training():
         for rank in range(2):  # same-numbered ranks hold the same shards
             _assert_same(r0[rank], r1[rank])
         assert r0[0]["sums"] != r0[1]["sums"]  # the two ranks of a group hold different shards
+        # and the shards are those of plain single-process training on the union of the four ranks' batches: the
+        # reduce-scatter inside a group and the managed all-reduce across groups together form the global mean gradient
+        want = _single_process_reference(steps=5)
+        for rank in range(2):
+            for got, full in zip(r0[rank]["sums"], want):
+                shard = full.chunk(2, dim=0)[rank]
+                assert abs(got - float(shard.double().sum())) <= 1e-4 * max(1.0, abs(got)), (rank, got, float(shard.double().sum()))
     finally:
         for p in procs:
             if p.poll() is None:
