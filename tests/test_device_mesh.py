@@ -182,7 +182,7 @@ def test_extend_device_mesh_inserts_a_registered_group():
     child = r'''
 import os, sys
 import torch, torch.distributed as dist
-os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="29972", RANK="0", WORLD_SIZE="1")
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(25000 + os.getpid() % 4000), RANK="0", WORLD_SIZE="1")
 dist.init_process_group("gloo", rank=0, world_size=1)
 from torch.distributed.device_mesh import init_device_mesh
 from torchft_b200.device_mesh import extend_device_mesh
