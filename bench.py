@@ -49,6 +49,10 @@ def _parse():
                     help="run a separate reduce-scatter kernel instead of storing weight-gradient tiles straight into "
                          "the shard owners' staging from the GEMM epilogue")
     ap.add_argument("--groups", type=int, default=0, help="replica groups (default: 1, 2, 2, 2 for 1, 2, 4, 8 GPUs)")
+    ap.add_argument("--ref-ac", default="auto", choices=["auto", "full", "selective", "none"],
+                    help="reference arm only: activation checkpointing of the torchtitan model (auto: full "
+                         "recomputation where the group is one GPU and the 8B state leaves no room, else "
+                         "torchtitan's per-op selective policy)")
     ap.add_argument("--watchdog-s", type=int, default=600,
                     help="dump every thread's stack and exit if the run has not finished after this many seconds")
     return ap.parse_args()
@@ -114,14 +118,14 @@ class ClockSampler:
 
 
 def _reference_arm(args):
-    # The reference's build backend (maturin + cargo/rustc for the torchft._torchft
-    # extension) is not installable offline on this image, so there is nothing to run.
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "reference cannot be installed offline: its build backend maturin (Rust/cargo, protoc) is "
-                       "absent, so torchft._torchft cannot be built and `import torchft` fails",
-    }))
-    return 0
+    """Runs the unmodified reference (``baseline/_ref/torchft``) on its stock path; see
+    ``baseline/reference_arm.py``.  Nothing of this package is imported in that process."""
+    sys.path.insert(0, os.path.join(REPO, "baseline"))
+    sys.path.remove(REPO)  # the product package stays out of the reference process
+    import reference_arm
+
+    args.clock_sampler = ClockSampler
+    return reference_arm.main(args)
 
 
 def main() -> int:

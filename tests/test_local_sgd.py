@@ -249,15 +249,36 @@ def test_flat_fragments_match_per_parameter_path(delay, alpha):
         backups = [f.original_parameters[n].clone() for f in d._fragments for n in sorted(f.original_parameters)]
         return [p.detach().clone() for p in model.parameters()], backups, hooks
 
-    p_ref, b_ref, _ = run(False)
+    p_ref, b_ref, hooks_ref = run(False)
     p_flat, b_flat, hooks = run(True)
     for a, b in zip(p_ref + b_ref, p_flat + b_flat):
         torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
-    # the healing state of a flat fragment round-trips, momentum included
+    # the healing state of a flat fragment has the per-parameter fragment's keys, and the outer
+    # optimizer's own state dict carries the momentum (a checkpoint of it restores the momentum)
     load, save = hooks["StreamingDiLoCoFragment_0"]
-    sd = save()
-    assert set(sd) == {"outer_optimizer", "original_parameters", "outer_momentum", "outer_steps"} and sd["outer_steps"] > 0
+    load_ref, save_ref = hooks_ref["StreamingDiLoCoFragment_0"]
+    sd, sd_ref = save(), save_ref()
+    assert set(sd) == set(sd_ref) == {"outer_optimizer", "original_parameters"}
+    mom = [st["momentum_buffer"] for st in sd["outer_optimizer"]["state"].values()]
+    mom_ref = [st["momentum_buffer"] for st in sd_ref["outer_optimizer"]["state"].values()]
+    assert len(mom) == len(mom_ref) > 0 and any(float(b.abs().max()) > 0 for b in mom)
+    for a, b in zip(mom, mom_ref):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    # the two layouts heal each other
+    load(sd_ref)
+    load_ref(sd)
     load(sd)
+
+
+def test_flat_fragment_detects_moved_parameter():
+    model = nn.Sequential(nn.Linear(4, 4))
+    inner = optim.SGD(model.parameters(), lr=0.1)
+    m = _delta_manager()
+    d = DiLoCo(m, [model], inner, optim.SGD(model.parameters(), lr=0.7, momentum=0.9, nesterov=True), sync_every=2,
+               flat_fragments=True)
+    model[0].weight.data = model[0].weight.data.clone()  # what .to() or load_state_dict(assign=True) does
+    with pytest.raises(RuntimeError, match="flat buffer"):
+        d._fragments[0].prepare_sync()
 
 
 def test_flat_fragments_reject_unsupported_outer_optimizer():

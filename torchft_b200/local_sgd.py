@@ -403,8 +403,9 @@ class _FlatDiLoCoFragment(_StreamingDiLoCoFragment):
     quantisation, reduction and averaging fused) and :func:`torchft_b200.ops.diloco.outer_step_`
     (momentum, Nesterov step, new backup, blend with the local weights).  The hyperparameters
     are read from the outer optimizer's single param group at every step, so LR schedulers on
-    it keep working; its momentum state lives in ``outer_momentum`` of the fragment's state
-    dict.  The scheduling and the state-dict key are those of the per-parameter fragment
+    it keep working; its ``momentum_buffer`` state entries are views of the flat momentum, so
+    ``outer_optimizer.state_dict()`` is what the per-parameter fragment would give and the two
+    layouts can heal each other.  The scheduling and the state-dict key are those of the per-parameter fragment
     (torchft/local_sgd.py:176-560).
     """
 
@@ -420,7 +421,7 @@ class _FlatDiLoCoFragment(_StreamingDiLoCoFragment):
         self._flat_backup = torch.zeros(padded, dtype=dtype, device=dev)
         self._flat_grad = torch.zeros(padded, dtype=dtype, device=dev)
         self._flat_momentum = torch.zeros(padded, dtype=torch.float32, device=dev)
-        self._outer_steps = 0
+        self._layout: List[Tuple[str, nn.Parameter, int, int]] = []
         off = 0
         with torch.no_grad():
             for name, p in self._model_fragment.named_parameters():
@@ -429,25 +430,64 @@ class _FlatDiLoCoFragment(_StreamingDiLoCoFragment):
                 view.copy_(p.data)
                 p.data = view
                 self.original_parameters[name] = self._flat_backup[off : off + k].view(p.shape)
+                self._layout.append((name, p, off, k))
                 off += k
+        self._publish_momentum()
+
+    def _publish_momentum(self) -> None:
+        """The outer optimizer's ``momentum_buffer`` entries are views of the flat momentum, so
+        ``outer_optimizer.state_dict()`` carries the momentum exactly as with the per-parameter
+        fragment (checkpoints written the reference's way keep working).  A zero buffer is the
+        same as torch's "no buffer yet": with dampening 0 the first step gives ``buf = grad``."""
+        owned = {id(q) for g in self._outer_optimizer.param_groups for q in g["params"]}
+        for _, p, off, k in self._layout:
+            if id(p) in owned:
+                self._outer_optimizer.state[p]["momentum_buffer"] = self._flat_momentum[off : off + k].view(p.shape)
+
+    def _adopt_momentum(self) -> None:
+        """After ``outer_optimizer.load_state_dict`` (which replaces state tensors by copies): take the
+        loaded buffers into the flat momentum and publish the views again."""
+        with torch.no_grad():
+            for _, p, off, k in self._layout:
+                buf = self._outer_optimizer.state.get(p, {}).get("momentum_buffer")
+                dst = self._flat_momentum[off : off + k]
+                if buf is None:
+                    dst.zero_()
+                elif buf.data_ptr() != dst.data_ptr():
+                    dst.copy_(buf.reshape(-1))
+        self._publish_momentum()
+
+    def _check_views(self) -> None:
+        """``model.to()``, ``load_state_dict(assign=True)`` or a later wrapper can re-point a parameter
+        away from the flat buffer; the fused kernels would then silently synchronise stale memory."""
+        base, es = self._flat_param.data_ptr(), self._flat_param.element_size()
+        for name, p, off, _ in self._layout:
+            if p.data_ptr() != base + off * es:
+                raise RuntimeError(
+                    f"parameter {name!r} no longer lives in its DiLoCo fragment's flat buffer (it was moved or "
+                    "re-assigned after DiLoCo was built); build DiLoCo after the last .to()/wrap, or pass "
+                    "flat_fragments=False")
 
     def register_state_dict_fn(self) -> None:
         key = f"StreamingDiLoCoFragment_{self._fragment_id}"
 
         def load_fn(sd: Dict[str, Any]) -> None:
+            # accepts what a per-parameter fragment (here or in the reference) saved, and the older
+            # flat layout that carried the momentum under "outer_momentum"
             for name, value in sd["original_parameters"].items():
                 if name in self.original_parameters:
                     self.original_parameters[name].copy_(value)
             self._outer_optimizer.load_state_dict(sd["outer_optimizer"])
-            self._flat_momentum.copy_(sd["outer_momentum"])
-            self._outer_steps = int(sd["outer_steps"])
+            if "outer_momentum" in sd:
+                self._flat_momentum.copy_(sd["outer_momentum"])
+                self._publish_momentum()
+            else:
+                self._adopt_momentum()
 
         def save_fn() -> Dict[str, Any]:
             return {
                 "outer_optimizer": self._outer_optimizer.state_dict(),
                 "original_parameters": {n: t.clone() for n, t in self.original_parameters.items()},
-                "outer_momentum": self._flat_momentum.clone(),
-                "outer_steps": self._outer_steps,
             }
 
         self._manager.register_state_dict_fn(key, load_fn, save_fn)
@@ -463,6 +503,7 @@ class _FlatDiLoCoFragment(_StreamingDiLoCoFragment):
     def prepare_sync(self) -> None:
         with torch.profiler.record_function("torchft::local_sgd::prepare_sync"), torch.no_grad():
             assert not self._allreduce_work
+            self._check_views()
             early = self._fragment_sync_delay > 0
             if early:
                 # inner steps go on while the exchange is in flight: take the difference now
@@ -494,8 +535,7 @@ class _FlatDiLoCoFragment(_StreamingDiLoCoFragment):
                 g = self._outer_optimizer.param_groups[0]
                 outer_step_(self._flat_grad, self._flat_momentum, self._flat_backup, self._flat_param, lr=float(g["lr"]),
                             momentum_coef=float(g.get("momentum", 0.0)), alpha=self._fragment_update_alpha,
-                            nesterov=bool(g.get("nesterov", False)), first_step=self._outer_steps == 0)
-                self._outer_steps += 1
+                            nesterov=bool(g.get("nesterov", False)), first_step=False)
             else:
                 # back to the last global weights; the manager step did not advance, so the window is retried
                 self._flat_param.copy_(self._flat_backup)
