@@ -160,8 +160,9 @@ def main(args) -> int:
         dev = torch.device("cuda", local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", str(29500 + (os.getpid() % 400)))
-    dist.init_process_group("gloo" if cpu else "nccl", rank=rank, world_size=world,
-                            **({} if cpu else {"device_id": dev}))
+    # no device_id: the reference's ProcessGroup.register() (torchft/process_group.py:326-345) creates a
+    # world-size-1 group of its own backend, which torch refuses on a default group bound to a device
+    dist.init_process_group("gloo" if cpu else "nccl", rank=rank, world_size=world)
 
     n_groups = args.groups if args.groups > 0 else (1 if world == 1 else 2)
     shard = world // n_groups
@@ -179,9 +180,9 @@ def main(args) -> int:
 
         ac_mode = args.ref_ac
         if ac_mode == "auto":
-            # 8B with fp32 master weights, fp32 gradients and AdamW moments is 128 GB when the group
-            # is one GPU: only full recomputation leaves room for the activations there
-            ac_mode = "full" if (shard == 1 and args.model == "llama3-8b") else "selective"
+            # torchtitan's stock Llama-3 8B setting (per-op selective checkpointing).  It fits at every
+            # layout (measured peak 131 GB where the group is one GPU) and is faster than full recomputation.
+            ac_mode = "selective"
         torch.manual_seed(1234)
         model, margs = build_model(args.model, S, dev, shard_mesh, ac_mode)
 
@@ -220,7 +221,7 @@ def main(args) -> int:
             if not cpu:
                 torch.cuda.synchronize()
             if world > 1:
-                dist.barrier()
+                dist.barrier(**({} if cpu else {"device_ids": [local_rank]}))
             if not cpu:
                 torch.cuda.synchronize()
 
@@ -334,6 +335,6 @@ def main(args) -> int:
             unavailable(f"reference arm failed at {world} GPU(s): {type(e).__name__}: {e}")
         os._exit(0)
     if world > 1:
-        dist.barrier()
+        dist.barrier(**({} if cpu else {"device_ids": [local_rank]}))
     dist.destroy_process_group()
     return 0

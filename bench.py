@@ -50,9 +50,8 @@ def _parse():
                          "the shard owners' staging from the GEMM epilogue")
     ap.add_argument("--groups", type=int, default=0, help="replica groups (default: 1, 2, 2, 2 for 1, 2, 4, 8 GPUs)")
     ap.add_argument("--ref-ac", default="auto", choices=["auto", "full", "selective", "none"],
-                    help="reference arm only: activation checkpointing of the torchtitan model (auto: full "
-                         "recomputation where the group is one GPU and the 8B state leaves no room, else "
-                         "torchtitan's per-op selective policy)")
+                    help="reference arm only: activation checkpointing of the torchtitan model (auto: torchtitan's "
+                         "stock per-op selective policy, the fastest setting that fits at every layout)")
     ap.add_argument("--watchdog-s", type=int, default=600,
                     help="dump every thread's stack and exit if the run has not finished after this many seconds")
     return ap.parse_args()

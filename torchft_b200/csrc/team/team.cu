@@ -265,6 +265,193 @@ __global__ void __launch_bounds__(512) p2p_copy_kernel(const CopySeg* __restrict
   }
 }
 
+// One-shot allreduce for small messages: every rank publishes its data in a symmetric
+// window, one ready round, then every rank sums all ranks' copies itself (same order on
+// every rank, so the results are bit-identical) and writes only to its own output.  Nothing
+// is written into a peer, so no done round is needed: the window has two halves that the
+// caller alternates, and passing the ready round of call k proves that every peer has left
+// call k-1, whose half is the one call k+1 overwrites.
+struct OneShotArgs {
+  void* bufs[MAX_RANKS];  // this call's half of the window in every rank's arena
+  const void* user_in;
+  void* user_out;
+  long long n;  // elements, multiple of the vector width
+  float scale;
+  int zero_contribution;
+};
+
+template <typename T>
+__device__ __forceinline__ void allreduce_oneshot_body(const TeamParams& tp, const OneShotArgs& a) {
+  __shared__ int sh_code;
+  constexpr int V = Vec<T>::N;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  T* mine = reinterpret_cast<T*>(a.bufs[tp.rank]);
+  const T* src = reinterpret_cast<const T*>(a.user_in);
+  for (long long i = tid * V; i < a.n; i += nthreads * V) {
+    float f[V];
+    if (a.zero_contribution) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) f[e] = 0.f;
+    } else {
+      Vec<T>::load(src + i, f);
+    }
+    Vec<T>::store(mine + i, f);
+  }
+  if (!grid_arrive(tp, 2, &sh_code)) return;
+  if (!team_round(tp, /*slot=*/0, /*go=*/0, &sh_code)) return;
+  T* dst = reinterpret_cast<T*>(a.user_out);
+  for (long long i = tid * V; i < a.n; i += nthreads * V) {
+    uint4 raw[MAX_RANKS];
+#pragma unroll
+    for (int p = 0; p < MAX_RANKS; ++p)
+      if (p < tp.world) raw[p] = *reinterpret_cast<const uint4*>(reinterpret_cast<const T*>(a.bufs[p]) + i);
+    float acc[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] = 0.f;
+#pragma unroll
+    for (int p = 0; p < MAX_RANKS; ++p) {
+      if (p < tp.world) {
+        float f[V];
+        Vec<T>::load(reinterpret_cast<const T*>(&raw[p]), f);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] += f[e];
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] *= a.scale;
+    Vec<T>::store(dst + i, acc);
+  }
+}
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_oneshot_kernel(const TeamParams tp, const OneShotArgs a) {
+  allreduce_oneshot_body<T>(tp, a);
+}
+template <typename T>
+__global__ void __launch_bounds__(512) allreduce_oneshot_emul_kernel(const TeamParams* tps, const OneShotArgs* as) {
+  allreduce_oneshot_body<T>(tps[blockIdx.y], as[blockIdx.y]);
+}
+
+// Generic pull: after a ready round every rank copies up to MAX_RANKS segments (peer or local
+// source, local destination); a done round keeps the sources valid until every reader is
+// through.  Broadcast is one segment from the root's window, all-to-all is one segment per
+// peer, a gather is `world` segments on the root and none elsewhere.
+struct PullArgs {
+  const void* src[MAX_RANKS];
+  void* dst[MAX_RANKS];
+  long long bytes[MAX_RANKS];  // multiples of 16
+  int nsegs;
+};
+
+__device__ __forceinline__ void copy16(const void* src, void* dst, long long bytes, long long tid, long long nthreads) {
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  const long long nv = bytes / 16;
+  constexpr int U = 8;  // independent 16-byte loads in flight per thread
+  for (long long i0 = tid; i0 < nv; i0 += nthreads * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < nv) v[u] = s[i];
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * nthreads;
+      if (i < nv) d[i] = v[u];
+    }
+  }
+}
+
+__device__ __forceinline__ void pull_body(const TeamParams& tp, const PullArgs& a) {
+  __shared__ int sh_code;
+  if (!team_round(tp, 0, 0, &sh_code)) return;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int s = 0; s < a.nsegs; ++s) {
+    // start at a rank-dependent segment so that the ranks do not all read the same peer at once
+    const int k = (s + tp.rank) % a.nsegs;
+    copy16(a.src[k], a.dst[k], a.bytes[k], tid, nthreads);
+  }
+  if (!grid_arrive(tp, 3, &sh_code)) return;
+  team_round(tp, 1, 1, &sh_code);
+}
+__global__ void __launch_bounds__(512) pull_kernel(const TeamParams tp, const PullArgs a) { pull_body(tp, a); }
+__global__ void __launch_bounds__(512) pull_emul_kernel(const TeamParams* tps, const PullArgs* as) {
+  pull_body(tps[blockIdx.y], as[blockIdx.y]);
+}
+
+// Point-to-point transfer between two ranks of a team, one launch on each side.  The sender
+// has put the payload into its symmetric send window (stream-ordered before this kernel),
+// tells the receiver so (flag slot 2) and waits until the receiver has taken it (slot 3);
+// the receiver waits for the payload, pulls it over NVLink into its destination and says
+// so.  Tokens count per ordered pair of ranks, so other ranks of the team are not involved.
+// Local words 4 (go) and 5 (arrival counter) are this kernel's own: a transfer may run on
+// another stream than the team's collectives.  All waits are bounded like the collectives'.
+struct SendRecvArgs {
+  int peer;
+  int is_send;
+  uint64_t token;
+  const void* src;  // receiver: the sender's window (peer-mapped)
+  void* dst;        // receiver: local destination
+  long long bytes;  // multiple of 16
+};
+
+__device__ __forceinline__ void sendrecv_body(const TeamParams& tp, const SendRecvArgs& a) {
+  __shared__ int sh_code;
+  const uint64_t t0 = ftb200::globaltimer_ns();
+  TeamParams tq = tp;
+  tq.token = a.token;
+  if (a.is_send) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) {
+      __threadfence_system();
+      st_release_sys(tp.flags[a.peer] + 2 * MAX_RANKS + tp.rank, a.token);
+      const int code = wait_equal<true>(tp.flags[tp.rank] + 3 * MAX_RANKS + a.peer, a.token, tq, t0);
+      if (code != FTB200_ST_OK && tp.status != nullptr) atomicMax(tp.status, code);
+    }
+    return;
+  }
+  uint64_t* go = tp.local_sync + 4;
+  uint64_t* ctr = tp.local_sync + 5;
+  if (threadIdx.x == 0) {
+    int code;
+    if (blockIdx.x == 0) {
+      code = wait_equal<true>(tp.flags[tp.rank] + 2 * MAX_RANKS + a.peer, a.token, tq, t0);
+      if (code != FTB200_ST_OK && tp.status != nullptr) atomicMax(tp.status, code);
+      st_release_gpu(go, code == FTB200_ST_OK ? a.token : GO_ABORT);
+    } else {
+      code = wait_equal<false>(go, a.token, tq, t0);
+      if (code == FTB200_ST_TIMEOUT && tp.status != nullptr) atomicMax(tp.status, code);
+    }
+    sh_code = code;
+  }
+  __syncthreads();
+  if (sh_code != FTB200_ST_OK) return;
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  copy16(a.src, a.dst, a.bytes, tid, nthreads);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    atomicAdd(reinterpret_cast<unsigned long long*>(ctr), 1ull);
+    if (blockIdx.x == 0) {
+      uint32_t spins = 0;
+      int code = FTB200_ST_OK;
+      while (ld_acquire_gpu(ctr) < gridDim.x) {
+        if ((++spins & 15u) == 0 && ftb200::globaltimer_ns() - t0 > tp.timeout_ns) { code = FTB200_ST_TIMEOUT; break; }
+      }
+      st_release_gpu(ctr, 0);
+      if (code != FTB200_ST_OK && tp.status != nullptr) atomicMax(tp.status, code);
+      // the sender may reuse its window now (also after a local failure: it must not wait for nothing)
+      st_release_sys(tp.flags[a.peer] + 3 * MAX_RANKS + tp.rank, a.token);
+    }
+  }
+}
+__global__ void __launch_bounds__(512) sendrecv_kernel(const TeamParams tp, const SendRecvArgs a) { sendrecv_body(tp, a); }
+__global__ void __launch_bounds__(512) sendrecv_emul_kernel(const TeamParams* tps, const SendRecvArgs* as) {
+  sendrecv_body(tps[blockIdx.y], as[blockIdx.y]);
+}
+
 int grid_for_bytes(long long bytes) {
   // enough CTAs to saturate NVLink without starving concurrent compute of SMs
   long long g = bytes / (512 * 16 * 4);
@@ -371,6 +558,73 @@ FTB200_API int ftb200_team_barrier(const ftb200_team_desc* d, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
+// One-shot allreduce of a small message (see allreduce_oneshot_body).  bufs[i] is this call's half
+// of the small-message window in rank i's arena; user_in/user_out are local (may be the same tensor).
+FTB200_API int ftb200_team_allreduce_oneshot(const ftb200_team_desc* d, void* const* bufs, const void* user_in,
+                                             void* user_out, long long n, int dtype, float scale, int zero_contribution,
+                                             cudaStream_t st) {
+  if (d->world < 1 || d->world > MAX_RANKS || n <= 0 || user_out == nullptr) return FTB200_E_BADARG;
+  if (user_in == nullptr && !zero_contribution) return FTB200_E_BADARG;
+  const int V = dtype == 0 ? 8 : 4;
+  if (n % V) return FTB200_E_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(user_in) | reinterpret_cast<uintptr_t>(user_out)) & 15) return FTB200_E_ALIGN;
+  OneShotArgs a;
+  for (int i = 0; i < MAX_RANKS; ++i) a.bufs[i] = i < d->world ? bufs[i] : nullptr;
+  a.user_in = user_in;
+  a.user_out = user_out;
+  a.n = n;
+  a.scale = scale;
+  a.zero_contribution = zero_contribution;
+  const long long vecs = n / V;
+  const int grid = static_cast<int>(std::max<long long>(1, std::min<long long>(16, (vecs + 511) / 512)));
+  if (dtype == 0)
+    allreduce_oneshot_kernel<__nv_bfloat16><<<grid, 512, 0, st>>>(to_params(d), a);
+  else
+    allreduce_oneshot_kernel<float><<<grid, 512, 0, st>>>(to_params(d), a);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+// Generic pull collective (see pull_body): src/dst/bytes describe this rank's nsegs copies.
+FTB200_API int ftb200_team_pull(const ftb200_team_desc* d, const void* const* src, void* const* dst,
+                                const long long* bytes, int nsegs, int ctas, cudaStream_t st) {
+  if (d->world < 1 || d->world > MAX_RANKS || nsegs < 0 || nsegs > MAX_RANKS) return FTB200_E_BADARG;
+  PullArgs a;
+  long long total = 0;
+  for (int i = 0; i < MAX_RANKS; ++i) {
+    a.src[i] = i < nsegs ? src[i] : nullptr;
+    a.dst[i] = i < nsegs ? dst[i] : nullptr;
+    a.bytes[i] = i < nsegs ? bytes[i] : 0;
+    if (i < nsegs) {
+      if (bytes[i] < 0 || (bytes[i] % 16)) return FTB200_E_ALIGN;
+      if ((reinterpret_cast<uintptr_t>(src[i]) | reinterpret_cast<uintptr_t>(dst[i])) & 15) return FTB200_E_ALIGN;
+      total += bytes[i];
+    }
+  }
+  a.nsegs = nsegs;
+  const int grid = ctas > 0 ? ctas : grid_for_bytes(total);
+  pull_kernel<<<grid, 512, 0, st>>>(to_params(d), a);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+// One side of a point-to-point transfer (see sendrecv_body).  pair_token = epoch << 32 | count of
+// transfers from the sender to the receiver so far, the same on both sides.
+FTB200_API int ftb200_team_sendrecv(const ftb200_team_desc* d, int peer, int is_send, unsigned long long pair_token,
+                                    const void* src, void* dst, long long bytes, int ctas, cudaStream_t st) {
+  if (d->world < 2 || d->world > MAX_RANKS || peer < 0 || peer >= d->world || peer == d->rank) return FTB200_E_BADARG;
+  if (bytes < 0 || (bytes % 16)) return FTB200_E_ALIGN;
+  if (!is_send && ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 15)) return FTB200_E_ALIGN;
+  SendRecvArgs a;
+  a.peer = peer;
+  a.is_send = is_send;
+  a.token = pair_token;
+  a.src = src;
+  a.dst = dst;
+  a.bytes = bytes;
+  const int grid = is_send ? 1 : (ctas > 0 ? ctas : std::max(grid_for_bytes(bytes), 1));
+  sendrecv_kernel<<<grid, is_send ? 32 : 512, 0, st>>>(to_params(d), a);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
 // segs: device array of {src, dst, bytes}; the caller keeps it alive until the stream reaches the kernel.
 FTB200_API int ftb200_p2p_copy(const void* segs_dev, int nsegs, long long total_bytes, const void* abort_word, int* status,
                                int ctas, cudaStream_t st) {
@@ -458,6 +712,73 @@ FTB200_API int ftb200_team_reduce_scatter_emulated(const ftb200_team_desc* descs
   }
   if (dtype == 0) return launch_emulated(reduce_scatter_emul_kernel<__nv_bfloat16>, tps, as, ctas > 0 ? ctas : 4, st);
   return launch_emulated(reduce_scatter_emul_kernel<float>, tps, as, ctas > 0 ? ctas : 4, st);
+}
+
+FTB200_API int ftb200_team_allreduce_oneshot_emulated(const ftb200_team_desc* descs, int launch_ranks, void* const* bufs,
+                                                      void* const* user_in, void* const* user_out, long long n,
+                                                      int dtype, float scale, int ctas, cudaStream_t st) {
+  const int world = descs[0].world;
+  std::vector<TeamParams> tps;
+  std::vector<OneShotArgs> as;
+  for (int r = 0; r < launch_ranks; ++r) {
+    tps.push_back(to_params(&descs[r]));
+    OneShotArgs a;
+    for (int i = 0; i < MAX_RANKS; ++i) a.bufs[i] = i < world ? bufs[i] : nullptr;
+    a.user_in = user_in[r];
+    a.user_out = user_out[r];
+    a.n = n;
+    a.scale = scale;
+    a.zero_contribution = 0;
+    as.push_back(a);
+  }
+  if (dtype == 0) return launch_emulated(allreduce_oneshot_emul_kernel<__nv_bfloat16>, tps, as, ctas > 0 ? ctas : 2, st);
+  return launch_emulated(allreduce_oneshot_emul_kernel<float>, tps, as, ctas > 0 ? ctas : 2, st);
+}
+
+// src/dst/bytes: [launch_ranks][MAX_RANKS] row-major; nsegs: [launch_ranks].
+FTB200_API int ftb200_team_pull_emulated(const ftb200_team_desc* descs, int launch_ranks, const void* const* src,
+                                         void* const* dst, const long long* bytes, const int* nsegs, int ctas,
+                                         cudaStream_t st) {
+  std::vector<TeamParams> tps;
+  std::vector<PullArgs> as;
+  for (int r = 0; r < launch_ranks; ++r) {
+    tps.push_back(to_params(&descs[r]));
+    PullArgs a;
+    for (int i = 0; i < MAX_RANKS; ++i) {
+      a.src[i] = src[r * MAX_RANKS + i];
+      a.dst[i] = dst[r * MAX_RANKS + i];
+      a.bytes[i] = bytes[r * MAX_RANKS + i];
+    }
+    a.nsegs = nsegs[r];
+    as.push_back(a);
+  }
+  return launch_emulated(pull_emul_kernel, tps, as, ctas > 0 ? ctas : 4, st);
+}
+
+// Both sides of one transfer in one cooperative launch: descs[0] sends, descs[1] receives
+// (launch_ranks = 1 launches the receiver only, whose wait then runs out).
+FTB200_API int ftb200_team_sendrecv_emulated(const ftb200_team_desc* send_desc, const ftb200_team_desc* recv_desc,
+                                             int launch_sender, unsigned long long pair_token, const void* src, void* dst,
+                                             long long bytes, int ctas, cudaStream_t st) {
+  std::vector<TeamParams> tps;
+  std::vector<SendRecvArgs> as;
+  SendRecvArgs r;
+  r.peer = send_desc->rank;
+  r.is_send = 0;
+  r.token = pair_token;
+  r.src = src;
+  r.dst = dst;
+  r.bytes = bytes;
+  tps.push_back(to_params(recv_desc));
+  as.push_back(r);
+  if (launch_sender) {
+    SendRecvArgs s = r;
+    s.peer = recv_desc->rank;
+    s.is_send = 1;
+    tps.push_back(to_params(send_desc));
+    as.push_back(s);
+  }
+  return launch_emulated(sendrecv_emul_kernel, tps, as, ctas > 0 ? ctas : 4, st);
 }
 
 // Export the allocation that contains `ptr` (any device pointer obtained from cudaMalloc,

@@ -302,9 +302,29 @@ class ShardedLlamaTrainer:
             self.manager.start_quorum()
         loss = self.forward_backward(tokens, targets)
         self._finish_comm()
+        self._check_shard_team()
         if self.manager is None or self.manager.should_commit():
             self.optimizer_step()
         return loss
+
+    def _check_shard_team(self) -> None:
+        """A shard-group kernel (all-gather, reduce-scatter, the GEMM-fused reduce stage) that ran into its
+        deadline or an abort returns with stale parameters or partial gradients behind it and says so only in
+        the team's status word.  Read it before the vote: with a manager the step is declined (and the error
+        latched, so the healthy groups do not average this group's gradients in); without one it raises."""
+        team = getattr(self.comm, "team", None)
+        if team is None:
+            return
+        code = team.status()
+        if code == 0:
+            return
+        from ..ops import _native as N
+        from .team import TeamError
+
+        err = TeamError(f"shard-group collective failed: {N.STATUS.get(code, code)}")
+        if self.manager is None:
+            raise err
+        self.manager.report_error(err)
 
     def invalidate_gathered(self, units) -> None:
         """The shards of ``units`` were rewritten outside :meth:`optimizer_step`: gather them

@@ -202,6 +202,13 @@ class SymmetricTeam:
         d.status = self._status.data_ptr()
         return d
 
+    def _desc_nocount(self) -> _TeamDesc:
+        """Descriptor for a point-to-point kernel: those count per pair of ranks, so the team's
+        collective sequence number (which every rank must advance identically) stays untouched."""
+        with self._lock:
+            self._seq -= 1
+        return self._desc()
+
     def _peer_ptrs(self, off: int) -> ctypes.Array:
         arr = (ctypes.c_void_p * MAX_RANKS)()
         for p in range(self.world):
@@ -263,6 +270,42 @@ class SymmetricTeam:
         d = self._desc()
         N.check(self.lib.ftb200_team_barrier(ctypes.byref(d), N.stream_ptr()), "team_barrier")
 
+    def allreduce_oneshot(self, half_off: int, src: torch.Tensor, dst: torch.Tensor, scale: float = 1.0,
+                          zero_contribution: bool = False) -> None:
+        """Small-message allreduce: one round instead of two.  ``half_off`` is the half of the small-message window
+        that this call uses (callers alternate the halves); ``src``/``dst`` are local, 16-byte aligned, and may be
+        the same tensor."""
+        d = self._desc()
+        N.check(
+            self.lib.ftb200_team_allreduce_oneshot(ctypes.byref(d), self._peer_ptrs(half_off), N.ptr(src), N.ptr(dst),
+                                                   ctypes.c_longlong(src.numel()), ctypes.c_int(_DT[src.dtype]),
+                                                   ctypes.c_float(scale), ctypes.c_int(int(zero_contribution)),
+                                                   N.stream_ptr()),
+            "team_allreduce_oneshot",
+        )
+
+    def pull(self, segs: List[tuple], ctas: int = 0) -> None:
+        """One collective launch in which this rank copies ``segs`` = ``[(src_ptr, dst_ptr, nbytes), ...]`` (at most
+        one per rank; peer or local sources) between a ready and a done round.  Every rank of the team calls it, with
+        an empty list if it has nothing to fetch."""
+        src = (ctypes.c_void_p * MAX_RANKS)()
+        dst = (ctypes.c_void_p * MAX_RANKS)()
+        nb = (ctypes.c_longlong * MAX_RANKS)()
+        for i, (sp, dp, b) in enumerate(segs):
+            src[i], dst[i], nb[i] = sp, dp, b
+        d = self._desc()
+        N.check(self.lib.ftb200_team_pull(ctypes.byref(d), src, dst, nb, ctypes.c_int(len(segs)),
+                                          ctypes.c_int(ctas or DEFAULT_CTAS), N.stream_ptr()), "team_pull")
+
+    def sendrecv(self, peer: int, is_send: bool, pair_seq: int, src_ptr: int, dst_ptr: int, nbytes: int) -> None:
+        """One side of a point-to-point transfer; ``pair_seq`` counts the transfers of this ordered pair."""
+        d = self._desc_nocount()
+        token = (self.epoch << 32) | (pair_seq & 0xFFFFFFFF)
+        N.check(self.lib.ftb200_team_sendrecv(ctypes.byref(d), ctypes.c_int(peer), ctypes.c_int(int(is_send)),
+                                              ctypes.c_ulonglong(token), ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr),
+                                              ctypes.c_longlong(nbytes), ctypes.c_int(DEFAULT_CTAS), N.stream_ptr()),
+                "team_sendrecv")
+
 
 # ======================================================================================= FSDP
 
@@ -305,6 +348,10 @@ class PeerShardComm(ShardComm):
 
         self.team.connect(_ListStore(), self.rank, self.size, epoch=1)  # type: ignore[arg-type]
         dist.barrier(group=group)
+        # scalars (the gradient norm) are reduced through the team too, so that nothing inside a step
+        # is out of reach of the team's abort word and deadline
+        self._scalar_n = 4 * MAX_RANKS
+        self._scalar = self.alloc(self._scalar_n, torch.float32, self.device)
 
     def alloc(self, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
         es = torch.empty((), dtype=dtype).element_size()
@@ -324,7 +371,14 @@ class PeerShardComm(ShardComm):
         self.team.reduce_scatter(self._off(full), shard, shard.numel(), shard.dtype)
 
     def all_reduce_sum_(self, t: torch.Tensor) -> None:
-        dist.all_reduce(t, group=self.group)
+        n = t.numel()
+        if t.dtype != torch.float32 or n > self._scalar_n:
+            dist.all_reduce(t, group=self.group)
+            return
+        self._scalar.zero_()
+        self._scalar[:n].copy_(t.reshape(-1))
+        self.team.allreduce_(self._off(self._scalar), self._scalar_n, torch.float32, ctas=1)
+        t.copy_(self._scalar[:n].view(t.shape))
 
     # ---- GEMM-fused reduce-scatter ------------------------------------------------------------
     supports_fused_scatter = True
@@ -384,23 +438,44 @@ class ProcessGroupB200(ProcessGroup):
     ``configure`` keeps this rank's arena, bumps the epoch, exchanges IPC handles under the
     given store prefix and maps the new peers.  ``allreduce`` is one fused kernel: stage
     (unless the tensor already lives in the arena, see :meth:`alloc`), two-shot reduce with
-    fp32 accumulation, ``scale`` (the manager passes ``1/num_participants``), write back.
+    fp32 accumulation, ``scale`` (the manager passes ``1/num_participants``), write back;
+    messages up to 256 KB take a one-shot kernel with a single cross-rank round.
     ``abort`` is a store to a host-mapped word that all kernels poll; ``errored`` reads the
-    status word after synchronising the stream.  Supported: allreduce (SUM, and AVG via
-    scale), barrier, and send/recv/broadcast through a staging window for checkpoint
-    transfer.  bf16 and fp32 tensors.
+    status word after synchronising the stream.
+
+    The rest of the c10d surface of the reference's groups (torchft/process_group.py:141-280)
+    is built from three more kernels over a staging window of the arena: a generic *pull*
+    (ready round, copies from peers' windows, done round) carries ``allgather``,
+    ``allgather_into_tensor_coalesced``, ``broadcast``/``broadcast_one`` and ``alltoall_base``
+    (equal splits) for any dtype; the pulling reduce-scatter carries ``reduce_scatter`` and
+    ``reduce_scatter_tensor_coalesced`` (SUM/AVG, bf16/fp32); ``send``/``recv`` are a pair of
+    kernels that hand a window from one rank to another without involving the rest of the
+    team.  All of them are ordered on the current stream and return a stream-ordered work.
+    A rank must not post a ``send`` to a peer that is itself blocked in a ``send`` to this
+    rank on the same stream (as with NCCL outside of a group call).
     """
 
     supports_fused_scale = True
 
+    SMALL_BYTES = 256 << 10  # messages up to this size take the one-shot allreduce
+
     def __init__(self, timeout: timedelta = timedelta(seconds=60), arena_bytes: int = 1 << 30,
-                 staging_bytes: int = 256 << 20, device: Optional[torch.device] = None) -> None:
+                 staging_bytes: int = 256 << 20, device: Optional[torch.device] = None,
+                 p2p_bytes: int = 64 << 20) -> None:
         super().__init__(0, 1)
         self._timeout = timeout
         self._device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self._team = SymmetricTeam(self._device, arena_bytes + staging_bytes + (1 << 16), timeout)
+        self._team = SymmetricTeam(self._device, arena_bytes + staging_bytes + p2p_bytes + 2 * self.SMALL_BYTES + (1 << 16),
+                                   timeout)
         self._staging_bytes = staging_bytes
         self._staging_off = self._team.arena.alloc(staging_bytes)
+        # send window of point-to-point transfers: its own, because a transfer (live recovery on
+        # the manager's recovery stream) may run beside a collective that uses the staging window
+        self._p2p_bytes = p2p_bytes // 16 * 16
+        self._p2p_off = self._team.arena.alloc(p2p_bytes)
+        self._small_off = self._team.arena.alloc(2 * self.SMALL_BYTES)
+        self._small_calls = 0
+        self._pair_seq: Dict[tuple, int] = {}
         self._rank, self._world = 0, 1
         self._errored: Optional[Exception] = None
         self._configured = False
@@ -424,6 +499,8 @@ class ProcessGroupB200(ProcessGroup):
             epoch = self._epoch
         self._team.connect(store, rank, world_size, epoch)
         self._rank, self._world = rank, world_size
+        self._small_calls = 0
+        self._pair_seq = {}
         self._errored = None
         self._configured = True
 
@@ -483,6 +560,18 @@ class ProcessGroupB200(ProcessGroup):
         if off is not None and n % gran == 0 and off % 16 == 0:
             self._team.allreduce_(off, n, t.dtype, scale, zero_contribution=zero)
             return
+        if n * es <= self.SMALL_BYTES:
+            vec = 16 // es
+            half = self._small_off + (self._small_calls % 2) * self.SMALL_BYTES
+            self._small_calls += 1
+            if n % vec == 0 and flat.data_ptr() % 16 == 0:
+                self._team.allreduce_oneshot(half, flat, flat, scale, zero_contribution=zero)
+            else:
+                tmp = torch.zeros((n + vec - 1) // vec * vec, dtype=t.dtype, device=t.device)
+                tmp[:n].copy_(flat)
+                self._team.allreduce_oneshot(half, tmp, tmp, scale, zero_contribution=zero)
+                flat.copy_(tmp[:n])
+            return
         # staged path, in chunks of the staging window
         cap = (self._staging_bytes // es) // gran * gran
         pos = 0
@@ -533,12 +622,223 @@ class ProcessGroupB200(ProcessGroup):
         self._team.barrier()
         return _StreamWork(self, None)
 
-    # point-to-point through the staging window (used by the PG checkpoint transport)
-    def send(self, tensors: List[torch.Tensor], dst_rank: int, tag: int) -> Work:
-        raise NotImplementedError("use P2PTransport for state transfer over peer memory")
+    def allreduce_coalesced(self, tensors: List[torch.Tensor], opts=None) -> Work:
+        return self.allreduce(tensors, opts)
 
-    def recv(self, tensors: List[torch.Tensor], src_rank: int, tag: int) -> Work:
-        raise NotImplementedError("use P2PTransport for state transfer over peer memory")
+    # ---- byte-moving collectives over the staging window --------------------------------------------
+    @staticmethod
+    def _u8(t: torch.Tensor) -> torch.Tensor:
+        if not t.is_contiguous():
+            raise ValueError("ProcessGroupB200 collectives need contiguous tensors")
+        return t.view(-1).view(torch.uint8)
+
+    def _check_cuda(self, *tensors: torch.Tensor) -> None:
+        for t in tensors:
+            if t.device != self._device:
+                raise ValueError(f"tensor on {t.device}, group on {self._device}")
+
+    def _stage(self, nbytes: int) -> torch.Tensor:
+        return self._team.arena.bytes_view[self._staging_off : self._staging_off + nbytes]
+
+    def _gather_bytes(self, out_u8: torch.Tensor, in_u8: torch.Tensor) -> None:
+        """out_u8[p * nb : (p + 1) * nb] = rank p's in_u8."""
+        nb, world = in_u8.numel(), self._world
+        if world == 1:
+            out_u8.copy_(in_u8)
+            return
+        cap = self._staging_bytes // 16 * 16
+        direct = nb % 16 == 0 and out_u8.data_ptr() % 16 == 0
+        pos = 0
+        while pos < nb:
+            m = min(cap, nb - pos)
+            mp = (m + 15) // 16 * 16
+            self._stage(mp)[:m].copy_(in_u8[pos : pos + m])
+            tmp = None if direct else torch.empty(world * mp, dtype=torch.uint8, device=self._device)
+            segs = []
+            for p in range(world):
+                dst = out_u8.data_ptr() + p * nb + pos if direct else tmp.data_ptr() + p * mp
+                segs.append((self._team.peer_base[p] + self._staging_off, dst, mp))
+            self._team.pull(segs)
+            if tmp is not None:
+                for p in range(world):
+                    out_u8[p * nb + pos : p * nb + pos + m].copy_(tmp[p * mp : p * mp + m])
+            pos += m
+
+    def allgather_into_tensor_coalesced(self, output_tensors: List[torch.Tensor], input_tensors: List[torch.Tensor],
+                                        opts=None) -> Work:
+        for out, inp in zip(output_tensors, input_tensors):
+            self._check_cuda(out, inp)
+            if out.numel() != inp.numel() * self._world or out.dtype != inp.dtype:
+                raise ValueError("allgather_into_tensor: output must hold world_size inputs of the same dtype")
+            self._gather_bytes(self._u8(out), self._u8(inp.contiguous()))
+        return _StreamWork(self, output_tensors)
+
+    def allgather(self, output_tensors: List[List[torch.Tensor]], input_tensor: List[torch.Tensor], opts=None) -> Work:
+        for outs, inp in zip(output_tensors, input_tensor):
+            self._check_cuda(inp, *outs)
+            if len(outs) != self._world:
+                raise ValueError("allgather: one output tensor per rank")
+            flat = torch.empty(self._world * inp.numel(), dtype=inp.dtype, device=self._device)
+            self._gather_bytes(self._u8(flat), self._u8(inp.contiguous()))
+            for p, o in enumerate(outs):
+                o.copy_(flat[p * inp.numel() : (p + 1) * inp.numel()].view(inp.shape))
+        return _StreamWork(self, output_tensors)
+
+    def broadcast(self, tensor_list: List[torch.Tensor], opts=None) -> Work:
+        root = int(getattr(opts, "rootRank", 0)) if opts is not None else 0
+        for t in tensor_list:
+            self._check_cuda(t)
+            if self._world == 1:
+                continue
+            contiguous = t if t.is_contiguous() else t.contiguous()
+            u8 = self._u8(contiguous)
+            nb = u8.numel()
+            cap = self._staging_bytes // 16 * 16
+            direct = u8.data_ptr() % 16 == 0
+            pos = 0
+            while pos < nb:
+                m = min(cap, nb - pos)
+                mp = (m + 15) // 16 * 16
+                direct_here = direct and m % 16 == 0
+                if self._rank == root:
+                    self._stage(mp)[:m].copy_(u8[pos : pos + m])
+                    self._team.pull([])
+                else:
+                    tmp = None if direct_here else torch.empty(mp, dtype=torch.uint8, device=self._device)
+                    dst = u8.data_ptr() + pos if direct_here else tmp.data_ptr()
+                    self._team.pull([(self._team.peer_base[root] + self._staging_off, dst, mp)])
+                    if tmp is not None:
+                        u8[pos : pos + m].copy_(tmp[:m])
+                pos += m
+            if contiguous is not t:
+                t.copy_(contiguous)
+        return _StreamWork(self, tensor_list)
+
+    def alltoall_base(self, output_buffer: torch.Tensor, input_buffer: torch.Tensor, output_split_sizes: List[int],
+                      input_split_sizes: List[int], opts=None) -> Work:
+        world = self._world
+        for splits, buf in ((output_split_sizes, output_buffer), (input_split_sizes, input_buffer)):
+            if splits and (len(splits) != world or len(set(splits)) != 1):
+                raise NotImplementedError("ProcessGroupB200.alltoall_base supports equal splits only")
+        self._check_cuda(output_buffer, input_buffer)
+        out_u8, in_u8 = self._u8(output_buffer), self._u8(input_buffer.contiguous())
+        if out_u8.numel() != in_u8.numel() or in_u8.numel() % world:
+            raise ValueError("alltoall_base: buffers must have the same size, divisible by the world size")
+        if world == 1:
+            out_u8.copy_(in_u8)
+            return _StreamWork(self, output_buffer)
+        chunk = in_u8.numel() // world
+        cap = (self._staging_bytes // world) // 16 * 16
+        direct = chunk % 16 == 0 and out_u8.data_ptr() % 16 == 0
+        in2, out2 = in_u8.view(world, chunk), out_u8.view(world, chunk)
+        pos = 0
+        while pos < chunk:
+            m = min(cap, chunk - pos)
+            mp = (m + 15) // 16 * 16
+            self._stage(world * mp).view(world, mp)[:, :m].copy_(in2[:, pos : pos + m])
+            tmp = None if direct else torch.empty(world, mp, dtype=torch.uint8, device=self._device)
+            segs = []
+            for p in range(world):
+                dst = out_u8.data_ptr() + p * chunk + pos if direct else tmp.data_ptr() + p * mp
+                segs.append((self._team.peer_base[p] + self._staging_off + self._rank * mp, dst, mp))
+            self._team.pull(segs)
+            if tmp is not None:
+                out2[:, pos : pos + m].copy_(tmp[:, :m])
+            pos += m
+        return _StreamWork(self, output_buffer)
+
+    def reduce_scatter_tensor_coalesced(self, output_tensors: List[torch.Tensor], input_tensors: List[torch.Tensor],
+                                        opts=None) -> Work:
+        op = _reduce_op(opts)
+        if op not in (ReduceOp.SUM, ReduceOp.AVG):
+            raise NotImplementedError(f"ProcessGroupB200.reduce_scatter supports SUM and AVG, got {op}")
+        world = self._world
+        scale = 1.0 / world if op == ReduceOp.AVG else 1.0
+        for out, inp in zip(output_tensors, input_tensors):
+            self._check_cuda(out, inp)
+            if inp.dtype not in _DT or out.dtype != inp.dtype:
+                raise NotImplementedError(f"dtype {inp.dtype} not supported by the peer-memory reduce-scatter")
+            if inp.numel() != out.numel() * world:
+                raise ValueError("reduce_scatter_tensor: input must hold world_size outputs")
+            if not out.is_contiguous():
+                raise ValueError("reduce_scatter_tensor needs a contiguous output")
+            shard = out.numel()
+            if world == 1:
+                out.view(-1).copy_(inp.reshape(-1))
+                if scale != 1.0:
+                    out.mul_(scale)
+                continue
+            es = inp.element_size()
+            vec = 16 // es
+            in2 = inp.contiguous().view(world, shard)
+            out1 = out.view(-1)
+            cap = (self._staging_bytes // es // world) // vec * vec
+            direct = shard % vec == 0 and out1.data_ptr() % 16 == 0
+            pos = 0
+            while pos < shard:
+                m = min(cap, shard - pos)
+                mp = (m + vec - 1) // vec * vec
+                stage = self._team.arena.tensor(self._staging_off, world * mp, inp.dtype).view(world, mp)
+                stage[:, :m].copy_(in2[:, pos : pos + m])
+                if mp != m:
+                    stage[:, m:].zero_()
+                dst = out1[pos : pos + m] if direct else torch.empty(mp, dtype=inp.dtype, device=self._device)
+                self._team.reduce_scatter(self._staging_off, dst, mp, inp.dtype, scale)
+                if not direct:
+                    out1[pos : pos + m].copy_(dst[:m])
+                pos += m
+        return _StreamWork(self, output_tensors)
+
+    def reduce_scatter(self, output_tensors: List[torch.Tensor], input_tensors: List[List[torch.Tensor]],
+                       opts=None) -> Work:
+        flat = [torch.cat([t.reshape(-1) for t in ins]) for ins in input_tensors]
+        return self.reduce_scatter_tensor_coalesced(output_tensors, flat, opts)
+
+    # ---- point to point -----------------------------------------------------------------------------
+    def _next_pair(self, src: int, dst: int) -> int:
+        k = self._pair_seq.get((src, dst), 0) + 1
+        self._pair_seq[(src, dst)] = k
+        return k
+
+    def send(self, tensors: List[torch.Tensor], dst_rank: int, tag: int = 0) -> Work:
+        """Hands ``tensors`` to ``dst_rank`` through this rank's send window; transfers between a pair of ranks
+        match in posting order (``tag`` is not used for matching)."""
+        for t in tensors:
+            self._check_cuda(t)
+            u8 = self._u8(t.contiguous())
+            nb, pos = u8.numel(), 0
+            while pos < nb or nb == 0:
+                m = min(self._p2p_bytes, nb - pos)
+                mp = (m + 15) // 16 * 16
+                window = self._team.arena.bytes_view[self._p2p_off : self._p2p_off + mp]
+                window[:m].copy_(u8[pos : pos + m])
+                self._team.sendrecv(dst_rank, True, self._next_pair(self._rank, dst_rank), 0, 0, mp)
+                pos += m
+                if nb == 0:
+                    break
+        return _StreamWork(self, tensors)
+
+    def recv(self, tensors: List[torch.Tensor], src_rank: int, tag: int = 0) -> Work:
+        for t in tensors:
+            self._check_cuda(t)
+            if not t.is_contiguous():
+                raise ValueError("recv needs contiguous tensors")
+            u8 = self._u8(t)
+            nb, pos = u8.numel(), 0
+            src = self._team.peer_base[src_rank] + self._p2p_off
+            while pos < nb or nb == 0:
+                m = min(self._p2p_bytes, nb - pos)
+                mp = (m + 15) // 16 * 16
+                direct = m % 16 == 0 and (u8.data_ptr() + pos) % 16 == 0
+                tmp = None if direct else torch.empty(mp, dtype=torch.uint8, device=self._device)
+                dst = u8.data_ptr() + pos if direct else tmp.data_ptr()
+                self._team.sendrecv(src_rank, False, self._next_pair(src_rank, self._rank), src, dst, mp)
+                if tmp is not None:
+                    u8[pos : pos + m].copy_(tmp[:m])
+                pos += m
+                if nb == 0:
+                    break
+        return _StreamWork(self, tensors)
 
     def __repr__(self) -> str:
         return f"ProcessGroupB200(rank={self._rank}, world={self._world}, epoch={self._team.epoch})"
