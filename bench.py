@@ -226,6 +226,23 @@ def main() -> int:
         loss = trainer.train_step(t[:, :-1], t[:, 1:])
     K.check_status(dev)
 
+    def committed_steps() -> int:
+        return manager.current_step() if manager is not None else trainer.opt_step
+
+    def check_commits(before: int, what: str) -> int:
+        """Every step of a timed region must have committed (a declined step skips the optimizer and would
+        overstate tokens/s) and the replica group must not have latched an error."""
+        done = committed_steps() - before
+        if done != args.steps:
+            raise SystemExit(f"{what}: {done} of {args.steps} steps committed")
+        if manager is not None and manager._pg.errored() is not None:
+            raise SystemExit(f"{what}: replica process group errored: {manager._pg.errored()}")
+        return done
+
+    torch.cuda.synchronize()
+    if committed_steps() != args.warmup:
+        raise SystemExit(f"warm-up: {committed_steps()} of {args.warmup} steps committed")
+
     # ---- device-resident timed region
     phase("timed region")
     sampler = ClockSampler(local_rank)
@@ -233,6 +250,7 @@ def main() -> int:
     if rank == 0:
         sampler.start()
     launches0 = N.launch_count
+    steps0 = committed_steps()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(args.steps):
@@ -248,11 +266,13 @@ def main() -> int:
     clocks = sampler.stop() if rank == 0 else None
     final_loss = float(loss.item())
     K.check_status(dev)
+    commits = check_commits(steps0, "timed region")
 
     phase("end-to-end region")
     # ---- end-to-end region: pinned host -> device copy of the inputs and loss read-back every step
     stage = torch.empty(B, S + 1, dtype=torch.long, device=dev)
     sync_all()
+    steps0 = committed_steps()
     w0 = time.perf_counter()
     e0.record()
     losses = []
@@ -267,6 +287,7 @@ def main() -> int:
     if world > 1:
         dist.all_reduce(ms2, op=dist.ReduceOp.MAX)
     K.check_status(dev)
+    commits += check_commits(steps0, "end-to-end region")
 
     tokens_per_step = world * B * S
     value = tokens_per_step * args.steps / (ms_total / 1e3)
@@ -307,6 +328,7 @@ def main() -> int:
                 "d2h_bytes_per_step": 4,
             },
             "gpu_launches": launches,
+            "commits": commits,
             "model_tflops_per_gpu": flops * args.steps / (ms_total / 1e3) / 1e12,
             "loss": final_loss,
         }

@@ -139,3 +139,123 @@ def test_missing_peer_times_out_with_status():
     assert int(emu.status[0].item()) == 1  # FTB200_ST_TIMEOUT
     # the device still works
     assert torch.ones(4, device=DEV).sum().item() == 4.0
+
+
+def test_missing_peer_with_abort_word_returns_aborted():
+    """The other half of the never-hang contract: with the abort word set, a rank whose peer never
+    shows up must come back ABORTED long before its (here: 20 s) deadline."""
+    import time
+
+    world, n = 2, 2 * 8 * 64
+    emu = Emu(world, n * 2, timeout_s=20.0)
+    lib = emu.lib
+    hp, dp = ctypes.POINTER(ctypes.c_int)(), ctypes.c_void_p()
+    assert lib.ftb200_abort_word_create(ctypes.byref(hp), ctypes.byref(dp)) == 0
+    try:
+        hp[0] = 1  # aborted before the launch
+        descs = emu.descs()
+        descs[0].abort_word = dp.value
+        bufs = [emu.buf(r, n, torch.bfloat16) for r in range(world)]
+        t0 = time.perf_counter()
+        rc = lib.ftb200_team_allreduce_emulated(
+            descs, ctypes.c_int(1), emu.ptrs(bufs), None, None, ctypes.c_longlong(n), ctypes.c_int(0),
+            ctypes.c_float(1.0), None, ctypes.c_int(2), N.stream_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 5.0
+        assert int(emu.status[0].item()) == 2  # FTB200_ST_ABORTED
+        assert torch.ones(4, device=DEV).sum().item() == 4.0
+    finally:
+        lib.ftb200_abort_word_destroy(hp)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_allreduce_oneshot_emulated(world, dtype):
+    torch.manual_seed(2)
+    n = 8 * 700
+    emu = Emu(world, n * 4)
+    window = [emu.buf(r, n, dtype) for r in range(world)]
+    data = [torch.randn(n, device=DEV).to(dtype) for _ in range(world)]
+    outs = [torch.empty(n, dtype=dtype, device=DEV) for _ in range(world)]
+    ref = sum(d.float() for d in data) / world
+    rc = emu.lib.ftb200_team_allreduce_oneshot_emulated(
+        emu.descs(), ctypes.c_int(world), emu.ptrs(window), emu.ptrs(data), emu.ptrs(outs), ctypes.c_longlong(n),
+        ctypes.c_int(0 if dtype == torch.bfloat16 else 1), ctypes.c_float(1.0 / world), ctypes.c_int(2), N.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert all(int(s.item()) == 0 for s in emu.status)
+    for o in outs:
+        assert torch.equal(o, outs[0])  # same summation order on every rank
+        torch.testing.assert_close(o.float(), ref, rtol=2e-2, atol=2e-2)
+
+
+def _pull_tables(world, rows):
+    """rows[r] = list of (src_ptr, dst_ptr, nbytes) for rank r -> flat ctypes tables."""
+    src = (ctypes.c_void_p * (world * MAX_RANKS))()
+    dst = (ctypes.c_void_p * (world * MAX_RANKS))()
+    nb = (ctypes.c_longlong * (world * MAX_RANKS))()
+    cnt = (ctypes.c_int * world)()
+    for r, segs in enumerate(rows):
+        cnt[r] = len(segs)
+        for i, (s, d, b) in enumerate(segs):
+            src[r * MAX_RANKS + i], dst[r * MAX_RANKS + i], nb[r * MAX_RANKS + i] = s, d, b
+    return src, dst, nb, cnt
+
+
+def test_pull_emulated_alltoall_and_broadcast():
+    world, chunk = 4, 16 * 50
+    emu = Emu(world, world * chunk)
+    stage = [emu.buf(r, world * chunk, torch.uint8) for r in range(world)]
+    for r, s in enumerate(stage):
+        s.copy_(torch.arange(world * chunk, device=DEV).remainder(251).add(r).to(torch.uint8))
+    outs = [torch.zeros(world * chunk, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    # all-to-all: rank r takes chunk r of every rank's window
+    rows = [[(stage[p].data_ptr() + r * chunk, outs[r].data_ptr() + p * chunk, chunk) for p in range(world)]
+            for r in range(world)]
+    src, dst, nb, cnt = _pull_tables(world, rows)
+    assert emu.lib.ftb200_team_pull_emulated(emu.descs(), ctypes.c_int(world), src, dst, nb, cnt, ctypes.c_int(2),
+                                             N.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    for r in range(world):
+        for p in range(world):
+            assert torch.equal(outs[r][p * chunk : (p + 1) * chunk], stage[p][r * chunk : (r + 1) * chunk])
+    # broadcast from rank 2: the root fetches nothing
+    outs = [torch.zeros(chunk, dtype=torch.uint8, device=DEV) for _ in range(world)]
+    rows = [[] if r == 2 else [(stage[2].data_ptr(), outs[r].data_ptr(), chunk)] for r in range(world)]
+    src, dst, nb, cnt = _pull_tables(world, rows)
+    assert emu.lib.ftb200_team_pull_emulated(emu.descs(), ctypes.c_int(world), src, dst, nb, cnt, ctypes.c_int(2),
+                                             N.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    assert all(int(s.item()) == 0 for s in emu.status)
+    for r in range(world):
+        if r != 2:
+            assert torch.equal(outs[r], stage[2][:chunk])
+
+
+def test_sendrecv_emulated_and_receiver_alone_times_out():
+    world, nbytes = 4, 16 * 1000
+    emu = Emu(world, nbytes, timeout_s=0.3)
+    window = emu.buf(1, nbytes, torch.uint8)  # rank 1 sends to rank 3
+    window.copy_(torch.arange(nbytes, device=DEV).remainder(253).to(torch.uint8))
+    dst = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    descs = emu.descs()
+    token = (emu.epoch << 32) | 1
+    rc = emu.lib.ftb200_team_sendrecv_emulated(ctypes.byref(descs[1]), ctypes.byref(descs[3]), ctypes.c_int(1),
+                                               ctypes.c_ulonglong(token), ctypes.c_void_p(window.data_ptr()),
+                                               ctypes.c_void_p(dst.data_ptr()), ctypes.c_longlong(nbytes), ctypes.c_int(2),
+                                               N.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst, window) and int(emu.status[1].item()) == 0 and int(emu.status[3].item()) == 0
+    # a receiver whose sender never posts gives up with TIMEOUT and leaves the destination alone
+    dst.zero_()
+    token = (emu.epoch << 32) | 2
+    rc = emu.lib.ftb200_team_sendrecv_emulated(ctypes.byref(descs[1]), ctypes.byref(descs[3]), ctypes.c_int(0),
+                                               ctypes.c_ulonglong(token), ctypes.c_void_p(window.data_ptr()),
+                                               ctypes.c_void_p(dst.data_ptr()), ctypes.c_longlong(nbytes), ctypes.c_int(2),
+                                               N.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(emu.status[3].item()) == 1 and int(dst.sum().item()) == 0
+    assert torch.ones(4, device=DEV).sum().item() == 4.0

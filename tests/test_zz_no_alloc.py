@@ -46,11 +46,37 @@ def test_noalloc_matches_regular_entry_point_twice():
         assert _call(lib, dy, x, w, rstd, dres, dx, dw, False) == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == before
+        if call > 0:
+            # torch's counter cannot see a raw cudaMalloc; the driver's free-memory figure can.  On a warm
+            # call (the address is resolved, the kernels are loaded) it must not move.
+            free0, _ = torch.cuda.mem_get_info()
+            assert _call(lib, dy, x, w, rstd, dres, dx, dw, False) == 0
+            torch.cuda.synchronize()
+            free1, _ = torch.cuda.mem_get_info()
+            assert free1 == free0
         assert _rel(dx, want_dx) < 1e-2
         assert _rel(dw, want_dw) < 2e-2
         # and against the fp32 reference of the op
         rdx, rdw = K.ref_rmsnorm_bwd(dy, x, w, rstd, dres)
         assert _rel(dx, rdx) < 1e-2 and _rel(dw, rdw) < 2e-2
+
+
+def test_noalloc_accumulates_into_dw():
+    """``accumulate_dw=1`` adds the weight gradient to what ``dw`` holds, as the regular entry point does."""
+    lib = N.lib()
+    torch.manual_seed(5)
+    T, D = 300, 2048
+    x = torch.randn(T, D, device="cuda").bfloat16()
+    dy = torch.randn(T, D, device="cuda").bfloat16()
+    w = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16()
+    _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
+    _, want_dw = K.rmsnorm_bwd(dy, x, w, rstd)
+    start = torch.randn(D, device="cuda").bfloat16()
+    dw = start.clone()
+    dx = torch.empty_like(x)
+    assert _call(lib, dy, x, w, rstd, None, dx, dw, True) == 0
+    torch.cuda.synchronize()
+    assert _rel(dw, start.float() + want_dw.float()) < 2e-2
 
 
 def test_noalloc_rejects_oversized():

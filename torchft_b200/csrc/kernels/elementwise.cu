@@ -528,13 +528,17 @@ FTB200_API int ftb200_clip_coef(const float* sumsq, float max_norm, float* coef,
 // See ftb200_noalloc.h.  The scratch lives in the library image; host code must not pass
 // the symbol itself to a kernel (on the host it is only a stand-in), so its device address
 // is looked up once per device and cached.
+#include <atomic>
+
 #include "ftb200_noalloc.h"
 
 static __device__ __align__(256) float g_noalloc_scratch[FTB200_NOALLOC_SCRATCH_FLOATS];
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_noalloc_scratch_addr[kMaxDevices] = {nullptr};
+// Host threads may make their first call on a device at the same time: they all resolve the
+// same address, and the atomic makes the concurrent store and loads well defined.
+std::atomic<float*> g_noalloc_scratch_addr[kMaxDevices];
 }  // namespace
 
 FTB200_API int ftb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
@@ -551,16 +555,17 @@ FTB200_API int ftb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const v
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return FTB200_E_CUDA;
   const int nblk = std::min(T, sms * 2);
   if (static_cast<long long>(nblk) * D > static_cast<long long>(FTB200_NOALLOC_SCRATCH_FLOATS)) return FTB200_E_TOOBIG;
-  if (g_noalloc_scratch_addr[dev] == nullptr) {
+  float* scratch = g_noalloc_scratch_addr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
     // one-time set-up for this device (which is current): resolve the array's device address
     float* p = nullptr;
     if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_scratch) != cudaSuccess || p == nullptr) {
       cudaGetLastError();
       return FTB200_E_CUDA;
     }
-    g_noalloc_scratch_addr[dev] = p;
+    g_noalloc_scratch_addr[dev].store(p, std::memory_order_release);
+    scratch = p;
   }
-  float* scratch = g_noalloc_scratch_addr[dev];
   const int D8 = D / 8;
   const int threads = D8 > 256 ? 512 : 256;  // wide rows: 16 warps per block, two blocks per SM
   const int maxv = (D8 + threads - 1) / threads;

@@ -18,7 +18,8 @@
 //    FTB200_E_TOOBIG (-4) before anything is launched.
 //  * First call on a device: looks up the device address of the array once
 //    (cudaGetSymbolAddress with that device current) and remembers it.  Make that first
-//    call outside of any stream capture.
+//    call outside of any stream capture.  Host threads may race on that first call: the
+//    remembered address is an atomic, and every thread resolves the same value.
 //  * No cudaMalloc, cudaFree or allocating library call is made, on any call.
 //  * All calls share the one array.  Every call overwrites the part it uses before reading
 //    it, so nothing has to be cleared between calls; but two calls that overlap on the same

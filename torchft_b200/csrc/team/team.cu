@@ -248,20 +248,79 @@ struct CopySeg {
 };
 
 // Live-recovery copy: a table of (peer src, local dst, bytes) segments pulled with 16-byte
-// vector loads; a bounds-free grid-stride loop per segment, all segments in one launch.
+// vector loads, eight in flight per thread (NVLink latency is microseconds: bandwidth comes
+// from bytes in flight), all segments in one launch.  Every 16 rounds of a block (some tens
+// of MB of the launch's traffic) thread 0 looks at the abort word and the deadline and the
+// block agrees on going on, so an abort or an expired deadline ends the copy within a
+// fraction of a millisecond instead of at the next segment.  With `sums`, the kernel also
+// leaves a 64-bit additive checksum of the 32-bit words it moved per segment, which the
+// caller compares with the source's own checksum of the same bytes.
+__device__ __forceinline__ unsigned long long sum4(const uint4& v) {
+  return static_cast<unsigned long long>(v.x) + v.y + v.z + v.w;
+}
+
 __global__ void __launch_bounds__(512) p2p_copy_kernel(const CopySeg* __restrict__ segs, int nsegs,
-                                                       const volatile int* abort_word, int* status) {
+                                                       const volatile int* abort_word, int* status,
+                                                       unsigned long long timeout_ns, unsigned long long* sums) {
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const uint64_t t0 = ftb200::globaltimer_ns();
+  constexpr int U = 8;
+  unsigned rounds = 0;
   for (int s = 0; s < nsegs; ++s) {
-    if (abort_word != nullptr && *abort_word != 0) {
-      if (tid == 0 && status != nullptr) atomicMax(status, FTB200_ST_ABORTED);
-      return;
-    }
     const uint4* src = reinterpret_cast<const uint4*>(segs[s].src);
     uint4* dst = reinterpret_cast<uint4*>(segs[s].dst);
     const long long nv = segs[s].bytes / 16;
-    for (long long i = tid; i < nv; i += nthreads) dst[i] = src[i];
+    unsigned long long acc = 0;
+    // uniform trip count per block, so that the block-wide vote below is reached by all threads
+    const long long first = static_cast<long long>(blockIdx.x) * blockDim.x;
+    for (long long b0 = first; b0 < nv; b0 += nthreads * U) {
+      if ((rounds++ & 15u) == 0) {
+        int stop = 0;
+        if (threadIdx.x == 0) {
+          if (abort_word != nullptr && *abort_word != 0) stop = FTB200_ST_ABORTED;
+          else if (timeout_ns != 0 && ftb200::globaltimer_ns() - t0 > timeout_ns) stop = FTB200_ST_TIMEOUT;
+          if (stop != 0 && status != nullptr) atomicMax(status, stop);
+        }
+        if (__syncthreads_or(stop)) return;
+      }
+      const long long i0 = b0 + threadIdx.x;
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < nv) v[u] = src[i];
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * nthreads;
+        if (i < nv) {
+          dst[i] = v[u];
+          acc += sum4(v[u]);
+        }
+      }
+    }
+    if (sums != nullptr) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if ((threadIdx.x & 31) == 0 && acc != 0) atomicAdd(sums + s, acc);
+    }
+  }
+}
+
+// The source's side of the end-to-end check: the same per-segment checksum over local memory.
+__global__ void __launch_bounds__(512) checksum_kernel(const CopySeg* __restrict__ segs, int nsegs,
+                                                       unsigned long long* sums) {
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  for (int s = 0; s < nsegs; ++s) {
+    const uint4* src = reinterpret_cast<const uint4*>(segs[s].src);
+    const long long nv = segs[s].bytes / 16;
+    unsigned long long acc = 0;
+    for (long long i = tid; i < nv; i += nthreads) acc += sum4(src[i]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if ((threadIdx.x & 31) == 0 && acc != 0) atomicAdd(sums + s, acc);
   }
 }
 
@@ -626,12 +685,33 @@ FTB200_API int ftb200_team_sendrecv(const ftb200_team_desc* d, int peer, int is_
 }
 
 // segs: device array of {src, dst, bytes}; the caller keeps it alive until the stream reaches the kernel.
+// abort_word (device pointer of a host-mapped word, may be null) and timeout_ns (0 = none) bound the copy;
+// sums (may be null): nsegs zeroed 64-bit words that receive the per-segment checksums of the moved bytes.
 FTB200_API int ftb200_p2p_copy(const void* segs_dev, int nsegs, long long total_bytes, const void* abort_word, int* status,
                                int ctas, cudaStream_t st) {
   if (nsegs <= 0) return 0;
   const int grid = ctas > 0 ? ctas : std::max(grid_for_bytes(total_bytes), 32);
   p2p_copy_kernel<<<grid, 512, 0, st>>>(reinterpret_cast<const CopySeg*>(segs_dev), nsegs,
-                                        reinterpret_cast<const volatile int*>(abort_word), status);
+                                        reinterpret_cast<const volatile int*>(abort_word), status, 0ull, nullptr);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+FTB200_API int ftb200_p2p_copy_checked(const void* segs_dev, int nsegs, long long total_bytes, const void* abort_word,
+                                       int* status, unsigned long long timeout_ns, unsigned long long* sums, int ctas,
+                                       cudaStream_t st) {
+  if (nsegs <= 0) return 0;
+  const int grid = ctas > 0 ? ctas : std::max(grid_for_bytes(total_bytes), 32);
+  p2p_copy_kernel<<<grid, 512, 0, st>>>(reinterpret_cast<const CopySeg*>(segs_dev), nsegs,
+                                        reinterpret_cast<const volatile int*>(abort_word), status, timeout_ns, sums);
+  return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+// Per-segment checksum of local memory (src and bytes of each segment; dst is ignored).
+FTB200_API int ftb200_checksum(const void* segs_dev, int nsegs, long long total_bytes, unsigned long long* sums,
+                               cudaStream_t st) {
+  if (nsegs <= 0) return 0;
+  const int grid = std::max(grid_for_bytes(total_bytes), 32) * 2;
+  checksum_kernel<<<grid, 512, 0, st>>>(reinterpret_cast<const CopySeg*>(segs_dev), nsegs, sums);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 

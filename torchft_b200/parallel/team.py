@@ -300,7 +300,10 @@ class SymmetricTeam:
     def sendrecv(self, peer: int, is_send: bool, pair_seq: int, src_ptr: int, dst_ptr: int, nbytes: int) -> None:
         """One side of a point-to-point transfer; ``pair_seq`` counts the transfers of this ordered pair."""
         d = self._desc_nocount()
-        token = (self.epoch << 32) | (pair_seq & 0xFFFFFFFF)
+        # the sender's rank is part of the token: a receiver's local go-word must never see the same value for
+        # transfers from two different senders
+        sender = self.rank if is_send else peer
+        token = (self.epoch << 32) | (sender << 28) | (pair_seq & 0x0FFFFFFF)
         N.check(self.lib.ftb200_team_sendrecv(ctypes.byref(d), ctypes.c_int(peer), ctypes.c_int(int(is_send)),
                                               ctypes.c_ulonglong(token), ctypes.c_void_p(src_ptr), ctypes.c_void_p(dst_ptr),
                                               ctypes.c_longlong(nbytes), ctypes.c_int(DEFAULT_CTAS), N.stream_ptr()),
