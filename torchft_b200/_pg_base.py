@@ -35,12 +35,14 @@ def create_store_client(store_addr: str, timeout: timedelta) -> Store:
     return PrefixStore(prefix, store)
 
 
-def _reduce_op(opts: Union[AllreduceOptions, ReduceOp, ReduceOp.RedOpType, None]) -> ReduceOp:
+def _reduce_op(opts: Union[AllreduceOptions, ReduceOp, ReduceOp.RedOpType, None]) -> ReduceOp.RedOpType:
+    """The reduction of an options object (or of a bare op) as the plain enum value, so that
+    ``op in (ReduceOp.SUM, ReduceOp.AVG)`` works (a ``ReduceOp`` object only compares equal to
+    the enum when it is the left operand)."""
     if opts is None:
         return ReduceOp.SUM
-    if isinstance(opts, (ReduceOp, ReduceOp.RedOpType)):
-        return opts  # type: ignore[return-value]
-    return opts.reduceOp
+    op = opts if isinstance(opts, (ReduceOp, ReduceOp.RedOpType)) else opts.reduceOp
+    return getattr(op, "op", op)  # a ReduceOp object carries its enum value in .op
 
 
 class ProcessGroup(BaseProcessGroup):
