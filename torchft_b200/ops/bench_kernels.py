@@ -162,6 +162,20 @@ def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare
     dqkv = torch.empty_like(qkv)
     dq, dk, dv = dqkv[:, : hq * D], dqkv[:, hq * D : (hq + hkv) * D], dqkv[:, (hq + hkv) * D :]
     fwd = timeit(lambda: K.attention_fwd(q, k, v, batch, seq, hq, hkv, D, out, lse), iters)
+    variants = {}
+    if seq % 256 == 0:
+        # the forward kernels side by side: one tile per CTA, and two tiles per CTA with none, a quarter
+        # and half of the exponentials on the FMA pipe
+        saved = {n: os.environ.get(n) for n in ("FTB200_ATTN_FWD", "FTB200_ATTN_POLY")}
+        for name, impl, poly in (("single", "single", "0"), ("pair_poly0", "pair", "0"), ("pair_poly2", "pair", "2"),
+                                 ("pair_poly4", "pair", "4")):
+            os.environ["FTB200_ATTN_FWD"], os.environ["FTB200_ATTN_POLY"] = impl, poly
+            variants[name + "_ms"] = timeit(lambda: K.attention_fwd(q, k, v, batch, seq, hq, hkv, D, out, lse), iters)
+        for n, val in saved.items():
+            if val is None:
+                os.environ.pop(n, None)
+            else:
+                os.environ[n] = val
     bwd = timeit(lambda: K.attention_bwd(q, k, v, out, d_o, lse, dq, dk, dv, batch, seq, hq, hkv, D), iters)
     K.check_status(qkv.device)
     _, tf, how = _peaks()
@@ -170,6 +184,7 @@ def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare
     res = {"kernel": "attention_tcgen05", "batch": batch, "seq": seq, "heads": hq, "kv_heads": hkv, "fwd_ms": fwd,
            "bwd_ms": bwd, "fwd_tflops": fl_fwd / fwd / 1e9, "bwd_tflops": fl_bwd / bwd / 1e9,
            f"fwd_frac_of_{how}_cublas_peak": fl_fwd / fwd / 1e9 / tf, f"bwd_frac_of_{how}_cublas_peak": fl_bwd / bwd / 1e9 / tf}
+    res["fwd_variants"] = variants
     if compare:
         q4 = q.reshape(batch, seq, hq, D).transpose(1, 2).detach().requires_grad_(True)
         k4 = k.reshape(batch, seq, hkv, D).transpose(1, 2).detach().requires_grad_(True)

@@ -169,6 +169,9 @@ class EngineDiLoCo:
         self.record_timing = record_timing and self.stream is not None
         self.timings: List[List[tuple]] = []
         self.exchange_timings: List[tuple] = []
+        # with record_timing: host time (monotonic seconds) at which this group reached each synchronisation
+        # with its stream drained; comparing them across the groups of one host gives their drift
+        self.arrivals: List[float] = []
 
     def _timed(self, fn, new_sync: bool):
         if not self.record_timing:
@@ -191,6 +194,12 @@ class EngineDiLoCo:
         self.manager.allow_state_dict_read()
         self._local_step += 1
         if self._local_step == self._every - self.fragment_sync_delay:
+            if self.record_timing:
+                import time
+
+                torch.cuda.current_stream().synchronize()
+                self.arrivals.append(time.monotonic())
+
             def begin() -> None:
                 self.manager.start_quorum()  # synchronous: a replica that is behind heals here
                 self._current().prepare()

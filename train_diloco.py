@@ -63,13 +63,17 @@ def main() -> None:
         return {"model": model.state_dict(), "inner_optim": inner.state_dict()}
 
     timeout = timedelta(seconds=30)
-    if use_cuda and os.environ.get("USE_PEER", "0") == "1":
+    # Replica dimension on GPUs: NVLink peer memory (ProcessGroupB200) unless told otherwise.  It needs all
+    # replica groups on one NVSwitch box; USE_PEER=0 (or an explicit USE_NCCL=1) selects NCCL, USE_NCCL=0 Gloo.
+    nccl_env = os.environ.get("USE_NCCL")
+    use_peer = use_cuda and nccl_env is None and os.environ.get("USE_PEER", "1") == "1"
+    if use_peer:
         from torchft_b200.parallel.team import ProcessGroupB200
 
         pg = ProcessGroupB200(timeout=timeout, device=device)
     else:
         # USE_NCCL=0 keeps the tensors on the GPU but moves the replica dimension to Gloo
-        use_nccl = use_cuda and os.environ.get("USE_NCCL", "1").lower() not in ("0", "false")
+        use_nccl = use_cuda and (nccl_env or "1").lower() not in ("0", "false")
         pg = ProcessGroupNCCL(timeout=timeout) if use_nccl else ProcessGroupGloo(timeout=timeout)
     manager = Manager(
         pg=pg,
