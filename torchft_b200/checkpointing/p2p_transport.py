@@ -250,9 +250,9 @@ class P2PTransport(HTTPTransport[T], Generic[T]):
                 ctypes.c_void_p(self._abort_dev), N.ptr(self._status), ctypes.c_ulonglong(timeout_ns), N.ptr(sums),
                 ctypes.c_int(0), N.stream_ptr()), "p2p_copy")
             self._table_keepalive = dev_table
-        cudart = torch.cuda.cudart()
         for src, dst, nb in tails:
-            cudart.cudaMemcpy(dst, src, nb, 3)  # cudaMemcpyDeviceToDevice
+            N.check(N.lib().ftb200_memcpy_d2d(ctypes.c_void_p(dst), ctypes.c_void_p(src), ctypes.c_longlong(nb),
+                                              N.stream_ptr()), "memcpy_d2d", 0)
 
         def mismatch() -> List[int]:
             if sums is None:

@@ -706,6 +706,15 @@ FTB200_API int ftb200_p2p_copy_checked(const void* segs_dev, int nsegs, long lon
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
+// Plain device-to-device copy (also from a peer-mapped source) for the ragged heads and tails that the
+// 16-byte copy kernel leaves out.
+FTB200_API int ftb200_memcpy_d2d(void* dst, const void* src, long long bytes, cudaStream_t st) {
+  if (bytes <= 0) return 0;
+  return cudaMemcpyAsync(dst, src, static_cast<size_t>(bytes), cudaMemcpyDeviceToDevice, st) == cudaSuccess
+             ? 0
+             : FTB200_E_CUDA;
+}
+
 // Per-segment checksum of local memory (src and bytes of each segment; dst is ignored).
 FTB200_API int ftb200_checksum(const void* segs_dev, int nsegs, long long total_bytes, unsigned long long* sums,
                                cudaStream_t st) {

@@ -24,6 +24,7 @@ import logging
 import os
 import socket
 import threading
+import time
 import traceback
 import uuid
 from concurrent.futures import ThreadPoolExecutor
@@ -241,6 +242,7 @@ class Manager:
         self._quorum_id = -1
         self._errored: Optional[ExceptionWithTraceback] = None
         self._healing = False
+        self.last_quorum_phases: Dict[str, float] = {}
         self._batches_committed = 0
         self._participating_replica_rank: Optional[int] = None
         self._participating_replica_world_size: int = 0
@@ -439,6 +441,10 @@ class Manager:
         if curr_device >= 0 and torch.cuda.is_available():
             torch.cuda.set_device(curr_device)
 
+        # host time of the phases of this quorum (seconds): what a slow step of a serving or healing replica is made of
+        phases: Dict[str, float] = {}
+        self.last_quorum_phases = phases
+        t_phase = time.perf_counter()
         with torch.profiler.record_function("torchft::manager::_client::_quorum"):
             quorum = self._client._quorum(
                 group_rank=self._group_rank,
@@ -450,6 +456,7 @@ class Manager:
                 commit_failures=self._commit_failures,
             )
 
+        phases["quorum_rpc_s"] = time.perf_counter() - t_phase
         # With async quorum (or healing disabled) only replicas already at the max step
         # count; with a synchronous quorum everyone has healed before the step runs.
         if self._use_async_quorum or not allow_heal:
@@ -478,6 +485,7 @@ class Manager:
             )
             prefixed = f"{quorum.store_address}/torchft/{quorum.quorum_id}/{self._group_rank}"
             self._logger.info(f"reconfiguring for quorum_id={quorum.quorum_id} store_prefixed_addr={prefixed}")
+            t_phase = time.perf_counter()
             try:
                 with torch.profiler.record_function("torchft::manager::_pg::configure"):
                     if torch.cuda.is_available():
@@ -486,6 +494,7 @@ class Manager:
                     self._pg.configure(prefixed, self._replica_id if self._replica_id is not None else "0",
                                        quorum.replica_rank, quorum.replica_world_size)
                 self._quorum_id = quorum.quorum_id
+                phases["configure_s"] = time.perf_counter() - t_phase
             except Exception as e:
                 self._logger.exception(f"got exception in pg configure: {e}")
                 self.report_error(e)
@@ -496,6 +505,7 @@ class Manager:
                 try:
                     if quorum.recover_dst_replica_ranks:
                         self._logger.info(f"peers need recovery from us {quorum.recover_dst_replica_ranks}")
+                        t_phase = time.perf_counter()
                         with torch.profiler.record_function("torchft::manager::_checkpoint_transport::send_checkpoint"):
                             self._checkpoint_transport.send_checkpoint(
                                 dst_ranks=quorum.recover_dst_replica_ranks,
@@ -503,6 +513,7 @@ class Manager:
                                 state_dict=self._manager_state_dict(),
                                 timeout=self._timeout,
                             )
+                        phases["send_checkpoint_s"] = time.perf_counter() - t_phase
                     if quorum.heal:
                         self._healing = True
                         src_addr = quorum.recover_src_manager_address
@@ -513,10 +524,12 @@ class Manager:
                         src_rank = quorum.recover_src_replica_rank
                         assert src_rank is not None, "must have a recover rank when healing"
                         self._logger.info(f"fetching checkpoint from recover_src_replica_rank={src_rank} with metadata={metadata}")
+                        t_phase = time.perf_counter()
                         with torch.profiler.record_function("torchft::manager::_checkpoint_transport::recv_checkpoint"):
                             # the user part is applied later from the main thread (should_commit)
                             self._pending_state_dict = self._checkpoint_transport.recv_checkpoint(
                                 src_rank=src_rank, metadata=metadata, step=quorum.max_step, timeout=self._timeout)
+                        phases["recv_checkpoint_s"] = time.perf_counter() - t_phase
                         self.load_state_dict(cast(Dict[str, int], self._pending_state_dict["torchft"]))
                         self._step = quorum.max_step
                 except Exception as e:
