@@ -109,7 +109,8 @@ def main(args) -> int:
             return (b - a) * 1e3 if cpu else a.elapsed_time(b)
 
         with DiLoCo(manager, fragments, inner, outers, sync_every=args.sync_every, backup_device=backup,
-                    should_quantize=quantize, fragment_sync_delay=args.delay, fragment_update_alpha=args.alpha):
+                    should_quantize=quantize, fragment_sync_delay=args.delay,
+                    fragment_update_alpha=args.alpha) as diloco_obj:
             def run_round(marks):
                 loss = None
                 for _ in range(args.sync_every):
@@ -124,7 +125,20 @@ def main(args) -> int:
                         marks.append(new_event())
                 return float(loss)
 
+            warm0 = manager.current_step()
             run_round(None)  # warm-up: every fragment synchronises once (Triton kernels compile here)
+            wire_note = None
+            if quantize and manager.current_step() == warm0:
+                # not one synchronisation committed: on this stack the reference's quantised allreduce raises in
+                # alltoall_base on its non-blocking NCCL communicator ("NCCL Error 7: NCCL operation in progress"),
+                # the manager swallows the error and declines every commit.  Measure the reference's working
+                # path instead: fp32 pseudo-gradients through its plain allreduce.
+                wire_note = ("fp32: with should_quantize=True no synchronisation committed in the warm-up round "
+                             "(the reference's allreduce_quantized fails on its ProcessGroupNCCL here)")
+                quantize = False
+                for f in diloco_obj._fragments:
+                    f.should_quantize = False
+                run_round(None)
             if not cpu:
                 torch.cuda.synchronize()
             if world > 1:
@@ -157,7 +171,7 @@ def main(args) -> int:
                 "tokens_per_s": round(world * B * S * steps / (float(stats[0]) / 1e3), 1),
                 "n_gpus": world, "inner_steps": steps, "syncs_timed": steps // (args.sync_every // nfrag),
                 "syncs_committed": commits,
-                "wire": "fp32" if not quantize else "fp8 e4m3, per-row scales (reference Triton kernels)",
+                "wire": wire_note or ("fp32" if not quantize else "fp8 e4m3, per-row scales (reference Triton kernels)"),
                 "final_loss": round(last, 4), "dtype": "bf16", "data": "synthetic",
                 "config": {"model": args.model, "seq_len": S, "micro_batch": B, "sync_every": args.sync_every,
                            "fragments": nfrag, "fragment_sync_delay": args.delay, "fragment_update_alpha": args.alpha,

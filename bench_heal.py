@@ -98,16 +98,33 @@ def worker(a) -> int:
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         before = manager.current_step()
-        loss = trainer.train_step(tokens[:, :-1], tokens[:, 1:])
+        # train_step, taken apart so that the parts of a slow step can be told from one another (the device is
+        # drained between the parts, which a plain train_step does not do)
+        manager.start_quorum()  # synchronous quorum: reconfiguration, serving and healing happen in here
         torch.cuda.synchronize()
-        dt = time.perf_counter() - t0
+        t1 = time.perf_counter()
+        loss = trainer.forward_backward(tokens[:, :-1], tokens[:, 1:])
+        trainer._finish_comm()
+        torch.cuda.synchronize()
+        t2 = time.perf_counter()
+        trainer._check_shard_team()
+        ok = manager.should_commit()
+        t3 = time.perf_counter()
+        if ok:
+            trainer.optimizer_step()
+        torch.cuda.synchronize()
+        t4 = time.perf_counter()
+        dt = t4 - t0
         n = manager.num_participants()
         committed = manager.current_step() > before
         if not committed:
             commits_failed += 1
+        phases = {k: round(v, 4) for k, v in (getattr(manager, "last_quorum_phases", {}) or {}).items()}
+        phases.update({"start_quorum_s": round(t1 - t0, 4), "forward_backward_s": round(t2 - t1, 4),
+                       "should_commit_s": round(t3 - t2, 4), "optimizer_s": round(t4 - t3, 4)})
         records.append({"step": manager.current_step(), "s": round(dt, 4), "participants": n, "loss": round(float(loss), 4),
                         "healed": bool(transport.last_recv) and len(records) == 0,
-                        "t_end": time.time(), "phases": dict(getattr(manager, "last_quorum_phases", {}) or {})})
+                        "t_end": time.time(), "phases": phases})
         if a.leave_at < 0 and step >= a.hold and rejoined_at is None:
             if n >= 2:
                 rejoined_at = manager.current_step()
@@ -194,8 +211,10 @@ def launcher(a) -> int:
     rec0 = r0[0]["records"]
     solo = [r["s"] for r in rec0 if r["participants"] == 1]
     duo = [r["s"] for r in rec0 if r["participants"] == 2]
-    # the survivor's step in which it served the checkpoint: the first one with two participants
-    serve = next((r for r in rec0 if r["participants"] == 2), None)
+    # the survivor's step in which it served the checkpoint: the first one with two participants after it ran alone
+    first_solo = next((i for i, r in enumerate(rec0) if r["participants"] == 1), len(rec0))
+    serve = next((r for r in rec0[first_solo:] if r["participants"] == 2), None)
+    duo = [r["s"] for r in rec0[first_solo:] if r["participants"] == 2 and r is not serve] or duo
     # quorum-to-commit of the healed group: from the end of the survivor's last solo step (the quorum that admits
     # the newcomer is issued in the step that follows) to the end of the healed group's first step
     last_solo_end = max((r["t_end"] for r in rec0 if r["participants"] == 1), default=None)
@@ -214,6 +233,7 @@ def launcher(a) -> int:
         "copy_ms": round(copy_ms, 3),
         "copy_gbs_per_rank": round((total_bytes / shard) / 1e6 / copy_ms, 1) if copy_ms else None,
         "copy_gbs_total": round(total_bytes / 1e6 / copy_ms, 1) if copy_ms else None,
+        "healed_step_phases": max((r["records"][0] for r in r1), key=lambda x: x["s"]).get("phases"),
         "survivor_step_s": {"alone_median": sorted(solo)[len(solo) // 2] if solo else None,
                             "with_peer_median": sorted(duo)[len(duo) // 2] if duo else None,
                             "serving_step": serve["s"] if serve else None,
