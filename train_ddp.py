@@ -112,6 +112,9 @@ def main() -> None:
             on_trace_ready=torch.profiler.tensorboard_trace_handler(os.path.join(os.environ["PROFILE_DIR"], f"group{replica_group}")))
         prof.start()
 
+    import time
+
+    t_mark = None  # (time, step) once the first ten steps (quorum set-up, warm-up) are behind us
     while manager.current_step() < steps:
         sampler.set_epoch(manager.current_step())
         for x, y in loader:
@@ -125,11 +128,21 @@ def main() -> None:
                       f"participants={manager.num_participants()} loss={loss.item():.4f}", flush=True)
             if prof is not None:
                 prof.step()
+            if t_mark is None and manager.current_step() >= 10:
+                if use_cuda:
+                    torch.cuda.synchronize()
+                t_mark = (time.perf_counter(), manager.current_step())
             # a durable checkpoint would save state_dict(), manager.state_dict() and the loader position here
             if manager.current_step() >= steps:
                 break
     if prof is not None:
         prof.stop()
+    if t_mark is not None and manager.current_step() > t_mark[1]:
+        if use_cuda:
+            torch.cuda.synchronize()
+        n = manager.current_step() - t_mark[1]
+        print(f"[{replica_group}] {n} committed steps in {time.perf_counter() - t_mark[0]:.3f} s "
+              f"({(time.perf_counter() - t_mark[0]) / n * 1e3:.3f} ms/step, replica dimension: {type(pg).__name__})", flush=True)
     manager.shutdown()
 
 

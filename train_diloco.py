@@ -96,7 +96,14 @@ def main() -> None:
     with DiLoCo(manager, fragments, inner, outers, sync_every=20 if streaming else 20,
                 fragment_sync_delay=5 if streaming else 0, should_quantize=quantize,
                 backup_device=device if use_cuda else None) as diloco:
+        import time
+
+        t_mark = None
         for step in range(steps):
+            if step == 40:  # two rounds of synchronisations are behind us
+                if use_cuda:
+                    torch.cuda.synchronize()
+                t_mark = time.perf_counter()
             x = torch.randn(64, 3 * 32 * 32, generator=g).to(device)
             y = torch.randint(0, 10, (64,), generator=g).to(device)
             inner.zero_grad()
@@ -109,6 +116,12 @@ def main() -> None:
             if step % 20 == 0:
                 print(f"[{replica_group}] local_step={step} manager_step={manager.current_step()} loss={loss.item():.4f}",
                       flush=True)
+        if t_mark is not None and steps > 40:
+            if use_cuda:
+                torch.cuda.synchronize()
+            dt = time.perf_counter() - t_mark
+            print(f"[{replica_group}] {steps - 40} inner steps in {dt:.3f} s ({dt / (steps - 40) * 1e3:.3f} ms/step, "
+                  f"manager_step={manager.current_step()}, replica dimension: {type(pg).__name__})", flush=True)
     if writer is not None:
         writer.close()
     manager.shutdown()
