@@ -61,15 +61,83 @@ class _RawMemory:
         self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
 
 
+class _FdServer:
+    """Hands one file descriptor to whoever connects to an abstract Unix-domain socket (SCM_RIGHTS): how a rank's
+    arena descriptor reaches its peers in other processes of the same host."""
+
+    def __init__(self, fd: int) -> None:
+        import socket
+
+        self._fd = fd
+        self._sock = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        self.address = f"\0ftb200-arena-{os.getpid()}-{id(self):x}"
+        self._sock.bind(self.address)
+        self._sock.listen(64)
+        self._stop = False
+        self._thread = threading.Thread(target=self._serve, name="ftb200-arena-fd", daemon=True)
+        self._thread.start()
+
+    def _serve(self) -> None:
+        import socket
+
+        while not self._stop:
+            try:
+                conn, _ = self._sock.accept()
+            except OSError:
+                return
+            try:
+                socket.send_fds(conn, [b"fd"], [self._fd])
+            except OSError:
+                pass
+            finally:
+                conn.close()
+
+    @staticmethod
+    def fetch(address: str, timeout_s: float) -> int:
+        import socket
+
+        with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as c:
+            c.settimeout(timeout_s)
+            c.connect(address)
+            _, fds, _, _ = socket.recv_fds(c, 16, 1)
+        if not fds:
+            raise TeamError(f"no descriptor received from {address!r}")
+        return fds[0]
+
+    def close(self) -> None:
+        self._stop = True
+        try:
+            self._sock.close()
+        except OSError:
+            pass
+
+
 class Arena:
-    """One exported slab of device memory with a bump allocator (256-byte granules)."""
+    """One exported slab of device memory with a bump allocator (256-byte granules).
+
+    By default the slab is a ``cuMemCreate`` allocation shared with the peers as a POSIX file descriptor
+    (``kind == "vmm"``): a peer that has imported it holds a reference of its own, so its mapping stays valid by
+    the documented semantics of the driver even after the exporting process is gone.  ``FTB200_ARENA=ipc`` (or a
+    driver without these entry points) selects a ``cudaMalloc`` slab shared through a legacy CUDA IPC handle."""
 
     def __init__(self, nbytes: int, device: torch.device) -> None:
         self.device = device
         self.nbytes = int(nbytes)
+        self.kind = "ipc"
+        self._fd_server: Optional[_FdServer] = None
         p = ctypes.c_void_p()
         with torch.cuda.device(device):
-            N.check(N.lib().ftb200_arena_alloc(ctypes.byref(p), ctypes.c_ulonglong(self.nbytes)), "arena_alloc", 0)
+            if os.environ.get("FTB200_ARENA", "vmm") != "ipc":
+                fd, padded = ctypes.c_int(-1), ctypes.c_ulonglong(0)
+                rc = N.lib().ftb200_vmm_alloc(ctypes.byref(p), ctypes.c_ulonglong(self.nbytes), ctypes.byref(fd),
+                                              ctypes.byref(padded))
+                if rc == 0:
+                    self.kind, self.mapped_bytes = "vmm", int(padded.value)
+                    self._fd_server = _FdServer(int(fd.value))
+                else:
+                    logger.warning("VMM arena unavailable (code %d): falling back to a legacy CUDA IPC arena", rc)
+            if self.kind == "ipc":
+                N.check(N.lib().ftb200_arena_alloc(ctypes.byref(p), ctypes.c_ulonglong(self.nbytes)), "arena_alloc", 0)
             self.base = int(p.value)
             self.bytes_view = torch.as_tensor(_RawMemory(self.base, self.nbytes, self), device=device)
         self._off = 0
@@ -88,10 +156,39 @@ class Arena:
         return self.bytes_view[off : off + nb].view(dtype)
 
     def export_handle(self) -> bytes:
+        """What a peer needs to map this arena: for a VMM arena the address of the descriptor server and the
+        mapped size, for a legacy arena the 64-byte CUDA IPC handle."""
+        if self.kind == "vmm":
+            assert self._fd_server is not None
+            return b"vmm:" + f"{self.mapped_bytes}:".encode() + self._fd_server.address.encode()
         buf = (ctypes.c_ubyte * 64)()
         with torch.cuda.device(self.device):
             N.check(N.lib().ftb200_ipc_export(ctypes.c_void_p(self.base), buf), "ipc_export", 0)
-        return bytes(buf)
+        return b"ipc:" + bytes(buf)
+
+    @staticmethod
+    def import_handle(handle: bytes, timeout_s: float = 30.0) -> tuple:
+        """Maps a peer's arena for the current device; returns ``(base address, kind)``."""
+        ptr = ctypes.c_void_p()
+        if handle.startswith(b"vmm:"):
+            size, _, address = handle[4:].partition(b":")
+            fd = _FdServer.fetch(address.decode(), timeout_s)
+            try:
+                N.check(N.lib().ftb200_vmm_import(ctypes.c_int(fd), ctypes.c_ulonglong(int(size)), ctypes.byref(ptr)),
+                        "vmm_import", 0)
+            finally:
+                os.close(fd)
+            return int(ptr.value), "vmm"
+        raw = handle[4:] if handle.startswith(b"ipc:") else handle
+        N.check(N.lib().ftb200_ipc_import((ctypes.c_ubyte * 64).from_buffer_copy(raw), ctypes.byref(ptr)), "ipc_import", 0)
+        return int(ptr.value), "ipc"
+
+    @staticmethod
+    def release_import(base: int, kind: str) -> None:
+        if kind == "vmm":
+            N.lib().ftb200_vmm_free(ctypes.c_void_p(base))
+        else:
+            N.lib().ftb200_ipc_close(ctypes.c_void_p(base))
 
     def contains(self, t: torch.Tensor) -> Optional[int]:
         """Offset of ``t`` inside the arena, or None."""
@@ -126,7 +223,7 @@ class SymmetricTeam:
         self.epoch = 0
         self._seq = 0
         self.peer_base: List[int] = [self.arena.base]
-        self._imported: List[int] = []
+        self._imported: List[tuple] = []
         self._lock = threading.Lock()
 
     # ---- membership -----------------------------------------------------------------------
@@ -151,11 +248,9 @@ class SymmetricTeam:
                     bases.append(self.arena.base)
                     continue
                 handle = store.get(f"arena/{p}")
-                ptr = ctypes.c_void_p()
-                N.check(self.lib.ftb200_ipc_import((ctypes.c_ubyte * 64).from_buffer_copy(handle), ctypes.byref(ptr)),
-                        "ipc_import", 0)
-                self._imported.append(int(ptr.value))
-                bases.append(int(ptr.value))
+                base, kind = Arena.import_handle(bytes(handle), self.timeout.total_seconds())
+                self._imported.append((base, kind))
+                bases.append(base)
             self.peer_base = bases
             # nobody may signal into flags that a slower peer has not cleared yet
             store.set(f"mapped/{rank}", b"1")
@@ -163,8 +258,8 @@ class SymmetricTeam:
                 store.get(f"mapped/{p}")
 
     def _close_peers(self) -> None:
-        for ptr in self._imported:
-            self.lib.ftb200_ipc_close(ctypes.c_void_p(ptr))
+        for base, kind in self._imported:
+            Arena.release_import(base, kind)
         self._imported = []
         self.peer_base = [self.arena.base]
 
@@ -335,13 +430,12 @@ class PeerShardComm(ShardComm):
         self.team = SymmetricTeam(self.device, arena_bytes, timeout)
         # exchange IPC handles through the (static) group itself
         handle = self.team.arena.export_handle()
-        mine = torch.tensor(list(handle), dtype=torch.uint8, device=self.device)
-        allh = [torch.empty_like(mine) for _ in range(self.size)]
-        dist.all_gather(allh, mine, group=group)
+        allh: List[Optional[bytes]] = [None] * self.size
+        dist.all_gather_object(allh, handle, group=group)
 
         class _ListStore:
             def __init__(s) -> None:
-                s.kv: Dict[str, bytes] = {f"arena/{p}": bytes(allh[p].cpu().tolist()) for p in range(self.size)}
+                s.kv: Dict[str, bytes] = {f"arena/{p}": bytes(allh[p]) for p in range(self.size)}
 
             def set(s, k: str, v: bytes) -> None:
                 s.kv[k] = v

@@ -52,7 +52,10 @@ def main() -> None:
     num_groups = int(os.environ.get("NUM_REPLICA_GROUPS", 2))
     steps = int(os.environ.get("STEPS", 100))
     use_cuda = torch.cuda.is_available()
-    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", 0))) if use_cuda else torch.device("cpu")
+    # GPU_OFFSET: first GPU of this replica group when several groups share one box (torchrun numbers
+    # LOCAL_RANK from 0 in every group)
+    gpu = int(os.environ.get("LOCAL_RANK", 0)) + int(os.environ.get("GPU_OFFSET", 0))
+    device = torch.device("cuda", gpu) if use_cuda else torch.device("cpu")
     if use_cuda:
         torch.cuda.set_device(device)
 
