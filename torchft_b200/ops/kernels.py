@@ -529,10 +529,10 @@ def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int,
     scale = 1.0 / math.sqrt(head_dim)
     impl = os.environ.get("FTB200_ATTN_FWD", "auto")
     if impl == "auto":
-        impl = "pair" if seq_len % 256 == 0 else "single"
+        impl = "single"  # same speed as "pair" at head dim 128 and fewer registers
     if impl == "pair" or head_dim != 128:
         # two query tiles per CTA, one softmax thread per row (head dim 64 or 128, seq % 256 == 0)
-        poly = int(os.environ.get("FTB200_ATTN_POLY", "2"))
+        poly = int(os.environ.get("FTB200_ATTN_POLY", "0"))
         N.check(
             N.lib().ftb200_attention_fwd2(ptr(q), ptr(k), ptr(v), ptr(out), ptr(lse), c_int(batch), c_int(seq_len),
                                           c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_ll(q.stride(0)),
