@@ -247,6 +247,26 @@ class Punisher:
         for g, pid in self._pids().items():
             signal_tree(pid, signal.SIGKILL)
 
+    @staticmethod
+    def deliver(launcher_pid: int, kind: str, hang_secs: float = 30.0) -> None:
+        """One failure of ``kind`` for the group whose launcher is ``launcher_pid``: ``kill`` takes the launcher and
+        everything below it, the other kinds go to the trainer processes (the launcher's children) only; a hung
+        group is killed after ``hang_secs`` so that whoever supervises the launcher can replace it."""
+        if kind not in FAILURE_KINDS:
+            raise ValueError(f"unknown failure kind {kind!r}; expected one of {FAILURE_KINDS}")
+        if kind == "kill":
+            signal_tree(launcher_pid, signal.SIGKILL)
+            return
+        sig = {"segfault": signal.SIGSEGV, "hang": signal.SIGSTOP, "comms": signal.SIGUSR1}[kind]
+        for q in _descendants(launcher_pid, max_depth=1):
+            try:
+                os.kill(q, sig)
+            except ProcessLookupError:
+                pass
+        if kind == "hang":
+            time.sleep(hang_secs)
+            signal_tree(launcher_pid, signal.SIGKILL)
+
     def inject(self, kind: str, group: Optional[int] = None, hang_secs: float = 30.0) -> Optional[int]:
         """Inject one failure of ``kind`` (see :data:`FAILURE_KINDS`) into ``group`` (random when None).
         ``segfault``, ``hang`` and ``comms`` go to the trainer processes only, not to their launcher; a hung
