@@ -123,8 +123,8 @@ def main() -> None:
             n = one_step(manager, ddp, optimizer)
             if n < 2:
                 time.sleep(0.01)  # alone: keep asking for quorums (that is how a joiner gets in) without racing ahead
-            if time.time() - t_start > 600:
-                print(json.dumps({"role": a.role, "error": "no target after 600 s", **stats}), flush=True)
+            if time.time() - t_start > 400:
+                print(json.dumps({"role": a.role, "error": "no target after 400 s", **stats}), flush=True)
                 os._exit(3)
     else:
         for cycle in range(a.cycles + 1):
@@ -137,6 +137,9 @@ def main() -> None:
                                                            f"(participants {n}, step {manager.current_step()})", **stats}), flush=True)
                 os._exit(4)
             stats["heals"] += 1
+            if cycle % 10 == 0:
+                print(f"[cycler] cycle {cycle} healed at step {manager.current_step()} after {time.time() - t_start:.1f} s",
+                      file=sys.stderr, flush=True)
             if cycle == a.cycles:
                 # the last join stays: agree on a final step
                 target = manager.current_step() + 20

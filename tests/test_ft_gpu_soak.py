@@ -7,6 +7,7 @@ import json
 import os
 import subprocess
 import sys
+import time
 
 import pytest
 import torch
@@ -18,7 +19,7 @@ WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ft_gpu_soak_
 CYCLES = int(os.environ.get("FTB200_SOAK_CYCLES", "100"))
 
 
-def _soak(cycles, cpu):
+def _soak(cycles, cpu, limit_s=420.0):
     lh = LighthouseServer("[::]:0", 1, join_timeout_ms=100, quorum_tick_ms=10, heartbeat_timeout_ms=400)
     addr = "http://127.0.0.1:" + lh.address().rsplit(":", 1)[1]
     control = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False)
@@ -30,11 +31,22 @@ def _soak(cycles, cpu):
                 [sys.executable, WORKER, "--role", role, "--gpu", str(gpu), "--lighthouse", addr, "--control",
                  f"127.0.0.1:{control.port}", "--cycles", str(cycles)] + (["--cpu"] if cpu else []),
                 stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, env=env))
-        results = {}
+        # wait for both; when one of them ends badly the other is stopped at once instead of running into its own limit
+        deadline = time.time() + limit_s
+        while any(p.poll() is None for p in procs):
+            if any(p.poll() not in (None, 0) for p in procs) or time.time() > deadline:
+                break
+            time.sleep(0.2)
+        outs = []
         for p in procs:
-            out, err = p.communicate(timeout=600)
+            if p.poll() is None:
+                p.kill()
+            outs.append(p.communicate())
+        results = {}
+        for p, (out, err) in zip(procs, outs):
             lines = [l for l in out.splitlines() if l.startswith("{")]
-            assert p.returncode == 0 and lines, f"rc={p.returncode}\nstdout={out[-2000:]}\nstderr={err[-3000:]}"
+            assert p.returncode == 0 and lines, (
+                f"rc={p.returncode}\nstdout={out[-2000:]}\nstderr={err[-3000:]}\nother stderr={outs[1 - procs.index(p)][1][-2000:]}")
             r = json.loads(lines[-1])
             results[r["role"]] = r
         anchor, cycler = results["anchor"], results["cycler"]
