@@ -2,7 +2,7 @@
 over NVLink peer memory, trains and leaves again a hundred times in a row -- every time as a new replica with
 fresh weights, every departure between steps with nothing in flight.  No hang, no failed commit on the
 survivor, a hundred heals, and identical weights at the end.  NVLS is off and all kernels use plain peer
-loads.  (A replica that dies inside a kernel is not tested on a GPU: closed on this pool.)"""
+loads.  (A replica that dies while one of its kernels is in flight is deliberately not part of any GPU test: the GPUs are shared.)"""
 import json
 import os
 import subprocess

@@ -149,7 +149,7 @@ def main() -> None:
                 raise SystemExit(f"peer group errored: {K_err}")
 
             # The reference's Triton kernels index with 32-bit offsets: at 4 GB (bf16: 2^31 elements) they made
-            # an illegal memory access on this pool, so they are run up to 1 GB only.
+            # an illegal memory access on a B200 (Triton 3.6), so they are run up to 1 GB only.
             if ref_fn is not None and nbytes <= (1 << 30):
                 shapes = [("ref-fp8 [n/4096, 4096]", (n // 4096, 4096))]
                 if mb <= 16:

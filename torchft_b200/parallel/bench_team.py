@@ -5,8 +5,8 @@
 
 One JSON line per (op, size): device-timed (CUDA events, max over ranks) time, algorithm
 and bus bandwidth (allreduce: 2(n-1)/n x bytes / t; all-gather and reduce-scatter:
-(n-1)/n x bytes / t) and the fraction of the 770 GB/s measured per-direction NVLink copy
-bandwidth on this pool.
+(n-1)/n x bytes / t) and the fraction of 770 GB/s, a measured per-direction NVLink peer-copy
+bandwidth of an HGX B200 box.
 """
 
 from __future__ import annotations
