@@ -245,6 +245,8 @@ def main() -> int:
 
     # ---- device-resident timed region
     phase("timed region")
+    if os.environ.get("FTB200_TIMELINE", "0") == "1":
+        trainer.exposed_comm_ms()  # drop what the warm-up recorded
     sampler = ClockSampler(local_rank)
     sync_all()
     if rank == 0:
@@ -259,6 +261,7 @@ def main() -> int:
     e1.record()
     sync_all()
     launches = N.launch_count - launches0
+    exposed = trainer.exposed_comm_ms() if os.environ.get("FTB200_TIMELINE", "0") == "1" else None
     ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
@@ -329,6 +332,7 @@ def main() -> int:
             },
             "gpu_launches": launches,
             "commits": commits,
+            **({"exposed_comm_ms_per_step": {k: round(v / args.steps, 3) for k, v in exposed.items()}} if exposed else {}),
             "model_tflops_per_gpu": flops * args.steps / (ms_total / 1e3) / 1e12,
             "loss": final_loss,
         }

@@ -15,6 +15,7 @@ whose replicate dimension is a ``ManagedProcessGroup`` (torchft/device_mesh.py:3
 
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -126,6 +127,10 @@ class ShardedLlamaTrainer:
         self._rs_event: Dict[int, Optional[torch.cuda.Event]] = {}
         self._gathered = [ws == 1] * U
         self._works: List = []
+        # FTB200_TIMELINE=1: bracket every point at which the compute stream waits for the communication stream with
+        # CUDA events; `exposed_comm_ms()` then says how much of the gathers and reductions was not hidden
+        self._timeline = self.cuda and os.environ.get("FTB200_TIMELINE", "0") == "1"
+        self._stalls: Dict[str, List[tuple]] = {"all_gather": [], "grad_buffer": [], "tail": []}
         self.sumsq = torch.zeros(1, dtype=f32, device=device)
         self.clip = torch.ones(1, dtype=f32, device=device)
         self.grad_norm = torch.zeros(1, dtype=f32, device=device)
@@ -180,7 +185,7 @@ class ShardedLlamaTrainer:
             self._issue_all_gather(u)
             ev = self._ag_event[u]
             if ev is not None:
-                torch.cuda.current_stream().wait_event(ev)
+                self._wait_timed("all_gather", lambda: torch.cuda.current_stream().wait_event(ev))
                 self._ag_event[u] = None
             if u + 1 < self.cfg.n_units:
                 self._issue_all_gather(u + 1)
@@ -189,7 +194,7 @@ class ShardedLlamaTrainer:
             key = self._grad_buf(u).data_ptr()
             ev = self._rs_event.pop(key, None)
             if ev is not None:
-                torch.cuda.current_stream().wait_event(ev)
+                self._wait_timed("grad_buffer", lambda: torch.cuda.current_stream().wait_event(ev))
 
     def _grad_fields(self, u: int):
         """Scatter targets for the matrices of unit ``u`` (None for the embedding unit, whose
@@ -278,8 +283,29 @@ class ShardedLlamaTrainer:
             w.wait()
         self._works.clear()
         if self.comm_stream is not None:
-            torch.cuda.current_stream().wait_stream(self.comm_stream)
+            self._wait_timed("tail", lambda: torch.cuda.current_stream().wait_stream(self.comm_stream))
         self._rs_event.clear()
+
+    def _wait_timed(self, kind: str, wait) -> None:
+        if not self._timeline:
+            wait()
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        wait()
+        b.record()
+        self._stalls[kind].append((a, b))
+
+    def exposed_comm_ms(self, reset: bool = True) -> Dict[str, float]:
+        """With ``FTB200_TIMELINE=1``: milliseconds the compute stream spent, since the last call, waiting for the
+        communication stream -- for a unit's all-gather before its first GEMM, for a gradient buffer still being
+        reduced, and for the tail of the reductions after the backward pass.  Synchronises the device."""
+        torch.cuda.synchronize(self.device)
+        out = {k: float(sum(a.elapsed_time(b) for a, b in v)) for k, v in self._stalls.items()}
+        if reset:
+            for v in self._stalls.values():
+                v.clear()
+        return out
 
     def optimizer_step(self) -> None:
         self.opt_step += 1
