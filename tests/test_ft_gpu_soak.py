@@ -46,7 +46,8 @@ def _soak(cycles, cpu, limit_s=420.0):
         for p, (out, err) in zip(procs, outs):
             lines = [l for l in out.splitlines() if l.startswith("{")]
             assert p.returncode == 0 and lines, (
-                f"rc={p.returncode}\nstdout={out[-2000:]}\nstderr={err[-3000:]}\nother stderr={outs[1 - procs.index(p)][1][-2000:]}")
+                f"rc={p.returncode}\nstdout={out[-2000:]}\nstderr={err[-3000:]}\n"
+                f"other stdout={outs[1 - procs.index(p)][0][-1000:]}\nother stderr={outs[1 - procs.index(p)][1][-2000:]}")
             r = json.loads(lines[-1])
             results[r["role"]] = r
         anchor, cycler = results["anchor"], results["cycler"]
