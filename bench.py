@@ -221,9 +221,12 @@ def main() -> int:
 
     # ---- warm-up
     phase("warm-up")
+    first_loss = None
     for i in range(args.warmup):
         t = dev_tok[i]
         loss = trainer.train_step(t[:, :-1], t[:, 1:])
+        if first_loss is None:
+            first_loss = float(loss.item())
     K.check_status(dev)
 
     def committed_steps() -> int:
@@ -334,6 +337,9 @@ def main() -> int:
             "commits": commits,
             **({"exposed_comm_ms_per_step": {k: round(v / args.steps, 3) for k, v in exposed.items()}} if exposed else {}),
             "model_tflops_per_gpu": flops * args.steps / (ms_total / 1e3) / 1e12,
+            # uniform-random targets cannot be learned: the loss stays near that of the random initialisation,
+            # ln(vocab) plus half the variance of the initial logits, and drifts down only as the logits shrink
+            "loss_first_step": first_loss,
             "loss": final_loss,
         }
         print(json.dumps(out), flush=True)

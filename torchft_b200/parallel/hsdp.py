@@ -74,13 +74,9 @@ class ShardedLlamaTrainer:
         # shards that peers of the shard group read (all-gather sources) come from the shard
         # communicator; gradient shards are what the replica dimension reduces, so they come
         # from the replica group's allocator when it has one (in-place peer-memory allreduce)
-        self.p_shard = [A(n, bf, device) for n in self.shard_numel]
-        if replica_alloc is not None:
-            self.g_shard = [replica_alloc(n, bf) for n in self.shard_numel]
-        else:
-            self.g_shard = [torch.empty(n, dtype=bf, device=device) for n in self.shard_numel]
-        # fp32 master weights and AdamW moments: one allocation each, units are views.  A peer that
-        # heals from this rank then maps three allocations instead of three per unit.
+        # Every kind of per-rank state is ONE allocation with the units as views: the optimizer and the gradient norm
+        # are then single launches over the whole model, and a peer that heals from this rank maps three allocations
+        # (master weights and the two AdamW moments) instead of three per unit.
         def carve(flat: torch.Tensor) -> List[torch.Tensor]:
             out, off = [], 0
             for n in self.shard_numel:
@@ -89,9 +85,14 @@ class ShardedLlamaTrainer:
             return out
 
         total = sum(self.shard_numel)
-        self.master = carve(torch.empty(total, dtype=f32, device=device))
-        self.m = carve(torch.zeros(total, dtype=f32, device=device))
-        self.v = carve(torch.zeros(total, dtype=f32, device=device))
+        self.p_flat = A(total, bf, device)
+        self.p_shard = carve(self.p_flat)
+        self.g_flat = replica_alloc(total, bf) if replica_alloc is not None else torch.empty(total, dtype=bf, device=device)
+        self.g_shard = carve(self.g_flat)
+        self.master_flat = torch.empty(total, dtype=f32, device=device)
+        self.m_flat = torch.zeros(total, dtype=f32, device=device)
+        self.v_flat = torch.zeros(total, dtype=f32, device=device)
+        self.master, self.m, self.v = carve(self.master_flat), carve(self.m_flat), carve(self.v_flat)
         if ws == 1:
             self.p_full = self.p_shard
             self._g_bufs: Dict[int, List[torch.Tensor]] = {}
@@ -310,14 +311,12 @@ class ShardedLlamaTrainer:
     def optimizer_step(self) -> None:
         self.opt_step += 1
         self.sumsq.zero_()
-        for u in range(self.cfg.n_units):
-            K.sumsq_(self.g_shard[u], self.sumsq)
+        K.sumsq_(self.g_flat, self.sumsq)
         self.comm.all_reduce_sum_(self.sumsq)
         K.clip_coef_(self.sumsq, self.max_grad_norm, self.clip, self.grad_norm)
         b1, b2 = self.betas
-        for u in range(self.cfg.n_units):
-            K.adamw_(self.master[u], self.m[u], self.v[u], self.g_shard[u], self.p_shard[u], self.lr, b1, b2, self.eps,
-                     self.wd, self.opt_step, self.clip)
+        K.adamw_(self.master_flat, self.m_flat, self.v_flat, self.g_flat, self.p_flat, self.lr, b1, b2, self.eps, self.wd,
+                 self.opt_step, self.clip)
         if self.comm.size > 1:
             self._gathered = [False] * self.cfg.n_units
 
