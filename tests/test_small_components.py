@@ -239,19 +239,35 @@ def test_open_group_store():
     assert [r["who"] for r in res] == ["group0", "group0", "group1", "group1"]
 
 
-def test_bench_reference_arm_reports_unavailable():
-    """`bench.py --impl reference` prints one JSON line saying why the reference cannot run here."""
+def test_bench_reference_arm():
+    """`bench.py --impl reference` runs the unmodified reference package (a copy under baseline/_ref) on the pure-Python
+    control-plane stand-in.  Without a GPU it prints one `unavailable` line and exits 0; with `FTB200_REF_DEVICE=cpu` the
+    same path runs a tiny model over Gloo, which checks the stand-in and the reference's manager, optimizer wrapper and
+    managed process group end to end."""
     import json
     import os
     import subprocess
     import sys
 
+    import pytest
+
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
-                        "--warmup", "3"], capture_output=True, text=True, timeout=120)
-    assert r.returncode == 0, r.stderr[-1000:]
+    if not os.path.isdir(os.path.join(root, "baseline", "_ref", "torchft")):
+        pytest.skip("no copy of the reference package under baseline/_ref")
+    cmd = [sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "3"]
+    import torch
+
+    if not torch.cuda.is_available():
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-1000:]
+        line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
+        assert line["impl"] == "reference" and "no CUDA device" in line["unavailable"]
+    env = dict(os.environ, FTB200_REF_DEVICE="cpu")
+    r = subprocess.run(cmd + ["--model", "debug", "--seq-len", "64"], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0, r.stderr[-1500:]
     line = json.loads([l for l in r.stdout.splitlines() if l.startswith("{")][-1])
-    assert line["impl"] == "reference" and "unavailable" in line and "maturin" in line["unavailable"]
+    assert line["impl"] == "reference" and line["commits"] == 4 and line["value"] > 0, line
+    assert "stand-in" in line["control_plane"]
 
 
 def test_thread_backed_mp_context_pipe_and_process():
