@@ -3,8 +3,8 @@ LeNet-style CNN on seeded synthetic images (batch 64, SGD lr 1e-3 momentum 0.9, 
 ``Manager``, ``DistributedDataParallel`` and ``OptimizerWrapper`` with ``ProcessGroupGloo`` and the default HTTP
 checkpoint transport; replica 1 is killed at step 20 and started again, and heals from its peer.
 
-    python baseline/reference_config1.py            # launcher; prints one JSON line
-    python baseline/reference_config1.py --impl ours   # the same script on the product package (same public names)
+    python baseline/config1_ft_ddp.py            # launcher; prints one JSON line
+    python baseline/config1_ft_ddp.py --impl ours   # the same script on the product package (same public names)
 
 The control plane is the pure-Python stand-in (``torchft_standin.py``): the reference's Rust extension cannot be
 built offline.  With ``--impl reference`` (the default) nothing of the product package is imported; ``--impl ours``
