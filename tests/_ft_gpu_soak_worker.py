@@ -121,12 +121,15 @@ def main() -> None:
             if target is not None and manager.current_step() >= target:
                 finish(manager)
             n = one_step(manager, ddp, optimizer)
+            if manager.current_step() == 3:
+                control.set("anchor_ready", "1")  # the cycler's first join must find a running job
             if n < 2:
                 time.sleep(0.01)  # alone: keep asking for quorums (that is how a joiner gets in) without racing ahead
             if time.time() - t_start > 400:
                 print(json.dumps({"role": a.role, "error": "no target after 400 s", **stats}), flush=True)
                 os._exit(3)
     else:
+        control.wait(["anchor_ready"], timedelta(seconds=120))
         for cycle in range(a.cycles + 1):
             manager, ddp, optimizer = fresh(1000 + cycle)
             before = float(sum(p.detach().double().sum().item() for p in model.parameters()))
