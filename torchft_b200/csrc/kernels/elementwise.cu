@@ -168,15 +168,28 @@ __global__ void __launch_bounds__(512, MAXV == 1 ? 2 : 1) rmsnorm_bwd_kernel(con
   }
 }
 
-// dw[c] (+)= sum_b partial[b][c]
+// dw[c] (+)= sum_b partial[b][c].  A block owns 32 columns; its 8 warps stride over the rows (each warp
+// instruction reads one 128-byte row segment) and meet in shared memory, so a few hundred rows are a few
+// dozen independent loads per thread instead of one long serial loop.
 __global__ void colsum_partials_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, int nblk, int D,
                                        int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int b = 0; b < nblk; ++b) s += partial[static_cast<int64_t>(b) * D + c];
-  if (accumulate) s += __bfloat162float(dw[c]);
-  dw[c] = __float2bfloat16(s);
+  if (c < D) {
+#pragma unroll 4
+    for (int b = ry; b < nblk; b += 8) s += partial[static_cast<int64_t>(b) * D + c];
+  }
+  red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cx];
+    if (accumulate) t += __bfloat162float(dw[c]);
+    dw[c] = __float2bfloat16(t);
+  }
 }
 
 // ------------------------------------------------------------------ RoPE (interleaved pairs)
@@ -451,7 +464,7 @@ FTB200_API int ftb200_rmsnorm_bwd(const void* dy, const void* x, const void* w, 
                                                     (const bf16x8*)dres, (bf16x8*)dx, dw_partial, T, D8);
   else
     return FTB200_E_TOOBIG;  // D > 8192
-  colsum_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
+  colsum_partials_kernel<<<(D + 31) / 32, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
@@ -578,7 +591,7 @@ FTB200_API int ftb200_rmsnorm_bwd_noalloc(const void* dy, const void* x, const v
   else
     rmsnorm_bwd_kernel<4><<<nblk, threads, 0, st>>>((const bf16x8*)dy, (const bf16x8*)x, (const bf16x8*)w, rstd,
                                                     (const bf16x8*)dres, (bf16x8*)dx, scratch, T, D8);
-  colsum_partials_kernel<<<(D + 255) / 256, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
+  colsum_partials_kernel<<<(D + 31) / 32, 256, 0, st>>>(scratch, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 

@@ -187,15 +187,26 @@ rmsnorm_bwd_pipe_kernel(const bf16x8* __restrict__ dy, const bf16x8* __restrict_
   }
 }
 
-// dw[c] (+)= sum_b partial[b][c]
+// dw[c] (+)= sum_b partial[b][c]: 32 columns per block, 8 warps striding over the rows
 __global__ void colsum_partials_pipe_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ dw, int nblk,
                                             int D, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= D) return;
+  __shared__ float red[8][33];
+  const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int b = 0; b < nblk; ++b) s += partial[static_cast<int64_t>(b) * D + c];
-  if (accumulate) s += __bfloat162float(dw[c]);
-  dw[c] = __float2bfloat16(s);
+  if (c < D) {
+#pragma unroll 4
+    for (int b = ry; b < nblk; b += 8) s += partial[static_cast<int64_t>(b) * D + c];
+  }
+  red[ry][cx] = s;
+  __syncthreads();
+  if (ry == 0 && c < D) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += red[k][cx];
+    if (accumulate) t += __bfloat162float(dw[c]);
+    dw[c] = __float2bfloat16(t);
+  }
 }
 
 }  // namespace
@@ -224,6 +235,6 @@ FTB200_API int ftb200_rmsnorm_bwd_pipe(const void* dy, const void* x, const void
   const int nblk = std::min(T, ftb200::sm_count());
   rmsnorm_bwd_pipe_kernel<<<nblk, consumers + 32, smem, st>>>((const bf16x8*)dy, (const bf16x8*)x, (const bf16x8*)w, rstd,
                                                               (const bf16x8*)dres, (bf16x8*)dx, dw_partial, T, D8, status);
-  colsum_partials_pipe_kernel<<<(D + 255) / 256, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
+  colsum_partials_pipe_kernel<<<(D + 31) / 32, 256, 0, st>>>(dw_partial, (__nv_bfloat16*)dw, nblk, D, accumulate_dw);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
