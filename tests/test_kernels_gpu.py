@@ -78,28 +78,6 @@ def test_rmsnorm(T, D):
     assert rel_err(dw, rdw) < 2e-2
 
 
-@pytest.mark.parametrize("T,D,with_res", [(64, 256, True), (33, 4096, True), (7, 1024, False), (701, 4096, True), (2500, 2048, False),
-                                          (300, 1600, True)])
-def test_rmsnorm_bwd_pipelined_kernel(monkeypatch, T, D, with_res):
-    """The RMSNorm backward that streams its rows through shared memory with bulk asynchronous copies: more rows
-    than the ring has stages, fewer rows than blocks, rows narrower than a full warp multiple, with and without the
-    residual gradient, and accumulation into dw."""
-    monkeypatch.setenv("FTB200_RMSNORM_BWD", "pipe")
-    torch.manual_seed(14)
-    x = torch.randn(T, D, device=DEV).bfloat16()
-    w = (1 + 0.1 * torch.randn(D, device=DEV)).bfloat16()
-    _, rstd, _ = K.rmsnorm_fwd(x, w, 1e-5)
-    dy = torch.randn(T, D, device=DEV).bfloat16()
-    dres = torch.randn(T, D, device=DEV).bfloat16() if with_res else None
-    start = torch.randn(D, device=DEV).bfloat16()
-    dw = start.clone()
-    dx, dw = K.rmsnorm_bwd(dy, x, w, rstd, dres=dres, dw=dw, accumulate_dw=True)
-    K.check_status(x.device)
-    rdx, rdw = K.ref_rmsnorm_bwd(dy, x, w, rstd, dres)
-    assert rel_err(dx, rdx) < 1e-2
-    assert rel_err(dw, start.float() + rdw.float()) < 2e-2
-
-
 def test_rope_roundtrip_and_ref():
     torch.manual_seed(5)
     S, Hq, Hkv, Dh = 64, 4, 2, 64

@@ -13,15 +13,10 @@
 //   warp 0        TMA: Q tiles once, K and V blocks into a 2-stage ring
 //   warp 1        tcgen05.mma, in the order  P0 V, S0', P1 V, S1'  (' = next block): the softmax of
 //                 a tile has the two MMAs of the other tile to hide under
-//   warps 2..9    softmax of tile 0, warps 10..17 softmax of tile 1: TWO threads per query row,
-//                 64 scores each (the 128 scores of a row sit in one TMEM lane; the two threads
-//                 are in warps of the same lane quarter).  They exchange their half-row maxima
-//                 through shared memory behind a named barrier of their two warps only.  With one
-//                 thread per row (an earlier version) a scheduler had two softmax warps to pick
-//                 from and issued on 29 % of its cycles: the loop was bound by instruction
-//                 latency, not by the exponential unit or the tensor pipe (35 % each).  P goes
-//                 back as packed bf16 into the first 64 columns of the scores and is the A operand
-//                 of P V straight from tensor memory.
+//   warps 2..5    softmax of tile 0, warps 6..9 softmax of tile 1: ONE thread per query row (the
+//                 128 scores of a row sit in one TMEM lane), so the row maximum and sum need no
+//                 exchange between threads.  P goes back as packed bf16 into the first 64 columns
+//                 of the scores and is the A operand of P V straight from tensor memory.
 //
 // A share of the exponentials (POLY of every 8) is computed with a cubic polynomial on the FMA
 // pipe instead of the exponential unit, which is the scarcer of the two; its relative error of
@@ -45,9 +40,8 @@ constexpr int BQ = 128;       // queries per tile
 constexpr int TILES = 2;      // tiles per CTA
 constexpr int BKV = 128;      // keys per block
 constexpr int KV_STAGES = 2;
-constexpr int NUM_THREADS = 576;
-constexpr int ROW_THREADS = 256;  // softmax threads per tile: two per query row
-constexpr int HALF = BKV / 2;     // score columns per softmax thread
+constexpr int NUM_THREADS = 320;
+constexpr int ROW_THREADS = 128;  // softmax threads per tile
 constexpr uint32_t TMEM_COLS = 512;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // in log2 units
 
@@ -59,8 +53,7 @@ struct Cfg {
   static constexpr uint32_t OFF_Q = 0;                      // Q0 Q1
   static constexpr uint32_t OFF_KV = TILES * TILE_BYTES;    // K0 V0 | K1 V1
   static constexpr uint32_t OFF_MISC = OFF_KV + KV_STAGES * 2 * TILE_BYTES;
-  static constexpr uint32_t XCHG_BYTES = 2 * TILES * 2 * BQ * 4;  // [parity][tile][half][row] floats
-  static constexpr uint32_t SMEM_BYTES = OFF_MISC + 256 + XCHG_BYTES + 1024;
+  static constexpr uint32_t SMEM_BYTES = OFF_MISC + 256 + 1024;
   static constexpr uint32_t COL_S = 0;                      // S_t at COL_S + t * 128
   static constexpr uint32_t COL_O = 256;                    // O_t at COL_O + t * D
 };
@@ -109,7 +102,6 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::OFF_MISC);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::OFF_MISC + 192);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + C::OFF_MISC + 196);
-  float* xchg = reinterpret_cast<float*>(smem + C::OFF_MISC + 256);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -285,61 +277,38 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     }
     __syncwarp();
   } else {
-    // ---------------- softmax + epilogue: two threads per query row ----------------
-    const int t = (warp - 2) >> 3;          // tile
-    const int half = ((warp - 2) >> 2) & 1; // which 64 score columns (and which half of the output columns)
-    const int quarter = warp & 3;           // TMEM lane quarter this warp may touch
+    // ---------------- softmax + epilogue: one thread per query row ----------------
+    const int t = (warp - 2) >> 2;   // tile
+    const int quarter = warp & 3;    // TMEM lane quarter this warp may touch
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    const uint32_t s_addr = tmem_base + C::COL_S + t * 128 + half * HALF + lane_addr;
-    const uint32_t p_addr = tmem_base + C::COL_S + t * 128 + half * (HALF / 2) + lane_addr;
-    const uint32_t o_addr = tmem_base + C::COL_O + t * D + half * (D / 2) + lane_addr;
-    const int pair_bar = 2 + t * 4 + quarter;  // named barrier of the two warps that share these rows
+    const uint32_t s_addr = tmem_base + C::COL_S + t * 128 + lane_addr;
+    const uint32_t o_addr = tmem_base + C::COL_O + t * D + lane_addr;
     const int n_kv = t == 0 ? n_kv0 : n_kv1;
-    float m_used = -INFINITY, l_part = 0.f;
-    // A wait that ran out must not leave the partner warp alone at the named barrier (that barrier has no
-    // limit): a warp that failed keeps walking to the next exchange, publishes FAIL_BITS instead of a number,
-    // and both warps leave together.
-    constexpr uint32_t FAIL_BITS = 0x7FC00000u;
-    bool failed = false;
-    auto xslot = [&](int parity, int h) { return xchg + ((parity * TILES + t) * 2 + h) * BQ + row; };
+    float m_used = -INFINITY, l_sum = 0.f;
+    bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
-      // (the outcome of a wait is made the same in all lanes: the tcgen05.ld/st below are warp-wide)
-      const bool got = __all_sync(0xffffffffu, !failed && mbar_wait(bar(BAR_S_FULL + t), static_cast<uint32_t>(j) & 1u, abort_flag));
-      failed = failed || !got;
-      uint32_t sv[HALF];
-      float mx = -INFINITY;
-      if (got) {
-        tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < HALF / 32; ++c) tmem_ld32(s_addr + c * 32, sv + c * 32);
-        tmem_wait_ld();
-        if (p.causal && j == n_kv - 1) {
-          // the diagonal block: key c of the block is visible to query `row` of the tile iff c <= row
-          const int key0 = half * HALF;
-#pragma unroll
-          for (int c = 0; c < HALF; ++c)
-            if (key0 + c > row) sv[c] = __float_as_uint(-INFINITY);
-        }
-        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int c = 0; c < HALF; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
-        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      } else {
-#pragma unroll
-        for (int c = 0; c < HALF; ++c) sv[c] = 0u;
-      }
-      // the other half of the row belongs to the thread with the same lane in the partner warp
-      *reinterpret_cast<volatile uint32_t*>(xslot(j & 1, half)) = __any_sync(0xffffffffu, failed) ? FAIL_BITS : __float_as_uint(mx);
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      const uint32_t other = *reinterpret_cast<volatile uint32_t*>(xslot(j & 1, half ^ 1));
-      if (__any_sync(0xffffffffu, failed || other == FAIL_BITS)) {
-        failed = true;
+      if (!mbar_wait(bar(BAR_S_FULL + t), static_cast<uint32_t>(j) & 1u, abort_flag)) {
+        ok = false;
         break;
       }
-      const float m_new = fmaxf(mx, __uint_as_float(other));
+      tc_fence_after();
+      uint32_t sv[BKV];
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) tmem_ld32(s_addr + c * 32, sv + c * 32);
+      tmem_wait_ld();
+      if (p.causal && j == n_kv - 1) {
+        // the diagonal block: key c of the block is visible to query `row` of the tile iff c <= row
+#pragma unroll
+        for (int c = 0; c < BKV; ++c)
+          if (c > row) sv[c] = __float_as_uint(-INFINITY);
+      }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < BKV; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sv[c]));
+      const float m_new = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
 
-      // raise the maximum only when it moved far; both threads of a row see the same numbers
+      // raise the maximum only when it moved far
       float alpha = 1.f;
       const bool raise = j > 0 && (m_new - m_used) * p.scale_log2 > RESCALE_THRESHOLD;
       const bool any_raise = __any_sync(0xffffffffu, raise);
@@ -348,14 +317,17 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       } else if (raise) {
         alpha = exp2f((m_used - m_new) * p.scale_log2);
         m_used = m_new;
-        l_part *= alpha;
+        l_sum *= alpha;
       }
       if (any_raise) {
         // O may only be touched once P V of the previous block is done; P V of this block waits for P
-        if (!__all_sync(0xffffffffu, mbar_wait(bar(BAR_O_DONE + t), static_cast<uint32_t>(j - 1) & 1u, abort_flag))) failed = true;
+        if (!mbar_wait(bar(BAR_O_DONE + t), static_cast<uint32_t>(j - 1) & 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < (failed ? 0 : D / 64); ++c) {
+        for (int c = 0; c < D / 32; ++c) {
           uint32_t ov[32];
           tmem_ld32(o_addr + c * 32, ov);
           tmem_wait_ld();
@@ -367,7 +339,7 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       const float neg_m = -m_used * p.scale_log2;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < HALF / 32; ++c) {
+      for (int c = 0; c < BKV / 32; ++c) {
         uint32_t packed[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
@@ -380,31 +352,22 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
           packed[e] = *reinterpret_cast<uint32_t*>(&pk);
         }
-        // P (two keys per column) goes into the first 64 columns of the tile's scores.  The partner's scores
-        // live there too: its thread passed the named barrier above, i.e. it has them in registers.
-        tmem_st16(p_addr + c * 16, packed);
+        // P replaces the first half of the scores this thread has already taken into registers
+        tmem_st16(s_addr + c * 16, packed);
       }
-      l_part += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l_sum += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL + t));
     }
 
-    {
-      const bool got = __all_sync(0xffffffffu, !failed && mbar_wait(bar(BAR_O_DONE + t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag));
-      failed = failed || !got;
+    if (ok && mbar_wait(bar(BAR_O_DONE + t), static_cast<uint32_t>(n_kv - 1) & 1u, abort_flag)) {
       tc_fence_after();
-      // total row sum: the two threads of a row hold partial sums over their keys (FAIL_BITS: see above)
-      *reinterpret_cast<volatile uint32_t*>(xslot(n_kv & 1, half)) = __any_sync(0xffffffffu, failed) ? FAIL_BITS : __float_as_uint(l_part);
-      asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-      const uint32_t other = *reinterpret_cast<volatile uint32_t*>(xslot(n_kv & 1, half ^ 1));
-      failed = __any_sync(0xffffffffu, failed || other == FAIL_BITS);
-      const float l_sum = l_part + __uint_as_float(other);
       const float inv = 1.f / l_sum;
       const long long grow = static_cast<long long>(q_row0 + t * BQ + row);
-      __nv_bfloat16* dst = p.O + grow * p.ld_o + h * D + half * (D / 2);
+      __nv_bfloat16* dst = p.O + grow * p.ld_o + h * D;
 #pragma unroll
-      for (int c = 0; c < (failed ? 0 : D / 64); ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t ov[32];
         tmem_ld32(o_addr + c * 32, ov);
         tmem_wait_ld();
@@ -416,7 +379,7 @@ attention_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
           reinterpret_cast<ftb200::bf16x8*>(dst + c * 32)[q4] = ftb200::pack8(f);
         }
       }
-      if (!failed && half == 0 && p.lse != nullptr) {
+      if (p.lse != nullptr) {
         p.lse[(static_cast<long long>(b) * p.n_heads + h) * p.seq + qp * BQ * TILES + t * BQ + row] =
             (m_used * p.scale_log2 + log2f(l_sum)) * 0.6931471805599453f;
       }

@@ -119,14 +119,6 @@ def bench_elementwise(iters: int) -> list:
     rstd = torch.rand(T, device=dev) + 0.5
     dx, dw = torch.empty(T, D, device=dev, dtype=torch.bfloat16), torch.zeros(D, device=dev, dtype=torch.bfloat16)
     row("rmsnorm_bwd", T * D * 2 * 4, timeit(lambda: K.rmsnorm_bwd(xs(), xs(), w, rstd, dres=xs(), dx=dx, dw=dw), iters))
-    saved = os.environ.get("FTB200_RMSNORM_BWD")
-    os.environ["FTB200_RMSNORM_BWD"] = "pipe" if saved != "pipe" else "plain"
-    row(f"rmsnorm_bwd[{os.environ['FTB200_RMSNORM_BWD']}]", T * D * 2 * 4,
-        timeit(lambda: K.rmsnorm_bwd(xs(), xs(), w, rstd, dres=xs(), dx=dx, dw=dw), iters))
-    if saved is None:
-        os.environ.pop("FTB200_RMSNORM_BWD")
-    else:
-        os.environ["FTB200_RMSNORM_BWD"] = saved
     # RoPE in place on the packed QKV activation (Q and K heads)
     qkvs = cycle(lambda: torch.randn(T, QKV, device=dev).bfloat16(), 6)
     table = K.rope_table(T, 128, 500000.0, torch.device(dev))

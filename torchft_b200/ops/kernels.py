@@ -283,15 +283,6 @@ def rmsnorm_bwd(
     if scratch is None:
         scratch = torch.empty(need, dtype=torch.float32, device=x.device)
         _rms_scratch[key] = scratch
-    if os.environ.get("FTB200_RMSNORM_BWD", "plain") == "pipe" and D <= 4096:
-        # rows streamed through shared memory by bulk asynchronous copies (csrc/kernels/rmsnorm_bwd_pipe.cu)
-        N.check(
-            L.ftb200_rmsnorm_bwd_pipe(ptr(dy), ptr(x), ptr(w), ptr(rstd), ptr(dres), ptr(dx), ptr(dw), ptr(scratch), c_int(T),
-                                      c_int(D), c_int(int(accumulate_dw)), ptr(status_word(x.device)), stream_ptr()),
-            "rmsnorm_bwd_pipe",
-            launches=2,
-        )
-        return dx, dw
     N.check(
         L.ftb200_rmsnorm_bwd(ptr(dy), ptr(x), ptr(w), ptr(rstd), ptr(dres), ptr(dx), ptr(dw), ptr(scratch), c_int(T),
                              c_int(D), c_int(int(accumulate_dw)), stream_ptr()),
