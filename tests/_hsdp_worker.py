@@ -1,7 +1,7 @@
 """torchrun child of tests/test_hsdp_gpu_multi.py: the sharded Llama trainer over 2+ GPUs with
 (a) torch.distributed/NCCL collectives, (b) peer-memory kernels, (c) peer-memory kernels with
-the reduce-scatter fused into the wgrad GEMM epilogue; all three must produce the same
-gradient shards and the same loss trajectory."""
+the reduce-scatter fused into the wgrad GEMM epilogue, (d) as (c) with the all-gather fused into
+the forward GEMMs; all must produce the same gradient shards and the same loss trajectory."""
 import json
 import os
 import sys
@@ -27,9 +27,12 @@ def main() -> None:
     g = torch.Generator().manual_seed(100 + rank)
     tok = torch.randint(0, cfg.vocab_size, (B, S + 1), generator=g).to(dev)
 
-    def run(comm, fused):
-        tr = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=comm, seed=3, logit_chunks=1, fused_reduce_scatter=fused)
-        assert tr.fused_rs == fused
+    def run(comm, fused, fused_ag=False):
+        tr = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=comm, seed=3, logit_chunks=1, fused_reduce_scatter=fused,
+                                 fused_all_gather=fused_ag)
+        assert tr.fused_rs == fused and tr.fused_ag == fused_ag
+        if fused_ag:
+            assert tr._ga_units == list(range(1, cfg.n_units))
         losses = []
         for _ in range(3):
             losses.append(tr.train_step(tok[:, :-1], tok[:, 1:]).item())
@@ -39,9 +42,9 @@ def main() -> None:
 
     ref, ref_losses = run(TorchShardComm(dist.group.WORLD), False)
     out = {"rank": rank, "ref_losses": ref_losses}
-    for name, fused in (("peer", False), ("fused", True)):
+    for name, fused, ag in (("peer", False, False), ("fused", True, False), ("fused_ag", True, True)):
         comm = PeerShardComm(dist.group.WORLD, dev, arena_bytes=256 << 20)
-        tr, losses = run(comm, fused)
+        tr, losses = run(comm, fused, ag)
         comm.team.check()
         worst = 0.0
         for u in range(cfg.n_units):

@@ -1,5 +1,5 @@
-"""Sharded trainer on 2 GPUs: NCCL collectives, peer-memory kernels and the GEMM-fused
-reduce-scatter must agree (needs >= 2 GPUs)."""
+"""Sharded trainer on 2 GPUs: NCCL collectives, peer-memory kernels, the GEMM-fused
+reduce-scatter and the GEMM-fused all-gather must agree (needs >= 2 GPUs)."""
 import json
 import os
 import subprocess
@@ -22,7 +22,7 @@ def test_sharded_trainer_backends_agree():
     lines = [json.loads(l) for l in p.stdout.splitlines() if l.startswith("{")]
     assert p.returncode == 0 and len(lines) == 2, p.stdout[-2000:] + p.stderr[-3000:]
     for r in lines:
-        for name in ("peer", "fused"):
+        for name in ("peer", "fused", "fused_ag"):
             assert r[name]["grad_rel_err"] < 2e-2, (name, r)
             for a, b in zip(r[name]["losses"], r["ref_losses"]):
                 assert abs(a - b) < 2e-2, (name, r)

@@ -240,3 +240,49 @@ def test_linear_swiglu_fused_epilogue():
     assert rel_err(gu, ref_gu) < 1e-2
     assert rel_err(s, K.ref_swiglu_fwd(gu)) < 1e-2
     assert rel_err(s, torch.nn.functional.silu(ref_gu[:, 0::2]) * ref_gu[:, 1::2]) < 2e-2
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("M,N,K_,swiglu", [(256, 256, 64, False), (1024, 1536, 512, False), (2048, 2048, 1024, True),
+                                           (200, 640, 192, False)])
+def test_gemm_with_fused_all_gather(world, M, N, K_, swiglu):
+    """The weight lies spread over `world` shard buffers (here all on this GPU: the kernel only sees pointers) at an
+    offset that makes it straddle shard boundaries; the GEMM gathers it into the local unit while it multiplies."""
+    import ctypes
+
+    torch.manual_seed(7)
+    unit_off = 8 * 331  # some field in front of the weight
+    numel = unit_off + N * K_ + 8 * 57
+    shard = -(-numel // (world * 8)) * 8
+    shard = max(shard, 8192)
+    unit = torch.zeros(shard * world, device=DEV, dtype=torch.bfloat16)
+    unit[:numel] = (torch.randn(numel, device=DEV) * 0.5).bfloat16()
+    shards = [unit[r * shard:(r + 1) * shard].clone() for r in range(world)]
+    peers = (ctypes.c_void_p * 8)()
+    for r in range(world):
+        peers[r] = shards[r].data_ptr()
+    full = torch.full((shard * world,), 7.0, device=DEV, dtype=torch.bfloat16)  # stale content must be overwritten
+    w_true = unit[unit_off:unit_off + N * K_].view(N, K_)
+    sync = torch.full((1 + N // 128,), 12345, device=DEV, dtype=torch.int32)  # the launcher zeroes it
+    field = K.GatherField(full[unit_off:unit_off + N * K_].view(N, K_), peers, world, shard, unit_off, sync)
+    assert K.GatherField.supported((N, K_), shard)
+    x = torch.randn(M, K_, device=DEV).bfloat16()
+    out = torch.empty(M, N, device=DEV, dtype=torch.bfloat16)
+    if swiglu:
+        s_out = torch.empty(M, N // 2, device=DEV, dtype=torch.bfloat16)
+        K.linear_swiglu_fwd(x, field, out, s_out)
+    else:
+        K.linear_fwd(x, field, out=out)
+    torch.cuda.synchronize()
+    K.check_status(out.device)
+    assert not field.pending
+    assert torch.equal(field.local, w_true)
+    assert torch.all(full[:unit_off] == 7.0) and torch.all(full[unit_off + N * K_:] == 7.0)  # nothing outside the field
+    ref = x.float() @ w_true.float().t()
+    assert rel_err(out, ref) < 1e-2
+    if swiglu:
+        g, u = out.float()[:, 0::2], out.float()[:, 1::2]
+        assert rel_err(s_out, torch.nn.functional.silu(g) * u) < 1e-2
+    # second use: an ordinary GEMM on the gathered weight
+    out2 = K.linear_fwd(x, field)
+    assert torch.equal(out2, out)

@@ -15,6 +15,17 @@
 //   tempty[a] (leader)  the 2 x 128 epilogue threads of the pair arrive (remote arrive
 //                       from the peer)
 // All waits are bounded as in the 1-CTA kernel.
+//
+// All-gather fused into the GEMM (ftb200_gemm_bf16_gather): B is a weight whose rows lie
+// spread over the ranks of a shard group, as one contiguous piece of a flat parameter unit
+// that the ranks shard evenly.  Four extra warps per CTA pull the weight out of the owners'
+// shard buffers over NVLink (plain 16-byte peer loads) into the local gathered unit, 16 KiB
+// at a time in row order, and count the finished pieces per block of 128 B rows; the TMA
+// producer of a tile waits (bounded) for the count of its 128 rows and then loads them from
+// local memory, so the tensor cores work on the first tiles while the rest of the weight
+// is still crossing the links, and every remote byte crosses them once.  The pieces are
+// handed out through a counter, so the CTAs that are running pull everything whether or
+// not the whole grid is resident.
 #include <algorithm>
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -34,11 +45,14 @@ constexpr uint32_t A_BYTES = BM * BK * 2;
 constexpr uint32_t B_BYTES = BNH * BK * 2;
 constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int NUM_THREADS = 192;
+constexpr int GATHER_WARPS = 4;  // only launched by the all-gather variant
+constexpr int NUM_THREADS_GATHER = NUM_THREADS + 32 * GATHER_WARPS;
+constexpr int GATHER_PIECE_V = 1024;  // 16-byte vectors per piece (16 KiB)
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 constexpr uint32_t SC_STAGE_WARP_BYTES = 32 * 256;  // scatter epilogue: 32 rows x 128 bf16 per warp
 constexpr uint32_t SMEM_BYTES_SCATTER = SMEM_BYTES + 4 * SC_STAGE_WARP_BYTES;
-constexpr int GROUP_M = 8;  // in 256-row pair tiles
+constexpr int GROUP_M = 8;  // in 256-row pair tiles (the all-gather variant uses twice that)
 
 using namespace ftb200::tc;
 
@@ -114,9 +128,36 @@ struct GemmParams {
   long long sc_shard;          // elements per shard (multiple of 8)
   long long sc_off;            // element offset of C inside the flat unit (multiple of 8)
   void* sc_peers[8];           // base of every rank's staging area (peer-mapped), [world][shard] elements
+  int group_m;                 // tile order: this many 256-row tiles share a B tile before the next B tile
+  // fused all-gather of B (see the head of the file); B points into the local gathered unit
+  int ga_world;                // 0 = off
+  long long ga_shard;          // elements per shard
+  long long ga_off;            // element offset of B inside the flat unit (multiple of 8)
+  const void* ga_peers[8];     // every rank's shard buffer (peer-mapped; [rank] is local)
+  void* ga_dst;                // == B
+  unsigned int* ga_sync;       // [0] next piece to hand out, [1 + c] pieces done of 128-row block c (zeroed per launch)
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+// Bounded wait until *p >= want (device-scope acquire).
+__device__ __forceinline__ bool count_wait(const unsigned int* p, unsigned int want, volatile int* abort_flag) {
+  const uint64_t t0 = ftb200::globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (v >= want) return true;
+    if ((++spins & 15u) == 0) {
+      if (*abort_flag) return false;
+      if (ftb200::globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        return false;
+      }
+      __nanosleep(64);
+    }
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS_GATHER, 1)
 gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                               const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -166,14 +207,15 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
   const int num_n = (p.N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_k = (p.K + BK - 1) / BK;
-  const int tiles_per_group = GROUP_M * num_n;
+  const int group_m = p.group_m;
+  const int tiles_per_group = group_m * num_n;
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
 
   auto tile_coords = [&](int t, int& m0, int& n0) {
     const int g = t / tiles_per_group;
-    const int first_m = g * GROUP_M;
-    const int gsz = min(num_m - first_m, GROUP_M);
+    const int first_m = g * group_m;
+    const int gsz = min(num_m - first_m, group_m);
     const int r = t - g * tiles_per_group;
     m0 = (first_m + r % gsz) * (2 * BM) + static_cast<int>(rank) * BM;  // this CTA's rows
     n0 = (r / gsz) * BN;
@@ -189,6 +231,15 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
         int m0, n0;
         tile_coords(t, m0, n0);
         const int nb = n0 + static_cast<int>(rank) * BNH;  // this CTA's half of the B tile
+        if (p.ga_world > 0 && nb < p.N) {
+          // these 128 rows of B are local once all their pieces are counted; the loads below go through the
+          // async proxy, the pieces were written through the generic one
+          if (!count_wait(p.ga_sync + 1 + nb / BNH, static_cast<unsigned int>(p.K / 64), abort_flag)) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             ok = false;
@@ -269,6 +320,54 @@ gemm_bf16_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __g
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // ---------------- all-gather of B (warps 6..9 of both CTAs, all-gather variant only) ----------------
+    if (p.ga_world > 0) {
+      const long long total_v = static_cast<long long>(p.N) * p.K / 8;
+      const long long pieces = (total_v + GATHER_PIECE_V - 1) / GATHER_PIECE_V;
+      const unsigned int pieces_per_block = static_cast<unsigned int>(p.K / 64);  // 128 rows x K x 2 B / 16 KiB
+      uint4* dstv = reinterpret_cast<uint4*>(p.ga_dst);
+      for (;;) {
+        unsigned int piece = 0;
+        if (lane == 0) piece = atomicAdd(p.ga_sync, 1u);
+        piece = __shfl_sync(0xffffffffu, piece, 0);
+        if (piece >= pieces) break;
+        const long long v0 = static_cast<long long>(piece) * GATHER_PIECE_V;
+        const long long flat0 = p.ga_off + v0 * 8;
+        const long long owner0 = flat0 / p.ga_shard;
+        const long long rem0 = flat0 - owner0 * p.ga_shard;
+#pragma unroll 1
+        for (int b = 0; b < GATHER_PIECE_V / 256; ++b) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = b * 256 + u * 32 + lane;
+            v[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (v0 + i < total_v) {
+              long long rem = rem0 + static_cast<long long>(i) * 8;
+              long long owner = owner0;
+              if (rem >= p.ga_shard) {  // a piece is shorter than a shard: at most one boundary inside it
+                rem -= p.ga_shard;
+                ++owner;
+              }
+              if (FTB_IN_RANGE(owner, p.ga_world))
+                v[u] = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.ga_peers[owner]) + rem);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int i = b * 256 + u * 32 + lane;
+            if (v0 + i < total_v) dstv[v0 + i] = v[u];
+          }
+        }
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          atomicAdd(p.ga_sync + 1 + piece / pieces_per_block, 1u);
+        }
+      }
+    }
   } else {
     // ---------------- epilogue (warps 2..5 of both CTAs) ----------------
     const int q = warp & 3;
@@ -476,9 +575,18 @@ struct ScatterSpec {
   void* const* peers = nullptr;
 };
 
+struct GatherSpec {
+  int world = 0;
+  long long shard = 0;
+  long long off = 0;
+  const void* const* peers = nullptr;
+  unsigned int* sync = nullptr;
+};
+
 static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, int K, int a_mn_major, int b_mn_major,
                           long long lda, long long ldb, long long ldc, int flags, int* status, int max_ctas, void* aux,
-                          long long ld_aux, cudaStream_t stream, const ScatterSpec* sc = nullptr) {
+                          long long ld_aux, cudaStream_t stream, const ScatterSpec* sc = nullptr,
+                          const GatherSpec* ga = nullptr) {
   if (M <= 0 || N <= 0 || K <= 0 || A == nullptr || B == nullptr || (C == nullptr && sc == nullptr)) return FTB200_E_BADARG;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) || (lda & 7) || (ldb & 7))
     return FTB200_E_ALIGN;
@@ -526,11 +634,34 @@ static int gemm_2cta_impl(const void* A, const void* B, void* C, int M, int N, i
     p.sc_off = sc->off;
     for (int i = 0; i < sc->world && i < 8; ++i) p.sc_peers[i] = sc->peers[i];
   }
+  p.group_m = GROUP_M;
+  p.ga_world = 0;
+  p.ga_shard = 0;
+  p.ga_off = 0;
+  p.ga_dst = nullptr;
+  p.ga_sync = nullptr;
+  for (int i = 0; i < 8; ++i) p.ga_peers[i] = nullptr;
+  if (ga != nullptr) {
+    p.ga_world = ga->world;
+    p.ga_shard = ga->shard;
+    p.ga_off = ga->off;
+    p.ga_dst = const_cast<void*>(B);
+    p.ga_sync = ga->sync;
+    for (int i = 0; i < ga->world && i < 8; ++i) p.ga_peers[i] = ga->peers[i];
+    // Sixteen row tiles share a B tile before the next B tile (eight without the gather).  The whole weight is
+    // needed by the end of the first group of row tiles; with M = 8192 that group is half of the GEMM instead of
+    // a quarter, which halves the link bandwidth the gather needs to stay ahead, and costs ~2.5 % of the GEMM's
+    // speed in L2 locality (measured; all of M per B tile costs ~9 %).
+    p.group_m = 2 * GROUP_M;
+    if (cudaMemsetAsync(ga->sync, 0, sizeof(unsigned int) * (1 + static_cast<size_t>(N) / BNH), stream) != cudaSuccess)
+      return FTB200_E_CUDA;
+  }
   const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
   int ctas = ftb200::sm_count() & ~1;
   if (max_ctas > 0 && max_ctas < ctas) ctas = std::max(2, max_ctas & ~1);
   if (2 * tiles < ctas) ctas = 2 * tiles;
-  gemm_bf16_tcgen05_2cta_kernel<<<ctas, NUM_THREADS, SMEM_BYTES_SCATTER, stream>>>(tmA, tmB, p);
+  gemm_bf16_tcgen05_2cta_kernel<<<ctas, ga != nullptr ? NUM_THREADS_GATHER : NUM_THREADS, SMEM_BYTES_SCATTER, stream>>>(
+      tmA, tmB, p);
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
 }
 
@@ -567,6 +698,31 @@ FTB200_API int ftb200_gemm_bf16_scatter(const void* A, const void* B, int M, int
   ScatterSpec sc;
   sc.world = world; sc.src = src_rank; sc.shard = shard_elems; sc.off = unit_off; sc.peers = peers;
   return gemm_2cta_impl(A, B, nullptr, M, N, K, a_mn_major, b_mn_major, lda, ldb, N, 0, status, max_ctas, nullptr, 0, stream, &sc);
+}
+
+// C[M,N] = A[M,K] . B[N,K]^T where B is still spread over the shard group: `B_local` points at the weight's place
+// inside this rank's gathered copy of a flat parameter unit (`unit_off` elements from the unit's start, row stride
+// K), `shard_peers[r]` at rank r's shard of that unit (`shard_elems` elements each; [rank] is local memory).  The
+// kernel fills B_local from the shards while it multiplies (see the head of this file); after it, B_local is an
+// ordinary gathered weight.  `sync_words`: 1 + N/128 32-bit words of scratch in local memory, zeroed here on
+// `stream`; it may be shared by all calls on one stream.  aux / ld_aux: optional SwiGLU output as in
+// ftb200_gemm_bf16_swiglu (then N must be a multiple of 32).  N a multiple of 128, K of 64, bf16 output.
+// The caller orders the call after every rank's shard has been written (a team round) and keeps the shards
+// unchanged until all ranks' calls have ended.
+FTB200_API int ftb200_gemm_bf16_gather(const void* A, void* B_local, void* C, int M, int N, int K, long long lda,
+                                       long long ldc, const void* const* shard_peers, int world, long long shard_elems,
+                                       long long unit_off, unsigned int* sync_words, void* aux, long long ld_aux,
+                                       int* status, int max_ctas, cudaStream_t stream) {
+  if (shard_peers == nullptr || sync_words == nullptr || world < 1 || world > 8) return FTB200_E_BADARG;
+  if ((N % BNH) || (K % 64) || (shard_elems % 8) || (unit_off % 8) || (ldc & 7)) return FTB200_E_ALIGN;
+  if (shard_elems < 8LL * GATHER_PIECE_V) return FTB200_E_BADARG;  // a piece may cross one shard boundary, not two
+  if (unit_off + static_cast<long long>(N) * K > shard_elems * world) return FTB200_E_TOOBIG;
+  for (int r = 0; r < world; ++r)
+    if (shard_peers[r] == nullptr || (reinterpret_cast<uintptr_t>(shard_peers[r]) & 15)) return FTB200_E_ALIGN;
+  if (aux != nullptr && ((N % 32) || (ld_aux & 3) || (reinterpret_cast<uintptr_t>(aux) & 7))) return FTB200_E_ALIGN;
+  GatherSpec ga;
+  ga.world = world; ga.shard = shard_elems; ga.off = unit_off; ga.peers = shard_peers; ga.sync = sync_words;
+  return gemm_2cta_impl(A, B_local, C, M, N, K, 0, 0, lda, K, ldc, 0, status, max_ctas, aux, ld_aux, stream, nullptr, &ga);
 }
 
 FTB_DEFINE_BOUNDS_QUERY(gemm_2cta)

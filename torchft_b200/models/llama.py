@@ -222,9 +222,13 @@ class LlamaEngine:
         logit_chunks: int = 4,
         grad_fields: Optional[Callable[[int], object]] = None,
         grad_scale: float = 1.0,
+        fwd_fields: Optional[Callable[[int], object]] = None,
     ):
         self.cfg, self.B, self.S, self.device = cfg, batch, seq_len, device
         self.grad_fields = grad_fields
+        # forward-pass view of a unit's parameters, when it differs from the plain views: a sharding layer may hand
+        # out `K.GatherField`s, weights that the first consuming GEMM gathers from the shard group as it runs
+        self.fwd_fields = fwd_fields
         # multiplies every gradient (not the reported loss): 1/shard-group size when the group's
         # gradients are summed, so that the result is the mean over all of the group's tokens
         self.grad_scale = float(grad_scale)
@@ -268,6 +272,13 @@ class LlamaEngine:
     def _p(self, u: int) -> _Fields:
         return _Fields(self.param_unit(u), self.cfg.unit_fields(u))
 
+    def _pf(self, u: int):
+        if self.fwd_fields is not None:
+            f = self.fwd_fields(u)
+            if f is not None:
+                return f
+        return self._p(u)
+
     def _g(self, u: int):
         """Gradient destinations of unit ``u``: views into its flat gradient buffer, or
         whatever ``grad_fields`` supplies (e.g. scatter targets of a GEMM-fused reduce-scatter)."""
@@ -291,7 +302,7 @@ class LlamaEngine:
         for l in range(L):
             u = l + 1
             self.before_unit(u, False)
-            W = self._p(u)
+            W = self._pf(u)
             # x[l] = stream (+ delta of the previous block); n1 = norm(x[l])
             if delta is None:
                 K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
@@ -310,7 +321,7 @@ class LlamaEngine:
             delta = self.ws_proj
         u = L + 1
         self.before_unit(u, False)
-        W = self._p(u)
+        W = self._pf(u)
         if delta is None:
             K.rmsnorm_fwd(self.x[L], W.final_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[L])
         else:
@@ -328,7 +339,7 @@ class LlamaEngine:
             K.cross_entropy_(self.logits, tgt[sl], self.grad_scale / T, loss=self.loss_rows[sl])
             if train:
                 K.linear_wgrad(self.logits, self.ws_n[sl], out=G.lm_head, accumulate=ci > 0)
-                K.linear_dgrad(self.logits, W.lm_head, out=self.ws_dn[sl])
+                K.linear_dgrad(self.logits, getattr(W.lm_head, "local", W.lm_head), out=self.ws_dn[sl])
         return self.loss_rows.mean()
 
     # -- backward --------------------------------------------------------------------------

@@ -65,6 +65,45 @@ def bench_gemm(m: int, n: int, k: int, layout: str, iters: int, compare: bool) -
     return out
 
 
+def bench_gemm_gather(m: int, n: int, k: int, world: int, iters: int) -> dict:
+    """Forward GEMM with the all-gather of its weight fused in, against the same GEMM on a weight that is already
+    gathered and against copy-then-GEMM.  On one GPU the `world` shard buffers are local memory: the figure is
+    what the gather warps and the tile waits cost the GEMM, not the NVLink transfer."""
+    import ctypes
+
+    dev = "cuda"
+    x = torch.randn(m, k, device=dev).bfloat16()
+    numel = n * k
+    shard = -(-numel // (world * 8)) * 8
+    shards = [torch.randn(shard, device=dev).bfloat16() for _ in range(world)]
+    peers = (ctypes.c_void_p * 8)()
+    for r in range(world):
+        peers[r] = shards[r].data_ptr()
+    full = torch.zeros(shard * world, device=dev, dtype=torch.bfloat16)
+    sync = torch.zeros(1 + n // 128, device=dev, dtype=torch.int32)
+    field = K.GatherField(full[:numel].view(n, k), peers, world, shard, 0, sync)
+    out = torch.empty(m, n, device=dev, dtype=torch.bfloat16)
+
+    def fused():
+        field.pending = True
+        K.linear_fwd(x, field, out=out)
+
+    def separate():
+        for r in range(world):
+            full[r * shard:(r + 1) * shard].copy_(shards[r])
+        K.linear_fwd(x, field.local, out=out)
+
+    ms_fused = timeit(fused, iters)
+    ref = out.clone()
+    ms_plain = timeit(lambda: K.linear_fwd(x, field.local, out=out), iters)
+    ms_sep = timeit(separate, iters)
+    K.check_status(x.device)
+    fl = 2.0 * m * n * k
+    return {"kernel": "gemm_bf16_gather", "m": m, "n": n, "k": k, "world": world, "fused_ms": ms_fused,
+            "plain_gemm_ms": ms_plain, "copy_then_gemm_ms": ms_sep, "fused_tflops": fl / ms_fused / 1e9,
+            "plain_tflops": fl / ms_plain / 1e9, "bit_equal_to_plain": bool(torch.equal(ref, out))}
+
+
 def bench_adamw(n: int, iters: int) -> dict:
     dev = "cuda"
     master, m, v = (torch.zeros(n, device=dev) for _ in range(3))
@@ -203,7 +242,8 @@ def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemm", "adamw", "rmsnorm", "attention", "elementwise", "all"])
+    ap.add_argument("what", choices=["gemm", "gemm_gather", "adamw", "rmsnorm", "attention", "elementwise", "all"])
+    ap.add_argument("--world", type=int, default=4)
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=32)
@@ -219,6 +259,8 @@ def main() -> None:
         layouts = ["fwd", "dgrad", "wgrad"] if a.what == "all" else [a.layout]
         for lay in layouts:
             print(json.dumps(bench_gemm(a.m, a.n, a.k, lay, a.iters, not a.no_compare)), flush=True)
+    if a.what == "gemm_gather":
+        print(json.dumps(bench_gemm_gather(a.m, a.n, a.k, a.world, a.iters)), flush=True)
     if a.what in ("adamw", "all"):
         print(json.dumps(bench_adamw(1 << 28 if a.what == "all" else a.n, a.iters)), flush=True)
     if a.what in ("attention", "all"):

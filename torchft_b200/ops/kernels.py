@@ -144,8 +144,48 @@ def scatter_to_stage(src: torch.Tensor, dst: ScatterField) -> None:
                                             c_int(dst.world), c_int(dst.src_rank), stream_ptr()), "scatter_to_stage")
 
 
-def linear_fwd(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``y = x @ w^T`` (x ``[T,K]``, w ``[N,K]``)."""
+class GatherField:
+    """A weight that is still spread over its shard group: ``local`` is its ``[N, K]`` place in this rank's gathered
+    copy of a flat parameter unit (``unit_off`` elements from the unit's start), ``peers`` the ranks' shard buffers
+    of that unit (``shard_elems`` elements each).  The first forward GEMM that consumes the field gathers it while
+    it multiplies (:func:`gemm_gather`) and clears ``pending``; from then on ``local`` is the gathered weight."""
+
+    def __init__(self, local: torch.Tensor, peers, world: int, shard_elems: int, unit_off: int, sync: torch.Tensor) -> None:
+        self.local, self.peers, self.world = local, peers, world
+        self.shard_elems, self.unit_off, self.sync = shard_elems, unit_off, sync
+        self.pending = True
+
+    @staticmethod
+    def supported(shape, shard_elems: int) -> bool:
+        return len(shape) == 2 and shape[0] % 128 == 0 and shape[1] % 64 == 0 and shard_elems >= 8192 and shard_elems % 8 == 0
+
+
+def gemm_gather(x: torch.Tensor, w: GatherField, out: torch.Tensor, aux: Optional[torch.Tensor] = None) -> None:
+    """``out = x @ W^T`` with the all-gather of ``W`` fused into the GEMM: extra warps of the kernel pull ``W``'s
+    rows out of the shard owners' memory over NVLink in tile order while the tensor cores already work on the
+    rows that have arrived.  ``aux`` as in :func:`linear_swiglu_fwd`."""
+    _check_2d_bf16(x, "x")
+    Nn, Kd = w.local.shape
+    T = x.shape[0]
+    if x.shape[1] != Kd or tuple(out.shape) != (T, Nn) or w.sync.numel() < 1 + Nn // 128:
+        raise ValueError(f"shape mismatch: x {tuple(x.shape)}, w {(Nn, Kd)}, out {tuple(out.shape)}")
+    rc = N.lib().ftb200_gemm_bf16_gather(
+        ptr(x), ptr(w.local), ptr(out), c_int(T), c_int(Nn), c_int(Kd), c_ll(x.stride(0)), c_ll(out.stride(0)), w.peers,
+        c_int(w.world), c_ll(w.shard_elems), c_ll(w.unit_off), ptr(w.sync), ptr(aux) if aux is not None else None,
+        c_ll(aux.stride(0) if aux is not None else 0), ptr(status_word(x.device)), c_int(0), stream_ptr())
+    N.check(rc, "gemm_bf16_gather")
+    w.pending = False
+
+
+def linear_fwd(x: torch.Tensor, w, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``y = x @ w^T`` (x ``[T,K]``, w ``[N,K]`` or a :class:`GatherField`)."""
+    if isinstance(w, GatherField):
+        if w.pending:
+            if out is None:
+                out = torch.empty(x.shape[0], w.local.shape[0], dtype=x.dtype, device=x.device)
+            gemm_gather(x, w, out)
+            return out
+        w = w.local
     return gemm(x, w, False, False, out=out)
 
 
@@ -379,6 +419,11 @@ def swiglu_bwd(ds: torch.Tensor, gu: torch.Tensor, dgu: Optional[torch.Tensor] =
 def linear_swiglu_fwd(x: torch.Tensor, w_gu: torch.Tensor, gu_out: torch.Tensor, s_out: torch.Tensor) -> None:
     """``gu_out = x @ w_gu^T`` and, from the same accumulator, ``s_out = silu(gate) * up``
     where ``w_gu``'s rows (``gu_out``'s columns) interleave gate and up."""
+    if isinstance(w_gu, GatherField):
+        if w_gu.pending:
+            gemm_gather(x, w_gu, gu_out, aux=s_out)
+            return
+        w_gu = w_gu.local
     T, Kd = x.shape
     N2 = w_gu.shape[0]
     if not x.is_cuda or N2 % 32 or GEMM_IMPL != "2cta":

@@ -55,6 +55,7 @@ class ShardedLlamaTrainer:
         logit_chunks: int = 4,
         replica_alloc=None,
         fused_reduce_scatter: bool = True,
+        fused_all_gather: Optional[bool] = None,
     ):
         self.cfg, self.device = cfg, device
         self.comm = shard_comm or LocalShardComm()
@@ -144,6 +145,21 @@ class ShardedLlamaTrainer:
         )
         self._fused_fields: Dict[int, object] = {}
         self._vec_tmp: Dict[str, torch.Tensor] = {}
+        # GEMM-fused all-gather (FTB200_AG_FUSED=1 or fused_all_gather=True): the decoder layers and the head are not
+        # gathered ahead of time; each forward GEMM pulls its own weight out of the shard owners' memory while it
+        # multiplies.  What is left for the communication stream at the start of a step is the embedding unit and
+        # one small copy kernel for the norm weights of all units.
+        if fused_all_gather is None:
+            fused_all_gather = os.environ.get("FTB200_AG_FUSED", "0") == "1"
+        self.fused_ag = bool(
+            fused_all_gather and ws > 1 and self.cuda and getattr(self.comm, "supports_fused_scatter", False)
+            and K.GEMM_IMPL == "2cta"
+        )
+        self._params_event: Optional[torch.cuda.Event] = None
+        self._ga_fields: Dict[int, object] = {}
+        self._ga_units: List[int] = []
+        if self.fused_ag:
+            self._build_gather_fields()
         if self.fused_rs:
             for bufs in self._g_bufs.values():
                 for b in bufs:
@@ -152,7 +168,9 @@ class ShardedLlamaTrainer:
             cfg, batch, seq_len, device, self._param_unit, self._grad_unit, self._before_unit, self._grad_done,
             attention=attention, logit_chunks=logit_chunks, grad_fields=self._grad_fields if self.fused_rs else None,
             grad_scale=1.0 / ws,  # the shard group sums its gradients: scale so that the sum is the mean over the group
+            fwd_fields=self._fwd_fields if self.fused_ag else None,
         )
+        self._mark_params_written()
 
     # ---- unit plumbing -------------------------------------------------------------------
     def _param_unit(self, u: int) -> torch.Tensor:
@@ -166,11 +184,105 @@ class ShardedLlamaTrainer:
     def _grad_unit(self, u: int) -> torch.Tensor:
         return self._grad_buf(u)[: self.unit_numel[u]]
 
+    def _mark_params_written(self) -> None:
+        """The parameter shards were just written on the current stream (optimizer step, state load, init): the
+        communication stream must not offer them to the peers before that work is done."""
+        if self.comm_stream is not None and self.comm.size > 1:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._params_event = ev
+
+    def _build_gather_fields(self) -> None:
+        import ctypes
+        import math
+
+        from ..checkpointing.p2p_transport import _seg_table
+
+        ws = self.comm.size
+        max_rows = 0
+        vec_segs = []
+        for u in range(1, self.cfg.n_units):
+            fields = self.cfg.unit_fields(u)
+            if not all(K.GatherField.supported(shape, self.shard_numel[u]) for _, shape in fields if len(shape) == 2):
+                continue
+            max_rows = max(max_rows, max(shape[0] for _, shape in fields if len(shape) == 2))
+            self._ga_units.append(u)
+        if not self._ga_units:
+            self.fused_ag = False
+            return
+        self._ga_sync = torch.zeros(1 + max_rows // 128, dtype=torch.int32, device=self.device)
+
+        class _F:
+            pass
+
+        for u in self._ga_units:
+            f = _F()
+            f.matrices = []
+            peers = self.comm.stage_peers(self.p_shard[u])
+            n = self.shard_numel[u]
+            off = 0
+            for name, shape in self.cfg.unit_fields(u):
+                numel = math.prod(shape)
+                local = self.p_full[u][off : off + numel].view(*shape)
+                if len(shape) == 2:
+                    g = K.GatherField(local, peers, ws, n, off, self._ga_sync)
+                    setattr(f, name, g)
+                    f.matrices.append(g)
+                else:
+                    setattr(f, name, local)
+                    # norm weights travel in one copy kernel per step: split at shard boundaries
+                    a = off
+                    while a < off + numel:
+                        owner = a // n
+                        b = min(off + numel, (owner + 1) * n)
+                        vec_segs.append((int(peers[owner]) + (a - owner * n) * 2, self.p_full[u].data_ptr() + a * 2, (b - a) * 2))
+                        a = b
+                off += numel
+            self._ga_fields[u] = f
+        if any(nb % 16 or src % 16 or dst % 16 for src, dst, nb in vec_segs):
+            raise ValueError("norm-weight fields must be 16-byte aligned pieces for the fused all-gather")
+        self._ga_vec_table = _seg_table(vec_segs, self.device)
+        self._ga_vec_n = len(vec_segs)
+        self._ga_vec_bytes = sum(s[2] for s in vec_segs)
+        self._ctypes = ctypes
+
+    def _fwd_fields(self, u: int):
+        return self._ga_fields.get(u)
+
+    def _issue_fused_prologue(self) -> None:
+        """Start of a step with the GEMM-fused all-gather: on the communication stream, after this rank's parameter
+        writes, gather the embedding unit (its rounds also tell every rank that all shards of all units are final)
+        and copy the norm weights of the fused units; the layers' matrices are marked as not yet gathered."""
+        from ..ops import _native as N
+
+        team = self.comm.team
+        with torch.cuda.stream(self.comm_stream):
+            if self._params_event is not None:
+                self.comm_stream.wait_event(self._params_event)
+            self.comm.all_gather(self.p_shard[0], self.p_full[0])
+            N.check(N.lib().ftb200_p2p_copy(
+                N.ptr(self._ga_vec_table), self._ctypes.c_int(self._ga_vec_n), self._ctypes.c_longlong(self._ga_vec_bytes),
+                self._ctypes.c_void_p(team._abort_dev), N.ptr(team._status), self._ctypes.c_int(4), N.stream_ptr()),
+                "p2p_copy")
+            ev = torch.cuda.Event()
+            ev.record(self.comm_stream)
+        self._ag_event[0] = ev
+        self._gathered[0] = True
+        for u in self._ga_units:
+            self._gathered[u] = True
+            for g in self._ga_fields[u].matrices:
+                g.pending = True
+
     def _issue_all_gather(self, u: int) -> None:
         if self._gathered[u] or u >= self.cfg.n_units:
             return
+        if self.fused_ag and u == 0:
+            self._issue_fused_prologue()
+            return
         if self.comm_stream is not None:
             with torch.cuda.stream(self.comm_stream):
+                if self._params_event is not None:
+                    self.comm_stream.wait_event(self._params_event)
                 self.comm.all_gather(self.p_shard[u], self.p_full[u])
                 ev = torch.cuda.Event()
                 ev.record(self.comm_stream)
@@ -319,6 +431,7 @@ class ShardedLlamaTrainer:
                  self.opt_step, self.clip)
         if self.comm.size > 1:
             self._gathered = [False] * self.cfg.n_units
+            self._mark_params_written()
 
     def train_step(self, tokens: torch.Tensor, targets: torch.Tensor) -> torch.Tensor:
         """One fault-tolerant step: quorum, forward/backward with overlapped gradient
@@ -376,3 +489,4 @@ class ShardedLlamaTrainer:
             self.p_shard[u].copy_(self.master[u].to(torch.bfloat16))
         if self.comm.size > 1:
             self._gathered = [False] * self.cfg.n_units
+            self._mark_params_written()
