@@ -92,14 +92,17 @@ def test_attention_fwd_at_the_benchmark_shape():
         torch.testing.assert_close(lse[:, kvh * 4 : kvh * 4 + 2], ref_lse, rtol=1e-3, atol=2e-3)
 
 
-@pytest.mark.parametrize("B,S,Hq,Hkv,causal", [
-    (1, 128, 1, 1, True),
-    (1, 256, 2, 1, True),
-    (2, 512, 4, 2, True),
-    (1, 384, 2, 2, False),
+@pytest.mark.parametrize("B,S,Hq,Hkv,causal,D", [
+    (1, 128, 1, 1, True, 128),
+    (1, 256, 2, 1, True, 128),
+    (2, 512, 4, 2, True, 128),
+    (1, 384, 2, 2, False, 128),
+    (1, 256, 1, 1, True, 64),       # head dim 64 (Llama-3.2-1B): the forward needs seq % 256 == 0
+    (2, 512, 8, 2, True, 64),
+    (1, 2048, 8, 2, True, 64),
+    (1, 768, 4, 4, False, 64),
 ])
-def test_attention_bwd_matches_reference(B, S, Hq, Hkv, causal):
-    D = 128
+def test_attention_bwd_matches_reference(B, S, Hq, Hkv, causal, D):
     qkv, q, k, v = _qkv(B, S, Hq, Hkv, D, seed=7 + S)
     out = torch.empty(B * S, Hq * D, dtype=torch.bfloat16, device="cuda")
     lse = torch.empty(B, Hq, S, dtype=torch.float32, device="cuda")

@@ -164,16 +164,18 @@ def test_embedding():
     assert rel_err(dtab, ref) < 2e-2
 
 
-@pytest.mark.parametrize("native_attention", [False, True])
-def test_engine_matches_autograd_gpu(native_attention):
+@pytest.mark.parametrize("variant", ["library", "head_dim_128", "head_dim_64"])
+def test_engine_matches_autograd_gpu(variant):
     from torchft_b200.models.llama import LLAMA_TINY, LlamaConfig, SdpaAttention, Tcgen05Attention, TorchLlama, _Fields
     from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
 
     torch.manual_seed(0)
-    # head dim 128 selects the tcgen05 attention kernels, LLAMA_TINY (head dim 64) the library fallback
+    # the tcgen05 attention kernels take head dim 128, and head dim 64 (LLAMA_TINY) when the sequence is a multiple
+    # of 256; LLAMA_TINY at sequence 128 falls back to the library
     cfg = (LlamaConfig(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, ffn_dim=512, vocab_size=1024, name="llama-hd128")
-           if native_attention else LLAMA_TINY)
-    B, S = 2, 128
+           if variant == "head_dim_128" else LLAMA_TINY)
+    B, S = 2, (256 if variant == "head_dim_64" else 128)
+    native_attention = variant != "library"
     dev = torch.device("cuda")
     tr = ShardedLlamaTrainer(cfg, B, S, dev, logit_chunks=2)
     assert isinstance(tr.engine.attn, Tcgen05Attention if native_attention else SdpaAttention)

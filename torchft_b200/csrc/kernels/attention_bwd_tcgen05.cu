@@ -46,7 +46,6 @@ using namespace ftb200::tc;
   } while (0)
 #endif
 
-constexpr int D = 128;
 constexpr int BKV = 128;
 constexpr int BQ = 64;
 constexpr int NUM_THREADS = 704;
@@ -56,22 +55,29 @@ constexpr int GROUPS = 4;          // threads per key row
 constexpr int CPT = BQ / GROUPS;   // query columns per thread
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t COL_S = 0, COL_DP = 128, COL_DQ = 192, COL_DV = 256, COL_DK = 384;
-constexpr uint32_t KV_TILE = BKV * D * 2;      // 32 KB, two slabs of [128 rows x 128 B]
-constexpr uint32_t KV_SLAB = KV_TILE / 2;
-constexpr uint32_t Q_TILE = BQ * D * 2;        // 16 KB, two slabs of [64 rows x 128 B]
-constexpr uint32_t Q_SLAB = Q_TILE / 2;
+constexpr uint32_t KV_SLAB = BKV * 128;        // 16 KB: [128 rows x 128 B], 64 head-dim elements per row
+constexpr uint32_t Q_SLAB = BQ * 128;          // 8 KB: [64 rows x 128 B]
 constexpr uint32_t PT_TILE = BKV * BQ * 2;     // 16 KB, one slab of [128 key rows x 64 q]
-constexpr uint32_t OFF_K = 0, OFF_V = KV_TILE;
-constexpr uint32_t OFF_STAGE = 2 * KV_TILE;    // per stage: Q, dO
-constexpr uint32_t STAGE_BYTES = 2 * Q_TILE;
 constexpr int QDO_STAGES = 3;  // a stage is held until the tile's dV/dK MMAs are done, two tiles after its load began
-constexpr uint32_t OFF_PDS = OFF_STAGE + QDO_STAGES * STAGE_BYTES;  // per buffer: dS^T
 constexpr uint32_t PDS_BYTES = PT_TILE;        // dS^T only: P^T never leaves tensor memory
-constexpr uint32_t OFF_STATS = OFF_PDS + 2 * PDS_BYTES;    // per stage: lse[64], delta[64]
-constexpr uint32_t STATS_BYTES = 2 * BQ * 4;
-constexpr uint32_t OFF_MISC = OFF_STATS + QDO_STAGES * STATS_BYTES;
-constexpr uint32_t SMEM_BYTES = OFF_MISC + 256 + 1024;
-static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+constexpr uint32_t STATS_BYTES = 2 * BQ * 4;   // per stage: lse[64], delta[64]
+
+// Shared-memory layout for head dim D (64 or 128): K and V tiles of D/64 slabs each, then the Q/dO stages, the
+// dS^T buffers, the statistics and the barriers.
+template <int D>
+struct Lay {
+  static constexpr int SLABS = D / 64;
+  static constexpr uint32_t KV_TILE = SLABS * KV_SLAB;
+  static constexpr uint32_t Q_TILE = SLABS * Q_SLAB;
+  static constexpr uint32_t OFF_K = 0, OFF_V = KV_TILE;
+  static constexpr uint32_t OFF_STAGE = 2 * KV_TILE;    // per stage: Q, dO
+  static constexpr uint32_t STAGE_BYTES = 2 * Q_TILE;
+  static constexpr uint32_t OFF_PDS = OFF_STAGE + QDO_STAGES * STAGE_BYTES;  // per buffer: dS^T
+  static constexpr uint32_t OFF_STATS = OFF_PDS + 2 * PDS_BYTES;
+  static constexpr uint32_t OFF_MISC = OFF_STATS + QDO_STAGES * STATS_BYTES;
+  static constexpr uint32_t SMEM_BYTES = OFF_MISC + 256 + 1024;
+  static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB of shared memory a CTA can have");
+};
 
 enum : int {
   BAR_KV = 0,
@@ -109,10 +115,16 @@ __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint
                : "memory");
 }
 
+template <int D>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                      const BwdParams p) {
+  using Ly = Lay<D>;
+  constexpr int SLABS = Ly::SLABS;
+  constexpr uint32_t KV_TILE = Ly::KV_TILE, Q_TILE = Ly::Q_TILE, OFF_K = Ly::OFF_K, OFF_V = Ly::OFF_V;
+  constexpr uint32_t OFF_STAGE = Ly::OFF_STAGE, STAGE_BYTES = Ly::STAGE_BYTES, OFF_PDS = Ly::OFF_PDS;
+  constexpr uint32_t OFF_STATS = Ly::OFF_STATS, OFF_MISC = Ly::OFF_MISC;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_MISC);
@@ -177,10 +189,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       mbar_expect_tx(bar(BAR_KV), 2 * KV_TILE);
-      tma_load_2d(smem_base + OFF_K, &tmK, bar(BAR_KV), hk * D, kv_row0);
-      tma_load_2d(smem_base + OFF_K + KV_SLAB, &tmK, bar(BAR_KV), hk * D + 64, kv_row0);
-      tma_load_2d(smem_base + OFF_V, &tmV, bar(BAR_KV), hk * D, kv_row0);
-      tma_load_2d(smem_base + OFF_V + KV_SLAB, &tmV, bar(BAR_KV), hk * D + 64, kv_row0);
+#pragma unroll
+      for (int sl = 0; sl < SLABS; ++sl) {
+        tma_load_2d(smem_base + OFF_K + sl * KV_SLAB, &tmK, bar(BAR_KV), hk * D + 64 * sl, kv_row0);
+        tma_load_2d(smem_base + OFF_V + sl * KV_SLAB, &tmV, bar(BAR_KV), hk * D + 64 * sl, kv_row0);
+      }
       bool ok = true;
       for (int t = 0; t < T && ok; ++t) {
         const int st = t % QDO_STAGES;
@@ -197,10 +210,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const uint32_t sst = smem_base + OFF_STATS + st * STATS_BYTES;
         const long long stat_off = (static_cast<long long>(b) * p.n_heads + h) * p.seq + qt * BQ;
         mbar_expect_tx(bar(BAR_QDO_FULL + st), 2 * Q_TILE + STATS_BYTES);
-        tma_load_2d(sq, &tmQ, bar(BAR_QDO_FULL + st), h * D, q_row0);
-        tma_load_2d(sq + Q_SLAB, &tmQ, bar(BAR_QDO_FULL + st), h * D + 64, q_row0);
-        tma_load_2d(sdo, &tmDO, bar(BAR_QDO_FULL + st), h * D, q_row0);
-        tma_load_2d(sdo + Q_SLAB, &tmDO, bar(BAR_QDO_FULL + st), h * D + 64, q_row0);
+#pragma unroll
+        for (int sl = 0; sl < SLABS; ++sl) {
+          tma_load_2d(sq + sl * Q_SLAB, &tmQ, bar(BAR_QDO_FULL + st), h * D + 64 * sl, q_row0);
+          tma_load_2d(sdo + sl * Q_SLAB, &tmDO, bar(BAR_QDO_FULL + st), h * D + 64 * sl, q_row0);
+        }
         bulk_load_1d(sst, p.lse + stat_off, BQ * 4, bar(BAR_QDO_FULL + st));
         bulk_load_1d(sst + BQ * 4, p.delta + stat_off, BQ * 4, bar(BAR_QDO_FULL + st));
       }
@@ -215,14 +229,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (lane == 0) {
       const uint32_t F = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(128 >> 4) << 24);
       const uint32_t idesc_st = F | (static_cast<uint32_t>(BQ >> 3) << 17);                             // N = 64, K-major both
-      const uint32_t idesc_kv = F | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17);                 // N = 128, B MN-major
+      const uint32_t idesc_kv = F | (1u << 16) | (static_cast<uint32_t>(D >> 3) << 17);                 // N = D, B MN-major
       const uint32_t idesc_dq = F | (1u << 15) | (1u << 16) | (static_cast<uint32_t>(BQ >> 3) << 17);   // N = 64, both MN-major
       // descriptor bases: one per buffer and operand role, constants per K step (the issue loop
       // must stay short: these MMAs are too small to hide descriptor arithmetic)
       constexpr uint32_t HI = smem_desc_hi(1024);
       const uint32_t k_km = smem_desc_lo(smem_base + OFF_K, 16);        // K as K-major A (S^T)
       const uint32_t v_km = smem_desc_lo(smem_base + OFF_V, 16);        // V as K-major A (dP^T)
-      const uint32_t k_mn = smem_desc_lo(smem_base + OFF_K, KV_SLAB);   // K as MN-major A (dQ^T)
+      // K as MN-major A (dQ^T): M = 128 runs over the head dim.  With head dim 64 the second 64 rows of that MMA
+      // read the slab behind K's only one, which is V's: lanes 64..127 of dQ^T then hold a product nobody reads.
+      const uint32_t k_mn = smem_desc_lo(smem_base + OFF_K, KV_SLAB);
       const uint32_t q_km0 = smem_desc_lo(smem_base + OFF_STAGE, 16);             // Q, stage 0, K-major B
       const uint32_t q_mn0 = smem_desc_lo(smem_base + OFF_STAGE, Q_SLAB);         // Q, stage 0, MN-major B
       const uint32_t ds_mn0 = smem_desc_lo(smem_base + OFF_PDS, PT_TILE);  // dS^T, buffer 0, MN-major B
@@ -308,15 +324,18 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (!mbar_wait(bar(BAR_DQ_FULL), static_cast<uint32_t>(u) & 1u, abort_flag)) break;
       tc_fence_after();
       uint32_t v[BQ];
-      tmem_ld32(tmem_base + COL_DQ + lane_addr, v);
-      tmem_ld32(tmem_base + COL_DQ + 32 + lane_addr, v + 32);
-      tmem_wait_ld();
+      const bool mine = quarter * 32 < D;  // head dim 64: only lanes 0..63 of dQ^T are real
+      if (mine) {
+        tmem_ld32(tmem_base + COL_DQ + lane_addr, v);
+        tmem_ld32(tmem_base + COL_DQ + 32 + lane_addr, v + 32);
+        tmem_wait_ld();
+      }
       tc_fence_before();
       mbar_arrive(bar(BAR_DQ_EMPTY));
       int h, qt;
       tile_of(u, h, qt);
       float* dst = p.dq_acc + (static_cast<long long>(b) * p.seq + qt * BQ) * ldq + h * D + dcol;
-      if (!(p.causal & 2))
+      if (mine && !(p.causal & 2))
 #pragma unroll
         for (int c = 0; c < BQ; ++c) atomicAdd(dst + c * ldq, __uint_as_float(v[c]));
     }
@@ -413,15 +432,19 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + g * 32;
+        constexpr int CW = D / GROUPS;  // head-dim columns per thread
+        const uint32_t col = (which == 0 ? COL_DV : COL_DK) + g * CW;
         __nv_bfloat16* base = which == 0 ? p.dV : p.dK;
         const long long ld = which == 0 ? p.ld_dv : p.ld_dk;
-        __nv_bfloat16* dst = base + static_cast<long long>(kv_row0 + row) * ld + hk * D + g * 32;
-        uint32_t v[32];
-        tmem_ld32(tmem_base + col + lane_addr, v);
+        __nv_bfloat16* dst = base + static_cast<long long>(kv_row0 + row) * ld + hk * D + g * CW;
+        uint32_t v[CW];
+        if constexpr (CW == 32)
+          tmem_ld32(tmem_base + col + lane_addr, v);
+        else
+          tmem_ld16(tmem_base + col + lane_addr, v);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CW / 8; ++c) {
           float f[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(v[8 * c + e]);
@@ -441,6 +464,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 }
 
 // delta[b, h, s] = sum_d dO[b, s, h, d] * O[b, s, h, d]; one warp per (row, head)
+template <int D>
 __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                                        float* __restrict__ delta, int batch, int seq, int n_heads, long long ld_o,
                                        long long ld_do) {
@@ -450,13 +474,18 @@ __global__ void attention_delta_kernel(const __nv_bfloat16* __restrict__ o, cons
   if (w >= total) return;
   const long long r = w / n_heads;
   const int h = static_cast<int>(w % n_heads);
-  const uint2 a = *reinterpret_cast<const uint2*>(o + r * ld_o + h * D + lane * 4);
-  const uint2 c = *reinterpret_cast<const uint2*>(d_o + r * ld_do + h * D + lane * 4);
-  const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
-  const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&c);
+  constexpr int PAIRS = D / 64;  // bf16 pairs per lane
+  __nv_bfloat162 a2[PAIRS], c2[PAIRS];
+  if constexpr (PAIRS == 2) {
+    *reinterpret_cast<uint2*>(a2) = *reinterpret_cast<const uint2*>(o + r * ld_o + h * D + lane * 4);
+    *reinterpret_cast<uint2*>(c2) = *reinterpret_cast<const uint2*>(d_o + r * ld_do + h * D + lane * 4);
+  } else {
+    *reinterpret_cast<uint32_t*>(a2) = *reinterpret_cast<const uint32_t*>(o + r * ld_o + h * D + lane * 2);
+    *reinterpret_cast<uint32_t*>(c2) = *reinterpret_cast<const uint32_t*>(d_o + r * ld_do + h * D + lane * 2);
+  }
   float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < PAIRS; ++i) {
     const float2 x = __bfloat1622float2(a2[i]), y = __bfloat1622float2(c2[i]);
     s += x.x * y.x + x.y * y.y;
   }
@@ -514,28 +543,20 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 }  // namespace
 
 // Scratch the backward pass needs, in bytes: fp32 dQ accumulator followed by delta.
+// (sized for head dim 128; enough for 64 as well)
 FTB200_API long long ftb200_attention_bwd_scratch_bytes(int batch, int seq, int n_heads) {
   const long long rows = static_cast<long long>(batch) * seq;
-  return rows * n_heads * D * 4 + rows * n_heads * 4;
+  return rows * n_heads * 128 * 4 + rows * n_heads * 4;
 }
 
-// q, k, v, o, d_o as in the forward pass (2-D views, row strides in elements); dq, dk, dv are
-// written (not accumulated).  lse is the forward's [batch, n_heads, seq].  scratch: at least
-// ftb200_attention_bwd_scratch_bytes, 16-byte aligned.
-FTB200_API int ftb200_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                                    const float* lse, void* dq, void* dk, void* dv, void* scratch, int batch, int seq,
-                                    int n_heads, int n_kv_heads, int head_dim, long long ld_q, long long ld_k,
-                                    long long ld_v, long long ld_o, long long ld_do, long long ld_dq, long long ld_dk,
-                                    long long ld_dv, float scale, int causal, int* status, cudaStream_t stream) {
-  if (head_dim != D || batch <= 0 || seq <= 0 || seq % BKV != 0 || n_heads <= 0 || n_kv_heads <= 0 ||
-      n_heads % n_kv_heads != 0)
-    return FTB200_E_BADARG;
-  const void* ptrs[] = {q, k, v, o, d_o, dq, dk, dv, scratch};
-  for (const void* x : ptrs)
-    if (!aligned16(x)) return FTB200_E_ALIGN;
-  const long long lds[] = {ld_q, ld_k, ld_v, ld_o, ld_do, ld_dq, ld_dk, ld_dv};
-  for (long long x : lds)
-    if (x & 7) return FTB200_E_ALIGN;
+namespace {
+
+template <int D>
+int attention_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* d_o, const float* lse,
+                       void* dq, void* dk, void* dv, void* scratch, int batch, int seq, int n_heads, int n_kv_heads,
+                       long long ld_q, long long ld_k, long long ld_v, long long ld_o, long long ld_do, long long ld_dq,
+                       long long ld_dk, long long ld_dv, float scale, int causal, int* status, cudaStream_t stream) {
+  constexpr uint32_t SMEM_BYTES = Lay<D>::SMEM_BYTES;
   const long long rows = static_cast<long long>(batch) * seq;
   float* dq_acc = reinterpret_cast<float*>(scratch);
   float* delta = dq_acc + rows * n_heads * D;
@@ -547,7 +568,8 @@ FTB200_API int ftb200_attention_bwd(const void* q, const void* k, const void* v,
   if (rc != 0) return rc;
   static bool attr_set = false;
   if (!attr_set) {
-    if (cudaFuncSetAttribute(attention_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+    if (cudaFuncSetAttribute(attention_bwd_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaSuccess)
       return FTB200_E_CUDA;
     attr_set = true;
   }
@@ -555,7 +577,7 @@ FTB200_API int ftb200_attention_bwd(const void* q, const void* k, const void* v,
   {
     const long long warps = rows * n_heads;
     const long long blocks = (warps * 32 + 255) / 256;
-    attention_delta_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
+    attention_delta_kernel<D><<<static_cast<unsigned>(blocks), 256, 0, stream>>>(
         reinterpret_cast<const __nv_bfloat16*>(o), reinterpret_cast<const __nv_bfloat16*>(d_o), delta, batch, seq, n_heads,
         ld_o, ld_do);
   }
@@ -571,11 +593,37 @@ FTB200_API int ftb200_attention_bwd(const void* q, const void* k, const void* v,
 #endif
   const long long grid = static_cast<long long>(batch) * n_kv_heads * (seq / BKV);
   if (grid > 0x7fffffffLL) return FTB200_E_TOOBIG;
-  attention_bwd_kernel<<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
+  attention_bwd_kernel<D><<<static_cast<unsigned>(grid), NUM_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, tdo, p);
   {
     const long long pieces = rows * (static_cast<long long>(n_heads) * D / 8);
     attention_dq_cast_kernel<<<static_cast<unsigned>((pieces + 255) / 256), 256, 0, stream>>>(
         dq_acc, reinterpret_cast<__nv_bfloat16*>(dq), rows, n_heads * D, ld_dq);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : FTB200_E_CUDA;
+}
+
+}  // namespace
+
+// q, k, v, o, d_o as in the forward pass (2-D views, row strides in elements); dq, dk, dv are
+// written (not accumulated).  lse is the forward's [batch, n_heads, seq].  scratch: at least
+// ftb200_attention_bwd_scratch_bytes, 16-byte aligned.  Head dim 64 or 128.
+FTB200_API int ftb200_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                    const float* lse, void* dq, void* dk, void* dv, void* scratch, int batch, int seq,
+                                    int n_heads, int n_kv_heads, int head_dim, long long ld_q, long long ld_k,
+                                    long long ld_v, long long ld_o, long long ld_do, long long ld_dq, long long ld_dk,
+                                    long long ld_dv, float scale, int causal, int* status, cudaStream_t stream) {
+  if ((head_dim != 64 && head_dim != 128) || batch <= 0 || seq <= 0 || seq % BKV != 0 || n_heads <= 0 ||
+      n_kv_heads <= 0 || n_heads % n_kv_heads != 0)
+    return FTB200_E_BADARG;
+  const void* ptrs[] = {q, k, v, o, d_o, dq, dk, dv, scratch};
+  for (const void* x : ptrs)
+    if (!aligned16(x)) return FTB200_E_ALIGN;
+  const long long lds[] = {ld_q, ld_k, ld_v, ld_o, ld_do, ld_dq, ld_dk, ld_dv};
+  for (long long x : lds)
+    if (x & 7) return FTB200_E_ALIGN;
+  if (head_dim == 64)
+    return attention_bwd_impl<64>(q, k, v, o, d_o, lse, dq, dk, dv, scratch, batch, seq, n_heads, n_kv_heads, ld_q, ld_k,
+                                  ld_v, ld_o, ld_do, ld_dq, ld_dk, ld_dv, scale, causal, status, stream);
+  return attention_bwd_impl<128>(q, k, v, o, d_o, lse, dq, dk, dv, scratch, batch, seq, n_heads, n_kv_heads, ld_q, ld_k,
+                                 ld_v, ld_o, ld_do, ld_dq, ld_dk, ld_dv, scale, causal, status, stream);
 }

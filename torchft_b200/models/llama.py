@@ -187,13 +187,14 @@ class Tcgen05Attention:
 
 
 def make_attention(cfg: LlamaConfig, seq_len: int, device: torch.device, kind: Optional[str] = None):
-    """``kind``: "tcgen05" (hand-written kernels; head dim 128, sequence a multiple of 128,
-    CUDA), "sdpa" (library), or None for tcgen05 where it applies.  The environment variable
+    """``kind``: "tcgen05" (hand-written kernels; CUDA, head dim 128 and a sequence that is a multiple of 128,
+    or head dim 64 and a multiple of 256), "sdpa" (library), or None for tcgen05 where it applies.  The environment variable
     ``FTB200_ATTENTION`` overrides None."""
     kind = kind or os.environ.get("FTB200_ATTENTION") or "auto"
     ok = device.type == "cuda" and K.attention_supported(seq_len, cfg.head_dim)
     if kind == "tcgen05" and not ok:
-        raise ValueError("tcgen05 attention needs CUDA, head_dim 128 and seq_len % 128 == 0")
+        raise ValueError("tcgen05 attention needs CUDA and head_dim 128 with seq_len % 128 == 0 or head_dim 64 with "
+                         "seq_len % 256 == 0")
     if kind == "tcgen05" or (kind == "auto" and ok):
         return Tcgen05Attention(cfg)
     return SdpaAttention(cfg)

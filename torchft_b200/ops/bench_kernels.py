@@ -188,11 +188,11 @@ def bench_elementwise(iters: int) -> list:
     return out
 
 
-def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare: bool) -> dict:
-    """Causal GQA attention, head dim 128, forward and backward; FLOPs count the causal half."""
+def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare: bool, head_dim: int = 128) -> dict:
+    """Causal GQA attention, head dim 128 or 64, forward and backward; FLOPs count the causal half."""
     import torch.nn.functional as F
 
-    dev, D = "cuda", 128
+    dev, D = "cuda", head_dim
     qkv = (torch.randn(batch * seq, (hq + 2 * hkv) * D, device=dev) * 0.5).bfloat16()
     q, k, v = qkv[:, : hq * D], qkv[:, hq * D : (hq + hkv) * D], qkv[:, (hq + hkv) * D :]
     out = torch.empty(batch * seq, hq * D, device=dev, dtype=torch.bfloat16)
@@ -202,7 +202,7 @@ def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare
     dq, dk, dv = dqkv[:, : hq * D], dqkv[:, hq * D : (hq + hkv) * D], dqkv[:, (hq + hkv) * D :]
     fwd = timeit(lambda: K.attention_fwd(q, k, v, batch, seq, hq, hkv, D, out, lse), iters)
     variants = {}
-    if seq % 256 == 0:
+    if seq % 256 == 0 and D == 128:
         # the forward kernels side by side: one tile per CTA, and two tiles per CTA with none, a quarter
         # and half of the exponentials on the FMA pipe
         saved = {n: os.environ.get(n) for n in ("FTB200_ATTN_FWD", "FTB200_ATTN_POLY")}
@@ -220,7 +220,7 @@ def bench_attention(batch: int, seq: int, hq: int, hkv: int, iters: int, compare
     _, tf, how = _peaks()
     fl_fwd = 4.0 * batch * hq * seq * seq * D / 2
     fl_bwd = 2.5 * fl_fwd
-    res = {"kernel": "attention_tcgen05", "batch": batch, "seq": seq, "heads": hq, "kv_heads": hkv, "fwd_ms": fwd,
+    res = {"kernel": "attention_tcgen05", "batch": batch, "seq": seq, "heads": hq, "kv_heads": hkv, "head_dim": D, "fwd_ms": fwd,
            "bwd_ms": bwd, "fwd_tflops": fl_fwd / fwd / 1e9, "bwd_tflops": fl_bwd / bwd / 1e9,
            f"fwd_frac_of_{how}_cublas_peak": fl_fwd / fwd / 1e9 / tf, f"bwd_frac_of_{how}_cublas_peak": fl_bwd / bwd / 1e9 / tf}
     res["fwd_variants"] = variants
@@ -248,6 +248,7 @@ def main() -> None:
     ap.add_argument("--seq", type=int, default=8192)
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128, choices=[64, 128])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
     ap.add_argument("--k", type=int, default=8192)
@@ -264,7 +265,7 @@ def main() -> None:
     if a.what in ("adamw", "all"):
         print(json.dumps(bench_adamw(1 << 28 if a.what == "all" else a.n, a.iters)), flush=True)
     if a.what in ("attention", "all"):
-        print(json.dumps(bench_attention(a.batch, a.seq, a.heads, a.kv_heads, a.iters, not a.no_compare)), flush=True)
+        print(json.dumps(bench_attention(a.batch, a.seq, a.heads, a.kv_heads, a.iters, not a.no_compare, a.head_dim)), flush=True)
     if a.what in ("elementwise", "all"):
         for r in bench_elementwise(a.iters):
             print(json.dumps(r), flush=True)

@@ -551,8 +551,9 @@ def ref_attention_lse(q, k, v, causal=True):
 
 
 def attention_supported(seq_len: int, head_dim: int) -> bool:
-    """Shapes the tcgen05 attention kernels take: head dim 128, 128-row blocks."""
-    return head_dim == 128 and seq_len % 128 == 0
+    """Shapes the tcgen05 attention kernels take: head dim 128 with 128-row blocks, or head dim 64 with
+    sequences that are a multiple of 256 (the forward kernel for it works on two 128-query tiles per CTA)."""
+    return (head_dim == 128 and seq_len % 128 == 0) or (head_dim == 64 and seq_len % 256 == 0)
 
 
 def attention_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, batch: int, seq_len: int, n_heads: int,
