@@ -159,9 +159,16 @@ def main() -> int:
 
     t_start = time.time()
 
+    watchdog_s = float(os.environ.get("FTB200_BENCH_WATCHDOG_S", "0"))
+
     def phase(name: str) -> None:
         # progress on stderr: if the run is ever cut off, the log says how far it got
         print(f"[bench rank {rank}] {name} (+{time.time() - t_start:.1f}s)", file=sys.stderr, flush=True)
+        if watchdog_s > 0:
+            # a phase that takes longer than this prints where every Python thread of the rank stands
+            import faulthandler
+
+            faulthandler.dump_traceback_later(watchdog_s, repeat=False, file=sys.stderr)
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
@@ -286,6 +293,9 @@ def main() -> int:
         stage.copy_(host_tok[args.warmup + i], non_blocking=True)
         loss = trainer.train_step(stage[:, :-1], stage[:, 1:])
         losses.append(float(loss.item()))  # device -> host read of the step result
+        if watchdog_s > 0:
+            phase(f"end-to-end step {i} done")
+            K.check_status(dev)
     e1.record()
     sync_all()
     wall = time.perf_counter() - w0
