@@ -101,6 +101,7 @@ def main() -> int:
     run_round()  # warm-up: every fragment synchronises once
     diloco.timings.clear()
     diloco.exchange_timings.clear()
+    diloco.arrival_times()
     diloco.arrivals.clear()
     commits0 = diloco.commits
     torch.cuda.synchronize()
@@ -134,7 +135,7 @@ def main() -> int:
     stats = torch.tensor([total_ms, sync_ms, exch_ms, excess_ms], dtype=torch.float64, device=device)
     lo = stats.clone()
     # when did each group reach each synchronisation (monotonic clock of the one host, stream drained)?
-    arr = torch.tensor(diloco.arrivals, dtype=torch.float64, device=device)
+    arr = torch.tensor(diloco.arrival_times(), dtype=torch.float64, device=device)
     arr_hi, arr_lo = arr.clone(), arr.clone()
     if world > 1:
         dist.all_reduce(stats, op=dist.ReduceOp.MAX)

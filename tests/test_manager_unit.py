@@ -445,3 +445,23 @@ def test_unreachable_store_fails_within_connect_timeout():
         Manager(pg=pg, min_replica_size=1, load_state_dict=None, state_dict=None, store_addr="127.0.0.1", store_port=dead_port,
                 rank=1, world_size=2, connect_timeout=timedelta(seconds=2), timeout=timedelta(seconds=5))
     assert time.monotonic() - t0 < 30
+
+
+@pytest.mark.gpu
+def test_quantized_allreduce_is_averaged_on_a_group_that_fuses_the_scale(h):
+    """A group that can fold 1/participants into its unquantised allreduce (``supports_fused_scale``) does not do
+    so for the quantised collective, which reduces with SUM: the manager has to divide."""
+    h.pg.supports_fused_scale = True
+    h.client._quorum.return_value = quorum()
+    h.manager.start_quorum()
+    x = torch.full((256,), 6.0, device="cuda")
+    with patch("torchft_b200.collectives.allreduce_quantized",
+               side_effect=lambda tensors, op, pg, stream=None: _DummyWork(tensors)) as q:
+        h.manager.allreduce(x, should_quantize=True).wait()
+    assert q.call_count == 1 and q.call_args[0][1] == ReduceOp.SUM
+    torch.cuda.synchronize()
+    assert torch.allclose(x, torch.full_like(x, 3.0))  # two participants
+    # the unquantised path of the same group passes the scale down instead
+    y = torch.full((256,), 6.0, device="cuda")
+    h.manager.allreduce(y).wait()
+    assert h.pg.allreduce.call_args.kwargs["scale"] == 0.5

@@ -197,7 +197,8 @@ def test_attention_selection_and_cpu_wrappers():
     assert isinstance(make_attention(LLAMA_TINY, 128, cpu, "sdpa"), SdpaAttention)
     with _pytest.raises(ValueError):
         make_attention(LLAMA_TINY, 128, cpu, "tcgen05")
-    assert K.attention_supported(8192, 128) and not K.attention_supported(8192, 64) and not K.attention_supported(100, 128)
+    assert K.attention_supported(8192, 128) and K.attention_supported(2048, 64) and not K.attention_supported(100, 128)
+    assert not K.attention_supported(128, 64) and not K.attention_supported(8192, 96)
     # the CPU restatement behind the wrappers: forward + backward agree with autograd of the reference
     B, S, Hq, Hkv, D = 1, 8, 2, 1, 4
     g = _torch.Generator().manual_seed(0)

@@ -315,8 +315,12 @@ class Manager:
                     raise ValueError("average reduce op is only supported for floating point tensors")
                 pg_op = ReduceOp.SUM
             try:
-                fused_scale = getattr(self._pg, "supports_fused_scale", False) and reduce_op == ReduceOp.AVG
-                if should_quantize and tensor.is_cuda:
+                quantized = should_quantize and tensor.is_cuda
+                # (the quantised collective reduces with SUM: the division below must then happen here, whatever
+                # the group could have fused into an unquantised allreduce)
+                fused_scale = (getattr(self._pg, "supports_fused_scale", False) and reduce_op == ReduceOp.AVG
+                               and not quantized)
+                if quantized:
                     from .collectives import allreduce_quantized
 
                     work = allreduce_quantized([tensor], pg_op, self._pg, torch.cuda.current_stream())

@@ -257,6 +257,7 @@ class LlamaEngine:
         self.rstd2 = [torch.empty(T, **f32) for _ in range(L)]
         # workspaces
         self.ws_n = torch.empty(T, D, **bf)
+        self.ws_n2 = torch.empty(T, D, **bf)  # the FFN-side norm recomputed in the backward pass (see _wgrad)
         self.ws_proj = torch.empty(T, D, **bf)
         self.ws_s = torch.empty(T, Fd, **bf)
         self.ws_ds = torch.empty(T, Fd, **bf)
@@ -268,6 +269,15 @@ class LlamaEngine:
         self.loss_rows = torch.empty(T, **f32)
         self.rope = K.rope_table(seq_len, cfg.head_dim, cfg.rope_theta, device)
         self.kernel_launches = 0
+        # Weight-gradient GEMMs on a stream of their own (FTB200_WGRAD_STREAM=0 turns it off).  The weight gradient
+        # and the data gradient of a layer are independent, and each of these persistent GEMMs ends with a partial
+        # wave that leaves most SMs idle (384 tiles on 74 CTA pairs are 5.2 waves); with the two on different streams
+        # the CTAs of one start on the SMs that the tail of the other has left.
+        self.wstream = None
+        if device.type == "cuda" and os.environ.get("FTB200_WGRAD_STREAM", "1") == "1":
+            self.wstream = torch.cuda.Stream(device=device)
+            self._w_events: Dict[Tuple[int, str], Tuple[torch.cuda.Event, torch.cuda.Event]] = {}
+            self._w_last: Dict[str, torch.cuda.Event] = {}
 
     # -- helpers ---------------------------------------------------------------------------
     def _p(self, u: int) -> _Fields:
@@ -279,6 +289,56 @@ class LlamaEngine:
             if f is not None:
                 return f
         return self._p(u)
+
+    def _wgrad(self, layer: int, name: str, dy: torch.Tensor, x: torch.Tensor, out, reads: Tuple[str, ...]) -> None:
+        """Weight gradient ``out = dy^T x`` of one matrix, on the weight-gradient stream when there is one.  ``reads``
+        names the reusable workspaces among its operands: before the main stream overwrites one of them it waits for
+        this GEMM (:meth:`_before_overwrite`)."""
+        if self.wstream is None:
+            K.linear_wgrad(dy, x, out=out)
+            return
+        evs = self._w_events.get((layer, name))
+        if evs is None:
+            evs = (torch.cuda.Event(), torch.cuda.Event())
+            self._w_events[(layer, name)] = evs
+        ready, done = evs
+        ready.record()  # the operands are complete on the main stream here
+        with torch.cuda.stream(self.wstream):
+            self.wstream.wait_event(ready)
+            K.linear_wgrad(dy, x, out=out)
+            done.record(self.wstream)
+        for r in reads:
+            self._w_last[r] = done
+
+    def _before_overwrite(self, *names: str) -> None:
+        """The main stream is about to overwrite these workspaces: wait for the weight-gradient GEMMs that read them."""
+        if self.wstream is None:
+            return
+        for n in names:
+            ev = self._w_last.pop(n, None)
+            if ev is not None:
+                torch.cuda.current_stream().wait_event(ev)
+
+    def _grad_done_after_wgrads(self, u: int) -> None:
+        """``grad_done(u)`` once the unit's weight gradients are complete: with a weight-gradient stream the hook runs
+        on that stream (after it has caught up with the main stream), so that whatever the hook orders after "the
+        current stream" -- the reduce-scatter on the communication stream -- follows both."""
+        if self.wstream is None:
+            self.grad_done(u)
+            return
+        evs = self._w_events.get((u, "grad_done"))
+        if evs is None:
+            evs = (torch.cuda.Event(), torch.cuda.Event())
+            self._w_events[(u, "grad_done")] = evs
+        ready, done = evs
+        ready.record()
+        with torch.cuda.stream(self.wstream):
+            self.wstream.wait_event(ready)
+            self.grad_done(u)
+            done.record(self.wstream)
+        # the hook may read gradient destinations that the next unit reuses (a sharding layer's staging vectors for
+        # the norm-weight gradients): the main stream waits for it before it writes the next norm-weight gradient
+        self._w_last["grad_done"] = done
 
     def _g(self, u: int):
         """Gradient destinations of unit ``u``: views into its flat gradient buffer, or
@@ -359,30 +419,39 @@ class LlamaEngine:
             self.before_unit(u, True)
             W, G = self._p(u), self._g(u)
             # ---- FFN
-            K.linear_wgrad(dy, self.s[l], out=G.wd)
+            self._wgrad(l, "wd", dy, self.s[l], G.wd, reads=("dy",))
             K.linear_dgrad(dy, W.wd, out=self.ws_ds)
             K.swiglu_bwd(self.ws_ds, self.gu[l], dgu=self.gu[l])
-            K.rmsnorm_fwd(self.h[l], W.ffn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd2[l])
-            K.linear_wgrad(self.gu[l], self.ws_n, out=G.wgu)
+            self._before_overwrite("ws_n2")
+            K.rmsnorm_fwd(self.h[l], W.ffn_norm, c.norm_eps, out=self.ws_n2, rstd=self.rstd2[l])
+            self._wgrad(l, "wgu", self.gu[l], self.ws_n2, G.wgu, reads=("ws_n2",))
             K.linear_dgrad(self.gu[l], W.wgu, out=self.ws_dn)
+            self._before_overwrite("ws_dh", "grad_done")
             K.rmsnorm_bwd(self.ws_dn, self.h[l], W.ffn_norm, self.rstd2[l], dres=dy, dx=self.ws_dh, dw=G.ffn_norm)
             # ---- attention
-            K.linear_wgrad(self.ws_dh, self.att[l], out=G.wo)
+            self._wgrad(l, "wo", self.ws_dh, self.att[l], G.wo, reads=("ws_dh",))
             K.linear_dgrad(self.ws_dh, W.wo, out=self.ws_dn)
+            self._before_overwrite("ws_dqkv")
             self.attn.backward(l, self.ws_dn, B, S, self.ws_dqkv)
             K.rope_(self.ws_dqkv, self.rope, S, c.n_heads + c.n_kv_heads, c.head_dim, backward=True)
+            self._before_overwrite("ws_n")
             K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
-            K.linear_wgrad(self.ws_dqkv, self.ws_n, out=G.wqkv)
+            self._wgrad(l, "wqkv", self.ws_dqkv, self.ws_n, G.wqkv, reads=("ws_dqkv", "ws_n"))
             K.linear_dgrad(self.ws_dqkv, W.wqkv, out=self.ws_dn)
+            self._before_overwrite("dy")
             K.rmsnorm_bwd(self.ws_dn, self.x[l], W.attn_norm, self.rstd1[l], dres=self.ws_dh, dx=self.ws_dy,
                           dw=G.attn_norm)
-            self.grad_done(u)
+            self._grad_done_after_wgrads(u)
             dy = self.ws_dy
         self.before_unit(0, True)
         G = self._g(0)
         G.tok_embeddings.zero_()
         K.embedding_bwd(tokens.reshape(-1), dy, G.tok_embeddings)
         self.grad_done(0)
+        if self.wstream is not None:
+            # the weight gradients are part of the backward pass: whoever runs after it on this stream sees them
+            torch.cuda.current_stream().wait_stream(self.wstream)
+            self._w_last.clear()
 
 
 def init_unit_(cfg: LlamaConfig, unit: int, flat: torch.Tensor, seed: int) -> None:

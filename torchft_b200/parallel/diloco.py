@@ -169,9 +169,37 @@ class EngineDiLoCo:
         self.record_timing = record_timing and self.stream is not None
         self.timings: List[List[tuple]] = []
         self.exchange_timings: List[tuple] = []
-        # with record_timing: host time (monotonic seconds) at which this group reached each synchronisation
-        # with its stream drained; comparing them across the groups of one host gives their drift
+        # with record_timing: host time (monotonic seconds) at which this group's training stream reached each
+        # synchronisation; comparing them across the groups of one host gives their drift
         self.arrivals: List[float] = []
+        self._arrival_threads: List = []
+
+    def _stamp_arrival(self) -> None:
+        """Host time at which the training stream reaches this point, taken by a helper thread that waits for an
+        event: the training thread itself must not wait for the device here, or it would lose the lead over the
+        device that hides the wait for slower groups."""
+        import threading
+        import time
+
+        ev = torch.cuda.Event()
+        ev.record()
+        slot = len(self.arrivals)
+        self.arrivals.append(float("nan"))
+
+        def wait() -> None:
+            ev.synchronize()
+            self.arrivals[slot] = time.monotonic()
+
+        t = threading.Thread(target=wait, name="diloco_arrival", daemon=True)
+        t.start()
+        self._arrival_threads.append(t)
+
+    def arrival_times(self) -> List[float]:
+        """The recorded arrivals, once the device has passed all of them."""
+        for t in self._arrival_threads:
+            t.join()
+        self._arrival_threads.clear()
+        return list(self.arrivals)
 
     def _timed(self, fn, new_sync: bool):
         if not self.record_timing:
@@ -195,10 +223,7 @@ class EngineDiLoCo:
         self._local_step += 1
         if self._local_step == self._every - self.fragment_sync_delay:
             if self.record_timing:
-                import time
-
-                torch.cuda.current_stream().synchronize()
-                self.arrivals.append(time.monotonic())
+                self._stamp_arrival()
 
             def begin() -> None:
                 self.manager.start_quorum()  # synchronous: a replica that is behind heals here
