@@ -447,21 +447,27 @@ def test_unreachable_store_fails_within_connect_timeout():
     assert time.monotonic() - t0 < 30
 
 
-@pytest.mark.gpu
+class _CudaLike(torch.Tensor):
+    """A CPU tensor that says it lives on a GPU: takes the manager down its CUDA-only branches without one."""
+    is_cuda = property(lambda self: True)
+
+
 def test_quantized_allreduce_is_averaged_on_a_group_that_fuses_the_scale(h):
     """A group that can fold 1/participants into its unquantised allreduce (``supports_fused_scale``) does not do
     so for the quantised collective, which reduces with SUM: the manager has to divide."""
     h.pg.supports_fused_scale = True
     h.client._quorum.return_value = quorum()
     h.manager.start_quorum()
-    x = torch.full((256,), 6.0, device="cuda")
-    with patch("torchft_b200.collectives.allreduce_quantized",
-               side_effect=lambda tensors, op, pg, stream=None: _DummyWork(tensors)) as q:
+    x = torch.full((256,), 6.0).as_subclass(_CudaLike)
+    with patch("torch.cuda.current_stream", return_value=None), \
+            patch("torchft_b200.collectives.allreduce_quantized",
+                  side_effect=lambda tensors, op, pg, stream=None: _DummyWork(tensors)) as q:
         h.manager.allreduce(x, should_quantize=True).wait()
     assert q.call_count == 1 and q.call_args[0][1] == ReduceOp.SUM
-    torch.cuda.synchronize()
-    assert torch.allclose(x, torch.full_like(x, 3.0))  # two participants
+    assert torch.allclose(x.as_subclass(torch.Tensor), torch.full((256,), 3.0))  # two participants
     # the unquantised path of the same group passes the scale down instead
-    y = torch.full((256,), 6.0, device="cuda")
+    h.pg.allreduce = MagicMock(side_effect=lambda tensors, op=None, **kw: _DummyWork(tensors))
+    y = torch.full((256,), 6.0)
     h.manager.allreduce(y).wait()
     assert h.pg.allreduce.call_args.kwargs["scale"] == 0.5
+    assert torch.allclose(y, torch.full((256,), 6.0)) and h.manager.errored() is None
