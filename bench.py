@@ -210,7 +210,8 @@ def main() -> int:
     # one logits chunk: the 2 GB of bf16 logits fit, and the head's wgrad then runs once with the full reduction depth
     trainer = ShardedLlamaTrainer(cfg, B, S, dev, shard_comm=shard_comm, manager=manager, seed=1234,
                                   replica_alloc=replica_alloc, logit_chunks=1, fused_reduce_scatter=not args.no_fused_rs,
-                                  attention=args.attention)
+                                  attention=args.attention,
+                                  wgrad_stream=True if world == 1 else None)
     if manager is not None:
         manager.register_state_dict_fn("trainer", trainer.load_state_dict, trainer.state_dict)
 

@@ -224,6 +224,7 @@ class LlamaEngine:
         grad_fields: Optional[Callable[[int], object]] = None,
         grad_scale: float = 1.0,
         fwd_fields: Optional[Callable[[int], object]] = None,
+        wgrad_stream: bool = True,
     ):
         self.cfg, self.B, self.S, self.device = cfg, batch, seq_len, device
         self.grad_fields = grad_fields
@@ -269,12 +270,13 @@ class LlamaEngine:
         self.loss_rows = torch.empty(T, **f32)
         self.rope = K.rope_table(seq_len, cfg.head_dim, cfg.rope_theta, device)
         self.kernel_launches = 0
-        # Weight-gradient GEMMs on a stream of their own (FTB200_WGRAD_STREAM=0 turns it off).  The weight gradient
-        # and the data gradient of a layer are independent, and each of these persistent GEMMs ends with a partial
-        # wave that leaves most SMs idle (384 tiles on 74 CTA pairs are 5.2 waves); with the two on different streams
-        # the CTAs of one start on the SMs that the tail of the other has left.
+        # Weight-gradient GEMMs on a stream of their own (`wgrad_stream`; FTB200_WGRAD_STREAM=0/1 overrides).  The
+        # weight gradient and the data gradient of a layer are independent, and each of these persistent GEMMs ends
+        # with a partial wave that leaves most SMs idle (384 tiles on 74 CTA pairs are 5.2 waves); with the two on
+        # different streams the CTAs of one start on the SMs that the tail of the other has left.
         self.wstream = None
-        if device.type == "cuda" and os.environ.get("FTB200_WGRAD_STREAM", "1") == "1":
+        env = os.environ.get("FTB200_WGRAD_STREAM", "")
+        if device.type == "cuda" and (env == "1" or (env != "0" and wgrad_stream)):
             self.wstream = torch.cuda.Stream(device=device)
             self._w_events: Dict[Tuple[int, str], Tuple[torch.cuda.Event, torch.cuda.Event]] = {}
             self._w_last: Dict[str, torch.cuda.Event] = {}

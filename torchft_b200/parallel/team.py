@@ -701,6 +701,11 @@ class ProcessGroupB200(ProcessGroup):
         if n % (Q.BLOCK * self._world) or src.dtype not in _DT or not src.is_contiguous():
             raise ValueError("allreduce_fp8 needs a contiguous bf16/fp32 tensor of 128*world-multiple length")
         cap = self._staging_bytes * Q.BLOCK // (Q.BLOCK + 4) // (Q.BLOCK * self._world) * (Q.BLOCK * self._world)
+        if self._world > 1:
+            # Wait for the slowest rank in a one-warp kernel first.  The exchange kernel holds up to 96 CTAs of 512
+            # threads at 96 registers, beside which no GEMM CTA fits on an SM: when it is the one that waits (tens
+            # of milliseconds between drifting DiLoCo groups) the training stream that runs next to it crawls.
+            self._team.barrier()
         pos = 0
         while pos < n:
             m = min(cap, n - pos)
