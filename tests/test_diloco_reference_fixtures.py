@@ -23,7 +23,11 @@ from torchft_b200.manager import Manager
 from torchft_b200.work import _DummyWork
 
 _REPO = Path(__file__).resolve().parent.parent
-_DIRS = [Path(os.environ.get("TORCHFT_REFERENCE", "/root/reference")) / "test_fixtures", _REPO / "baseline" / "_ref" / "test_fixtures"]
+# the reference's golden histories: in the plain copy of the reference that the benchmarks' reference arm uses, or in
+# a checkout of the reference named by TORCHFT_REFERENCE
+_DIRS = [_REPO / "baseline" / "_ref" / "test_fixtures"]
+if os.environ.get("TORCHFT_REFERENCE"):
+    _DIRS.insert(0, Path(os.environ["TORCHFT_REFERENCE"]) / "test_fixtures")
 _NAME = "torchft.diloco_regression_test.DiLoCoMockedUpdateTest.test_diloco_mocked_updates_{}.json"
 # the order of the reference's parameter grid: (fragment_sync_delay, fragment_update_alpha)
 CASES = [(0, 0.0), (0, 0.5), (0, 1.0), (1, 0.0), (1, 0.5), (1, 1.0)]
