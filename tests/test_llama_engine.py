@@ -41,6 +41,23 @@ def test_engine_matches_autograd_cpu():
     assert l2.item() < loss.item()
 
 
+def test_kept_norm_outputs_give_the_same_gradients_as_recomputed_ones():
+    """`save_norms`: the forward pass keeps the normalised GEMM inputs per layer instead of recomputing them in the
+    backward pass; same kernels on the same values, so the gradients are bit-identical."""
+    cfg, B, S = LLAMA_TINY, 2, 16
+    dev = torch.device("cpu")
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(5))
+    targets = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(6))
+    grads = []
+    for keep in (False, True):
+        tr = ShardedLlamaTrainer(cfg, B, S, dev, logit_chunks=1, seed=11, save_norms=keep)
+        assert (tr.engine.n1 is not None) == keep
+        tr.forward_backward(tokens, targets)
+        grads.append([tr._grad_unit(u).clone() for u in range(cfg.n_units)])
+    for a, b in zip(*grads):
+        assert torch.equal(a, b)
+
+
 def test_sharded_trainer_two_gloo_ranks(tmp_path):
     """Two CPU ranks, parameters, gradients and optimizer state sharded between them, each with its own
     micro-batch: the reduce-scattered gradient equals the gradient one process computes on both

@@ -225,6 +225,7 @@ class LlamaEngine:
         grad_scale: float = 1.0,
         fwd_fields: Optional[Callable[[int], object]] = None,
         wgrad_stream: bool = True,
+        save_norms: Optional[bool] = None,
     ):
         self.cfg, self.B, self.S, self.device = cfg, batch, seq_len, device
         self.grad_fields = grad_fields
@@ -270,6 +271,17 @@ class LlamaEngine:
         self.loss_rows = torch.empty(T, **f32)
         self.rope = K.rope_table(seq_len, cfg.head_dim, cfg.rope_theta, device)
         self.kernel_launches = 0
+        # The normalised inputs of the QKV and gate/up GEMMs are needed again by their weight gradients.  They are
+        # recomputed in the backward pass (two more norm kernels per layer) unless `save_norms`: then the forward
+        # pass keeps them per layer (2 x T x D bf16 per layer).  None: keep them when the device has room to spare.
+        if save_norms is None:
+            save_norms = False
+            if device.type == "cuda":
+                need = 2 * L * T * D * 2
+                free, _ = torch.cuda.mem_get_info(device)
+                save_norms = free > need + (20 << 30)
+        self.n1 = [torch.empty(T, D, **bf) for _ in range(L)] if save_norms else None
+        self.n2 = [torch.empty(T, D, **bf) for _ in range(L)] if save_norms else None
         # Weight-gradient GEMMs on a stream of their own (`wgrad_stream`; FTB200_WGRAD_STREAM=0/1 overrides).  The
         # weight gradient and the data gradient of a layer are independent, and each of these persistent GEMMs ends
         # with a partial wave that leaves most SMs idle (384 tiles on 74 CTA pairs are 5.2 waves); with the two on
@@ -366,20 +378,23 @@ class LlamaEngine:
             u = l + 1
             self.before_unit(u, False)
             W = self._pf(u)
+            keep = train and self.n1 is not None
+            n1 = self.n1[l] if keep else self.ws_n
+            n2 = self.n2[l] if keep else self.ws_n
             # x[l] = stream (+ delta of the previous block); n1 = norm(x[l])
             if delta is None:
-                K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
+                K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=n1, rstd=self.rstd1[l])
             else:
-                K.rmsnorm_fwd(self.h[l - 1], W.attn_norm, c.norm_eps, res=delta, h_out=self.x[l], out=self.ws_n,
+                K.rmsnorm_fwd(self.h[l - 1], W.attn_norm, c.norm_eps, res=delta, h_out=self.x[l], out=n1,
                               rstd=self.rstd1[l])
-            K.linear_fwd(self.ws_n, W.wqkv, out=self.qkv[l])
+            K.linear_fwd(n1, W.wqkv, out=self.qkv[l])
             K.rope_(self.qkv[l], self.rope, S, c.n_heads + c.n_kv_heads, c.head_dim)
             self.attn.forward(l, self.qkv[l], B, S, self.att[l], train)
             K.linear_fwd(self.att[l], W.wo, out=self.ws_proj)
-            K.rmsnorm_fwd(self.x[l], W.ffn_norm, c.norm_eps, res=self.ws_proj, h_out=self.h[l], out=self.ws_n,
+            K.rmsnorm_fwd(self.x[l], W.ffn_norm, c.norm_eps, res=self.ws_proj, h_out=self.h[l], out=n2,
                           rstd=self.rstd2[l])
             s_buf = self.s[l] if train else self.ws_s
-            K.linear_swiglu_fwd(self.ws_n, W.wgu, self.gu[l], s_buf)  # activation fused into the GEMM epilogue
+            K.linear_swiglu_fwd(n2, W.wgu, self.gu[l], s_buf)  # activation fused into the GEMM epilogue
             K.linear_fwd(s_buf, W.wd, out=self.ws_proj)
             delta = self.ws_proj
         u = L + 1
@@ -424,9 +439,12 @@ class LlamaEngine:
             self._wgrad(l, "wd", dy, self.s[l], G.wd, reads=("dy",))
             K.linear_dgrad(dy, W.wd, out=self.ws_ds)
             K.swiglu_bwd(self.ws_ds, self.gu[l], dgu=self.gu[l])
-            self._before_overwrite("ws_n2")
-            K.rmsnorm_fwd(self.h[l], W.ffn_norm, c.norm_eps, out=self.ws_n2, rstd=self.rstd2[l])
-            self._wgrad(l, "wgu", self.gu[l], self.ws_n2, G.wgu, reads=("ws_n2",))
+            if self.n2 is not None:
+                self._wgrad(l, "wgu", self.gu[l], self.n2[l], G.wgu, reads=())
+            else:
+                self._before_overwrite("ws_n2")
+                K.rmsnorm_fwd(self.h[l], W.ffn_norm, c.norm_eps, out=self.ws_n2, rstd=self.rstd2[l])
+                self._wgrad(l, "wgu", self.gu[l], self.ws_n2, G.wgu, reads=("ws_n2",))
             K.linear_dgrad(self.gu[l], W.wgu, out=self.ws_dn)
             self._before_overwrite("ws_dh", "grad_done")
             K.rmsnorm_bwd(self.ws_dn, self.h[l], W.ffn_norm, self.rstd2[l], dres=dy, dx=self.ws_dh, dw=G.ffn_norm)
@@ -436,9 +454,12 @@ class LlamaEngine:
             self._before_overwrite("ws_dqkv")
             self.attn.backward(l, self.ws_dn, B, S, self.ws_dqkv)
             K.rope_(self.ws_dqkv, self.rope, S, c.n_heads + c.n_kv_heads, c.head_dim, backward=True)
-            self._before_overwrite("ws_n")
-            K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
-            self._wgrad(l, "wqkv", self.ws_dqkv, self.ws_n, G.wqkv, reads=("ws_dqkv", "ws_n"))
+            if self.n1 is not None:
+                self._wgrad(l, "wqkv", self.ws_dqkv, self.n1[l], G.wqkv, reads=("ws_dqkv",))
+            else:
+                self._before_overwrite("ws_n")
+                K.rmsnorm_fwd(self.x[l], W.attn_norm, c.norm_eps, out=self.ws_n, rstd=self.rstd1[l])
+                self._wgrad(l, "wqkv", self.ws_dqkv, self.ws_n, G.wqkv, reads=("ws_dqkv", "ws_n"))
             K.linear_dgrad(self.ws_dqkv, W.wqkv, out=self.ws_dn)
             self._before_overwrite("dy")
             K.rmsnorm_bwd(self.ws_dn, self.x[l], W.attn_norm, self.rstd1[l], dres=self.ws_dh, dx=self.ws_dy,

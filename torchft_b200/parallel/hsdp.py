@@ -15,6 +15,8 @@ whose replicate dimension is a ``ManagedProcessGroup`` (torchft/device_mesh.py:3
 
 from __future__ import annotations
 
+import ctypes
+import math
 import os
 from typing import Dict, List, Optional
 
@@ -57,6 +59,7 @@ class ShardedLlamaTrainer:
         fused_reduce_scatter: bool = True,
         fused_all_gather: Optional[bool] = None,
         wgrad_stream: Optional[bool] = None,
+        save_norms: Optional[bool] = None,
     ):
         self.cfg, self.device = cfg, device
         self.comm = shard_comm or LocalShardComm()
@@ -175,6 +178,7 @@ class ShardedLlamaTrainer:
             # groups, so by default they are used only without a shard group and without a manager.  A job that
             # knows it runs a single replica group passes True.
             wgrad_stream=(ws == 1 and manager is None) if wgrad_stream is None else bool(wgrad_stream),
+            save_norms=save_norms,
         )
         self._mark_params_written()
 
@@ -199,9 +203,6 @@ class ShardedLlamaTrainer:
             self._params_event = ev
 
     def _build_gather_fields(self) -> None:
-        import ctypes
-        import math
-
         from ..checkpointing.p2p_transport import _seg_table
 
         ws = self.comm.size
@@ -250,7 +251,6 @@ class ShardedLlamaTrainer:
         self._ga_vec_table = _seg_table(vec_segs, self.device)
         self._ga_vec_n = len(vec_segs)
         self._ga_vec_bytes = sum(s[2] for s in vec_segs)
-        self._ctypes = ctypes
 
     def _fwd_fields(self, u: int):
         return self._ga_fields.get(u)
@@ -267,8 +267,8 @@ class ShardedLlamaTrainer:
                 self.comm_stream.wait_event(self._params_event)
             self.comm.all_gather(self.p_shard[0], self.p_full[0])
             N.check(N.lib().ftb200_p2p_copy(
-                N.ptr(self._ga_vec_table), self._ctypes.c_int(self._ga_vec_n), self._ctypes.c_longlong(self._ga_vec_bytes),
-                self._ctypes.c_void_p(team._abort_dev), N.ptr(team._status), self._ctypes.c_int(4), N.stream_ptr()),
+                N.ptr(self._ga_vec_table), ctypes.c_int(self._ga_vec_n), ctypes.c_longlong(self._ga_vec_bytes),
+                ctypes.c_void_p(team._abort_dev), N.ptr(team._status), ctypes.c_int(4), N.stream_ptr()),
                 "p2p_copy")
             ev = torch.cuda.Event()
             ev.record(self.comm_stream)
@@ -322,7 +322,6 @@ class ShardedLlamaTrainer:
             return None
         f = self._fused_fields.get(u)
         if f is None:
-            import math
 
             class _F:
                 pass
