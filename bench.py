@@ -346,6 +346,8 @@ def main() -> int:
             },
             "gpu_launches": launches,
             "commits": commits,
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 1e9, 2),
+            "free_mem_gb": round(torch.cuda.mem_get_info(dev)[0] / 1e9, 2),
             **({"exposed_comm_ms_per_step": {k: round(v / args.steps, 3) for k, v in exposed.items()}} if exposed else {}),
             "model_tflops_per_gpu": flops * args.steps / (ms_total / 1e3) / 1e12,
             # uniform-random targets cannot be learned: the loss stays near that of the random initialisation,

@@ -274,6 +274,8 @@ class LlamaEngine:
         # The normalised inputs of the QKV and gate/up GEMMs are needed again by their weight gradients.  They are
         # recomputed in the backward pass (two more norm kernels per layer) unless `save_norms`: then the forward
         # pass keeps them per layer (2 x T x D bf16 per layer).  None: keep them when the device has room to spare.
+        if os.environ.get("FTB200_SAVE_NORMS", "") in ("0", "1"):
+            save_norms = os.environ["FTB200_SAVE_NORMS"] == "1"
         if save_norms is None:
             save_norms = False
             if device.type == "cuda":
