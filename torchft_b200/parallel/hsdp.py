@@ -475,6 +475,7 @@ class ShardedLlamaTrainer:
         if self.comm.size > 1:
             for u in units:
                 self._gathered[u] = False
+            self._mark_params_written()  # (the caller wrote the shards on the current stream)
 
     # ---- state dict (heal / durable checkpoints) -------------------------------------------
     def state_dict(self) -> Dict[str, object]:
