@@ -97,3 +97,17 @@ def test_sharded_trainer_two_gloo_ranks(tmp_path):
         assert err < 3e-2, (u, float(err))
     for r in res:  # the same micro-batch every step: the loss has to fall
         assert r["losses"][-1] < r["losses"][0]
+
+
+def test_shard_pieces_cut_a_field_at_shard_boundaries():
+    """The fused all-gather copies small fields (norm weights) piecewise from their owners."""
+    from torchft_b200.parallel.hsdp import shard_pieces
+
+    assert shard_pieces(10, 30, 16) == [(0, 10, 10, 6), (1, 0, 16, 16), (2, 0, 32, 8)]
+    assert shard_pieces(0, 8, 8) == [(0, 0, 0, 8)]
+    assert shard_pieces(16, 16, 16) == [(1, 0, 16, 16)]
+    for off, n, shard in ((5, 3, 100), (96, 4096, 1000), (0, 1, 1)):
+        pieces = shard_pieces(off, n, shard)
+        assert sum(p[3] for p in pieces) == n
+        assert pieces[0][2] == off and all(a[2] + a[3] == b[2] for a, b in zip(pieces, pieces[1:]))
+        assert all(o * shard + s == u and s + c <= shard for o, s, u, c in pieces)

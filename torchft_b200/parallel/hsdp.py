@@ -15,7 +15,6 @@ whose replicate dimension is a ``ManagedProcessGroup`` (torchft/device_mesh.py:3
 
 from __future__ import annotations
 
-import ctypes
 import math
 import os
 from typing import Dict, List, Optional
@@ -29,6 +28,19 @@ from .shard_comm import LocalShardComm, ShardComm
 
 def _round_up(x: int, m: int) -> int:
     return (x + m - 1) // m * m
+
+
+def shard_pieces(offset: int, numel: int, shard_numel: int) -> List[tuple]:
+    """The pieces of the element range ``[offset, offset + numel)`` of a flat unit that is sharded evenly in shards of
+    ``shard_numel`` elements: ``(owner rank, offset inside the owner's shard, offset inside the unit, elements)``, cut
+    at the shard boundaries."""
+    out, a, end = [], offset, offset + numel
+    while a < end:
+        owner = a // shard_numel
+        b = min(end, (owner + 1) * shard_numel)
+        out.append((owner, a - owner * shard_numel, a, b - a))
+        a = b
+    return out
 
 
 class ShardedLlamaTrainer:
@@ -238,12 +250,8 @@ class ShardedLlamaTrainer:
                 else:
                     setattr(f, name, local)
                     # norm weights travel in one copy kernel per step: split at shard boundaries
-                    a = off
-                    while a < off + numel:
-                        owner = a // n
-                        b = min(off + numel, (owner + 1) * n)
-                        vec_segs.append((int(peers[owner]) + (a - owner * n) * 2, self.p_full[u].data_ptr() + a * 2, (b - a) * 2))
-                        a = b
+                    for owner, in_shard, in_unit, count in shard_pieces(off, numel, n):
+                        vec_segs.append((int(peers[owner]) + in_shard * 2, self.p_full[u].data_ptr() + in_unit * 2, count * 2))
                 off += numel
             self._ga_fields[u] = f
         if any(nb % 16 or src % 16 or dst % 16 for src, dst, nb in vec_segs):
@@ -259,17 +267,11 @@ class ShardedLlamaTrainer:
         """Start of a step with the GEMM-fused all-gather: on the communication stream, after this rank's parameter
         writes, gather the embedding unit (its rounds also tell every rank that all shards of all units are final)
         and copy the norm weights of the fused units; the layers' matrices are marked as not yet gathered."""
-        from ..ops import _native as N
-
-        team = self.comm.team
         with torch.cuda.stream(self.comm_stream):
             if self._params_event is not None:
                 self.comm_stream.wait_event(self._params_event)
             self.comm.all_gather(self.p_shard[0], self.p_full[0])
-            N.check(N.lib().ftb200_p2p_copy(
-                N.ptr(self._ga_vec_table), ctypes.c_int(self._ga_vec_n), ctypes.c_longlong(self._ga_vec_bytes),
-                ctypes.c_void_p(team._abort_dev), N.ptr(team._status), ctypes.c_int(4), N.stream_ptr()),
-                "p2p_copy")
+            self.comm.copy_segments(self._ga_vec_table, self._ga_vec_n, self._ga_vec_bytes)
             ev = torch.cuda.Event()
             ev.record(self.comm_stream)
         self._ag_event[0] = ev

@@ -487,6 +487,14 @@ class PeerShardComm(ShardComm):
     def reduce_stage(self, stage: torch.Tensor, shard: torch.Tensor) -> None:
         self.team.reduce_local_slices(self._off(stage), shard, shard.numel(), shard.dtype)
 
+    def copy_segments(self, table: torch.Tensor, nsegs: int, total_bytes: int, ctas: int = 4) -> None:
+        """One copy kernel over a device table of ``(peer source, local destination, bytes)`` segments (16-byte
+        multiples), bounded by the team's abort word and reporting into its status word.  No rounds: the caller
+        orders it after a collective that has told every rank that the sources are final."""
+        N.check(N.lib().ftb200_p2p_copy(N.ptr(table), ctypes.c_int(nsegs), ctypes.c_longlong(total_bytes),
+                                        ctypes.c_void_p(self.team._abort_dev), N.ptr(self.team._status), ctypes.c_int(ctas),
+                                        N.stream_ptr()), "p2p_copy")
+
     def barrier(self) -> None:
         self.team.barrier()
 
