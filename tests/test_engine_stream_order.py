@@ -1,0 +1,215 @@
+"""Ordering of the engine's two backward streams, checked without a GPU.
+
+The weight-gradient GEMMs of the backward pass run on a stream of their own, ordered against the main stream by
+events per operand workspace.  A missing wait is a data race that a GPU test may never show, so this test runs the
+backward pass on CPU with stand-ins for CUDA streams and events, records which stream every kernel call was issued
+on and which buffers it reads and writes, derives the happens-before relation from the streams' program order and
+the recorded event waits, and requires every pair of conflicting accesses from different streams to be ordered.
+"""
+import contextlib
+import itertools
+
+import pytest
+import torch
+
+from torchft_b200.models import llama as L
+from torchft_b200.ops import kernels as K
+from torchft_b200.parallel.hsdp import ShardedLlamaTrainer
+
+
+class _Stream:
+    _ids = itertools.count()
+
+    def __init__(self, *a, **k):
+        self.id = next(self._ids)
+        self.clock = {}  # stream id -> number of that stream's operations known to precede this stream's next one
+        self.n_ops = 0
+
+    def _merge(self, other_clock):
+        for k, v in other_clock.items():
+            if v > self.clock.get(k, 0):
+                self.clock[k] = v
+
+    def wait_event(self, ev):
+        if ev.snapshot is not None:
+            self._merge(ev.snapshot)
+
+    def wait_stream(self, other):
+        snap = dict(other.clock)
+        snap[other.id] = other.n_ops
+        self._merge(snap)
+
+    def synchronize(self):
+        pass
+
+
+class _Event:
+    def __init__(self, *a, **k):
+        self.snapshot = None
+
+    def record(self, stream=None):
+        s = stream if stream is not None else _Cuda.current
+        snap = dict(s.clock)
+        snap[s.id] = s.n_ops
+        self.snapshot = snap
+
+
+class _Cuda:
+    main = None
+    current = None
+
+
+@contextlib.contextmanager
+def _stream_ctx(s):
+    prev = _Cuda.current
+    _Cuda.current = s if s is not None else prev
+    try:
+        yield
+    finally:
+        _Cuda.current = prev
+
+
+def _span(t):
+    """(storage, first byte, last byte + 1) of a contiguous tensor."""
+    es = t.element_size()
+    lo = t.storage_offset() * es
+    return (t.untyped_storage().data_ptr(), lo, lo + t.numel() * es)
+
+
+class _Log:
+    def __init__(self):
+        self.ops = []
+
+    def add(self, name, reads, writes):
+        s = _Cuda.current
+        s.n_ops += 1
+        clock = dict(s.clock)
+        clock[s.id] = s.n_ops  # this operation is number n_ops on its stream
+        self.ops.append((name, s.id, s.n_ops, clock, [_span(t) for t in reads if t is not None],
+                         [_span(t) for t in writes if t is not None]))
+
+
+def _overlap(a, b):
+    return a[0] == b[0] and a[1] < b[2] and b[1] < a[2]
+
+
+def _ordered(first, second):
+    """`first` happens before `second` (different streams): second's clock has seen first's position."""
+    _, sid, pos, _, _, _ = first
+    return second[3].get(sid, 0) >= pos
+
+
+def _check(log):
+    races = []
+    for i, a in enumerate(log.ops):
+        for b in log.ops[i + 1:]:
+            if a[1] == b[1]:
+                continue  # same stream: program order
+            conflict = any(_overlap(w, x) for w in a[5] for x in b[4] + b[5]) or any(_overlap(w, x) for w in b[5] for x in a[4])
+            if conflict and not _ordered(a, b):
+                races.append((a[0], b[0]))
+    return races
+
+
+@pytest.fixture
+def fake_cuda(monkeypatch):
+    main = _Stream()
+    _Cuda.main = _Cuda.current = main
+    monkeypatch.setattr(torch.cuda, "Stream", _Stream)
+    monkeypatch.setattr(torch.cuda, "Event", _Event)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a, **k: _Cuda.current)
+    monkeypatch.setattr(torch.cuda, "stream", _stream_ctx)
+    yield main
+    _Cuda.main = _Cuda.current = None
+
+
+def _instrument(monkeypatch, log):
+    def wrap(name, fn, reads, writes):
+        def inner(*a, **k):
+            log.add(name, reads(*a, **k), writes(*a, **k))
+            return fn(*a, **k)
+
+        monkeypatch.setattr(K, name, inner)
+
+    wrap("linear_wgrad", K.linear_wgrad, lambda dy, x, out=None, **k: [dy, x], lambda dy, x, out=None, **k: [out])
+    wrap("linear_dgrad", K.linear_dgrad, lambda dy, w, out=None, **k: [dy, w], lambda dy, w, out=None, **k: [out])
+    wrap("rmsnorm_fwd", K.rmsnorm_fwd,
+         lambda x, w, eps=1e-5, res=None, h_out=None, out=None, rstd=None, **k: [x, w, res],
+         lambda x, w, eps=1e-5, res=None, h_out=None, out=None, rstd=None, **k: [h_out, out, rstd])
+    wrap("rmsnorm_bwd", K.rmsnorm_bwd,
+         lambda dy, x, w, rstd, dres=None, dx=None, dw=None, **k: [dy, x, w, rstd, dres],
+         lambda dy, x, w, rstd, dres=None, dx=None, dw=None, **k: [dx, dw])
+    wrap("swiglu_bwd", K.swiglu_bwd, lambda ds, gu, dgu=None: [ds, gu], lambda ds, gu, dgu=None: [dgu])
+    wrap("rope_", K.rope_, lambda buf, *a, **k: [buf], lambda buf, *a, **k: [buf])
+    wrap("embedding_bwd", K.embedding_bwd, lambda tok, dout, dtable: [dout], lambda tok, dout, dtable: [dtable])
+
+
+@pytest.mark.parametrize("save_norms", [False, True])
+def test_backward_streams_are_ordered(monkeypatch, fake_cuda, save_norms):
+    cfg, B, S = L.LLAMA_TINY, 2, 16
+    dev = torch.device("cpu")
+    log = _Log()
+    done_units = []
+    tr = ShardedLlamaTrainer(cfg, B, S, dev, logit_chunks=1, seed=3, save_norms=save_norms)
+    eng = tr.engine
+    # what a sharding layer's hook does with a finished unit: read its whole gradient buffer (reduce-scatter)
+    eng.grad_done = lambda u: (done_units.append((u, _Cuda.current.id)), log.add(f"grad_done[{u}]", [tr._grad_unit(u)], []))
+    # switch the second stream on by hand (the engine only creates it on a CUDA device)
+    eng.wstream = _Stream()
+    eng._w_events, eng._w_last = {}, {}
+    # the library attention of the CPU path: one op that reads dout and writes the packed dQKV workspace
+    orig_attn_bwd = eng.attn.backward
+
+    def attn_bwd(layer, dout, batch, seq, dqkv):
+        log.add("attention.backward", [dout], [dqkv])
+        return orig_attn_bwd(layer, dout, batch, seq, dqkv)
+
+    monkeypatch.setattr(eng.attn, "backward", attn_bwd)
+    _instrument(monkeypatch, log)
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1))
+    targets = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(2))
+    loss = tr.forward_backward(tokens, targets)
+    assert torch.isfinite(loss)
+
+    on_w = [o for o in log.ops if o[1] == eng.wstream.id]
+    assert sum(o[0] == "linear_wgrad" for o in on_w) == 4 * cfg.n_layers  # the layers' weight gradients moved over
+    assert [u for u, sid in done_units if sid == eng.wstream.id] == list(range(cfg.n_layers, 0, -1))
+    assert _check(log) == []
+    # after the backward pass the main stream has seen everything the second stream did
+    assert fake_cuda.clock.get(eng.wstream.id, 0) == eng.wstream.n_ops
+
+    # the checker itself: without the waits before a workspace is overwritten it must report races
+    monkeypatch.setattr(eng, "_before_overwrite", lambda *names: None)
+    n_before = len(log.ops)
+    tr.forward_backward(tokens, targets)
+    broken = _Log()
+    broken.ops = log.ops[n_before:]
+    assert _check(broken) != []
+
+
+def test_shared_norm_gradient_staging_is_not_overwritten_before_the_hook_read_it(monkeypatch, fake_cuda):
+    """A sharding layer may hand out the same small staging tensors for the norm-weight gradients of every unit and
+    read them in its ``grad_done`` hook (which the engine runs on the second stream): the next unit's norm backward
+    on the main stream has to wait for that hook."""
+    cfg, B, S = L.LLAMA_TINY, 2, 16
+    log = _Log()
+    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), logit_chunks=1, seed=3)
+    eng = tr.engine
+    staging = {n: torch.zeros(cfg.dim, dtype=torch.bfloat16) for n in ("attn_norm", "ffn_norm")}
+
+    def fields(u):
+        if u == 0 or u == cfg.n_layers + 1:
+            return None
+        f = L._Fields(tr._grad_unit(u), cfg.unit_fields(u))
+        f.attn_norm, f.ffn_norm = staging["attn_norm"], staging["ffn_norm"]
+        return f
+
+    eng.grad_fields = fields
+    eng.grad_done = lambda u: log.add(f"grad_done[{u}]", [tr._grad_unit(u)] + (list(staging.values()) if 0 < u <= cfg.n_layers else []), [])
+    eng.wstream = _Stream()
+    eng._w_events, eng._w_last = {}, {}
+    monkeypatch.setattr(eng.attn, "backward", lambda layer, dout, batch, seq, dqkv: (log.add("attention.backward", [dout], [dqkv]), dqkv.zero_()))
+    _instrument(monkeypatch, log)
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1))
+    tr.forward_backward(tokens, tokens)
+    assert _check(log) == []
