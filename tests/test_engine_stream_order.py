@@ -70,7 +70,9 @@ def _stream_ctx(s):
 
 
 def _span(t):
-    """(storage, first byte, last byte + 1) of a contiguous tensor."""
+    """(storage, first byte, last byte + 1) of a contiguous tensor (for a scatter target: of its staging buffer)."""
+    if hasattr(t, "peers"):
+        t = t.peers.tensor
     es = t.element_size()
     lo = t.storage_offset() * es
     return (t.untyped_storage().data_ptr(), lo, lo + t.numel() * es)
@@ -212,4 +214,171 @@ def test_shared_norm_gradient_staging_is_not_overwritten_before_the_hook_read_it
     _instrument(monkeypatch, log)
     tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1))
     tr.forward_backward(tokens, tokens)
+    assert _check(log) == []
+
+
+class _LoggingShardComm:
+    """A shard group of two as seen from rank 0, in one process: the collectives copy locally and log what they
+    read and write on the stream they are issued on."""
+
+    rank, size = 0, 2
+    supports_fused_scatter = False
+
+    def __init__(self, log):
+        self.log = log
+
+    def alloc(self, numel, dtype, device):
+        return torch.zeros(numel, dtype=dtype, device=device)
+
+    def all_gather(self, shard, full):
+        self.log.add("all_gather", [shard], [full])
+        n = shard.numel()
+        full[:n].copy_(shard)
+        full[n:2 * n].copy_(shard)
+
+    def reduce_scatter(self, full, shard):
+        self.log.add("reduce_scatter", [full], [shard])
+        shard.copy_(full[: shard.numel()])
+
+    def all_reduce_sum_(self, t):
+        self.log.add("all_reduce_sum", [t], [t])
+
+    def barrier(self):
+        pass
+
+    def shutdown(self):
+        pass
+
+
+def test_sharded_trainer_streams_are_ordered(monkeypatch, fake_cuda):
+    """The sharded trainer's own stream logic on a shard group of two: parameter gathers one unit ahead on the
+    communication stream, gradient buffers shared by alternating units, reduce-scatters behind the backward pass,
+    the optimizer's parameter writes against the next step's gathers.  Two steps, so that the hand-over from one
+    step to the next is part of the check."""
+    cfg, B, S = L.LLAMA_TINY, 2, 16
+    log = _Log()
+    comm = _LoggingShardComm(log)
+    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), shard_comm=comm, logit_chunks=1, seed=3, fused_reduce_scatter=False)
+    assert tr.comm_stream is None and not tr.fused_rs and not tr.fused_ag
+    # what the constructor does on a CUDA device
+    tr.cuda = True
+    tr.comm_stream = _Stream()
+    tr._gathered = [False] * cfg.n_units
+    tr._mark_params_written()
+    log.ops.clear()
+    _instrument(monkeypatch, log)
+
+    def wrap(name, reads, writes):
+        fn = getattr(K, name)
+
+        def inner(*a, **k):
+            log.add(name, reads(*a, **k), writes(*a, **k))
+            return fn(*a, **k)
+
+        monkeypatch.setattr(K, name, inner)
+
+    wrap("linear_fwd", lambda x, w, out=None: [x, w], lambda x, w, out=None: [out])
+    wrap("linear_swiglu_fwd", lambda x, w, gu, s: [x, w], lambda x, w, gu, s: [gu, s])
+    wrap("embedding_fwd", lambda tok, table, out=None: [table], lambda tok, table, out=None: [out])
+    wrap("cross_entropy_", lambda logits, *a, **k: [logits], lambda logits, *a, loss=None, **k: [logits, loss])
+    wrap("sumsq_", lambda x, out: [x], lambda x, out: [out])
+    wrap("adamw_", lambda master, m, v, grad, param_lp, *a, **k: [grad], lambda master, m, v, grad, param_lp, *a, **k: [master, m, v, param_lp])
+    monkeypatch.setattr(tr.engine.attn, "backward",
+                        lambda layer, dout, batch, seq, dqkv: (log.add("attention.backward", [dout], [dqkv]), dqkv.zero_()))
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1))
+    for _ in range(2):
+        loss = tr.train_step(tokens, tokens)
+    assert torch.isfinite(loss)
+    on_comm = [o[0] for o in log.ops if o[1] == tr.comm_stream.id]
+    assert on_comm.count("all_gather") == 2 * cfg.n_units and on_comm.count("reduce_scatter") == 2 * cfg.n_units
+    assert _check(log) == []
+
+    # the checker sees the race that the wait for the parameter writes prevents: drop it and run another step
+    tr._mark_params_written = lambda: None
+    tr._params_event = None
+    n_before = len(log.ops)
+    tr.train_step(tokens, tokens)
+    tr.train_step(tokens, tokens)
+    broken = _Log()
+    broken.ops = log.ops[n_before:]
+    assert any("adamw_" in pair and "all_gather" in pair for pair in _check(broken))
+
+
+class _Peers(list):
+    """Stands in for the ctypes array of peer pointers; remembers the local tensor the pointers belong to."""
+
+    def __init__(self, tensor, world):
+        super().__init__([tensor.data_ptr()] * world)
+        self.tensor = tensor
+
+
+class _FusedLoggingShardComm(_LoggingShardComm):
+    supports_fused_scatter = True
+
+    def stage_peers(self, t):
+        return _Peers(t, self.size)
+
+    def reduce_stage(self, stage, shard):
+        self.log.add("reduce_stage", [stage], [shard])
+
+    def copy_segments(self, table, nsegs, total_bytes, ctas=4):
+        self.log.add("copy_segments", [self.trainer.p_flat], [self.trainer.p_full[u] for u in self.trainer._ga_units])
+
+
+def test_sharded_trainer_streams_are_ordered_with_the_fused_collectives(monkeypatch, fake_cuda):
+    """The same check with the reduce-scatter fused into the weight-gradient GEMMs (which then write the staging
+    buffers that the communication stream reduces) and the all-gather fused into the forward GEMMs (which then read
+    the shard buffers that the optimizer writes and fill the gathered units themselves)."""
+    cfg, B, S = L.LLAMA_TINY, 2, 16
+    log = _Log()
+    comm = _FusedLoggingShardComm(log)
+    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), shard_comm=comm, logit_chunks=1, seed=3, fused_reduce_scatter=False)
+    comm.trainer = tr
+    tr.cuda = True
+    tr.comm_stream = _Stream()
+    tr._gathered = [False] * cfg.n_units
+    # what the constructor does on a CUDA device when both fusions are on
+    tr.fused_rs = True
+    tr.engine.grad_fields = tr._grad_fields
+    tr.fused_ag = True
+    tr._build_gather_fields()
+    assert tr._ga_units == list(range(1, cfg.n_units))
+    tr.engine.fwd_fields = tr._fwd_fields
+    tr._mark_params_written()
+    log.ops.clear()
+    _instrument(monkeypatch, log)
+
+    def wrap(name, reads, writes, replace=None):
+        fn = replace or getattr(K, name)
+
+        def inner(*a, **k):
+            log.add(name, reads(*a, **k), writes(*a, **k))
+            return fn(*a, **k)
+
+        monkeypatch.setattr(K, name, inner)
+
+    def gather_gemm(x, w, out, aux=None):
+        K.gemm(x, w.local, False, False, out=out)
+        if aux is not None:
+            K.swiglu_fwd(out, out=aux)
+        w.pending = False
+
+    wrap("gemm_gather", lambda x, w, out, aux=None: [x, w.peers.tensor], lambda x, w, out, aux=None: [w.local, out, aux], gather_gemm)
+    wrap("gemm_scatter", lambda a, b, a_mn, b_mn, dst: [a, b], lambda a, b, a_mn, b_mn, dst: [dst.peers.tensor], lambda *a, **k: None)
+    wrap("scatter_to_stage", lambda src, dst: [src], lambda src, dst: [dst.peers.tensor], lambda *a, **k: None)
+    wrap("linear_fwd", lambda x, w, out=None: [x] + ([w] if isinstance(w, torch.Tensor) else []), lambda x, w, out=None: [out])
+    wrap("linear_swiglu_fwd", lambda x, w, gu, s: [x] + ([w] if isinstance(w, torch.Tensor) else []), lambda x, w, gu, s: [gu, s])
+    wrap("embedding_fwd", lambda tok, table, out=None: [table], lambda tok, table, out=None: [out])
+    wrap("cross_entropy_", lambda logits, *a, **k: [logits], lambda logits, *a, loss=None, **k: [logits, loss])
+    wrap("sumsq_", lambda x, out: [x], lambda x, out: [out])
+    wrap("adamw_", lambda master, m, v, grad, param_lp, *a, **k: [grad], lambda master, m, v, grad, param_lp, *a, **k: [master, m, v, param_lp])
+    monkeypatch.setattr(tr.engine.attn, "backward",
+                        lambda layer, dout, batch, seq, dqkv: (log.add("attention.backward", [dout], [dqkv]), dqkv.zero_()))
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1))
+    for _ in range(3):
+        tr.train_step(tokens, tokens)
+    names = [o[0] for o in log.ops]
+    assert names.count("all_gather") == 3 and names.count("copy_segments") == 3  # only the embedding unit and the norm weights
+    assert names.count("gemm_gather") == 3 * (4 * cfg.n_layers + 1)
+    assert names.count("gemm_scatter") == 3 * (4 * cfg.n_layers + 1) and names.count("reduce_stage") == 3 * (cfg.n_layers + 1)
     assert _check(log) == []
