@@ -325,7 +325,8 @@ class _FusedLoggingShardComm(_LoggingShardComm):
         self.log.add("copy_segments", [self.trainer.p_flat], [self.trainer.p_full[u] for u in self.trainer._ga_units])
 
 
-def test_sharded_trainer_streams_are_ordered_with_the_fused_collectives(monkeypatch, fake_cuda):
+@pytest.mark.parametrize("wgrad_stream", [False, True])
+def test_sharded_trainer_streams_are_ordered_with_the_fused_collectives(monkeypatch, fake_cuda, wgrad_stream):
     """The same check with the reduce-scatter fused into the weight-gradient GEMMs (which then write the staging
     buffers that the communication stream reduces) and the all-gather fused into the forward GEMMs (which then read
     the shard buffers that the optimizer writes and fill the gathered units themselves)."""
@@ -344,6 +345,9 @@ def test_sharded_trainer_streams_are_ordered_with_the_fused_collectives(monkeypa
     tr._build_gather_fields()
     assert tr._ga_units == list(range(1, cfg.n_units))
     tr.engine.fwd_fields = tr._fwd_fields
+    if wgrad_stream:  # three streams: main, weight gradients, communication
+        tr.engine.wstream = _Stream()
+        tr.engine._w_events, tr.engine._w_last = {}, {}
     tr._mark_params_written()
     log.ops.clear()
     _instrument(monkeypatch, log)
