@@ -259,3 +259,31 @@ def test_sendrecv_emulated_and_receiver_alone_times_out():
     torch.cuda.synchronize()
     assert int(emu.status[3].item()) == 1 and int(dst.sum().item()) == 0
     assert torch.ones(4, device=DEV).sum().item() == 4.0
+
+
+def test_a_peer_that_is_already_one_call_ahead_does_not_stall_the_round():
+    """Tokens of a team only grow and every flag word has one writer, so a word that already holds a later token of
+    the same epoch proves that the awaited one was posted (a peer may overwrite it when a single-round collective is
+    followed at once by the next one).  A later token passes; a token of another epoch does not."""
+    world, n = 2, 2 * 8 * 64
+
+    def run(peer_token_of):
+        emu = Emu(world, n * 2, timeout_s=0.2)
+        bufs = [emu.buf(r, n, torch.bfloat16) for r in range(world)]
+        for b in bufs:
+            b.fill_(1.0)
+        descs = emu.descs()
+        words = emu.arenas[0][: emu.fb].view(torch.int64)
+        for slot in (0, 1):  # what rank 1 would have written into rank 0's ready and done words
+            words[slot * MAX_RANKS + 1] = peer_token_of(int(descs[0].token))
+        rc = emu.lib.ftb200_team_allreduce_emulated(
+            descs, ctypes.c_int(1), emu.ptrs(bufs), None, None, ctypes.c_longlong(n), ctypes.c_int(0),
+            ctypes.c_float(1.0), None, ctypes.c_int(2), N.stream_ptr())
+        assert rc == 0
+        torch.cuda.synchronize()
+        return int(emu.status[0].item())
+
+    assert run(lambda tok: tok) == 0          # the awaited token itself
+    assert run(lambda tok: tok + 3) == 0      # the peer is three calls further on in the same epoch
+    assert run(lambda tok: tok - 1) == 1      # an earlier call: TIMEOUT
+    assert run(lambda tok: tok + (1 << 32)) == 1  # another epoch: never matches

@@ -42,6 +42,10 @@ __device__ __forceinline__ uint64_t ld_acquire_gpu(const uint64_t* p) {
 }
 
 // Bounded spin until *p == want.  Returns 0 on success, a FTB200_ST_* code otherwise.
+// A cross-rank word (SYS) also passes when it already holds a LATER token of the same epoch: tokens of a team
+// only grow, every word has one writer, and a peer that is one single-round call ahead (a barrier or a one-shot
+// allreduce followed at once by the next collective) may overwrite its token before this rank has looked -- it
+// has then certainly posted the one waited for.
 // Only system-scope waits (block 0's per-peer threads) look at the host-mapped abort word,
 // and only every 256 polls: it sits across PCIe and many concurrent readers are slow.
 // Every other waiter learns of an abort through the GO_ABORT value of its go-word.
@@ -51,6 +55,7 @@ __device__ __forceinline__ int wait_equal(const uint64_t* p, uint64_t want, cons
   for (;;) {
     const uint64_t v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
     if (v == want) return FTB200_ST_OK;
+    if (SYS && v > want && (v >> 32) == (want >> 32)) return FTB200_ST_OK;
     if (!SYS && v == GO_ABORT) return FTB200_ST_ABORTED;
     ++spins;
     if ((spins & 15u) == 0) {
