@@ -6,6 +6,31 @@ import pytest
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def free_port(span: int = 1) -> int:
+    """A port that is free right now, chosen by the OS (for ``span`` > 1: the first of that many consecutive free
+    ones).  Ports derived from the process id collide with whatever else runs on the host."""
+    import socket
+
+    for _ in range(64):
+        socks = []
+        try:
+            s = socket.socket()
+            s.bind(("127.0.0.1", 0))
+            socks.append(s)
+            base = s.getsockname()[1]
+            for i in range(1, span):
+                t = socket.socket()
+                socks.append(t)
+                t.bind(("127.0.0.1", base + i))
+            return base
+        except OSError:
+            continue
+        finally:
+            for s in socks:
+                s.close()
+    raise RuntimeError("no free port range found")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA device (B200)")
 

@@ -7,6 +7,7 @@ from unittest.mock import MagicMock
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
+from conftest import free_port
 
 
 def _worker(rank: int, world: int, port: int) -> None:
@@ -52,7 +53,7 @@ def _worker(rank: int, world: int, port: int) -> None:
 
 def test_managed_device_mesh_gloo():
     world = 2
-    port = 29000 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_worker, args=(world, port), nprocs=world, join=True)
 
 
@@ -119,7 +120,7 @@ def test_fully_shard_on_managed_mesh_gloo(tmp_path):
     """HSDP as the reference wires it (torchft/fsdp_test.py:82-92): FSDP2 shards inside the group over a real
     process group and reduces over the replicate dimension through the manager."""
     world = 2
-    port = 31000 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_fsdp_worker, args=(world, port, str(tmp_path / "dcp")), nprocs=world, join=True)
 
 
@@ -168,7 +169,7 @@ def test_tensor_parallel_and_fsdp2_on_a_3d_managed_mesh():
     styles work, and FSDP2 composes with them over the managed (replicate, shard) part
     (the reference's fsdp_test.py:84-92 builds the same (1, 2, 2) layout)."""
     world = 4
-    port = 33000 + os.getpid() % 2000
+    port = free_port()
     mp.spawn(_tp_worker, args=(world, port), nprocs=world, join=True)
 
 
@@ -182,7 +183,7 @@ def test_extend_device_mesh_inserts_a_registered_group():
     child = r'''
 import os, sys
 import torch, torch.distributed as dist
-os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(25000 + os.getpid() % 4000), RANK="0", WORLD_SIZE="1")
+os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT="@PORT@", RANK="0", WORLD_SIZE="1")
 dist.init_process_group("gloo", rank=0, world_size=1)
 from torch.distributed.device_mesh import init_device_mesh
 from torchft_b200.device_mesh import extend_device_mesh
@@ -205,5 +206,6 @@ pg.unregister()
 print("extend ok")
 '''
     repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    r = subprocess.run([sys.executable, "-c", child], capture_output=True, text=True, timeout=240, env=dict(os.environ, PYTHONPATH=repo))
+    r = subprocess.run([sys.executable, "-c", child.replace("@PORT@", str(free_port()))], capture_output=True, text=True,
+                       timeout=240, env=dict(os.environ, PYTHONPATH=repo))
     assert r.returncode == 0 and "extend ok" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]

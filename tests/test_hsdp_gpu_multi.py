@@ -7,6 +7,7 @@ import sys
 
 import pytest
 import torch
+from conftest import free_port
 
 pytestmark = pytest.mark.gpu
 WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_hsdp_worker.py")
@@ -15,7 +16,7 @@ WORKER = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_hsdp_worker.
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 def test_sharded_trainer_backends_agree():
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    port = 29000 + os.getpid() % 1000
+    port = free_port()
     p = subprocess.run(
         [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
          "--master-port", str(port), WORKER], capture_output=True, text=True, env=env, timeout=300)

@@ -10,6 +10,7 @@ import urllib.request
 
 import pytest
 import torch
+from conftest import free_port
 
 
 def _fake_tool(dirpath, name, body):
@@ -123,7 +124,7 @@ def test_runner_restarts_a_group_after_an_injected_segfault(tmp_path):
 
     repo = Path(__file__).resolve().parent.parent
     pid_file = str(tmp_path / "pids.json")
-    runner = Runner([str(repo / "tests" / "_sleepy_worker.py")], num_groups=1, base_port=24000 + os.getpid() % 4000,
+    runner = Runner([str(repo / "tests" / "_sleepy_worker.py")], num_groups=1, base_port=free_port(8),
                     max_restarts=2, pid_file=pid_file, poll_secs=0.2, log_dir=str(tmp_path / "logs"),
                     extra_env={"SLEEPY_DIR": str(tmp_path)})
     result = {}
@@ -160,7 +161,7 @@ def test_punisher_hang_stops_then_kills_the_group(tmp_path):
 
     repo = Path(__file__).resolve().parent.parent
     pid_file = str(tmp_path / "pids.json")
-    runner = Runner([str(repo / "tests" / "_sleepy_worker.py")], num_groups=1, base_port=20000 + os.getpid() % 4000,
+    runner = Runner([str(repo / "tests" / "_sleepy_worker.py")], num_groups=1, base_port=free_port(8),
                     max_restarts=2, pid_file=pid_file, poll_secs=0.2, log_dir=str(tmp_path / "logs"),
                     extra_env={"SLEEPY_DIR": str(tmp_path)})
     result = {}
