@@ -120,6 +120,14 @@ def build_model(name, seq_len, device, shard_mesh, ac_mode):
     return model, margs
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def main(args) -> int:
     try:
         torchft, standin = load_reference()
@@ -144,7 +152,7 @@ def main(args) -> int:
         if world == 1 and args.gpus > 1:
             import subprocess
 
-            port = 29500 + (os.getpid() % 400)
+            port = _free_port()
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                    "--master-addr", "127.0.0.1", "--master-port", str(port),
                    os.path.join(os.path.dirname(HERE), "bench.py")] + sys.argv[1:]
@@ -159,7 +167,7 @@ def main(args) -> int:
         torch.cuda.set_device(local_rank)
         dev = torch.device("cuda", local_rank)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", str(29500 + (os.getpid() % 400)))
+    os.environ.setdefault("MASTER_PORT", str(_free_port()))
     # no device_id: the reference's ProcessGroup.register() (torchft/process_group.py:326-345) creates a
     # world-size-1 group of its own backend, which torch refuses on a default group bound to a device
     dist.init_process_group("gloo" if cpu else "nccl", rank=rank, world_size=world)

@@ -25,7 +25,7 @@ import time
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 
-from reference_arm import build_model, load_reference, make_manager, unavailable  # noqa: E402
+from reference_arm import _free_port, build_model, load_reference, make_manager, unavailable  # noqa: E402
 
 
 def sync_excess_ms(step_ms, sync_every, fragments, delay):
@@ -66,7 +66,7 @@ def main(args) -> int:
     if not cpu:
         torch.cuda.set_device(dev)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-    os.environ.setdefault("MASTER_PORT", str(29500 + (os.getpid() % 400)))
+    os.environ.setdefault("MASTER_PORT", str(_free_port()))
     dist.init_process_group("gloo" if cpu else "nccl", rank=rank, world_size=world)
     B, S = args.micro_batch, args.seq_len
     try:

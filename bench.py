@@ -127,6 +127,14 @@ def _reference_arm(args):
     return reference_arm.main(args)
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def main() -> int:
     args = _parse()
     if args.impl == "reference":
@@ -151,7 +159,7 @@ def main() -> int:
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             # convenience: relaunch under torchrun
-            port = 29500 + (os.getpid() % 400)
+            port = _free_port()
             cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
                    "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.abspath(__file__)] + sys.argv[1:]
             return subprocess.call(cmd)
