@@ -386,3 +386,93 @@ def test_sharded_trainer_streams_are_ordered_with_the_fused_collectives(monkeypa
     assert names.count("gemm_gather") == 3 * (4 * cfg.n_layers + 1)
     assert names.count("gemm_scatter") == 3 * (4 * cfg.n_layers + 1) and names.count("reduce_stage") == 3 * (cfg.n_layers + 1)
     assert _check(log) == []
+
+
+class _LoggingManager:
+    """What `EngineDiLoCo` needs of a manager, with the collectives logged on the stream they are issued on."""
+
+    _use_async_quorum = False
+
+    def __init__(self, log):
+        self.log, self.step = log, 0
+
+    def register_state_dict_fn(self, *a, **k):
+        pass
+
+    def disallow_state_dict_read(self):
+        pass
+
+    def allow_state_dict_read(self):
+        pass
+
+    def start_quorum(self, *a, **k):
+        pass
+
+    def current_step(self):
+        return self.step
+
+    def should_commit(self):
+        self.step += 1
+        return True
+
+    def allreduce(self, tensor, should_quantize=False, **k):
+        from torchft_b200.work import _DummyWork
+
+        self.log.add("allreduce", [tensor], [tensor])
+        return _DummyWork(tensor)
+
+    def allreduce_delta(self, out, a, b, should_quantize=False):
+        from torchft_b200.work import _DummyWork
+
+        self.log.add("allreduce_delta", [a, b], [out])
+        out.copy_(a - b)
+        return _DummyWork(out)
+
+
+@pytest.mark.parametrize("delay", [0, 1])
+def test_diloco_exchange_stream_is_ordered(monkeypatch, fake_cuda, delay):
+    """Streaming DiLoCo on the engine: the pseudo-gradient exchange runs on a stream of its own, with a delay beside
+    the next inner step (whose optimizer rewrites the weights the pseudo-gradient was taken from), the outer step
+    back on the training stream, the weight-gradient stream inside every inner step."""
+    import torchft_b200.parallel.diloco as D
+
+    cfg, B, S = L.LLAMA_TINY, 2, 16
+    log = _Log()
+    tr = ShardedLlamaTrainer(cfg, B, S, torch.device("cpu"), logit_chunks=1, seed=3)
+    tr.engine.wstream = _Stream()
+    tr.engine._w_events, tr.engine._w_last = {}, {}
+    mgr = _LoggingManager(log)
+    d = D.EngineDiLoCo(tr, mgr, n_fragments=2, sync_every=4, fragment_sync_delay=delay)
+    d.stream = _Stream()  # the constructor only creates it on a CUDA device
+    _instrument(monkeypatch, log)
+    real_sub, real_outer = torch.sub, D.outer_step_
+
+    def sub(a, b, *args, out=None, **k):
+        if out is not None:
+            log.add("sub", [a, b], [out])
+        return real_sub(a, b, *args, out=out, **k)
+
+    def outer(g, m, backup, param, *a, **k):
+        log.add("outer_step", [g, m, backup, param], [m, backup, param])
+        return real_outer(g, m, backup, param, *a, **k)
+
+    monkeypatch.setattr(torch, "sub", sub)
+    monkeypatch.setattr(D, "outer_step_", outer)
+    for name, reads, writes in (
+        ("linear_fwd", lambda x, w, out=None: [x, w], lambda x, w, out=None: [out]),
+        ("linear_swiglu_fwd", lambda x, w, gu, s: [x, w], lambda x, w, gu, s: [gu, s]),
+        ("embedding_fwd", lambda tok, table, out=None: [table], lambda tok, table, out=None: [out]),
+        ("sumsq_", lambda x, out: [x], lambda x, out: [out]),
+        ("adamw_", lambda master, m, v, grad, param_lp, *a, **k: [grad, master], lambda master, m, v, grad, param_lp, *a, **k: [master, m, v, param_lp]),
+    ):
+        fn = getattr(K, name)
+        monkeypatch.setattr(K, name, (lambda fn, name, reads, writes: lambda *a, **k: (log.add(name, reads(*a, **k), writes(*a, **k)), fn(*a, **k))[1])(fn, name, reads, writes))
+    monkeypatch.setattr(tr.engine.attn, "backward",
+                        lambda layer, dout, batch, seq, dqkv: (log.add("attention.backward", [dout], [dqkv]), dqkv.zero_()))
+    tokens = torch.randint(0, cfg.vocab_size, (B, S), generator=torch.Generator().manual_seed(1))
+    for _ in range(8):  # two synchronisations of each fragment
+        d.train_step(tokens, tokens)
+    assert d.commits == 4
+    names = [o for o in log.ops if o[1] == d.stream.id]
+    assert names and all(o[0] in ("allreduce", "allreduce_delta") for o in names)
+    assert _check(log) == []
